@@ -1,0 +1,120 @@
+// Runtime support: per-thread error string, per-device status block, tensor-map encoding.
+#include "runtime.cuh"
+
+#include <cudaTypedefs.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+
+namespace of3 {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+static const int kMaxDevices = 64;
+static int* g_status[kMaxDevices] = {nullptr};
+static int g_sm_count[kMaxDevices] = {0};
+static std::mutex g_mu;
+
+int* device_status_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_status[dev] == nullptr) {
+        int* p = nullptr;
+        if (cudaMalloc(&p, 16 * sizeof(int)) != cudaSuccess) return nullptr;
+        if (cudaMemset(p, 0, 16 * sizeof(int)) != cudaSuccess) return nullptr;
+        g_status[dev] = p;
+    }
+    return g_status[dev];
+}
+
+int sm_count() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (g_sm_count[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        g_sm_count[dev] = n;
+    }
+    return g_sm_count[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+                cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                   const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+    EncodeTiledFn fn = encode_fn();
+    OF3_REQUIRE(fn != nullptr, OF3_ERR_DRIVER, "cuTensorMapEncodeTiled entry point unavailable");
+    OF3_REQUIRE(((uintptr_t)base & 15) == 0, OF3_ERR_ALIGN, "tensor map base not 16-byte aligned");
+    cuuint64_t gdim[5];
+    cuuint64_t gstr[5];
+    cuuint32_t bx[5];
+    cuuint32_t es[5];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = 1;
+        if (i > 0) {
+            OF3_REQUIRE((strides_bytes[i - 1] & 15) == 0, OF3_ERR_ALIGN,
+                        "tensor map stride %d (%llu B) not a multiple of 16", i,
+                        (unsigned long long)strides_bytes[i - 1]);
+            gstr[i - 1] = strides_bytes[i - 1];
+        }
+    }
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base),
+                    gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    OF3_REQUIRE(r == CUDA_SUCCESS, OF3_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d",
+                (int)r);
+    return OF3_OK;
+}
+
+}  // namespace of3
+
+extern "C" const char* of3_last_error_string(void) { return of3::g_err; }
+
+extern "C" int of3_device_status(int* out4) {
+    int* p = of3::device_status_ptr();
+    OF3_REQUIRE(p != nullptr, OF3_ERR_ARG, "no device status block (no CUDA device?)");
+    OF3_REQUIRE(out4 != nullptr, OF3_ERR_ARG, "out4 is null");
+    OF3_CUDA_CHECK(cudaMemcpy(out4, p, 4 * sizeof(int), cudaMemcpyDeviceToHost));
+    return OF3_OK;
+}
+
+extern "C" int of3_device_status_clear(void) {
+    int* p = of3::device_status_ptr();
+    OF3_REQUIRE(p != nullptr, OF3_ERR_ARG, "no device status block (no CUDA device?)");
+    OF3_CUDA_CHECK(cudaMemset(p, 0, 16 * sizeof(int)));
+    return OF3_OK;
+}
