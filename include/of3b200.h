@@ -1,0 +1,199 @@
+/* C ABI of the B200-native Pairformer hot-path library (libof3b200.so).
+ *
+ * Plain C: raw device pointers, explicit shapes, a cudaStream_t passed as void*. No torch
+ * or C++ types cross this boundary. All "reference" citations are paths inside the
+ * aqlaboratory/openfold-3 source tree.
+ *
+ * Conventions
+ *  - Return value: 0 ok; < 0 argument / shape / alignment / workspace error (OF3_ERR_*);
+ *    > 0 a cudaError_t. of3_last_error_string() describes the last failure of the calling
+ *    thread. Nothing throws or aborts.
+ *  - dtype: OF3_DTYPE_BF16 (bf16 storage, fp32 accumulation and statistics) or
+ *    OF3_DTYPE_F32 (fp32 storage and true fp32 arithmetic: the validation mode). Activations,
+ *    masks and parameters of one call share the dtype.
+ *  - Every buffer is owned by the caller. Entry points enqueue work on `stream` and return;
+ *    they allocate nothing (except a 64-byte per-device status block on first use) and keep
+ *    no reference after the enqueued work completes. `workspace` must hold at least the
+ *    matching *_workspace_bytes() and stay valid until the stream reaches the end of the call.
+ *  - `out` may alias the input activation (in-place residual update) where noted.
+ *  - flags: OF3_FLAG_ADD_RESIDUAL writes input + update instead of the update;
+ *    OF3_FLAG_FORCE_GENERIC selects the shape-generic SIMT kernels even where a tcgen05
+ *    kernel exists (used by tests to cross-check the two families).
+ *  - Thread safety: re-entrant; calls are ordered by the stream they are given.
+ */
+#ifndef OF3B200_H
+#define OF3B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OF3_OK 0
+#define OF3_ERR_ARG (-1)
+#define OF3_ERR_SHAPE (-2)
+#define OF3_ERR_ALIGN (-3)
+#define OF3_ERR_WORKSPACE (-4)
+#define OF3_ERR_DRIVER (-5)
+#define OF3_ERR_DEVICE_WAIT (-6)
+
+#define OF3_DTYPE_BF16 0
+#define OF3_DTYPE_F32 1
+
+#define OF3_FLAG_ADD_RESIDUAL 1
+#define OF3_FLAG_FORCE_GENERIC 2
+#define OF3_FLAG_OUTGOING 4    /* trimul: outgoing edges (else incoming) */
+#define OF3_FLAG_TRANSPOSED 8  /* triangle attention around the ending node */
+#define OF3_FLAG_ADA_LN 16     /* attention pair bias: adaptive LayerNorm conditioning on s */
+
+/* Message for the last non-zero return code seen by the calling thread. */
+const char* of3_last_error_string(void);
+
+/* Device-side status block: kernels with bounded waits (mbarrier / TMEM pipelines) record
+ * {code, kernel id, block, wait site} here instead of spinning forever. Synchronises the device. */
+int of3_device_status(int* out4);
+int of3_device_status_clear(void);
+
+/* 1 when the tcgen05 kernel family covers this shape and dtype, else 0 (generic kernels run). */
+int of3_fast_path_available(int module_id, int dtype, int c, int c_hidden, int heads, int head_dim);
+#define OF3_MODULE_TRIMUL 1
+#define OF3_MODULE_TRIATTN 2
+#define OF3_MODULE_TRANSITION 3
+
+/* ---- Triangle multiplicative update ------------------------------------------------------
+ * Replaces TriangleMultiplicativeUpdate.forward / _inference_forward
+ * (openfold3/core/model/layers/triangular_multiplicative_update.py:421-503, 154-419) and the
+ * operator seam _cueq_triangle_mult (:689-741).
+ * z, out: [B, N, N, c_z]; mask: [B, N, N] or NULL (all ones). out may alias z. */
+typedef struct {
+    const void* ln_in_w;   /* [c_z] layer_norm_in.weight */
+    const void* ln_in_b;   /* [c_z] layer_norm_in.bias */
+    const void* w_a_p;     /* [c_h, c_z] linear_a_p.weight */
+    const void* w_a_g;     /* [c_h, c_z] linear_a_g.weight */
+    const void* w_b_p;     /* [c_h, c_z] linear_b_p.weight */
+    const void* w_b_g;     /* [c_h, c_z] linear_b_g.weight */
+    const void* w_g;       /* [c_z, c_z] linear_g.weight */
+    const void* ln_out_w;  /* [c_h] layer_norm_out.weight */
+    const void* ln_out_b;  /* [c_h] layer_norm_out.bias */
+    const void* w_z;       /* [c_z, c_h] linear_z.weight */
+} of3_trimul_params;
+
+size_t of3_trimul_workspace_bytes(int B, int N, int c_z, int c_h, int dtype, int flags);
+int of3_trimul_forward(const void* z, const void* mask, void* out, int B, int N, int c_z, int c_h,
+                       int dtype, int flags, const of3_trimul_params* p, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/* ---- Triangle attention ------------------------------------------------------------------
+ * Replaces TriangleAttention.forward (openfold3/core/model/layers/triangular_attention.py:
+ * 102-167) including the gated multi-head attention it calls
+ * (openfold3/core/model/primitives/attention.py:346-413, _attention :94-135) and the operator
+ * seams _cueq_triangle_attn (:625-672) / _deepspeed_evo_attn (:489-560).
+ * With OF3_FLAG_TRANSPOSED the layer acts on z^T and mask^T and the update is transposed back,
+ * which is both TriangleAttentionEndingNode and what PairBlock.tri_att_start_end does around
+ * tri_att_end (openfold3/core/model/latent/base_blocks.py:380-404) -- without moving z.
+ * z, out: [B, N, N, c_z]; mask: [B, N, N] or NULL. out may alias z. inf: the mask constant. */
+typedef struct {
+    const void* ln_w;    /* [c_z] layer_norm.weight */
+    const void* ln_b;    /* [c_z] layer_norm.bias */
+    const void* w_bias;  /* [H, c_z] linear_z.weight (triangle bias) */
+    const void* w_q;     /* [H*d, c_z] mha.linear_q.weight */
+    const void* w_k;     /* [H*d, c_z] mha.linear_k.weight */
+    const void* w_v;     /* [H*d, c_z] mha.linear_v.weight */
+    const void* w_g;     /* [H*d, c_z] mha.linear_g.weight */
+    const void* w_o;     /* [c_z, H*d] mha.linear_o.weight */
+} of3_triattn_params;
+
+size_t of3_triattn_workspace_bytes(int B, int N, int c_z, int H, int d, int dtype, int flags);
+int of3_triattn_forward(const void* z, const void* mask, void* out, int B, int N, int c_z, int H,
+                        int d, float inf, int dtype, int flags, const of3_triattn_params* p,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---- SwiGLU transition -------------------------------------------------------------------
+ * Replaces SwiGLUTransition (openfold3/core/model/layers/transition.py:225-271) with its
+ * SwiGLU (openfold3/core/model/primitives/activations.py:33-61), for the pair (c=128) and the
+ * single (c=384) track. x, out: [rows, c]; mask: [rows] or NULL; hidden width n*c.
+ * out may alias x. */
+typedef struct {
+    const void* ln_w;   /* [c] layer_norm.weight */
+    const void* ln_b;   /* [c] layer_norm.bias */
+    const void* w_a;    /* [n*c, c] swiglu.linear_a.weight */
+    const void* w_b;    /* [n*c, c] swiglu.linear_b.weight */
+    const void* w_out;  /* [c, n*c] linear_out.weight */
+} of3_transition_params;
+
+size_t of3_transition_workspace_bytes(long long rows, int c, int n, int dtype, int flags);
+int of3_transition_forward(const void* x, const void* mask, void* out, long long rows, int c, int n,
+                           int dtype, int flags, const of3_transition_params* p, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* ---- Attention with pair bias ------------------------------------------------------------
+ * Replaces AttentionPairBias.forward (openfold3/core/model/layers/attention_pair_bias.py:
+ * 123-227) for the trunk single track (LayerNorm) and, with OF3_FLAG_ADA_LN, for the diffusion
+ * token track (AdaLN, openfold3/core/model/primitives/normalization.py:89-140).
+ * a, out: [Ba, N, c_a]; z: [Bz, N, N, c_z] with Ba a multiple of Bz (samples sharing one pair
+ * tensor are consecutive); s: [Ba, N, c_s] (AdaLN only, else NULL); mask: [Ba, N] or NULL.
+ * out may alias a. */
+typedef struct {
+    const void* ln_a_w;      /* [c_a] layer_norm_a.weight              (LayerNorm variant) */
+    const void* ln_a_b;      /* [c_a] layer_norm_a.bias                (LayerNorm variant) */
+    const void* ada_ln_s_w;  /* [c_s] layer_norm_a.layer_norm_s.weight (AdaLN variant) */
+    const void* ada_w_g;     /* [c_a, c_s] layer_norm_a.linear_g.weight */
+    const void* ada_b_g;     /* [c_a] layer_norm_a.linear_g.bias */
+    const void* ada_w_s;     /* [c_a, c_s] layer_norm_a.linear_s.weight */
+    const void* w_ada_out;   /* [c_a, c_s] linear_ada_out.weight       (AdaLN variant) */
+    const void* b_ada_out;   /* [c_a] linear_ada_out.bias */
+    const void* ln_z_w;      /* [c_z] layer_norm_z.weight */
+    const void* ln_z_b;      /* [c_z] layer_norm_z.bias or NULL */
+    const void* w_z;         /* [H, c_z] linear_z.weight */
+    const void* w_q;         /* [H*d, c_a] mha.linear_q.weight */
+    const void* b_q;         /* [H*d] mha.linear_q.bias or NULL */
+    const void* w_k;         /* [H*d, c_a] */
+    const void* w_v;         /* [H*d, c_a] */
+    const void* w_g;         /* [H*d, c_a] */
+    const void* w_o;         /* [c_a, H*d] */
+} of3_attn_pair_bias_params;
+
+size_t of3_attn_pair_bias_workspace_bytes(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H,
+                                          int d, int dtype, int flags);
+int of3_attn_pair_bias_forward(const void* a, const void* z, const void* s, const void* mask,
+                               void* out, int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H,
+                               int d, float inf, int dtype, int flags,
+                               const of3_attn_pair_bias_params* p, void* workspace,
+                               size_t workspace_bytes, void* stream);
+
+/* ---- Conditioned (AdaLN) SwiGLU transition -----------------------------------------------
+ * Replaces ConditionedTransitionBlock (openfold3/core/model/layers/transition.py:274-380).
+ * a, out: [rows, c_a]; s: [rows, c_s]; mask: [rows] or NULL. out may alias a. */
+typedef struct {
+    const void* ada_ln_s_w;  /* [c_s] layer_norm.layer_norm_s.weight */
+    const void* ada_w_g;     /* [c_a, c_s] layer_norm.linear_g.weight */
+    const void* ada_b_g;     /* [c_a] layer_norm.linear_g.bias */
+    const void* ada_w_s;     /* [c_a, c_s] layer_norm.linear_s.weight */
+    const void* w_a;         /* [n*c_a, c_a] swiglu.linear_a.weight */
+    const void* w_b;         /* [n*c_a, c_a] swiglu.linear_b.weight */
+    const void* w_g;         /* [c_a, c_s] linear_g.weight */
+    const void* b_g;         /* [c_a] linear_g.bias */
+    const void* w_out;       /* [c_a, n*c_a] linear_out.weight */
+} of3_cond_transition_params;
+
+size_t of3_cond_transition_workspace_bytes(long long rows, int c_a, int c_s, int n, int dtype,
+                                           int flags);
+int of3_cond_transition_forward(const void* a, const void* s, const void* mask, void* out,
+                                long long rows, int c_a, int c_s, int n, int dtype, int flags,
+                                const of3_cond_transition_params* p, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
+/* ---- Building block exported for tests and profiling --------------------------------------
+ * X[b][i][j] = sum_k A[b][i][k] * B[b][j][k], bf16 in / fp32 accumulate / bf16 out, the
+ * tcgen05 kernel behind the triangle contraction (einsum of
+ * triangular_multiplicative_update.py:71-97). Pitches and batch strides in elements. */
+int of3_contract_nt_bf16(const void* a, const void* b, void* out, int batch, int M, int N, int K,
+                         int lda, int ldb, int ldo, long long a_batch_stride,
+                         long long b_batch_stride, long long out_batch_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OF3B200_H */

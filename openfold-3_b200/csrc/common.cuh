@@ -9,16 +9,7 @@
 #include <stdint.h>
 #include <stddef.h>
 
-#define OF3_OK 0
-#define OF3_ERR_ARG (-1)          // null pointer, non-positive size
-#define OF3_ERR_SHAPE (-2)        // shape not supported by the selected kernel family
-#define OF3_ERR_ALIGN (-3)        // pointer or pitch not aligned as the kernel needs
-#define OF3_ERR_WORKSPACE (-4)    // caller-owned workspace too small
-#define OF3_ERR_DRIVER (-5)       // driver entry point (tensor-map encode) unavailable
-#define OF3_ERR_DEVICE_WAIT (-6)  // a bounded device-side wait ran out (status word set)
-
-#define OF3_DTYPE_BF16 0
-#define OF3_DTYPE_F32 1
+#include "of3b200.h"
 
 namespace of3 {
 

@@ -1,0 +1,48 @@
+// Internal module-level interfaces behind the C ABI: the shape-generic family (any shape,
+// fp32 or bf16 storage) and the tcgen05 family (bf16, the OpenFold3 Pairformer widths).
+#pragma once
+#include "common.cuh"
+#include "of3b200.h"
+
+namespace of3 {
+
+namespace generic {
+template <typename T>
+int trimul(const T* z, const T* mask, T* out, int B, int N, int c_z, int c_h, int flags,
+           const of3_trimul_params* p, Arena& ws, cudaStream_t st);
+template <typename T>
+int triattn(const T* z, const T* mask, T* out, int B, int N, int c_z, int H, int d, float inf,
+            int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st);
+template <typename T>
+int transition(const T* x, const T* mask, T* out, long long rows, int c, int n, int flags,
+               const of3_transition_params* p, Arena& ws, cudaStream_t st);
+template <typename T>
+int attn_pair_bias(const T* a, const T* z, const T* s, const T* mask, T* out, int Ba, int Bz, int N,
+                   int c_a, int c_s, int c_z, int H, int d, float inf, int flags,
+                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st);
+template <typename T>
+int cond_transition(const T* a, const T* s, const T* mask, T* out, long long rows, int c_a, int c_s,
+                    int n, int flags, const of3_cond_transition_params* p, Arena& ws,
+                    cudaStream_t st);
+}  // namespace generic
+
+namespace fast {
+// bf16, c_z = c_hidden = 128
+bool trimul_supported(int c_z, int c_h);
+int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
+           int flags, const of3_trimul_params* p, Arena& ws, cudaStream_t st);
+// bf16, c_z = 128, 4 heads x 32
+bool triattn_supported(int c_z, int H, int d);
+int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
+            float inf, int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st);
+// bf16, c = 128, n = 4
+bool transition_supported(int c, int n);
+int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows,
+               int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
+}  // namespace fast
+
+int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
+                     int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
+                     long long o_bs, cudaStream_t stream);
+
+}  // namespace of3

@@ -1,0 +1,576 @@
+"""Drop-in module classes for the Pairformer hot path.
+
+Each class keeps the reference class's name, constructor arguments, parameter names and
+shapes (so ``load_state_dict(strict=True)`` of reference weights works) and forward keyword
+set; its forward enqueues the fused CUDA kernels of ``libof3b200.so`` instead of a chain
+of ATen ops. The kernel-selection and memory flags of the reference (``chunk_size``,
+``use_deepspeed_evo_attention``, ``use_cueq_triangle_kernels``, ``use_lma``,
+``_attn_chunk_size`` …) are accepted and all select the same native kernels: the attention
+kernels stream keys with an online softmax, so there is nothing to chunk.
+
+Forward only: autograd and training-mode dropout are not provided and raise.
+"""
+
+from __future__ import annotations
+
+import math
+from functools import partialmethod
+
+import torch
+import torch.nn as nn
+
+from . import init_config as lin_init
+from . import lib
+
+
+# --------------------------------------------------------------------------- primitives
+def _trunc_normal_(w: torch.Tensor, scale: float, fan: int):
+    # variance-scaled truncated normal on [-2, 2] sigma; 0.8796... is the std of that truncation
+    std = math.sqrt(scale / max(1, fan)) / 0.87962566103423978
+    nn.init.trunc_normal_(w, mean=0.0, std=std, a=-2.0 * std, b=2.0 * std)
+
+
+class Linear(nn.Linear):
+    """Parameter holder with the reference's named initialisers
+    (openfold3/core/model/primitives/linear.py:38-138). Called alone it is a plain library GEMM."""
+
+    def __init__(self, in_dim: int, out_dim: int, bias: bool = True, init: str = "default",
+                 init_fn=None, precision=None):
+        super().__init__(in_dim, out_dim, bias=bias)
+        self.precision = precision
+        with torch.no_grad():
+            if bias:
+                self.bias.fill_(0)
+            if init_fn is not None:
+                init_fn(self.weight, self.bias)
+            elif init == "default":
+                _trunc_normal_(self.weight, 1.0, in_dim)
+            elif init in ("relu", "he_normal"):
+                _trunc_normal_(self.weight, 2.0, in_dim)
+            elif init == "glorot":
+                nn.init.xavier_uniform_(self.weight, gain=1)
+            elif init == "gating":
+                self.weight.fill_(0.0)
+                if bias:
+                    self.bias.fill_(1.0)
+            elif init == "gating_ada_zero":
+                self.weight.fill_(0.0)
+                self.bias.fill_(-2.0)
+            elif init == "normal":
+                nn.init.kaiming_normal_(self.weight, nonlinearity="linear")
+            elif init == "final":
+                self.weight.fill_(0.0)
+            else:
+                raise ValueError("Invalid init string.")
+
+
+class LayerNorm(nn.Module):
+    """Parameter holder (openfold3/core/model/primitives/normalization.py:33-86)."""
+
+    def __init__(self, c_in: int, create_scale: bool = True, create_offset: bool = True, eps=1e-5):
+        super().__init__()
+        self.c_in = (c_in,)
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(c_in)) if create_scale else None
+        self.bias = nn.Parameter(torch.zeros(c_in)) if create_offset else None
+
+    def forward(self, x):
+        d = x.dtype
+        w = self.weight.to(d) if self.weight is not None else None
+        b = self.bias.to(d) if self.bias is not None else None
+        return nn.functional.layer_norm(x, self.c_in, w, b, self.eps)
+
+
+class AdaLN(nn.Module):
+    """Parameter holder for adaptive LayerNorm
+    (openfold3/core/model/primitives/normalization.py:89-140); the arithmetic is fused into
+    the kernels of the modules that own it."""
+
+    def __init__(self, c_a: int, c_s: int, eps: float = 1e-5, linear_init_params=lin_init.ada_ln_init):
+        super().__init__()
+        self.c_a, self.c_s, self.eps = c_a, c_s, eps
+        self.layer_norm_a = LayerNorm(c_a, create_scale=False, create_offset=False, eps=eps)
+        self.layer_norm_s = LayerNorm(c_s, create_scale=True, create_offset=False, eps=eps)
+        self.linear_g = Linear(c_s, c_a, **linear_init_params.linear_g)
+        self.linear_s = Linear(c_s, c_a, **linear_init_params.linear_s)
+
+
+class SwiGLU(nn.Module):
+    """Parameter holder (openfold3/core/model/primitives/activations.py:33-61)."""
+
+    def __init__(self, c_in: int, c_out: int, linear_init_params=lin_init.swiglu_init):
+        super().__init__()
+        self.c_in, self.c_out = c_in, c_out
+        self.linear_a = Linear(c_in, c_out, **linear_init_params.linear_a)
+        self.linear_b = Linear(c_in, c_out, **linear_init_params.linear_b)
+
+
+class Attention(nn.Module):
+    """Parameter holder for gated multi-head attention
+    (openfold3/core/model/primitives/attention.py:199-268). ``c_hidden`` is per head."""
+
+    def __init__(self, c_q, c_k, c_v, c_hidden, no_heads, gating=True, linear_init_params=lin_init.mha_init):
+        super().__init__()
+        self.c_q, self.c_k, self.c_v = c_q, c_k, c_v
+        self.c_hidden, self.no_heads, self.gating = c_hidden, no_heads, gating
+        self.linear_q = Linear(c_q, c_hidden * no_heads, **linear_init_params.linear_q)
+        self.linear_k = Linear(c_k, c_hidden * no_heads, **linear_init_params.linear_k)
+        self.linear_v = Linear(c_v, c_hidden * no_heads, **linear_init_params.linear_v)
+        self.linear_o = Linear(c_hidden * no_heads, c_q, **linear_init_params.linear_o)
+        self.linear_g = None
+        if gating:
+            self.linear_g = Linear(c_q, c_hidden * no_heads, **linear_init_params.linear_g)
+
+
+class DropoutRowwise(nn.Module):
+    """Identity in eval mode (openfold3/core/model/primitives/dropout.py:57-58); training-mode
+    shared dropout is outside the forward-only scope."""
+
+    def __init__(self, r: float):
+        super().__init__()
+        self.r = r
+
+    def forward(self, x):
+        if self.training and self.r > 0:
+            raise NotImplementedError("training-mode dropout is not provided by the B200 forward kernels")
+        return x
+
+
+# --------------------------------------------------------------------------- helpers
+def _forward_only(module: nn.Module, *tensors):
+    if torch.is_grad_enabled() and (
+        any(t is not None and t.requires_grad for t in tensors)
+        or (module.training and any(p.requires_grad for p in module.parameters()))
+    ):
+        raise NotImplementedError(
+            f"{type(module).__name__}: the B200 kernels are forward-only; call under torch.no_grad() "
+            "in eval() mode"
+        )
+
+
+class _PackedParams:
+    """Caches contiguous copies of a module's parameters in the activation dtype."""
+
+    def __init__(self):
+        self._key = None
+        self._val = None
+
+    def get(self, tensors, dtype, device):
+        key = (dtype, device, tuple((t.data_ptr(), t._version) if t is not None else None for t in tensors))
+        if key != self._key:
+            self._val = tuple(
+                None if t is None else t.detach().to(device=device, dtype=dtype).contiguous() for t in tensors
+            )
+            self._key = key
+        return self._val
+
+
+def _mask_like(mask, shape, dtype):
+    if mask is None:
+        return None
+    return mask.to(dtype).expand(shape).contiguous()
+
+
+# --------------------------------------------------------------------------- triangle multiplication
+class TriangleMultiplicativeUpdate(nn.Module):
+    """AF3 Algorithms 12/13. Drop-in for
+    openfold3/core/model/layers/triangular_multiplicative_update.py:123-503."""
+
+    def __init__(self, c_z, c_hidden, _outgoing=True, linear_init_params=lin_init.tri_mul_init):
+        super().__init__()
+        self.c_z, self.c_hidden, self._outgoing = c_z, c_hidden, _outgoing
+        self.linear_g = Linear(c_z, c_z, **linear_init_params.linear_g)
+        self.linear_z = Linear(c_hidden, c_z, **linear_init_params.linear_z)
+        self.layer_norm_in = LayerNorm(c_z)
+        self.layer_norm_out = LayerNorm(c_hidden)
+        self.linear_a_p = Linear(c_z, c_hidden, **linear_init_params.linear_a_p)
+        self.linear_a_g = Linear(c_z, c_hidden, **linear_init_params.linear_a_g)
+        self.linear_b_p = Linear(c_z, c_hidden, **linear_init_params.linear_b_p)
+        self.linear_b_g = Linear(c_z, c_hidden, **linear_init_params.linear_b_g)
+        self._packed = _PackedParams()
+
+    def _params(self, dtype, device):
+        return self._packed.get(
+            (self.layer_norm_in.weight, self.layer_norm_in.bias, self.linear_a_p.weight,
+             self.linear_a_g.weight, self.linear_b_p.weight, self.linear_b_g.weight, self.linear_g.weight,
+             self.layer_norm_out.weight, self.layer_norm_out.bias, self.linear_z.weight), dtype, device)
+
+    def forward(self, z, mask=None, inplace_safe=False, use_cueq_triangle_kernels=False,
+                _add_with_inplace=False, _inplace_chunk_size=256):
+        """z [*, N, N, C_z], mask [*, N, N]. Returns the update, or (as the reference's inference
+        path does) ``z`` itself updated in place when ``inplace_safe and _add_with_inplace``."""
+        _forward_only(self, z)
+        in_place = inplace_safe and _add_with_inplace and not use_cueq_triangle_kernels and z.is_contiguous()
+        N = z.shape[-2]
+        zc = z.contiguous().view(-1, N, N, self.c_z)
+        m = _mask_like(mask, z.shape[:-1], z.dtype)
+        m = None if m is None else m.view(-1, N, N)
+        out = zc if in_place else torch.empty_like(zc)
+        lib.trimul_forward(zc, m, out, self._params(z.dtype, z.device), self.c_hidden, self._outgoing,
+                           add_residual=in_place)
+        return z if in_place else out.view(z.shape)
+
+
+class TriangleMultiplicationOutgoing(TriangleMultiplicativeUpdate):
+    __init__ = partialmethod(TriangleMultiplicativeUpdate.__init__, _outgoing=True)
+
+
+class TriangleMultiplicationIncoming(TriangleMultiplicativeUpdate):
+    __init__ = partialmethod(TriangleMultiplicativeUpdate.__init__, _outgoing=False)
+
+
+# --------------------------------------------------------------------------- triangle attention
+class TriangleAttention(nn.Module):
+    """AF3 Algorithms 14/15. Drop-in for openfold3/core/model/layers/triangular_attention.py:30-179."""
+
+    def __init__(self, c_in, c_hidden, no_heads, starting=True, inf=1e9, linear_init_params=lin_init.tri_att_init):
+        super().__init__()
+        self.c_in, self.c_hidden, self.no_heads = c_in, c_hidden, no_heads
+        self.starting, self.inf = starting, inf
+        self.layer_norm = LayerNorm(c_in)
+        self.linear_z = Linear(c_in, no_heads, **linear_init_params.linear_z)
+        self.mha = Attention(c_in, c_in, c_in, c_hidden, no_heads, linear_init_params=linear_init_params.mha)
+        self._packed = _PackedParams()
+
+    def _params(self, dtype, device):
+        return self._packed.get(
+            (self.layer_norm.weight, self.layer_norm.bias, self.linear_z.weight, self.mha.linear_q.weight,
+             self.mha.linear_k.weight, self.mha.linear_v.weight, self.mha.linear_g.weight,
+             self.mha.linear_o.weight), dtype, device)
+
+    def _run(self, x, mask, transposed: bool, in_place: bool):
+        N = x.shape[-2]
+        xc = x.contiguous().view(-1, N, N, self.c_in)
+        m = _mask_like(mask, x.shape[:-1], x.dtype)
+        m = None if m is None else m.view(-1, N, N)
+        out = xc if in_place else torch.empty_like(xc)
+        lib.triattn_forward(xc, m, out, self._params(x.dtype, x.device), self.no_heads, self.c_hidden,
+                            self.inf, transposed, add_residual=in_place)
+        return out.view(x.shape)
+
+    def forward(self, x, mask=None, chunk_size=None, use_deepspeed_evo_attention=False,
+                use_cueq_triangle_kernels=False, use_lma=False, inplace_safe=False):
+        """x [*, I, J, C_in] -> update [*, I, J, C_in]."""
+        _forward_only(self, x)
+        if use_lma and (use_deepspeed_evo_attention or use_cueq_triangle_kernels):
+            raise ValueError("Choose at most one alternative attention algorithm")
+        return self._run(x, mask, transposed=not self.starting, in_place=False)
+
+
+TriangleAttentionStartingNode = TriangleAttention
+
+
+class TriangleAttentionEndingNode(TriangleAttention):
+    __init__ = partialmethod(TriangleAttention.__init__, starting=False)
+
+
+# --------------------------------------------------------------------------- transitions
+class SwiGLUTransition(nn.Module):
+    """AF3 Algorithm 11. Drop-in for openfold3/core/model/layers/transition.py:225-271."""
+
+    def __init__(self, c_in: int, n: int, linear_init_params=lin_init.swiglu_transition_init):
+        super().__init__()
+        self.c_in, self.n = c_in, n
+        self.layer_norm = LayerNorm(c_in)
+        self.swiglu = SwiGLU(c_in, n * c_in, linear_init_params=linear_init_params.swiglu)
+        self.linear_out = Linear(n * c_in, c_in, **linear_init_params.linear_out)
+        self._packed = _PackedParams()
+
+    def _params(self, dtype, device):
+        return self._packed.get(
+            (self.layer_norm.weight, self.layer_norm.bias, self.swiglu.linear_a.weight,
+             self.swiglu.linear_b.weight, self.linear_out.weight), dtype, device)
+
+    def _run(self, x, mask, in_place: bool):
+        xc = x.contiguous().view(-1, self.c_in)
+        m = _mask_like(mask, x.shape[:-1], x.dtype)
+        m = None if m is None else m.view(-1)
+        out = xc if in_place else torch.empty_like(xc)
+        lib.transition_forward(xc, m, out, self._params(x.dtype, x.device), self.n, add_residual=in_place)
+        return out.view(x.shape)
+
+    def forward(self, x, mask=None, chunk_size=None, ckpt_chunk_size=None):
+        """x [*, N, C_in], mask [*, N] -> update [*, N, C_in]."""
+        _forward_only(self, x)
+        return self._run(x, mask, in_place=False)
+
+
+class ConditionedTransitionBlock(nn.Module):
+    """AF3 Algorithm 25. Drop-in for openfold3/core/model/layers/transition.py:274-380."""
+
+    def __init__(self, c_a: int, c_s: int, n: int, linear_init_params=lin_init.cond_transition_init):
+        super().__init__()
+        self.c_a, self.c_s, self.n = c_a, c_s, n
+        self.layer_norm = AdaLN(c_a=c_a, c_s=c_s, linear_init_params=linear_init_params.ada_ln)
+        self.swiglu = SwiGLU(c_a, n * c_a, linear_init_params=linear_init_params.swiglu)
+        self.linear_g = Linear(c_s, c_a, **linear_init_params.linear_g)
+        self.linear_out = Linear(n * c_a, c_a, **linear_init_params.linear_out)
+        self._packed = _PackedParams()
+
+    def _params(self, dtype, device):
+        ln = self.layer_norm
+        return self._packed.get(
+            (ln.layer_norm_s.weight, ln.linear_g.weight, ln.linear_g.bias, ln.linear_s.weight,
+             self.swiglu.linear_a.weight, self.swiglu.linear_b.weight, self.linear_g.weight,
+             self.linear_g.bias, self.linear_out.weight), dtype, device)
+
+    def _run(self, a, s, mask, in_place: bool):
+        ac = a.contiguous().view(-1, self.c_a)
+        sc = s.expand(*a.shape[:-1], self.c_s).contiguous().view(-1, self.c_s)
+        m = _mask_like(mask, a.shape[:-1], a.dtype)
+        m = None if m is None else m.view(-1)
+        out = ac if in_place else torch.empty_like(ac)
+        lib.cond_transition_forward(ac, sc, m, out, self._params(a.dtype, a.device), self.n,
+                                    add_residual=in_place)
+        return out.view(a.shape)
+
+    def forward(self, a, s, mask=None, chunk_size=None):
+        _forward_only(self, a, s)
+        return self._run(a, s, mask, in_place=False)
+
+
+# --------------------------------------------------------------------------- attention with pair bias
+class AttentionPairBias(nn.Module):
+    """AF3 Algorithm 24. Drop-in for openfold3/core/model/layers/attention_pair_bias.py:33-227."""
+
+    def __init__(self, c_q, c_k, c_v, c_s, c_z, c_hidden, no_heads, use_ada_layer_norm=False, gating=True,
+                 inf=1e9, linear_init_params=None):
+        super().__init__()
+        if not gating:
+            raise NotImplementedError("AttentionPairBias without gating is not used by OpenFold3")
+        self.c_q, self.c_s, self.c_z, self.inf = c_q, c_s, c_z, inf
+        self.c_hidden, self.no_heads = c_hidden, no_heads
+        self.use_ada_layer_norm = use_ada_layer_norm
+        if linear_init_params is None:
+            linear_init_params = (lin_init.diffusion_att_pair_bias_init if use_ada_layer_norm
+                                  else lin_init.att_pair_bias_init)
+        if use_ada_layer_norm:
+            self.layer_norm_a = AdaLN(c_a=c_q, c_s=c_s, linear_init_params=linear_init_params.ada_ln)
+            self.linear_ada_out = Linear(c_s, c_q, **linear_init_params.linear_ada_out)
+        else:
+            self.layer_norm_a = LayerNorm(c_in=c_q)
+        self.layer_norm_z = LayerNorm(c_z, **linear_init_params.layer_norm_z)
+        self.linear_z = Linear(c_z, no_heads, **linear_init_params.linear_z)
+        self.mha = Attention(c_q, c_k, c_v, c_hidden, no_heads, gating=gating,
+                             linear_init_params=linear_init_params.mha)
+        self._packed = _PackedParams()
+
+    def _params(self, dtype, device):
+        if self.use_ada_layer_norm:
+            ln = self.layer_norm_a
+            head = (None, None, ln.layer_norm_s.weight, ln.linear_g.weight, ln.linear_g.bias,
+                    ln.linear_s.weight, self.linear_ada_out.weight, self.linear_ada_out.bias)
+        else:
+            head = (self.layer_norm_a.weight, self.layer_norm_a.bias, None, None, None, None, None, None)
+        m = self.mha
+        return self._packed.get(
+            head + (self.layer_norm_z.weight, self.layer_norm_z.bias, self.linear_z.weight,
+                    m.linear_q.weight, m.linear_q.bias, m.linear_k.weight, m.linear_v.weight,
+                    m.linear_g.weight, m.linear_o.weight), dtype, device)
+
+    def _run(self, a, z, s, mask, in_place: bool):
+        N = a.shape[-2]
+        batch = a.shape[:-2]
+        ac = a.contiguous().view(-1, N, self.c_q)
+        Ba = ac.shape[0]
+        # z's batch dims broadcast against a's; samples that share one pair tensor must be consecutive
+        zb = z.shape[:-3]
+        zb = (1,) * (len(batch) - len(zb)) + tuple(zb)
+        lead = 0
+        while lead < len(batch) and zb[lead] == batch[lead]:
+            lead += 1
+        if all(d == 1 for d in zb[lead:]):
+            zc = z.contiguous().view(-1, N, N, self.c_z)
+        else:
+            zc = z.expand(*batch, N, N, self.c_z).contiguous().view(-1, N, N, self.c_z)
+        sc = None
+        if self.use_ada_layer_norm:
+            if s is None:
+                raise ValueError("AttentionPairBias with adaptive LayerNorm needs s")
+            sc = s.expand(*batch, N, self.c_s).contiguous().view(-1, N, self.c_s)
+        m = _mask_like(mask, a.shape[:-1], a.dtype)
+        m = None if m is None else m.view(-1, N)
+        out = ac if in_place else torch.empty_like(ac)
+        lib.attn_pair_bias_forward(ac, zc, sc, m, out, self._params(a.dtype, a.device), self.no_heads,
+                                   self.c_hidden, self.inf, self.use_ada_layer_norm, add_residual=in_place)
+        assert Ba % zc.shape[0] == 0
+        return out.view(a.shape)
+
+    def forward(self, a, z, s=None, mask=None, use_deepspeed_evo_attention=False,
+                use_cueq_triangle_kernels=False, use_lma=False, use_high_precision_attention=False):
+        """a [*, N, C_q], z [*, N, N, C_z], s [*, N, C_s], mask [*, N] -> update [*, N, C_q]."""
+        _forward_only(self, a, z, s)
+        return self._run(a, z, s, mask, in_place=False)
+
+
+# --------------------------------------------------------------------------- blocks and stacks
+class PairBlock(nn.Module):
+    """Pair stack of one block. Drop-in for openfold3/core/model/latent/base_blocks.py:219-480."""
+
+    def __init__(self, c_z, c_hidden_mul, c_hidden_pair_att, no_heads_pair, transition_type, transition_n,
+                 pair_dropout, fuse_projection_weights, inf, linear_init_params=lin_init.pair_block_init):
+        super().__init__()
+        if fuse_projection_weights:
+            raise NotImplementedError("the fused-projection (AF2-multimer) triangle update is not part of "
+                                      "the OpenFold3 Pairformer")
+        if transition_type != "swiglu":
+            raise ValueError(f"Transition type {transition_type} is not available")
+        self.tri_mul_out = TriangleMultiplicationOutgoing(c_z, c_hidden_mul,
+                                                          linear_init_params=linear_init_params.tri_mul)
+        self.tri_mul_in = TriangleMultiplicationIncoming(c_z, c_hidden_mul,
+                                                         linear_init_params=linear_init_params.tri_mul)
+        self.tri_att_start = TriangleAttention(c_z, c_hidden_pair_att, no_heads_pair, inf=inf,
+                                               linear_init_params=linear_init_params.tri_att)
+        self.tri_att_end = TriangleAttention(c_z, c_hidden_pair_att, no_heads_pair, inf=inf,
+                                             linear_init_params=linear_init_params.tri_att)
+        self.pair_transition = SwiGLUTransition(c_in=c_z, n=transition_n,
+                                                linear_init_params=linear_init_params.pair_transition.swiglu)
+        self.ps_dropout_row_layer = DropoutRowwise(pair_dropout)
+
+    def tri_mul_out_in(self, z, pair_mask, inplace_safe, use_cueq_triangle_kernels=False):
+        z = z if inplace_safe and z.is_contiguous() else z.clone(memory_format=torch.contiguous_format)
+        self.tri_mul_out(z, mask=pair_mask, inplace_safe=True, _add_with_inplace=True)
+        self.tri_mul_in(z, mask=pair_mask, inplace_safe=True, _add_with_inplace=True)
+        return z
+
+    def tri_att_start_end(self, z, _attn_chunk_size, pair_mask, use_deepspeed_evo_attention,
+                          use_cueq_triangle_kernels, use_lma, inplace_safe):
+        z = z if inplace_safe and z.is_contiguous() else z.clone(memory_format=torch.contiguous_format)
+        self.tri_att_start._run(z, pair_mask, transposed=False, in_place=True)
+        # the ending-node layer acts on z^T with mask^T; the kernel reads the transposed view in place
+        self.tri_att_end._run(z, pair_mask, transposed=True, in_place=True)
+        return z
+
+    def forward(self, z, pair_mask, chunk_size=None, use_deepspeed_evo_attention=False,
+                use_cueq_triangle_kernels=False, use_lma=False, inplace_safe=False, _mask_trans=True,
+                _attn_chunk_size=None):
+        """z [*, N, N, C_z], pair_mask [*, N, N] -> updated z."""
+        _forward_only(self, z)
+        self.ps_dropout_row_layer(z)  # raises in training mode with a non-zero rate
+        z = z if inplace_safe and z.is_contiguous() else z.clone(memory_format=torch.contiguous_format)
+        z = self.tri_mul_out_in(z, pair_mask, inplace_safe=True)
+        z = self.tri_att_start_end(z, _attn_chunk_size, pair_mask, use_deepspeed_evo_attention,
+                                   use_cueq_triangle_kernels, use_lma, inplace_safe=True)
+        self.pair_transition._run(z, pair_mask if _mask_trans else None, in_place=True)
+        return z
+
+
+class PairFormerBlock(nn.Module):
+    """Block of AF3 Algorithm 17. Drop-in for openfold3/core/model/latent/pairformer.py:38-213."""
+
+    def __init__(self, c_s, c_z, c_hidden_pair_bias, no_heads_pair_bias, c_hidden_mul, c_hidden_pair_att,
+                 no_heads_pair, transition_type, transition_n, pair_dropout, fuse_projection_weights, inf,
+                 linear_init_params=lin_init.pairformer_init):
+        super().__init__()
+        self.pair_stack = PairBlock(c_z=c_z, c_hidden_mul=c_hidden_mul, c_hidden_pair_att=c_hidden_pair_att,
+                                    no_heads_pair=no_heads_pair, transition_type=transition_type,
+                                    transition_n=transition_n, pair_dropout=pair_dropout,
+                                    fuse_projection_weights=fuse_projection_weights, inf=inf,
+                                    linear_init_params=linear_init_params.pair_block)
+        self.attn_pair_bias = AttentionPairBias(c_q=c_s, c_k=c_s, c_v=c_s, c_s=c_s, c_z=c_z,
+                                                c_hidden=c_hidden_pair_bias, no_heads=no_heads_pair_bias,
+                                                use_ada_layer_norm=False, gating=True, inf=inf,
+                                                linear_init_params=linear_init_params.att_pair_bias)
+        self.single_transition = SwiGLUTransition(c_in=c_s, n=transition_n,
+                                                  linear_init_params=linear_init_params.transition)
+
+    def forward(self, s, z, single_mask, pair_mask, chunk_size=None, use_deepspeed_evo_attention=False,
+                use_cueq_triangle_kernels=False, use_lma=False, inplace_safe=False, _mask_trans=True,
+                _attn_chunk_size=None):
+        _forward_only(self, s, z)
+        z = self.pair_stack(z=z, pair_mask=pair_mask, chunk_size=chunk_size, inplace_safe=inplace_safe,
+                            _mask_trans=_mask_trans, _attn_chunk_size=_attn_chunk_size)
+        s = s if inplace_safe and s.is_contiguous() else s.clone(memory_format=torch.contiguous_format)
+        self.attn_pair_bias._run(s, z, None, single_mask, in_place=True)
+        self.single_transition._run(s, single_mask if _mask_trans else None, in_place=True)
+        return s, z
+
+
+class PairFormerStack(nn.Module):
+    """AF3 Algorithm 17. Drop-in for openfold3/core/model/latent/pairformer.py:217-464."""
+
+    def __init__(self, c_s, c_z, c_hidden_pair_bias, no_heads_pair_bias, c_hidden_mul, c_hidden_pair_att,
+                 no_heads_pair, no_blocks, transition_type, transition_n, pair_dropout,
+                 fuse_projection_weights, blocks_per_ckpt, inf, linear_init_params=lin_init.pairformer_init,
+                 use_reentrant=None, clear_cache_between_blocks=False, tune_chunk_size=False, **kwargs):
+        super().__init__()
+        self.blocks_per_ckpt = blocks_per_ckpt
+        self.use_reentrant = use_reentrant
+        self.clear_cache_between_blocks = clear_cache_between_blocks
+        self.tune_chunk_size = tune_chunk_size
+        self.chunk_size_tuner = None  # nothing to tune: the kernels never materialise N^3 logits
+        self.blocks = nn.ModuleList([
+            PairFormerBlock(c_s=c_s, c_z=c_z, c_hidden_pair_bias=c_hidden_pair_bias,
+                            no_heads_pair_bias=no_heads_pair_bias, c_hidden_mul=c_hidden_mul,
+                            c_hidden_pair_att=c_hidden_pair_att, no_heads_pair=no_heads_pair,
+                            transition_type=transition_type, transition_n=transition_n,
+                            pair_dropout=pair_dropout, fuse_projection_weights=fuse_projection_weights,
+                            inf=inf, linear_init_params=linear_init_params)
+            for _ in range(no_blocks)
+        ])
+
+    def forward(self, s, z, single_mask, pair_mask, chunk_size=None, use_deepspeed_evo_attention=False,
+                use_cueq_triangle_kernels=False, use_lma=False, inplace_safe=False, _mask_trans=True):
+        _forward_only(self, s, z)
+        if not (inplace_safe and z.is_contiguous()):
+            z = z.clone(memory_format=torch.contiguous_format)
+        if not (inplace_safe and s.is_contiguous()):
+            s = s.clone(memory_format=torch.contiguous_format)
+        for b in self.blocks:
+            s, z = b(s, z, single_mask, pair_mask, chunk_size=chunk_size, inplace_safe=True,
+                     _mask_trans=_mask_trans)
+        return s, z
+
+
+class DiffusionTransformerBlock(nn.Module):
+    """AF3 Algorithm 23 block. Drop-in for openfold3/core/model/layers/diffusion_transformer.py:30-179
+    (the ``n_query is None`` token-level branch)."""
+
+    def __init__(self, c_a, c_s, c_z, c_hidden, no_heads, n_transition, use_ada_layer_norm, n_query, n_key,
+                 inf=1e9, linear_init_params=lin_init.diffusion_transformer_init):
+        super().__init__()
+        if n_query is not None:
+            raise NotImplementedError("the blocked atom-level cross attention is outside the Pairformer/"
+                                      "token-stack hot path")
+        self.use_cross_attention = False
+        self.attention_pair_bias = AttentionPairBias(c_q=c_a, c_k=c_a, c_v=c_a, c_s=c_s, c_z=c_z,
+                                                     c_hidden=c_hidden, no_heads=no_heads,
+                                                     use_ada_layer_norm=use_ada_layer_norm, gating=True,
+                                                     inf=inf,
+                                                     linear_init_params=linear_init_params.att_pair_bias)
+        self.conditioned_transition = ConditionedTransitionBlock(
+            c_a=c_a, c_s=c_s, n=n_transition, linear_init_params=linear_init_params.cond_transition)
+
+    def forward(self, a, s, z, mask=None, use_deepspeed_evo_attention=False, use_cueq_triangle_kernels=False,
+                use_lma=False, use_high_precision_attention=False, _mask_trans=True, _in_place=False):
+        _forward_only(self, a, s, z)
+        a = a if _in_place and a.is_contiguous() else a.clone(memory_format=torch.contiguous_format)
+        self.attention_pair_bias._run(a, z, s, mask, in_place=True)
+        self.conditioned_transition._run(a, s, mask if _mask_trans else None, in_place=True)
+        return a
+
+
+class DiffusionTransformer(nn.Module):
+    """AF3 Algorithm 23. Drop-in for openfold3/core/model/layers/diffusion_transformer.py:182-322."""
+
+    def __init__(self, c_a, c_s, c_z, c_hidden, no_heads, no_blocks, n_transition, use_ada_layer_norm,
+                 n_query, n_key, inf, blocks_per_ckpt=None, linear_init_params=lin_init.diffusion_transformer_init,
+                 use_reentrant=None):
+        super().__init__()
+        self.blocks_per_ckpt = blocks_per_ckpt
+        self.use_reentrant = use_reentrant
+        self.blocks = nn.ModuleList([
+            DiffusionTransformerBlock(c_a=c_a, c_s=c_s, c_z=c_z, c_hidden=c_hidden, no_heads=no_heads,
+                                      n_transition=n_transition, use_ada_layer_norm=use_ada_layer_norm,
+                                      n_query=n_query, n_key=n_key, inf=inf,
+                                      linear_init_params=linear_init_params)
+            for _ in range(no_blocks)
+        ])
+
+    def forward(self, a, s, z, mask=None, use_deepspeed_evo_attention=False, use_cueq_triangle_kernels=False,
+                use_lma=False, use_high_precision_attention=False, _mask_trans=True):
+        _forward_only(self, a, s, z)
+        a = a.clone(memory_format=torch.contiguous_format)
+        for b in self.blocks:
+            a = b(a, s, z, mask=mask, _mask_trans=_mask_trans, _in_place=True)
+        return a
