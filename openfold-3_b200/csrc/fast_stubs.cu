@@ -3,14 +3,8 @@
 #include "modules.cuh"
 namespace of3 {
 namespace fast {
-bool trimul_supported(int, int) { return false; }
-int trimul(const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, int, int, int,
-           const of3_trimul_params*, Arena&, cudaStream_t) { return OF3_ERR_SHAPE; }
 bool triattn_supported(int, int, int) { return false; }
 int triattn(const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, int, int, float, int,
             const of3_triattn_params*, Arena&, cudaStream_t) { return OF3_ERR_SHAPE; }
-bool transition_supported(int, int) { return false; }
-int transition(const __nv_bfloat16*, const __nv_bfloat16*, __nv_bfloat16*, long long, int,
-               const of3_transition_params*, Arena&, cudaStream_t) { return OF3_ERR_SHAPE; }
 }  // namespace fast
 }  // namespace of3

@@ -1,0 +1,529 @@
+// Triangle multiplicative update, bf16 / tcgen05 family (c_z = c_hidden = 128).
+//
+// Three kernels per layer, all fed by TMA:
+//   trimul_in   z tile -> LayerNorm_in (in place in the A operand) -> [a_p|a_g|b_p|b_g] projection
+//               (tcgen05, N = 256 per MMA) -> mask * sigmoid(gate) * proj -> a, b stored
+//               CHANNEL-MAJOR with the contracted index innermost: a_t[c][i][k], b_t[c][j][k].
+//               For the incoming update the tile walks z along its first index instead, so that
+//               both directions feed the same K-major x K-major contraction.
+//   contract    x_t[c][i][j] = sum_k a_t[c][i][k] * b_t[c][j][k]      (contract.cu)
+//   trimul_out  x tile (all channels of 128 positions) -> LayerNorm_out -> linear_z, and in the
+//               same pass z tile -> LayerNorm_in -> linear_g (recomputing the gate is one more
+//               128^3 MMA and saves writing and re-reading an N^2 x 128 gate tensor);
+//               out = z + sigmoid(gate) * update, TMA-stored.
+// Reference: openfold3/core/model/layers/triangular_multiplicative_update.py:421-503.
+#include "modules.cuh"
+#include "rowtile.cuh"
+#include "runtime.cuh"
+
+namespace of3 {
+namespace fast {
+namespace {
+
+using namespace umma;
+using namespace rowtile;
+
+constexpr int kKidIn = 2;
+constexpr int kKidOut = 3;
+
+struct TileCoord {
+    int b, fixed, t0;  // sample, fixed index (i), first row of the tile along the walking index
+};
+__device__ __forceinline__ TileCoord tile_coord(long long t, int N, int tiles_per_line) {
+    TileCoord c;
+    c.t0 = (int)(t % tiles_per_line) * kRows;
+    const long long line = t / tiles_per_line;
+    c.fixed = (int)(line % N);
+    c.b = (int)(line / N);
+    return c;
+}
+
+// =====================================================================================
+// trimul_in
+// =====================================================================================
+struct InSmem {
+    static constexpr uint32_t kW = 0;                          // 2 k-blocks x [512 rows x 128 B]
+    static constexpr uint32_t kWKb = 512 * 128;                // 65536
+    static constexpr uint32_t kZ = 2 * kWKb;                   // 2 stages x 32768
+    static constexpr uint32_t kGamma = kZ + 2 * kTileBytes;    // 128 floats
+    static constexpr uint32_t kBeta = kGamma + 512;
+    static constexpr uint32_t kBars = kBeta + 512;
+    static constexpr uint32_t kTotal = kBars + 128;
+    static constexpr uint32_t kDyn = kTotal + 1024;
+};
+
+// outgoing: tmZ is 3-D {c, second index, b*N + first index}; incoming: 4-D {c, second, first, b}
+template <bool kOutgoing>
+__global__ void __launch_bounds__(320, 1)
+trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWap,
+                 const __grid_constant__ CUtensorMap tmWag, const __grid_constant__ CUtensorMap tmWbp,
+                 const __grid_constant__ CUtensorMap tmWbg, const __nv_bfloat16* __restrict__ mask,
+                 const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
+                 __nv_bfloat16* __restrict__ a_t, __nv_bfloat16* __restrict__ b_t, int B, int N,
+                 int ld, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
+    float* gamma = reinterpret_cast<float*>(gbase + InSmem::kGamma);
+    float* beta = reinterpret_cast<float*>(gbase + InSmem::kBeta);
+    const uint32_t bars = sbase + InSmem::kBars;
+    const uint32_t w_full = bars;
+    auto z_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto z_empty = [&](int s) { return bars + 8u * (3 + s); };
+    auto a_ready = [&](int s) { return bars + 8u * (5 + s); };
+    auto slot_full = [&](int q) { return bars + 8u * (7 + q); };
+    auto slot_empty = [&](int q) { return bars + 8u * (9 + q); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + InSmem::kBars + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + InSmem::kBars + 104);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_per_line = (N + kRows - 1) / kRows;
+    const long long num_tiles = (long long)B * N * tiles_per_line;
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(z_full(s), 1);
+            mbar_init(z_empty(s), 1);
+            mbar_init(a_ready(s), 4);
+            mbar_init(slot_full(s), 1);
+            mbar_init(slot_empty(s), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmZ);
+    }
+    if (threadIdx.x < 128) {
+        gamma[threadIdx.x] = __bfloat162float(ln_w[threadIdx.x]);
+        beta[threadIdx.x] = __bfloat162float(ln_b[threadIdx.x]);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_full, 2 * InSmem::kWKb);
+            const CUtensorMap* wm[4] = {&tmWap, &tmWag, &tmWbp, &tmWbg};
+            for (int w = 0; w < 4; ++w)
+                for (int kb = 0; kb < 2; ++kb)
+                    tma_load_2d(sbase + InSmem::kW + kb * InSmem::kWKb + w * 128 * 128, wm[w], w_full,
+                                kb * 64, 0);
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(z_empty(s), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidIn, 1);
+                    break;
+                }
+                const TileCoord tc = tile_coord(t, N, tiles_per_line);
+                mbar_arrive_expect_tx(z_full(s), kTileBytes);
+                const uint32_t dst = sbase + InSmem::kZ + s * kTileBytes;
+                for (int kb = 0; kb < 2; ++kb) {
+                    if (kOutgoing)
+                        tma_load_3d(dst + kb * kKBlockBytes, &tmZ, z_full(s), kb * 64, tc.t0,
+                                    tc.b * N + tc.fixed);
+                    else
+                        tma_load_4d(dst + kb * kKBlockBytes, &tmZ, z_full(s), kb * 64, tc.fixed, tc.t0,
+                                    tc.b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 256);
+            bool ok = mbar_wait(w_full, 0, abort_flag);
+            if (!ok) report_wait_failure(status, abort_flag, kKidIn, 2);
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(a_ready(s), (it >> 1) & 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidIn, 3);
+                    break;
+                }
+                for (int q = 0; q < 2; ++q) {
+                    if (!mbar_wait(slot_empty(q), (it & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidIn, 4);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    mma_k128(tmem_base + q * 256, sbase + InSmem::kZ + s * kTileBytes,
+                             sbase + InSmem::kW + q * 256 * 128, InSmem::kWKb, idesc, false);
+                    mma_commit(slot_full(q));
+                }
+                if (ok) mma_commit(z_empty(s));
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- LayerNorm warps (2..5)
+        const int row = (warp - 2) * 32 + lane;
+        uint32_t it = 0;
+        for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const int s = it & 1;
+            if (!mbar_wait(z_full(s), (it >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 5);
+                break;
+            }
+            const uint32_t tile = sbase + InSmem::kZ + s * kTileBytes;
+            uint32_t raw[64];
+            load_row(tile, row, raw);
+            float mean, rstd;
+            row_stats(raw, mean, rstd);
+            store_normalized_row(tile, row, raw, mean, rstd, gamma, beta);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_ready(s));
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warps (6..9)
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const TileCoord tc = tile_coord(t, N, tiles_per_line);
+            const int k = tc.t0 + row;
+            const bool valid = k < N;
+            float m = 1.0f;
+            if (valid && mask != nullptr) {
+                const long long lin = kOutgoing ? ((long long)(tc.b * N + tc.fixed) * N + k)
+                                                : ((long long)(tc.b * N + k) * N + tc.fixed);
+                m = __bfloat162float(mask[lin]);
+            }
+            for (int q = 0; q < 2; ++q) {
+                if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                __nv_bfloat16* dst = (q == 0 ? a_t : b_t) +
+                                     ((long long)tc.b * kC * N + tc.fixed) * ld + k;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + q * 256;
+#pragma unroll 1
+                for (int cb = 0; cb < 4; ++cb) {
+                    uint32_t p[32], g[32];
+                    tmem_ld32(taddr + cb * 32, p);
+                    tmem_ld32(taddr + 128 + cb * 32, g);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            const float v = m * __uint_as_float(p[e]) * sigmoid_fast(__uint_as_float(g[e]));
+                            dst[(long long)(cb * 32 + e) * N * ld] = __float2bfloat16_rn(v);
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(slot_empty(q));
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// =====================================================================================
+// trimul_out
+// =====================================================================================
+struct OutSmem {
+    static constexpr uint32_t kWg = 0;                        // [128 x 128] as 2 k-blocks of 16 KB
+    static constexpr uint32_t kWz = kTileBytes;
+    static constexpr uint32_t kZ = 2 * kTileBytes;            // 2 groups x 32768 (z tile, then output)
+    static constexpr uint32_t kX = kZ + 2 * kTileBytes;       // 2 groups x 32768 (x tile [c][j], then A)
+    static constexpr uint32_t kParams = kX + 2 * kTileBytes;  // gamma_in, beta_in, gamma_out, beta_out
+    static constexpr uint32_t kBars = kParams + 4 * 512;
+    static constexpr uint32_t kTotal = kBars + 128;
+    static constexpr uint32_t kDyn = kTotal + 1024;
+};
+
+__global__ void __launch_bounds__(320, 1)
+trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmX,
+                  const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmWg,
+                  const __grid_constant__ CUtensorMap tmWz, const __nv_bfloat16* __restrict__ ln_in_w,
+                  const __nv_bfloat16* __restrict__ ln_in_b, const __nv_bfloat16* __restrict__ ln_out_w,
+                  const __nv_bfloat16* __restrict__ ln_out_b, int B, int N, int add_residual,
+                  int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
+    float* prm = reinterpret_cast<float*>(gbase + OutSmem::kParams);
+    const uint32_t bars = sbase + OutSmem::kBars;
+    const uint32_t w_full = bars;
+    auto full = [&](int g) { return bars + 8u * (1 + g); };     // TMA landed (z + x tiles)
+    auto empty = [&](int g) { return bars + 8u * (3 + g); };    // group released its buffers
+    auto a_ready = [&](int g) { return bars + 8u * (5 + g); };  // both A operands written
+    auto d_full = [&](int g) { return bars + 8u * (7 + g); };   // MMAs of the group's tile done
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + OutSmem::kBars + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OutSmem::kBars + 104);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_per_line = (N + kRows - 1) / kRows;
+    const long long num_tiles = (long long)B * N * tiles_per_line;
+    // tiles of this CTA alternate between the two groups: local tile index lt -> group lt & 1
+    const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full, 1);
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(full(g), 1);
+            mbar_init(empty(g), 1);
+            mbar_init(a_ready(g), 4);
+            mbar_init(d_full(g), 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmZ);
+        prefetch_tmap(&tmX);
+        prefetch_tmap(&tmOut);
+    }
+    if (threadIdx.x < 128) {
+        prm[threadIdx.x] = __bfloat162float(ln_in_w[threadIdx.x]);
+        prm[128 + threadIdx.x] = __bfloat162float(ln_in_b[threadIdx.x]);
+        prm[256 + threadIdx.x] = __bfloat162float(ln_out_w[threadIdx.x]);
+        prm[384 + threadIdx.x] = __bfloat162float(ln_out_b[threadIdx.x]);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_full, 2 * kTileBytes);
+            for (int kb = 0; kb < 2; ++kb) {
+                tma_load_2d(sbase + OutSmem::kWg + kb * kKBlockBytes, &tmWg, w_full, kb * 64, 0);
+                tma_load_2d(sbase + OutSmem::kWz + kb * kKBlockBytes, &tmWz, w_full, kb * 64, 0);
+            }
+            for (long long lt = 0; lt < my_tiles; ++lt) {
+                const int g = (int)(lt & 1);
+                const uint32_t use = (uint32_t)(lt >> 1);
+                if (!mbar_wait(empty(g), (use & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidOut, 1);
+                    break;
+                }
+                const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+                mbar_arrive_expect_tx(full(g), 2 * kTileBytes);
+                const uint32_t zdst = sbase + OutSmem::kZ + g * kTileBytes;
+                for (int kb = 0; kb < 2; ++kb)
+                    tma_load_3d(zdst + kb * kKBlockBytes, &tmZ, full(g), kb * 64, tc.t0, tc.b * N + tc.fixed);
+                // x tile: all 128 channels of positions (fixed, t0 .. t0+127), layout [c][j]
+                tma_load_3d(sbase + OutSmem::kX + g * kTileBytes, &tmX, full(g), tc.t0, tc.fixed, tc.b * kC);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 128);
+            bool ok = mbar_wait(w_full, 0, abort_flag);
+            if (!ok) report_wait_failure(status, abort_flag, kKidOut, 2);
+            for (long long lt = 0; lt < my_tiles && ok; ++lt) {
+                const int g = (int)(lt & 1);
+                const uint32_t use = (uint32_t)(lt >> 1);
+                if (!mbar_wait(a_ready(g), use & 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidOut, 3);
+                    break;
+                }
+                tc_fence_after_sync();
+                // gate = LN_in(z) W_g^T -> columns [0,128); update = LN_out(x) W_z^T -> [128,256)
+                mma_k128(tmem_base + g * 256, sbase + OutSmem::kZ + g * kTileBytes, sbase + OutSmem::kWg,
+                         kKBlockBytes, idesc, false);
+                mma_k128(tmem_base + g * 256 + 128, sbase + OutSmem::kX + g * kTileBytes,
+                         sbase + OutSmem::kWz, kKBlockBytes, idesc, false);
+                mma_commit(d_full(g));
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- two row groups (warps 2..5, 6..9)
+        const int g = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int gtid = (warp - 2 - g * 4) * 32 + lane;  // 0..127 inside the group
+        const uint32_t ztile = sbase + OutSmem::kZ + g * kTileBytes;
+        const uint32_t xtile = sbase + OutSmem::kX + g * kTileBytes;
+        for (long long lt = g; lt < my_tiles; lt += 2) {
+            const uint32_t use = (uint32_t)(lt >> 1);
+            const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+            if (!mbar_wait(full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 4);
+                break;
+            }
+            float mean, rstd;
+            // --- x column of this position: 128 channels, [c][j] layout, stride 256 B
+            {
+                uint32_t xraw[64];
+                const uint32_t col = xtile + row * 2;
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    uint32_t lo, hi;
+                    if ((i & 7) == 0) asm volatile("" ::: "memory");  // cap the loads in flight per batch
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(lo) : "r"(col + (2 * i) * 256));
+                    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(hi) : "r"(col + (2 * i + 1) * 256));
+                    xraw[i] = lo | (hi << 16);
+                }
+                row_stats(xraw, mean, rstd);
+                group_sync(1 + g, 128);  // everyone has read its column before rows overwrite the buffer
+                store_normalized_row(xtile, row, xraw, mean, rstd, prm + 256, prm + 384);
+            }
+            // --- z row: keep the raw values for the residual, normalise in place (A operand 1)
+            uint32_t zraw[64];
+            load_row(ztile, row, zraw);
+            row_stats(zraw, mean, rstd);
+            store_normalized_row(ztile, row, zraw, mean, rstd, prm, prm + 128);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_ready(g));
+            // --- wait for both GEMMs, combine, write the output tile over the z buffer
+            if (!mbar_wait(d_full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
+#pragma unroll
+            for (int cb = 0; cb < 8; ++cb) {  // 16 channels per step
+                uint32_t gate[16], upd[16];
+                tmem_ld16(taddr + cb * 16, gate);
+                tmem_ld16(taddr + 128 + cb * 16, upd);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int e = ch * 8 + j * 2;
+                        const uint32_t zr = zraw[cb * 8 + ch * 4 + j];
+                        float v0 = sigmoid_fast(__uint_as_float(gate[e])) * __uint_as_float(upd[e]);
+                        float v1 = sigmoid_fast(__uint_as_float(gate[e + 1])) * __uint_as_float(upd[e + 1]);
+                        if (add_residual) {
+                            v0 += bf16lo(zr);
+                            v1 += bf16hi(zr);
+                        }
+                        o[j] = pack_bf16x2(v0, v1);
+                    }
+                    sts128(chunk_addr(ztile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
+                }
+            }
+            tc_fence_before_sync();
+            fence_proxy_async_smem();
+            group_sync(1 + g, 128);
+            if (gtid == 0) {
+                for (int kb = 0; kb < 2; ++kb)
+                    tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * N + tc.fixed);
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                mbar_arrive(empty(g));
+            }
+        }
+        if (gtid == 0) tma_store_wait_all<0>();
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+int weight_tmap(CUtensorMap* m, const void* w, int rows) {
+    uint64_t dims[2] = {128, (uint64_t)rows};
+    uint64_t str[1] = {256};
+    uint32_t box[2] = {64, 128};
+    return make_tmap_bf16(m, w, 2, dims, str, box, true);
+}
+
+}  // namespace
+
+bool trimul_supported(int c_z, int c_h) { return c_z == 128 && c_h == 128; }
+
+int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
+           int flags, const of3_trimul_params* p, Arena& ws, cudaStream_t st) {
+    const int ld = (int)align_up(N, 8);
+    const size_t plane = (size_t)B * kC * N * ld * sizeof(__nv_bfloat16);
+    __nv_bfloat16* a_t = (__nv_bfloat16*)ws.take(plane);
+    __nv_bfloat16* b_t = (__nv_bfloat16*)ws.take(plane);
+    __nv_bfloat16* x_t = (__nv_bfloat16*)ws.take(plane);
+    if (!ws.base) return OF3_OK;
+    OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "trimul: workspace too small (%zu needed)", ws.off);
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
+                "trimul: z/out must be 16-byte aligned");
+    const bool outgoing = (flags & OF3_FLAG_OUTGOING) != 0;
+    int rc;
+    CUtensorMap tmZin, tmZrow, tmOut, tmX, tmW[6];
+    {   // z as rows of one line: {c, second index, b*N + first index}
+        uint64_t dims[3] = {128, (uint64_t)N, (uint64_t)B * N};
+        uint64_t str[2] = {256, (uint64_t)N * 256};
+        uint32_t box[3] = {64, 128, 1};
+        if ((rc = make_tmap_bf16(&tmZrow, z, 3, dims, str, box, true))) return rc;
+        if ((rc = make_tmap_bf16(&tmOut, out, 3, dims, str, box, true))) return rc;
+    }
+    if (outgoing) {
+        tmZin = tmZrow;
+    } else {  // walk the first index: {c, second, first, b}
+        uint64_t dims[4] = {128, (uint64_t)N, (uint64_t)N, (uint64_t)B};
+        uint64_t str[3] = {256, (uint64_t)N * 256, (uint64_t)N * N * 256};
+        uint32_t box[4] = {64, 1, 128, 1};
+        if ((rc = make_tmap_bf16(&tmZin, z, 4, dims, str, box, true))) return rc;
+    }
+    {   // x_t[b*128 + c][i][j], pitch ld: box = 128 positions j x 1 x 128 channels, no swizzle
+        uint64_t dims[3] = {(uint64_t)N, (uint64_t)N, (uint64_t)B * kC};
+        uint64_t str[2] = {(uint64_t)ld * 2, (uint64_t)N * ld * 2};
+        uint32_t box[3] = {128, 1, 128};
+        if ((rc = make_tmap_bf16(&tmX, x_t, 3, dims, str, box, false))) return rc;
+    }
+    const void* ws6[6] = {p->w_a_p, p->w_a_g, p->w_b_p, p->w_b_g, p->w_g, p->w_z};
+    for (int i = 0; i < 6; ++i)
+        if ((rc = weight_tmap(&tmW[i], ws6[i], 128))) return rc;
+
+    static bool attr_done = false;
+    if (!attr_done) {
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, OutSmem::kDyn));
+        attr_done = true;
+    }
+    int* status = device_status_ptr();
+    const long long tiles = (long long)B * N * ceil_div(N, kRows);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    if (outgoing)
+        trimul_in_kernel<true><<<grid, 320, InSmem::kDyn, st>>>(
+            tmZin, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, N, ld, status);
+    else
+        trimul_in_kernel<false><<<grid, 320, InSmem::kDyn, st>>>(
+            tmZin, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, N, ld, status);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    rc = contract_nt_bf16(a_t, b_t, x_t, B * kC, N, N, N, ld, ld, ld, (long long)N * ld,
+                          (long long)N * ld, (long long)N * ld, st);
+    if (rc) return rc;
+    trimul_out_kernel<<<grid, 320, OutSmem::kDyn, st>>>(
+        tmZrow, tmX, tmOut, tmW[4], tmW[5], (const __nv_bfloat16*)p->ln_in_w,
+        (const __nv_bfloat16*)p->ln_in_b, (const __nv_bfloat16*)p->ln_out_w,
+        (const __nv_bfloat16*)p->ln_out_b, B, N, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, status);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+}  // namespace fast
+}  // namespace of3

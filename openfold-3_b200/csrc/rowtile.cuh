@@ -1,0 +1,117 @@
+// Device helpers shared by the "row tile" kernels: a tile is 128 rows (pair positions) of 128
+// bf16 channels held in shared memory as a K-major, 128-byte-swizzled tcgen05 A operand made of
+// two k-blocks [128 rows x 64 channels] (16 KB each) -- exactly what two TMA boxes {64, 128}
+// with CU_TENSOR_MAP_SWIZZLE_128B deposit. One thread owns one row.
+#pragma once
+#include "umma.cuh"
+
+namespace of3 {
+namespace rowtile {
+
+constexpr int kRows = 128;
+constexpr int kC = 128;
+constexpr int kKBlockBytes = kRows * 64 * 2;  // 16384
+constexpr int kTileBytes = 2 * kKBlockBytes;  // 32768
+constexpr float kLnEps = 1e-5f;
+
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// sigmoid through one MUFU op (tanh.approx); absolute error ~5e-4, well inside bf16 rounding.
+__device__ __forceinline__ float sigmoid_fast(float x) {
+    return fmaf(0.5f, tanh_approx(0.5f * x), 0.5f);
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Named barrier for a subset of the CTA's warps (id 1..15; nthreads multiple of 32).
+__device__ __forceinline__ void group_sync(int id, int nthreads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// Shared-memory address of 16-byte chunk `chunk` (0..15, 8 channels each) of row `row`.
+__device__ __forceinline__ uint32_t chunk_addr(uint32_t tile, int row, int chunk) {
+    return tile + (uint32_t)((chunk >> 3) * kKBlockBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+                 "r"(v.w)
+                 : "memory");
+}
+
+// Reads this thread's row (128 bf16) of a swizzled tile into 64 packed registers.
+__device__ __forceinline__ void load_row(uint32_t tile, int row, uint32_t (&raw)[64]) {
+#pragma unroll
+    for (int ch = 0; ch < 16; ++ch) {
+        const uint4 v = lds128(chunk_addr(tile, row, ch));
+        raw[ch * 4 + 0] = v.x;
+        raw[ch * 4 + 1] = v.y;
+        raw[ch * 4 + 2] = v.z;
+        raw[ch * 4 + 3] = v.w;
+    }
+}
+
+// LayerNorm statistics of 128 packed bf16 values (fp32, two-pass on registers).
+__device__ __forceinline__ void row_stats(const uint32_t (&raw)[64], float& mean, float& rstd) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) s += bf16lo(raw[i]) + bf16hi(raw[i]);
+    mean = s * (1.0f / kC);
+    float v = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; ++i) {
+        const float a = bf16lo(raw[i]) - mean, b = bf16hi(raw[i]) - mean;
+        v = fmaf(a, a, v);
+        v = fmaf(b, b, v);
+    }
+    rstd = rsqrtf(v * (1.0f / kC) + kLnEps);
+}
+
+// Writes LN(raw) * gamma + beta (bf16) as this thread's row of a swizzled tile.
+// gamma/beta: fp32 arrays of 128 in shared memory (broadcast reads).
+__device__ __forceinline__ void store_normalized_row(uint32_t tile, int row, const uint32_t (&raw)[64],
+                                                     float mean, float rstd, const float* gamma,
+                                                     const float* beta) {
+#pragma unroll
+    for (int ch = 0; ch < 16; ++ch) {
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = ch * 8 + j * 2;
+            const float a = (bf16lo(raw[ch * 4 + j]) - mean) * rstd * gamma[c] + beta[c];
+            const float b = (bf16hi(raw[ch * 4 + j]) - mean) * rstd * gamma[c + 1] + beta[c + 1];
+            o[j] = pack_bf16x2(a, b);
+        }
+        sts128(chunk_addr(tile, row, ch), make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+
+// 8 tcgen05.mma (K = 128 in steps of 16) of one row tile against a weight slab:
+// D[128 x N] (+)= A[128 x 128] * W[N x 128]^T. `w_kb_stride` = bytes between the slab's k-blocks.
+__device__ __forceinline__ void mma_k128(uint32_t d_tmem, uint32_t a_tile, uint32_t w_slab,
+                                         uint32_t w_kb_stride, uint32_t idesc, bool accumulate) {
+#pragma unroll
+    for (int kb = 0; kb < 2; ++kb) {
+        const uint64_t ad = umma::smem_desc_k_sw128(a_tile + kb * kKBlockBytes);
+        const uint64_t bd = umma::smem_desc_k_sw128(w_slab + kb * w_kb_stride);
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+            umma::mma_bf16(d_tmem, ad + 2u * k4, bd + 2u * k4, idesc,
+                           (accumulate || kb != 0 || k4 != 0) ? 1u : 0u);
+    }
+}
+
+}  // namespace rowtile
+}  // namespace of3

