@@ -28,7 +28,7 @@ int trimul_dispatch(const void* z, const void* mask, void* out, int B, int N, in
 int triattn_dispatch(const void* z, const void* mask, void* out, int B, int N, int c_z, int H, int d,
                      float inf, int dtype, int flags, const of3_triattn_params* p, Arena& ws,
                      cudaStream_t st) {
-    if (use_fast(dtype, flags) && fast::triattn_supported(c_z, H, d))
+    if (use_fast(dtype, flags) && fast::triattn_supported(c_z, H, d, N))
         return fast::triattn((const __nv_bfloat16*)z, (const __nv_bfloat16*)mask, (__nv_bfloat16*)out,
                              B, N, inf, flags, p, ws, st);
     if (dtype == OF3_DTYPE_BF16)
@@ -84,7 +84,7 @@ int of3_fast_path_available(int module_id, int dtype, int c, int c_hidden, int h
     if (dtype != OF3_DTYPE_BF16) return 0;
     switch (module_id) {
         case OF3_MODULE_TRIMUL: return fast::trimul_supported(c, c_hidden) ? 1 : 0;
-        case OF3_MODULE_TRIATTN: return fast::triattn_supported(c, heads, head_dim) ? 1 : 0;
+        case OF3_MODULE_TRIATTN: return fast::triattn_supported(c, heads, head_dim, 1) ? 1 : 0;
         case OF3_MODULE_TRANSITION: return fast::transition_supported(c, c_hidden) ? 1 : 0;
         default: return 0;
     }

@@ -234,6 +234,7 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
     const long long tiles = (long long)batch * ceil_div(M, kBM) * ceil_div(N, BN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     int* status = device_status_ptr();
+    LaunchScope scope(kKernelIdContract, stream);
     contract_nt_kernel<BN><<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, batch,
                                                                    o_bs, ldo, status);
     OF3_CUDA_CHECK(cudaGetLastError());

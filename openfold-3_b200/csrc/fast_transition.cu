@@ -353,6 +353,7 @@ int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16*
     long long grid = sm_count();
     if (tiles < 2 * grid) grid = (tiles + 1) / 2;
     if (grid < 1) grid = 1;
+    LaunchScope scope(kKidTrans, st);
     transition_kernel<<<(int)grid, 320, TrSmem::kDyn, st>>>(
         tmX, tmOut, tmWa, tmWb, tmWo, mask, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
         rows, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, device_status_ptr());

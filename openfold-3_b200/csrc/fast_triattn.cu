@@ -1,0 +1,925 @@
+// Triangle attention, bf16 / tcgen05 family (c_z = 128, 4 heads x 32).
+//
+//   triattn_proj   z tile -> LayerNorm (in place in the A operand) -> [q|k|v] projection on
+//                  tcgen05; the 4-wide triangle-bias projection is folded into the LayerNorm
+//                  pass (fp32 dot products). q is stored pre-scaled by log2(e)/sqrt(d), the bias
+//                  pre-scaled by log2(e), so the softmax runs on exp2. Layouts:
+//                  q,k [line][head][pos][32] (K-major operands of Q K^T), v transposed
+//                  [line][head][32][pos] (K-major operand of P V), bias [head][q][k].
+//   triattn_core   streaming attention for one (line, head, 128 queries): S = Q K^T and
+//                  O_blk = P V on tcgen05 with S/O accumulators double-buffered in TMEM, online
+//                  softmax (fp32, exp2) by one thread per query row, mask + pair bias added in
+//                  fp32 exactly in the reference's order; N^3 logits are never materialised.
+//   triattn_out    z tile -> LayerNorm -> linear_g (gate recomputed instead of stored), o tile
+//                  * sigmoid(gate) -> linear_o -> + z, TMA-stored.
+// "line" is the leading index of the (possibly transposed) pair tensor: with kTransposed the
+// kernels read and write z through transposed TMA boxes, which gives the ending-node layer
+// (and PairBlock's transpose / tri_att_end / transpose) without moving z.
+// Reference: openfold3/core/model/layers/triangular_attention.py:102-167,
+//            openfold3/core/model/primitives/attention.py:94-135, 270-310.
+#include "modules.cuh"
+#include "rowtile.cuh"
+#include "runtime.cuh"
+
+namespace of3 {
+namespace fast {
+namespace {
+
+using namespace umma;
+using namespace rowtile;
+
+constexpr int kH = 4;
+constexpr int kD = 32;
+constexpr int kKidProj = 5;
+constexpr int kKidCore = 6;
+constexpr int kKidOut = 7;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct LineTile {
+    int b, line, t0;
+};
+__device__ __forceinline__ LineTile line_tile(long long t, int N, int tiles_per_line) {
+    LineTile c;
+    c.t0 = (int)(t % tiles_per_line) * kRows;
+    const long long l = t / tiles_per_line;
+    c.line = (int)(l % N);
+    c.b = (int)(l / N);
+    return c;
+}
+// z tile of a line: rows (line, t0..t0+127) of the view; transposed view = z[b, t, line, :]
+template <bool kTransposed>
+__device__ __forceinline__ void load_z_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                            const LineTile& c, int N) {
+    for (int kb = 0; kb < 2; ++kb) {
+        if (kTransposed)
+            tma_load_4d(dst + kb * kKBlockBytes, tm, bar, kb * 64, c.line, c.t0, c.b);
+        else
+            tma_load_3d(dst + kb * kKBlockBytes, tm, bar, kb * 64, c.t0, c.b * N + c.line);
+    }
+}
+
+// =====================================================================================
+// triattn_proj
+// =====================================================================================
+struct ProjSmem {
+    static constexpr uint32_t kWKb = 384 * 128;               // one k-block of [q|k|v]: 49152
+    static constexpr uint32_t kW = 0;
+    static constexpr uint32_t kZ = 2 * kWKb;                  // 2 stages x 32768
+    static constexpr uint32_t kGamma = kZ + 2 * kTileBytes;
+    static constexpr uint32_t kBeta = kGamma + 512;
+    static constexpr uint32_t kWb = kBeta + 512;              // float [4][128]
+    static constexpr uint32_t kBars = kWb + 2048;
+    static constexpr uint32_t kTotal = kBars + 128;
+    static constexpr uint32_t kDyn = kTotal + 1024;
+};
+
+template <bool kTransposed>
+__global__ void __launch_bounds__(320, 1)
+triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWq,
+                    const __grid_constant__ CUtensorMap tmWk, const __grid_constant__ CUtensorMap tmWv,
+                    const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
+                    const __nv_bfloat16* __restrict__ w_bias, __nv_bfloat16* __restrict__ q_out,
+                    __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ vt_out,
+                    __nv_bfloat16* __restrict__ tb_out, int B, int N, int ldn, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
+    float* gamma = reinterpret_cast<float*>(gbase + ProjSmem::kGamma);
+    float* beta = reinterpret_cast<float*>(gbase + ProjSmem::kBeta);
+    float* wb = reinterpret_cast<float*>(gbase + ProjSmem::kWb);
+    const uint32_t bars = sbase + ProjSmem::kBars;
+    const uint32_t w_full = bars;
+    auto z_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto z_empty = [&](int s) { return bars + 8u * (3 + s); };
+    auto a_ready = [&](int s) { return bars + 8u * (5 + s); };
+    auto slot_full = [&](int q) { return bars + 8u * (7 + q); };
+    auto slot_empty = [&](int q) { return bars + 8u * (9 + q); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + ProjSmem::kBars + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + ProjSmem::kBars + 104);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_per_line = (N + kRows - 1) / kRows;
+    const long long num_tiles = (long long)B * N * tiles_per_line;
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(z_full(s), 1);
+            mbar_init(z_empty(s), 1);
+            mbar_init(a_ready(s), 4);
+            mbar_init(slot_full(s), 1);
+            mbar_init(slot_empty(s), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmZ);
+    }
+    if (threadIdx.x < 128) {
+        gamma[threadIdx.x] = __bfloat162float(ln_w[threadIdx.x]);
+        beta[threadIdx.x] = __bfloat162float(ln_b[threadIdx.x]);
+    }
+    for (int i = threadIdx.x; i < kH * kC; i += blockDim.x) wb[i] = __bfloat162float(w_bias[i]);
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr;
+    // TMEM: slot 0 = [q|k] columns [0,256), slot 1 = v columns [256,384)
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_full, 2 * ProjSmem::kWKb);
+            const CUtensorMap* wm[3] = {&tmWq, &tmWk, &tmWv};
+            for (int w = 0; w < 3; ++w)
+                for (int kb = 0; kb < 2; ++kb)
+                    tma_load_2d(sbase + ProjSmem::kW + kb * ProjSmem::kWKb + w * 128 * 128, wm[w], w_full,
+                                kb * 64, 0);
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(z_empty(s), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidProj, 1);
+                    break;
+                }
+                const LineTile tc = line_tile(t, N, tiles_per_line);
+                mbar_arrive_expect_tx(z_full(s), kTileBytes);
+                load_z_tile<kTransposed>(sbase + ProjSmem::kZ + s * kTileBytes, &tmZ, z_full(s), tc, N);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = mbar_wait(w_full, 0, abort_flag);
+            if (!ok) report_wait_failure(status, abort_flag, kKidProj, 2);
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(a_ready(s), (it >> 1) & 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidProj, 3);
+                    break;
+                }
+                for (int q = 0; q < 2; ++q) {
+                    if (!mbar_wait(slot_empty(q), (it & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidProj, 4);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    mma_k128(tmem_base + q * 256, sbase + ProjSmem::kZ + s * kTileBytes,
+                             sbase + ProjSmem::kW + q * 256 * 128, ProjSmem::kWKb,
+                             q == 0 ? idesc_bf16_f32(128, 256) : idesc_bf16_f32(128, 128), false);
+                    mma_commit(slot_full(q));
+                }
+                if (ok) mma_commit(z_empty(s));
+            }
+        }
+    } else if (warp < 6) {
+        // LayerNorm warps: normalise in place and project the triangle bias in fp32
+        const int row = (warp - 2) * 32 + lane;
+        uint32_t it = 0;
+        for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const int s = it & 1;
+            if (!mbar_wait(z_full(s), (it >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 5);
+                break;
+            }
+            const LineTile tc = line_tile(t, N, tiles_per_line);
+            const uint32_t tile = sbase + ProjSmem::kZ + s * kTileBytes;
+            uint32_t raw[64];
+            load_row(tile, row, raw);
+            float mean, rstd;
+            row_stats(raw, mean, rstd);
+            float tb[kH] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ch = 0; ch < 16; ++ch) {
+                uint32_t o[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int c = ch * 8 + j * 2;
+                    const float a = (bf16lo(raw[ch * 4 + j]) - mean) * rstd * gamma[c] + beta[c];
+                    const float bb = (bf16hi(raw[ch * 4 + j]) - mean) * rstd * gamma[c + 1] + beta[c + 1];
+#pragma unroll
+                    for (int h = 0; h < kH; ++h) {
+                        const float2 w2 = *reinterpret_cast<const float2*>(wb + h * kC + c);
+                        tb[h] = fmaf(a, w2.x, tb[h]);
+                        tb[h] = fmaf(bb, w2.y, tb[h]);
+                    }
+                    o[j] = pack_bf16x2(a, bb);
+                }
+                sts128(chunk_addr(tile, row, ch), make_uint4(o[0], o[1], o[2], o[3]));
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_ready(s));
+            const int pos = tc.t0 + row;
+            if (pos < ldn) {  // the row padding [N, ldn) is read by the attention kernel: keep it finite
+#pragma unroll
+                for (int h = 0; h < kH; ++h)
+                    tb_out[(((long long)tc.b * kH + h) * N + tc.line) * ldn + pos] =
+                        __float2bfloat16_rn(pos < N ? tb[h] * kLog2e : 0.f);
+            }
+        }
+    } else {
+        // epilogue warps
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const float qscale = kLog2e * rsqrtf((float)kD);
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const LineTile tc = line_tile(t, N, tiles_per_line);
+            const int pos = tc.t0 + row;
+            const bool valid = pos < N;
+            const long long lineh = ((long long)tc.b * N + tc.line) * kH;  // (line, head 0)
+            // ---- slot 0: q (columns 0..127) and k (128..255), [line][head][pos][32]
+            if (!mbar_wait(slot_full(0), it & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 6);
+                break;
+            }
+            tc_fence_after_sync();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+            for (int qk = 0; qk < 2; ++qk) {
+                __nv_bfloat16* base = qk == 0 ? q_out : k_out;
+                const float sc = qk == 0 ? qscale : 1.0f;
+#pragma unroll 1
+                for (int h = 0; h < kH; ++h) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + qk * 128 + h * 32, r);
+                    tmem_ld_wait();
+                    if (valid) {
+                        uint4* dst = reinterpret_cast<uint4*>(base + ((lineh + h) * N + pos) * kD);
+#pragma unroll
+                        for (int v4 = 0; v4 < 4; ++v4) {
+                            uint4 v;
+                            v.x = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 0]), sc * __uint_as_float(r[v4 * 8 + 1]));
+                            v.y = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 2]), sc * __uint_as_float(r[v4 * 8 + 3]));
+                            v.z = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 4]), sc * __uint_as_float(r[v4 * 8 + 5]));
+                            v.w = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 6]), sc * __uint_as_float(r[v4 * 8 + 7]));
+                            dst[v4] = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(slot_empty(0));
+            // ---- slot 1: v, stored transposed [line][head][32][pos]
+            if (!mbar_wait(slot_full(1), it & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 7);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll 1
+            for (int h = 0; h < kH; ++h) {
+                uint32_t r[32];
+                tmem_ld32(taddr + 256 + h * 32, r);
+                tmem_ld_wait();
+                if (valid) {
+                    __nv_bfloat16* dst = vt_out + ((lineh + h) * kD) * ldn + pos;
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) dst[(long long)e * ldn] = __float2bfloat16_rn(__uint_as_float(r[e]));
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(slot_empty(1));
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// =====================================================================================
+// triattn_core
+// =====================================================================================
+constexpr int kBQ = 128;      // queries per CTA
+constexpr int kBK = 64;       // keys per block
+constexpr int kMaxKeys = 4096;
+
+struct CoreSmem {
+    static constexpr uint32_t kQ = 0;                        // 128 x 64 B (64-byte swizzle)  8 KB
+    static constexpr uint32_t kK = 8192;                     // 2 stages x (64 x 64 B)        8 KB
+    static constexpr uint32_t kV = kK + 2 * 4096;            // 2 stages x (32 x 128 B)       8 KB
+    static constexpr uint32_t kP = kV + 2 * 4096;            // 2 x (128 x 128 B)            32 KB
+    static constexpr uint32_t kMb = kP + 2 * kKBlockBytes;   // mask bias, fp32 [kMaxKeys + 64]
+    static constexpr uint32_t kBars = kMb + (kMaxKeys + 64) * 4;
+    static constexpr uint32_t kTotal = kBars + 160;
+    static constexpr uint32_t kDyn = kTotal + 1024;
+};
+
+template <bool kTransposed>
+__global__ void __launch_bounds__(192, 2)
+triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __nv_bfloat16* __restrict__ tb,
+                    const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
+                    int N, int ldn, float inf, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
+    float* mbs = reinterpret_cast<float*>(gbase + CoreSmem::kMb);
+    const uint32_t bars = sbase + CoreSmem::kBars;
+    const uint32_t q_full = bars;
+    auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
+    auto s_full = [&](int s) { return bars + 8u * (5 + s); };
+    auto s_empty = [&](int s) { return bars + 8u * (7 + s); };
+    auto p_ready = [&](int s) { return bars + 8u * (9 + s); };
+    auto o_full = [&](int s) { return bars + 8u * (11 + s); };
+    auto o_empty = [&](int s) { return bars + 8u * (13 + s); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 136);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_qt = (N + kBQ - 1) / kBQ;
+    const int qt = blockIdx.x % n_qt;
+    const int h = (blockIdx.x / n_qt) % kH;
+    const long long bl = blockIdx.x / (n_qt * kH);  // b * N + line
+    const int line = (int)(bl % N);
+    const int b = (int)(bl / N);
+    const int q0 = qt * kBQ;
+    const int nblk = (N + kBK - 1) / kBK;
+    const int lh = (int)(bl * kH + h);  // (line, head) index of q/k/v
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+            mbar_init(s_full(s), 1);
+            mbar_init(s_empty(s), 4);
+            mbar_init(p_ready(s), 4);
+            mbar_init(o_full(s), 1);
+            mbar_init(o_empty(s), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmQ);
+        prefetch_tmap(&tmK);
+        prefetch_tmap(&tmV);
+    }
+    // additive key mask of this line, pre-scaled for exp2: inf * (mask - 1) * log2(e); -inf beyond N
+    for (int k = threadIdx.x; k < nblk * kBK; k += blockDim.x) {
+        float v = -INFINITY;
+        if (k < N) {
+            v = 0.f;
+            if (mask != nullptr) {
+                const long long idx = kTransposed ? ((long long)b * N + k) * N + line
+                                                  : ((long long)b * N + line) * N + k;
+                v = inf * (__bfloat162float(mask[idx]) - 1.0f) * kLog2e;
+            }
+        }
+        mbs[k] = v;
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 256);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr;
+    // TMEM columns: S0 [0,64) S1 [64,128) O0 [128,160) O1 [160,192)
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(q_full, kBQ * 64);
+            tma_load_3d(sbase + CoreSmem::kQ, &tmQ, q_full, 0, q0, lh);
+            for (int j = 0; j < nblk; ++j) {
+                const int s = j & 1;
+                if (!mbar_wait(kv_empty(s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidCore, 1);
+                    break;
+                }
+                mbar_arrive_expect_tx(kv_full(s), 8192);
+                tma_load_3d(sbase + CoreSmem::kK + s * 4096, &tmK, kv_full(s), 0, j * kBK, lh);
+                tma_load_3d(sbase + CoreSmem::kV + s * 4096, &tmV, kv_full(s), j * kBK, 0, lh);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);
+            constexpr uint32_t idesc_o = idesc_bf16_f32(128, kD);
+            bool ok = mbar_wait(q_full, 0, abort_flag);
+            if (!ok) report_wait_failure(status, abort_flag, kKidCore, 2);
+            const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ);
+            for (int j = 0; j <= nblk && ok; ++j) {
+                if (j < nblk) {  // S_j = Q K_j^T
+                    const int s = j & 1;
+                    if (!mbar_wait(kv_full(s), (j >> 1) & 1u, abort_flag) ||
+                        !mbar_wait(s_empty(s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 3);
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + s * 4096);
+                    mma_bf16(tmem_base + s * kBK, qdesc, kdesc, idesc_s, 0u);
+                    mma_bf16(tmem_base + s * kBK, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
+                    mma_commit(s_full(s));
+                }
+                if (j >= 1) {  // O_{j-1} = P_{j-1} V_{j-1}
+                    const int jj = j - 1;
+                    const int s = jj & 1;
+                    if (!mbar_wait(p_ready(s), (jj >> 1) & 1u, abort_flag) ||
+                        !mbar_wait(o_empty(s), ((jj >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 4);
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint64_t pdesc = smem_desc_k_sw128(sbase + CoreSmem::kP + s * kKBlockBytes);
+                    const uint64_t vdesc = smem_desc_k_sw128(sbase + CoreSmem::kV + s * 4096);
+#pragma unroll
+                    for (int k4 = 0; k4 < 4; ++k4)
+                        mma_bf16(tmem_base + 128 + s * kD, pdesc + 2u * k4, vdesc + 2u * k4, idesc_o,
+                                 k4 != 0 ? 1u : 0u);
+                    mma_commit(o_full(s));
+                    mma_commit(kv_empty(s));
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax warps (2..5)
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int qpos = q0 + row;
+        const int qclamp = qpos < N ? qpos : N - 1;
+        const __nv_bfloat16* tbrow = tb + (((long long)b * kH + h) * N + qclamp) * ldn;
+        const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16);
+        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        float o[kD];
+#pragma unroll
+        for (int e = 0; e < kD; ++e) o[e] = 0.f;
+        bool ok = true;
+        for (int j = 0; j < nblk && ok; ++j) {
+            const int s = j & 1;
+            // pair bias of this row for the block's 64 keys (8 x 16 B), issued before the wait
+            uint4 tbv[8];
+            const int k0 = j * kBK;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                // ldn is padded to a multiple of 64, so the loads stay inside the row's allocation
+                tbv[i] = __ldg(reinterpret_cast<const uint4*>(tbrow + k0) + i);
+            }
+            if (!mbar_wait(s_full(s), (j >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 5);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            float sv[kBK];
+            {
+                uint32_t r0[32], r1[32];
+                tmem_ld32(trow + s * kBK, r0);
+                tmem_ld32(trow + s * kBK + 32, r1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    sv[e] = __uint_as_float(r0[e]);
+                    sv[32 + e] = __uint_as_float(r1[e]);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s_empty(s));
+            float mx = m;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const uint32_t w[4] = {tbv[i].x, tbv[i].y, tbv[i].z, tbv[i].w};
+                const float4 mb0 = *reinterpret_cast<const float4*>(mbs + k0 + i * 8);
+                const float4 mb1 = *reinterpret_cast<const float4*>(mbs + k0 + i * 8 + 4);
+                const float mbv[8] = {mb0.x, mb0.y, mb0.z, mb0.w, mb1.x, mb1.y, mb1.z, mb1.w};
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int e = i * 8 + jj * 2;
+                    // (q.k + mask bias) + pair bias: the reference's order, in fp32
+                    sv[e] = (sv[e] + mbv[jj * 2]) + bf16lo(w[jj]);
+                    sv[e + 1] = (sv[e + 1] + mbv[jj * 2 + 1]) + bf16hi(w[jj]);
+                    mx = fmaxf(mx, fmaxf(sv[e], sv[e + 1]));
+                }
+            }
+            const float corr = ex2_approx(m - mx);
+            m = mx;
+            float sum = 0.f;
+            uint32_t ppk[32];
+#pragma unroll
+            for (int e = 0; e < kBK; e += 2) {
+                const float p0 = ex2_approx(sv[e] - mx);
+                const float p1 = ex2_approx(sv[e + 1] - mx);
+                sum += p0 + p1;
+                ppk[e >> 1] = pack_bf16x2(p0, p1);
+            }
+            l = fmaf(l, corr, sum);
+            const uint32_t ptile = sbase + CoreSmem::kP + s * kKBlockBytes;
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+                sts128(chunk_addr(ptile, row, ch),
+                       make_uint4(ppk[ch * 4], ppk[ch * 4 + 1], ppk[ch * 4 + 2], ppk[ch * 4 + 3]));
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_ready(s));
+            // fold in the previous block's P V while this block's MMA runs
+            if (j >= 1) {
+                const int ps = (j - 1) & 1;
+                if (!mbar_wait(o_full(ps), ((j - 1) >> 1) & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t r[32];
+                tmem_ld32(trow + 128 + ps * kD, r);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(o_empty(ps));
+#pragma unroll
+                for (int e = 0; e < kD; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(r[e]));
+            }
+            corr_prev = corr;
+        }
+        if (ok) {
+            const int ps = (nblk - 1) & 1;
+            if (mbar_wait(o_full(ps), ((nblk - 1) >> 1) & 1u, abort_flag)) {
+                tc_fence_after_sync();
+                uint32_t r[32];
+                tmem_ld32(trow + 128 + ps * kD, r);
+                tmem_ld_wait();
+                const float inv = 1.0f / l;
+                if (qpos < N) {
+                    uint4* dst = reinterpret_cast<uint4*>(o_out + ((bl * N + qpos) * (long long)kC) + h * kD);
+#pragma unroll
+                    for (int v4 = 0; v4 < 4; ++v4) {
+                        float f[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e)
+                            f[e] = fmaf(o[v4 * 8 + e], corr_prev, __uint_as_float(r[v4 * 8 + e])) * inv;
+                        dst[v4] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
+                                             pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+                    }
+                }
+            } else if (lane == 0) {
+                report_wait_failure(status, abort_flag, kKidCore, 7);
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 256);
+    }
+}
+
+// =====================================================================================
+// triattn_out
+// =====================================================================================
+struct AOutSmem {
+    static constexpr uint32_t kWg = 0;
+    static constexpr uint32_t kWo = kTileBytes;
+    static constexpr uint32_t kZ = 2 * kTileBytes;            // 2 groups: z tile, then output
+    static constexpr uint32_t kO = kZ + 2 * kTileBytes;       // 2 groups: o tile, gated in place
+    static constexpr uint32_t kParams = kO + 2 * kTileBytes;  // gamma, beta
+    static constexpr uint32_t kBars = kParams + 1024;
+    static constexpr uint32_t kTotal = kBars + 160;
+    static constexpr uint32_t kDyn = kTotal + 1024;
+};
+
+template <bool kTransposed>
+__global__ void __launch_bounds__(320, 1)
+triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmO,
+                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmWg,
+                   const __grid_constant__ CUtensorMap tmWo, const __nv_bfloat16* __restrict__ ln_w,
+                   const __nv_bfloat16* __restrict__ ln_b, int B, int N, int add_residual, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
+    float* prm = reinterpret_cast<float*>(gbase + AOutSmem::kParams);
+    const uint32_t bars = sbase + AOutSmem::kBars;
+    const uint32_t w_full = bars;
+    auto full = [&](int g) { return bars + 8u * (1 + g); };
+    auto empty = [&](int g) { return bars + 8u * (3 + g); };
+    auto a1_ready = [&](int g) { return bars + 8u * (5 + g); };
+    auto g_full = [&](int g) { return bars + 8u * (7 + g); };
+    auto a2_ready = [&](int g) { return bars + 8u * (9 + g); };
+    auto d_full = [&](int g) { return bars + 8u * (11 + g); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + AOutSmem::kBars + 128);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + AOutSmem::kBars + 136);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_per_line = (N + kRows - 1) / kRows;
+    const long long num_tiles = (long long)B * N * tiles_per_line;
+    const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full, 1);
+        for (int g = 0; g < 2; ++g) {
+            mbar_init(full(g), 1);
+            mbar_init(empty(g), 1);
+            mbar_init(a1_ready(g), 4);
+            mbar_init(g_full(g), 1);
+            mbar_init(a2_ready(g), 4);
+            mbar_init(d_full(g), 1);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmZ);
+        prefetch_tmap(&tmO);
+        prefetch_tmap(&tmOut);
+    }
+    if (threadIdx.x < 128) {
+        prm[threadIdx.x] = __bfloat162float(ln_w[threadIdx.x]);
+        prm[128 + threadIdx.x] = __bfloat162float(ln_b[threadIdx.x]);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_full, 2 * kTileBytes);
+            for (int kb = 0; kb < 2; ++kb) {
+                tma_load_2d(sbase + AOutSmem::kWg + kb * kKBlockBytes, &tmWg, w_full, kb * 64, 0);
+                tma_load_2d(sbase + AOutSmem::kWo + kb * kKBlockBytes, &tmWo, w_full, kb * 64, 0);
+            }
+            for (long long lt = 0; lt < my_tiles; ++lt) {
+                const int g = (int)(lt & 1);
+                const uint32_t use = (uint32_t)(lt >> 1);
+                if (!mbar_wait(empty(g), (use & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidOut, 1);
+                    break;
+                }
+                const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+                mbar_arrive_expect_tx(full(g), 2 * kTileBytes);
+                load_z_tile<kTransposed>(sbase + AOutSmem::kZ + g * kTileBytes, &tmZ, full(g), tc, N);
+                const uint32_t odst = sbase + AOutSmem::kO + g * kTileBytes;
+                for (int kb = 0; kb < 2; ++kb)
+                    tma_load_3d(odst + kb * kKBlockBytes, &tmO, full(g), kb * 64, tc.t0, tc.b * N + tc.line);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 128);
+            bool ok = mbar_wait(w_full, 0, abort_flag);
+            if (!ok) report_wait_failure(status, abort_flag, kKidOut, 2);
+            // gate GEMM of tile lt is issued before the output GEMM of tile lt-1, so the two groups
+            // overlap: one gates its o tile while the other's gate GEMM runs
+            for (long long lt = 0; lt <= my_tiles && ok; ++lt) {
+                if (lt < my_tiles) {
+                    const int g = (int)(lt & 1);
+                    if (!mbar_wait(a1_ready(g), (uint32_t)(lt >> 1) & 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidOut, 3);
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    mma_k128(tmem_base + g * 256, sbase + AOutSmem::kZ + g * kTileBytes, sbase + AOutSmem::kWg,
+                             kKBlockBytes, idesc, false);
+                    mma_commit(g_full(g));
+                }
+                if (lt >= 1) {
+                    const long long pt = lt - 1;
+                    const int g = (int)(pt & 1);
+                    if (!mbar_wait(a2_ready(g), (uint32_t)(pt >> 1) & 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidOut, 4);
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    mma_k128(tmem_base + g * 256 + 128, sbase + AOutSmem::kO + g * kTileBytes,
+                             sbase + AOutSmem::kWo, kKBlockBytes, idesc, false);
+                    mma_commit(d_full(g));
+                }
+            }
+        }
+    } else {
+        const int g = (warp - 2) >> 2;
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        const int gtid = (warp - 2 - g * 4) * 32 + lane;
+        const uint32_t ztile = sbase + AOutSmem::kZ + g * kTileBytes;
+        const uint32_t otile = sbase + AOutSmem::kO + g * kTileBytes;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
+        for (long long lt = g; lt < my_tiles; lt += 2) {
+            const uint32_t use = (uint32_t)(lt >> 1);
+            const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+            if (!mbar_wait(full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
+                break;
+            }
+            uint32_t zraw[64];
+            load_row(ztile, row, zraw);
+            {
+                float mean, rstd;
+                row_stats(zraw, mean, rstd);
+                store_normalized_row(ztile, row, zraw, mean, rstd, prm, prm + 128);
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a1_ready(g));
+            // ---- gate: o <- o * sigmoid(LN(z) W_g^T), in place in the o tile
+            if (!mbar_wait(g_full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 6);
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int cb = 0; cb < 8; ++cb) {
+                uint32_t gate[16];
+                tmem_ld16(taddr + cb * 16, gate);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    const uint32_t addr = chunk_addr(otile, row, cb * 2 + ch);
+                    const uint4 ov = lds128(addr);
+                    const uint32_t w[4] = {ov.x, ov.y, ov.z, ov.w};
+                    uint32_t o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int e = ch * 8 + j * 2;
+                        o[j] = pack_bf16x2(bf16lo(w[j]) * sigmoid_fast(__uint_as_float(gate[e])),
+                                           bf16hi(w[j]) * sigmoid_fast(__uint_as_float(gate[e + 1])));
+                    }
+                    sts128(addr, make_uint4(o[0], o[1], o[2], o[3]));
+                }
+            }
+            tc_fence_before_sync();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a2_ready(g));
+            // ---- output projection + residual, written over the z tile and TMA-stored
+            if (!mbar_wait(d_full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 7);
+                break;
+            }
+            tc_fence_after_sync();
+#pragma unroll
+            for (int cb = 0; cb < 8; ++cb) {
+                uint32_t upd[16];
+                tmem_ld16(taddr + 128 + cb * 16, upd);
+                tmem_ld_wait();
+#pragma unroll
+                for (int ch = 0; ch < 2; ++ch) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int e = ch * 8 + j * 2;
+                        const uint32_t zr = zraw[cb * 8 + ch * 4 + j];
+                        float v0 = __uint_as_float(upd[e]), v1 = __uint_as_float(upd[e + 1]);
+                        if (add_residual) {
+                            v0 += bf16lo(zr);
+                            v1 += bf16hi(zr);
+                        }
+                        o[j] = pack_bf16x2(v0, v1);
+                    }
+                    sts128(chunk_addr(ztile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
+                }
+            }
+            tc_fence_before_sync();
+            fence_proxy_async_smem();
+            group_sync(1 + g, 128);
+            if (gtid == 0) {
+                for (int kb = 0; kb < 2; ++kb) {
+                    if (kTransposed) {
+                        asm volatile(
+                            "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
+                                "l"(reinterpret_cast<uint64_t>(&tmOut)),
+                            "r"(ztile + kb * kKBlockBytes), "r"(kb * 64), "r"(tc.line), "r"(tc.t0), "r"(tc.b)
+                            : "memory");
+                    } else {
+                        tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * N + tc.line);
+                    }
+                }
+                tma_store_commit();
+                tma_store_wait_read<0>();
+                mbar_arrive(empty(g));
+            }
+        }
+        if (gtid == 0) tma_store_wait_all<0>();
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+int weight_tmap128(CUtensorMap* m, const void* w) {
+    uint64_t dims[2] = {128, 128};
+    uint64_t str[1] = {256};
+    uint32_t box[2] = {64, 128};
+    return make_tmap_bf16(m, w, 2, dims, str, box, 1);
+}
+
+int z_tmap(CUtensorMap* m, const void* z, int B, int N, bool transposed) {
+    if (!transposed) {
+        uint64_t dims[3] = {128, (uint64_t)N, (uint64_t)B * N};
+        uint64_t str[2] = {256, (uint64_t)N * 256};
+        uint32_t box[3] = {64, 128, 1};
+        return make_tmap_bf16(m, z, 3, dims, str, box, 1);
+    }
+    uint64_t dims[4] = {128, (uint64_t)N, (uint64_t)N, (uint64_t)B};
+    uint64_t str[3] = {256, (uint64_t)N * 256, (uint64_t)N * N * 256};
+    uint32_t box[4] = {64, 1, 128, 1};
+    return make_tmap_bf16(m, z, 4, dims, str, box, 1);
+}
+
+template <bool kT>
+int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
+               float inf, int flags, const of3_triattn_params* p, __nv_bfloat16* q, __nv_bfloat16* k,
+               __nv_bfloat16* vt, __nv_bfloat16* tb, __nv_bfloat16* o, int ldn, cudaStream_t st) {
+    int rc;
+    CUtensorMap tmZ, tmOut, tmO, tmW[5], tmQ, tmK, tmV;
+    if ((rc = z_tmap(&tmZ, z, B, N, kT))) return rc;
+    if ((rc = z_tmap(&tmOut, out, B, N, kT))) return rc;
+    if ((rc = z_tmap(&tmO, o, B, N, false))) return rc;  // o is [line][pos][128] in view order
+    const void* w5[5] = {p->w_q, p->w_k, p->w_v, p->w_g, p->w_o};
+    for (int i = 0; i < 5; ++i)
+        if ((rc = weight_tmap128(&tmW[i], w5[i]))) return rc;
+    const long long lines = (long long)B * N * kH;
+    {
+        uint64_t dims[3] = {kD, (uint64_t)N, (uint64_t)lines};
+        uint64_t str[2] = {kD * 2, (uint64_t)N * kD * 2};
+        uint32_t boxq[3] = {kD, kBQ, 1};
+        uint32_t boxk[3] = {kD, kBK, 1};
+        if ((rc = make_tmap_bf16(&tmQ, q, 3, dims, str, boxq, 2))) return rc;
+        if ((rc = make_tmap_bf16(&tmK, k, 3, dims, str, boxk, 2))) return rc;
+        uint64_t dimv[3] = {(uint64_t)N, kD, (uint64_t)lines};
+        uint64_t strv[2] = {(uint64_t)ldn * 2, (uint64_t)kD * ldn * 2};
+        uint32_t boxv[3] = {kBK, kD, 1};
+        if ((rc = make_tmap_bf16(&tmV, vt, 3, dimv, strv, boxv, 1))) return rc;
+    }
+    static bool attr_done = false;
+    if (!attr_done) {
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_proj_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ProjSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_core_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, CoreSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_out_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, AOutSmem::kDyn));
+        attr_done = true;
+    }
+    int* status = device_status_ptr();
+    const long long tiles = (long long)B * N * ceil_div(N, kRows);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    {
+    LaunchScope scope(kKidProj, st);
+    triattn_proj_kernel<kT><<<grid, 320, ProjSmem::kDyn, st>>>(
+        tmZ, tmW[0], tmW[1], tmW[2], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
+        (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, N, ldn, status);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    const long long ctas = lines * ceil_div(N, kBQ);
+    OF3_REQUIRE(ctas < (1LL << 31), OF3_ERR_SHAPE, "triattn: too many attention tiles");
+    {
+    LaunchScope scope(kKidCore, st);
+    triattn_core_kernel<kT><<<(unsigned)ctas, 192, CoreSmem::kDyn, st>>>(tmQ, tmK, tmV, tb, mask, o, B, N,
+                                                                        ldn, inf, status);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    LaunchScope scope(kKidOut, st);
+    triattn_out_kernel<kT><<<grid, 320, AOutSmem::kDyn, st>>>(
+        tmZ, tmO, tmOut, tmW[3], tmW[4], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, B, N,
+        (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, status);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+}  // namespace
+
+bool triattn_supported(int c_z, int H, int d, int N) {
+    return c_z == 128 && H == kH && d == kD && N <= kMaxKeys;
+}
+
+int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
+            float inf, int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st) {
+    const int ldn = (int)align_up(N, 64);
+    const size_t plane = (size_t)B * N * N * kC * sizeof(__nv_bfloat16);
+    __nv_bfloat16* q = (__nv_bfloat16*)ws.take(plane);
+    __nv_bfloat16* k = (__nv_bfloat16*)ws.take(plane);
+    __nv_bfloat16* vt = (__nv_bfloat16*)ws.take((size_t)B * N * kC * ldn * sizeof(__nv_bfloat16));
+    __nv_bfloat16* o = (__nv_bfloat16*)ws.take(plane);
+    __nv_bfloat16* tb = (__nv_bfloat16*)ws.take((size_t)B * kH * N * ldn * sizeof(__nv_bfloat16) + 256);
+    if (!ws.base) return OF3_OK;
+    OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "triattn: workspace too small (%zu needed)", ws.off);
+    OF3_REQUIRE(N <= kMaxKeys, OF3_ERR_SHAPE, "triattn: N %d above the %d keys one CTA keeps a mask row for",
+                N, kMaxKeys);
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
+                "triattn: z/out must be 16-byte aligned");
+    if (flags & OF3_FLAG_TRANSPOSED)
+        return launch_all<true>(z, mask, out, B, N, inf, flags, p, q, k, vt, tb, o, ldn, st);
+    return launch_all<false>(z, mask, out, B, N, inf, flags, p, q, k, vt, tb, o, ldn, st);
+}
+
+}  // namespace fast
+}  // namespace of3

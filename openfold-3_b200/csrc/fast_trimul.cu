@@ -505,6 +505,8 @@ int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out
     int* status = device_status_ptr();
     const long long tiles = (long long)B * N * ceil_div(N, kRows);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    {
+    LaunchScope scope(kKidIn, st);
     if (outgoing)
         trimul_in_kernel<true><<<grid, 320, InSmem::kDyn, st>>>(
             tmZin, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
@@ -513,10 +515,12 @@ int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out
         trimul_in_kernel<false><<<grid, 320, InSmem::kDyn, st>>>(
             tmZin, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
             (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, N, ld, status);
+    }
     OF3_CUDA_CHECK(cudaGetLastError());
     rc = contract_nt_bf16(a_t, b_t, x_t, B * kC, N, N, N, ld, ld, ld, (long long)N * ld,
                           (long long)N * ld, (long long)N * ld, st);
     if (rc) return rc;
+    LaunchScope scope(kKidOut, st);
     trimul_out_kernel<<<grid, 320, OutSmem::kDyn, st>>>(
         tmZrow, tmX, tmOut, tmW[4], tmW[5], (const __nv_bfloat16*)p->ln_in_w,
         (const __nv_bfloat16*)p->ln_in_b, (const __nv_bfloat16*)p->ln_out_w,

@@ -1,5 +1,6 @@
 // Shape-generic SIMT kernels: see generic_ops.cuh. True fp32 arithmetic throughout.
 #include "generic_ops.cuh"
+#include "runtime.cuh"
 
 namespace of3 {
 namespace generic {
@@ -277,6 +278,7 @@ int layernorm(const TX* x, const TP* gamma, const TP* beta, float* y, long long 
               float eps, long long inner, long long outer_stride, long long inner_stride,
               cudaStream_t stream) {
     if (rows <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     layernorm_kernel<TX, TP><<<grid_for(rows, kThreads / 32), kThreads, 0, stream>>>(
         x, gamma, beta, y, rows, C, eps, inner, outer_stride, inner_stride);
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -299,6 +301,7 @@ int gemm_nt(const float* A, const TW* W, const TW* bias, float* out, const GemmD
     OF3_REQUIRE(d.batch <= 65535, OF3_ERR_SHAPE, "gemm_nt: batch %d > 65535", d.batch);
     dim3 grid(ceil_div(d.N, kTN), ceil_div(d.M, kTM), d.batch);
     OF3_REQUIRE(grid.y <= 65535, OF3_ERR_SHAPE, "gemm_nt: M %d too large for one launch", d.M);
+    LaunchScope scope(20, stream);
     gemm_nt_kernel<TW><<<grid, 256, 0, stream>>>(A, W, bias, out, d);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
@@ -317,6 +320,7 @@ int attention(const float* q, const float* k, const float* v, const float* mask_
     OF3_REQUIRE(ceil_div(N, kAttWarps) <= 65535, OF3_ERR_SHAPE, "attention: N %d too large", N);
     if (BB <= 0) return OF3_OK;
     dim3 grid((unsigned)BB, H, ceil_div(N, kAttWarps));
+    LaunchScope scope(20, stream);
     attention_kernel<<<grid, kAttWarps * 32, 0, stream>>>(q, k, v, mask_bias, pair_bias, out, N, H, d,
                                                           scale, rows_per_bias);
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -327,6 +331,7 @@ template <typename T>
 int gate_mul_mask(const float* g, const float* p, int ld, const T* mask, float* dst, long long rows,
                   int C, cudaStream_t stream) {
     if (rows <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     gate_mul_mask_kernel<T><<<grid_for(rows * C, kThreads), kThreads, 0, stream>>>(g, p, ld, mask, dst,
                                                                                   rows, C);
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -340,6 +345,7 @@ template int gate_mul_mask<__nv_bfloat16>(const float*, const float*, int, const
 int sigmoid_mul(const float* x, int ldx, const float* g, int ldg, float* dst, long long rows, int C,
                 cudaStream_t stream) {
     if (rows <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     sigmoid_mul_kernel<<<grid_for(rows * C, kThreads), kThreads, 0, stream>>>(x, ldx, g, ldg, dst,
                                                                              rows, C);
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -348,6 +354,7 @@ int sigmoid_mul(const float* x, int ldx, const float* g, int ldg, float* dst, lo
 int silu_mul(const float* a, const float* b, int ld, float* dst, long long rows, int C,
              cudaStream_t stream) {
     if (rows <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     silu_mul_kernel<<<grid_for(rows * C, kThreads), kThreads, 0, stream>>>(a, b, ld, dst, rows, C);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
@@ -355,6 +362,7 @@ int silu_mul(const float* a, const float* b, int ld, float* dst, long long rows,
 int ada_combine(const float* g, const float* a, const float* s, float* dst, long long n,
                 cudaStream_t stream) {
     if (n <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     ada_combine_kernel<<<grid_for(n, kThreads), kThreads, 0, stream>>>(g, a, s, dst, n);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
@@ -363,6 +371,7 @@ template <typename T>
 int mask_to_bias(const T* mask, float* dst, long long rows, int N, float inf, long long row_stride,
                  long long k_stride, cudaStream_t stream) {
     if (rows <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     mask_to_bias_kernel<T><<<grid_for(rows * N, kThreads), kThreads, 0, stream>>>(
         mask, dst, rows, N, inf, row_stride, k_stride);
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -378,6 +387,7 @@ int finalize(const float* upd, const float* gate, const T* residual, const T* ma
              long long rows, int C, long long inner, long long outer_stride,
              long long inner_stride, cudaStream_t stream) {
     if (rows <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     finalize_kernel<T><<<grid_for(rows * C, kThreads), kThreads, 0, stream>>>(
         upd, gate, residual, mask, out, rows, C, inner, outer_stride, inner_stride);
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -392,6 +402,7 @@ template int finalize<__nv_bfloat16>(const float*, const float*, const __nv_bflo
 int permute_bias(const float* src, float* dst, long long B, int N, int H, cudaStream_t stream) {
     const long long total = B * H * (long long)N * N;
     if (total <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     permute_bias_kernel<<<grid_for(total, kThreads), kThreads, 0, stream>>>(src, dst, B, N, H);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
@@ -400,6 +411,7 @@ int permute_bias(const float* src, float* dst, long long B, int N, int H, cudaSt
 template <typename T>
 int to_f32(const T* src, float* dst, long long n, cudaStream_t stream) {
     if (n <= 0) return OF3_OK;
+    LaunchScope scope(20, stream);
     to_f32_kernel<T><<<grid_for(n, kThreads), kThreads, 0, stream>>>(src, dst, n);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;

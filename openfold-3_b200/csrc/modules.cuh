@@ -32,7 +32,7 @@ bool trimul_supported(int c_z, int c_h);
 int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
            int flags, const of3_trimul_params* p, Arena& ws, cudaStream_t st);
 // bf16, c_z = 128, 4 heads x 32
-bool triattn_supported(int c_z, int H, int d);
+bool triattn_supported(int c_z, int H, int d, int N);
 int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
             float inf, int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st);
 // bf16, c = 128, n = 4

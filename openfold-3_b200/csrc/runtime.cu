@@ -7,6 +7,7 @@
 #include <string.h>
 
 #include <mutex>
+#include <vector>
 
 namespace of3 {
 
@@ -72,7 +73,7 @@ static EncodeTiledFn encode_fn() {
 }
 
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
-                   const uint64_t* strides_bytes, const uint32_t* box, bool swizzle128) {
+                   const uint64_t* strides_bytes, const uint32_t* box, int swizzle) {
     EncodeTiledFn fn = encode_fn();
     OF3_REQUIRE(fn != nullptr, OF3_ERR_DRIVER, "cuTensorMapEncodeTiled entry point unavailable");
     OF3_REQUIRE(((uintptr_t)base & 15) == 0, OF3_ERR_ALIGN, "tensor map base not 16-byte aligned");
@@ -93,14 +94,89 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
     }
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base),
                     gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                 : (swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_NONE),
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     OF3_REQUIRE(r == CUDA_SUCCESS, OF3_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d",
                 (int)r);
     return OF3_OK;
 }
 
+// ------------------------------------------------------------------ launch accounting
+struct ProfRec {
+    cudaEvent_t a, b;
+    int kid;
+};
+static std::vector<ProfRec> g_recs;      // event pairs of the current profiling window
+static std::vector<cudaEvent_t> g_pool;  // recycled events
+static long long g_launches[kMaxKernelIds] = {0};
+static bool g_prof_on = false;
+
+static cudaEvent_t take_event() {
+    if (!g_pool.empty()) {
+        cudaEvent_t e = g_pool.back();
+        g_pool.pop_back();
+        return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+}
+
+LaunchScope::LaunchScope(int kernel_id, cudaStream_t st) : kid(kernel_id), stream(st), rec(nullptr) {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (kid >= 0 && kid < kMaxKernelIds) g_launches[kid]++;
+    if (g_prof_on) {
+        ProfRec r{take_event(), take_event(), kid};
+        if (r.a && r.b) {
+            cudaEventRecord(r.a, stream);
+            g_recs.push_back(r);
+            rec = (void*)(uintptr_t)g_recs.size();  // index + 1
+        }
+    }
+}
+LaunchScope::~LaunchScope() {
+    if (rec) {
+        std::lock_guard<std::mutex> lk(g_mu);
+        const size_t idx = (size_t)(uintptr_t)rec - 1;
+        if (idx < g_recs.size()) cudaEventRecord(g_recs[idx].b, stream);
+    }
+}
+
 }  // namespace of3
+
+extern "C" int of3_profile_enable(int on) {
+    std::lock_guard<std::mutex> lk(of3::g_mu);
+    of3::g_prof_on = on != 0;
+    return OF3_OK;
+}
+
+extern "C" int of3_profile_reset(void) {
+    std::lock_guard<std::mutex> lk(of3::g_mu);
+    for (auto& r : of3::g_recs) {
+        of3::g_pool.push_back(r.a);
+        of3::g_pool.push_back(r.b);
+    }
+    of3::g_recs.clear();
+    for (int i = 0; i < of3::kMaxKernelIds; ++i) of3::g_launches[i] = 0;
+    return OF3_OK;
+}
+
+extern "C" int of3_profile_read(int kernel_id, long long* launches, float* total_ms) {
+    OF3_REQUIRE(kernel_id >= 0 && kernel_id < of3::kMaxKernelIds && launches && total_ms, OF3_ERR_ARG,
+                "of3_profile_read: bad argument");
+    OF3_CUDA_CHECK(cudaDeviceSynchronize());
+    std::lock_guard<std::mutex> lk(of3::g_mu);
+    *launches = of3::g_launches[kernel_id];
+    float sum = 0.f;
+    for (auto& r : of3::g_recs) {
+        if (r.kid != kernel_id) continue;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) sum += ms;
+    }
+    *total_ms = sum;
+    return OF3_OK;
+}
 
 extern "C" const char* of3_last_error_string(void) { return of3::g_err; }
 

@@ -166,6 +166,17 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                    // SWIZZLE_128B
     return d;
 }
+// Same for 64-byte rows (32 bf16, e.g. a head dimension of 32) with the 64-byte swizzle that
+// TMA's CU_TENSOR_MAP_SWIZZLE_64B produces: 8-row groups 512 B apart, base 512-byte aligned.
+__device__ __forceinline__ uint64_t smem_desc_k_sw64(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(512 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)4 << 61;  // SWIZZLE_64B
+    return d;
+}
 // Instruction descriptor: bf16 x bf16 -> fp32, both operands K-major, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(int M, int N) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) |
