@@ -56,6 +56,16 @@ const char* of3_last_error_string(void);
 int of3_device_status(int* out4);
 int of3_device_status_clear(void);
 
+/* Launch accounting. Every kernel launch of the library is counted per kernel id; with timing
+ * enabled a CUDA-event pair is recorded around each launch on the launching stream (the events
+ * come from a pool that grows on demand). of3_profile_read synchronises the device and returns the
+ * launches since the last reset and the summed device time of the timed ones.
+ * Kernel ids: 1 triangle contraction, 2 trimul projection/gate, 3 trimul output, 4 SwiGLU
+ * transition, 5 attention projection, 6 attention core, 7 attention output, 20 generic kernels. */
+int of3_profile_enable(int on);
+int of3_profile_reset(void);
+int of3_profile_read(int kernel_id, long long* launches, float* total_ms);
+
 /* 1 when the tcgen05 kernel family covers this shape and dtype, else 0 (generic kernels run). */
 int of3_fast_path_available(int module_id, int dtype, int c, int c_hidden, int heads, int head_dim);
 #define OF3_MODULE_TRIMUL 1

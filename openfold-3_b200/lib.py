@@ -43,6 +43,9 @@ SIGNATURES = {
     "of3_last_error_string": (c_char_p, []),
     "of3_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "of3_device_status_clear": (c_int, []),
+    "of3_profile_enable": (c_int, [c_int]),
+    "of3_profile_reset": (c_int, []),
+    "of3_profile_read": (c_int, [c_int, ctypes.POINTER(c_longlong), ctypes.POINTER(c_float)]),
     "of3_fast_path_available": (c_int, [c_int] * 6),
     "of3_trimul_workspace_bytes": (c_size_t, [c_int] * 6),
     "of3_trimul_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -103,6 +106,30 @@ def check_device_status():
         raise RuntimeError(
             f"device-side wait ran out: code {arr[0]}, kernel {arr[1]}, block {arr[2]}, site {arr[3]}"
         )
+
+
+KERNEL_NAMES = {1: "trimul_contract", 2: "trimul_in", 3: "trimul_out", 4: "transition", 5: "triattn_proj",
+                6: "triattn_core", 7: "triattn_out", 20: "generic"}
+
+
+def profile_begin(timing: bool = True):
+    """Resets the launch counters and (optionally) starts recording an event pair per launch."""
+    lib = load()
+    _check(lib.of3_profile_reset(), "of3_profile_reset")
+    _check(lib.of3_profile_enable(1 if timing else 0), "of3_profile_enable")
+
+
+def profile_end() -> dict:
+    """Stops timing; returns {kernel name: (launches, total device ms)} since profile_begin."""
+    lib = load()
+    _check(lib.of3_profile_enable(0), "of3_profile_enable")
+    out = {}
+    for kid, name in KERNEL_NAMES.items():
+        n, ms = c_longlong(0), c_float(0)
+        _check(lib.of3_profile_read(kid, ctypes.byref(n), ctypes.byref(ms)), "of3_profile_read")
+        if n.value:
+            out[name] = (int(n.value), float(ms.value))
+    return out
 
 
 def fast_path_available(module_id, dtype, c, c_hidden=0, heads=0, head_dim=0) -> bool:
