@@ -95,6 +95,23 @@ int of3_trimul_forward(const void* z, const void* mask, void* out, int B, int N,
                        int dtype, int flags, const of3_trimul_params* p, void* workspace,
                        size_t workspace_bytes, void* stream);
 
+/* Triangle multiplicative update for callers that cannot allocate device memory (a process with a
+ * frozen memory budget, a plugin running inside another component's stream-ordered region, an
+ * embedder that only forwards the tensors it was given). No counterpart in the reference: its
+ * modules always allocate their temporaries through PyTorch.
+ * Same arguments and semantics as of3_trimul_forward minus the workspace: the intermediates live
+ * in a 16 MiB array built into the library (held by every GPU that loads it, until exit). It runs
+ * the shape-generic kernels and calls no cudaMalloc / cudaFree or allocating library routine.
+ *  - Limit: B*N*N*max(c_z, c_h)*24 bytes must fit in of3_trimul_static_scratch_bytes()
+ *    (N <= 73 at B = 1, c = 128); beyond it the call returns OF3_ERR_WORKSPACE.
+ *  - The first call on a device resolves the array's device address; make it before any stream
+ *    capture.
+ *  - Every call uses the same array, which keeps the previous call's contents (none of it needs
+ *    to start at zero). Calls that overlap on the GPU race on it: keep them ordered. */
+size_t of3_trimul_static_scratch_bytes(void);
+int of3_trimul_forward_static(const void* z, const void* mask, void* out, int B, int N, int c_z, int c_h,
+                              int dtype, int flags, const of3_trimul_params* p, void* stream);
+
 /* ---- Triangle attention ------------------------------------------------------------------
  * Replaces TriangleAttention.forward (openfold3/core/model/layers/triangular_attention.py:
  * 102-167) including the gated multi-head attention it calls

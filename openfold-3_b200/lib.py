@@ -50,6 +50,9 @@ SIGNATURES = {
     "of3_trimul_workspace_bytes": (c_size_t, [c_int] * 6),
     "of3_trimul_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                    ctypes.POINTER(TrimulParams), c_void_p, c_size_t, c_void_p]),
+    "of3_trimul_static_scratch_bytes": (c_size_t, []),
+    "of3_trimul_forward_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          ctypes.POINTER(TrimulParams), c_void_p]),
     "of3_triattn_workspace_bytes": (c_size_t, [c_int] * 7),
     "of3_triattn_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float,
                                     c_int, c_int, ctypes.POINTER(TriattnParams), c_void_p, c_size_t,
