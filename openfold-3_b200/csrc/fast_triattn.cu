@@ -301,107 +301,136 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 // =====================================================================================
 // triattn_core
 // =====================================================================================
+// One CTA = one head, 128 queries and TWO lines of the pair tensor. The pair-bias tile
+// [128 q x 64 k] does not depend on the line, so it is fetched once per key block by TMA and read
+// by both lines' softmax warpgroups from shared memory (conflict-free swizzled rows) instead of
+// every thread gathering its own row from L2.
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 64;       // keys per block
 constexpr int kMaxKeys = 4096;
+constexpr int kLines = 2;     // lines per CTA
 
 struct CoreSmem {
-    static constexpr uint32_t kQ = 0;                        // 128 x 64 B (64-byte swizzle)  8 KB
-    static constexpr uint32_t kK = 8192;                     // 2 stages x (64 x 64 B)        8 KB
-    static constexpr uint32_t kV = kK + 2 * 4096;            // 2 stages x (32 x 128 B)       8 KB
-    static constexpr uint32_t kP = kV + 2 * 4096;            // 2 x (128 x 128 B)            32 KB
-    static constexpr uint32_t kMb = kP + 2 * kKBlockBytes;   // mask bias, fp32 [kMaxKeys + 64]
-    static constexpr uint32_t kBars = kMb + (kMaxKeys + 64) * 4;
-    static constexpr uint32_t kTotal = kBars + 160;
-    static constexpr uint32_t kDyn = kTotal + 1024;
+    static constexpr uint32_t kQ = 0;                               // lines x 8 KB (64-byte swizzle)
+    static constexpr uint32_t kK = kQ + kLines * 8192;              // lines x 2 stages x 4 KB
+    static constexpr uint32_t kV = kK + kLines * 2 * 4096;          // lines x 2 stages x 4 KB
+    static constexpr uint32_t kTb = kV + kLines * 2 * 4096;         // 2 stages x 16 KB
+    static constexpr uint32_t kP = kTb + 2 * kKBlockBytes;          // lines x 2 x 16 KB
+    static constexpr uint32_t kBars = kP + kLines * 2 * kKBlockBytes;
+    static constexpr uint32_t kFlags = kBars + 256;                 // lines x 64 block flags (bytes)
+    static constexpr uint32_t kMb = kFlags + 128;                   // lines x nkeys_pad floats
+    static uint32_t dyn_bytes(int nblk) { return kMb + kLines * nblk * kBK * 4 + 1024; }
 };
 
 template <bool kTransposed>
-__global__ void __launch_bounds__(192, 2)
+__global__ void __launch_bounds__(320, 1)
 triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __nv_bfloat16* __restrict__ tb,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTb,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
-                    int N, int ldn, float inf, int* status) {
+                    int N, float inf, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
     float* mbs = reinterpret_cast<float*>(gbase + CoreSmem::kMb);
+    volatile uint8_t* mbflag = gbase + CoreSmem::kFlags;
     const uint32_t bars = sbase + CoreSmem::kBars;
     const uint32_t q_full = bars;
     auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-    auto s_full = [&](int s) { return bars + 8u * (5 + s); };
-    auto s_empty = [&](int s) { return bars + 8u * (7 + s); };
-    auto p_ready = [&](int s) { return bars + 8u * (9 + s); };
-    auto o_full = [&](int s) { return bars + 8u * (11 + s); };
-    auto o_empty = [&](int s) { return bars + 8u * (13 + s); };
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 128);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 136);
+    auto s_full = [&](int L, int s) { return bars + 8u * (5 + L * 2 + s); };
+    auto s_empty = [&](int L, int s) { return bars + 8u * (9 + L * 2 + s); };
+    auto p_ready = [&](int L, int s) { return bars + 8u * (13 + L * 2 + s); };
+    auto o_full = [&](int L, int s) { return bars + 8u * (17 + L * 2 + s); };
+    auto o_empty = [&](int L, int s) { return bars + 8u * (21 + L * 2 + s); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 208);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 216);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (N + kBQ - 1) / kBQ;
+    const int pairs_per_b = (N + kLines - 1) / kLines;
     const int qt = blockIdx.x % n_qt;
     const int h = (blockIdx.x / n_qt) % kH;
-    const long long bl = blockIdx.x / (n_qt * kH);  // b * N + line
-    const int line = (int)(bl % N);
-    const int b = (int)(bl / N);
+    const int lp = blockIdx.x / (n_qt * kH);
+    const int b = lp / pairs_per_b;
+    const int line0 = (lp % pairs_per_b) * kLines;
     const int q0 = qt * kBQ;
     const int nblk = (N + kBK - 1) / kBK;
-    const int lh = (int)(bl * kH + h);  // (line, head) index of q/k/v
+    const int nkp = nblk * kBK;
+    // an odd N leaves the last pair with one line: the second group recomputes the first, unsaved
+    auto line_of = [&](int L) { return (line0 + L < N) ? line0 + L : line0; };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) {
             mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), 1);
-            mbar_init(s_full(s), 1);
-            mbar_init(s_empty(s), 4);
-            mbar_init(p_ready(s), 4);
-            mbar_init(o_full(s), 1);
-            mbar_init(o_empty(s), 4);
+            mbar_init(kv_empty(s), 1 + 4 * kLines);  // MMA commit + every softmax warp (bias tile read)
+            for (int L = 0; L < kLines; ++L) {
+                mbar_init(s_full(L, s), 1);
+                mbar_init(s_empty(L, s), 4);
+                mbar_init(p_ready(L, s), 4);
+                mbar_init(o_full(L, s), 1);
+                mbar_init(o_empty(L, s), 4);
+            }
         }
         *abort_flag = 0;
         mbar_fence_init();
         prefetch_tmap(&tmQ);
         prefetch_tmap(&tmK);
         prefetch_tmap(&tmV);
+        prefetch_tmap(&tmTb);
     }
-    // additive key mask of this line, pre-scaled for exp2: inf * (mask - 1) * log2(e); -inf beyond N
-    for (int k = threadIdx.x; k < nblk * kBK; k += blockDim.x) {
+    // additive key mask of each line, pre-scaled for exp2: inf * (mask - 1) * log2(e); -inf beyond N
+    for (int idx = threadIdx.x; idx < kLines * nkp; idx += blockDim.x) {
+        const int L = idx / nkp, k = idx % nkp;
+        const int line = line_of(L);
         float v = -INFINITY;
         if (k < N) {
             v = 0.f;
             if (mask != nullptr) {
-                const long long idx = kTransposed ? ((long long)b * N + k) * N + line
-                                                  : ((long long)b * N + line) * N + k;
-                v = inf * (__bfloat162float(mask[idx]) - 1.0f) * kLog2e;
+                const long long mi = kTransposed ? ((long long)b * N + k) * N + line
+                                                 : ((long long)b * N + line) * N + k;
+                v = inf * (__bfloat162float(mask[mi]) - 1.0f) * kLog2e;
             }
         }
-        mbs[k] = v;
+        mbs[idx] = v;
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32((const void*)tmem_ptr), 256);
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
         tmem_relinquish();
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
+    // per (line, block): does any key carry a non-zero mask bias?
+    for (int idx = threadIdx.x; idx < kLines * nblk; idx += blockDim.x) {
+        const float* m = mbs + (idx / nblk) * nkp + (idx % nblk) * kBK;
+        bool any = false;
+        for (int e = 0; e < kBK; ++e) any |= (m[e] != 0.f);
+        mbflag[(idx / nblk) * 64 + (idx % nblk)] = any ? 1 : 0;
+    }
+    __syncthreads();
     const uint32_t tmem_base = *tmem_ptr;
-    // TMEM columns: S0 [0,64) S1 [64,128) O0 [128,160) O1 [160,192)
+    // TMEM columns of line L: L*256 + { S0 [0,64)  S1 [64,128)  O0 [128,160)  O1 [160,192) }
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(q_full, kBQ * 64);
-            tma_load_3d(sbase + CoreSmem::kQ, &tmQ, q_full, 0, q0, lh);
+            mbar_arrive_expect_tx(q_full, kLines * kBQ * 64);
+            for (int L = 0; L < kLines; ++L)
+                tma_load_3d(sbase + CoreSmem::kQ + L * 8192, &tmQ, q_full, 0, q0,
+                            (b * N + line_of(L)) * kH + h);
             for (int j = 0; j < nblk; ++j) {
                 const int s = j & 1;
                 if (!mbar_wait(kv_empty(s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidCore, 1);
                     break;
                 }
-                mbar_arrive_expect_tx(kv_full(s), 8192);
-                tma_load_3d(sbase + CoreSmem::kK + s * 4096, &tmK, kv_full(s), 0, j * kBK, lh);
-                tma_load_3d(sbase + CoreSmem::kV + s * 4096, &tmV, kv_full(s), j * kBK, 0, lh);
+                mbar_arrive_expect_tx(kv_full(s), kLines * 8192 + kKBlockBytes);
+                for (int L = 0; L < kLines; ++L) {
+                    const int lh = (b * N + line_of(L)) * kH + h;
+                    tma_load_3d(sbase + CoreSmem::kK + (L * 2 + s) * 4096, &tmK, kv_full(s), 0, j * kBK, lh);
+                    tma_load_3d(sbase + CoreSmem::kV + (L * 2 + s) * 4096, &tmV, kv_full(s), j * kBK, 0, lh);
+                }
+                tma_load_3d(sbase + CoreSmem::kTb + s * kKBlockBytes, &tmTb, kv_full(s), j * kBK, q0, b * kH + h);
             }
         }
     } else if (warp == 1) {
@@ -410,49 +439,61 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             constexpr uint32_t idesc_o = idesc_bf16_f32(128, kD);
             bool ok = mbar_wait(q_full, 0, abort_flag);
             if (!ok) report_wait_failure(status, abort_flag, kKidCore, 2);
-            const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ);
             for (int j = 0; j <= nblk && ok; ++j) {
-                if (j < nblk) {  // S_j = Q K_j^T
+                if (j < nblk) {  // S_j = Q K_j^T for both lines
                     const int s = j & 1;
-                    if (!mbar_wait(kv_full(s), (j >> 1) & 1u, abort_flag) ||
-                        !mbar_wait(s_empty(s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                    if (!mbar_wait(kv_full(s), (j >> 1) & 1u, abort_flag)) {
                         report_wait_failure(status, abort_flag, kKidCore, 3);
                         break;
                     }
-                    tc_fence_after_sync();
-                    const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + s * 4096);
-                    mma_bf16(tmem_base + s * kBK, qdesc, kdesc, idesc_s, 0u);
-                    mma_bf16(tmem_base + s * kBK, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
-                    mma_commit(s_full(s));
+                    for (int L = 0; L < kLines && ok; ++L) {
+                        if (!mbar_wait(s_empty(L, s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                            report_wait_failure(status, abort_flag, kKidCore, 4);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ + L * 8192);
+                        const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (L * 2 + s) * 4096);
+                        const uint32_t d = tmem_base + L * 256 + s * kBK;
+                        mma_bf16(d, qdesc, kdesc, idesc_s, 0u);
+                        mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
+                        mma_commit(s_full(L, s));
+                    }
                 }
-                if (j >= 1) {  // O_{j-1} = P_{j-1} V_{j-1}
+                if (j >= 1 && ok) {  // O_{j-1} = P_{j-1} V_{j-1} for both lines
                     const int jj = j - 1;
                     const int s = jj & 1;
-                    if (!mbar_wait(p_ready(s), (jj >> 1) & 1u, abort_flag) ||
-                        !mbar_wait(o_empty(s), ((jj >> 1) & 1u) ^ 1u, abort_flag)) {
-                        report_wait_failure(status, abort_flag, kKidCore, 4);
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint64_t pdesc = smem_desc_k_sw128(sbase + CoreSmem::kP + s * kKBlockBytes);
-                    const uint64_t vdesc = smem_desc_k_sw128(sbase + CoreSmem::kV + s * 4096);
+                    for (int L = 0; L < kLines && ok; ++L) {
+                        if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag) ||
+                            !mbar_wait(o_empty(L, s), ((jj >> 1) & 1u) ^ 1u, abort_flag)) {
+                            report_wait_failure(status, abort_flag, kKidCore, 5);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint64_t pdesc = smem_desc_k_sw128(sbase + CoreSmem::kP + (L * 2 + s) * kKBlockBytes);
+                        const uint64_t vdesc = smem_desc_k_sw128(sbase + CoreSmem::kV + (L * 2 + s) * 4096);
 #pragma unroll
-                    for (int k4 = 0; k4 < 4; ++k4)
-                        mma_bf16(tmem_base + 128 + s * kD, pdesc + 2u * k4, vdesc + 2u * k4, idesc_o,
-                                 k4 != 0 ? 1u : 0u);
-                    mma_commit(o_full(s));
-                    mma_commit(kv_empty(s));
+                        for (int k4 = 0; k4 < 4; ++k4)
+                            mma_bf16(tmem_base + L * 256 + 128 + s * kD, pdesc + 2u * k4, vdesc + 2u * k4,
+                                     idesc_o, k4 != 0 ? 1u : 0u);
+                        mma_commit(o_full(L, s));
+                    }
+                    if (ok) mma_commit(kv_empty(s));
                 }
             }
         }
     } else {
-        // ---------------------------------------------------------------- softmax warps (2..5)
+        // ---------------------------------------------------------------- softmax warpgroups
+        const int L = (warp - 2) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int qpos = q0 + row;
-        const int qclamp = qpos < N ? qpos : N - 1;
-        const __nv_bfloat16* tbrow = tb + (((long long)b * kH + h) * N + qclamp) * ldn;
-        const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16);
+        const bool line_valid = line0 + L < N;
+        const long long bl = (long long)b * N + line_of(L);
+        const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 256;
+        const float* mbl = mbs + L * nkp;
         float m = -INFINITY, l = 0.f, corr_prev = 1.f;
         float o[kD];
 #pragma unroll
@@ -460,16 +501,23 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
-            // pair bias of this row for the block's 64 keys (8 x 16 B), issued before the wait
-            uint4 tbv[8];
             const int k0 = j * kBK;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                // ldn is padded to a multiple of 64, so the loads stay inside the row's allocation
-                tbv[i] = __ldg(reinterpret_cast<const uint4*>(tbrow + k0) + i);
+            if (!mbar_wait(kv_full(s), (j >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
+                ok = false;
+                break;
             }
-            if (!mbar_wait(s_full(s), (j >> 1) & 1u, abort_flag)) {
-                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 5);
+            // this row's 64 pair-bias values from the shared tile
+            uint4 tbv[8];
+            {
+                const uint32_t tbt = sbase + CoreSmem::kTb + s * kKBlockBytes;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) tbv[i] = lds128(chunk_addr(tbt, row, i));
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(kv_empty(s));
+            if (!mbar_wait(s_full(L, s), (j >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 7);
                 ok = false;
                 break;
             }
@@ -488,20 +536,27 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             }
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(s));
+            if (lane == 0) mbar_arrive(s_empty(L, s));
+            // (q.k + mask bias) + pair bias: the reference's order, in fp32
+            if (mbflag[L * 64 + j]) {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float4 mb = *reinterpret_cast<const float4*>(mbl + k0 + i * 4);
+                    sv[i * 4] += mb.x;
+                    sv[i * 4 + 1] += mb.y;
+                    sv[i * 4 + 2] += mb.z;
+                    sv[i * 4 + 3] += mb.w;
+                }
+            }
             float mx = m;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const uint32_t w[4] = {tbv[i].x, tbv[i].y, tbv[i].z, tbv[i].w};
-                const float4 mb0 = *reinterpret_cast<const float4*>(mbs + k0 + i * 8);
-                const float4 mb1 = *reinterpret_cast<const float4*>(mbs + k0 + i * 8 + 4);
-                const float mbv[8] = {mb0.x, mb0.y, mb0.z, mb0.w, mb1.x, mb1.y, mb1.z, mb1.w};
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
                     const int e = i * 8 + jj * 2;
-                    // (q.k + mask bias) + pair bias: the reference's order, in fp32
-                    sv[e] = (sv[e] + mbv[jj * 2]) + bf16lo(w[jj]);
-                    sv[e + 1] = (sv[e + 1] + mbv[jj * 2 + 1]) + bf16hi(w[jj]);
+                    sv[e] += bf16lo(w[jj]);
+                    sv[e + 1] += bf16hi(w[jj]);
                     mx = fmaxf(mx, fmaxf(sv[e], sv[e + 1]));
                 }
             }
@@ -517,19 +572,19 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 ppk[e >> 1] = pack_bf16x2(p0, p1);
             }
             l = fmaf(l, corr, sum);
-            const uint32_t ptile = sbase + CoreSmem::kP + s * kKBlockBytes;
+            const uint32_t ptile = sbase + CoreSmem::kP + (L * 2 + s) * kKBlockBytes;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch)
                 sts128(chunk_addr(ptile, row, ch),
                        make_uint4(ppk[ch * 4], ppk[ch * 4 + 1], ppk[ch * 4 + 2], ppk[ch * 4 + 3]));
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_ready(s));
+            if (lane == 0) mbar_arrive(p_ready(L, s));
             // fold in the previous block's P V while this block's MMA runs
             if (j >= 1) {
                 const int ps = (j - 1) & 1;
-                if (!mbar_wait(o_full(ps), ((j - 1) >> 1) & 1u, abort_flag)) {
-                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
+                if (!mbar_wait(o_full(L, ps), ((j - 1) >> 1) & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 8);
                     ok = false;
                     break;
                 }
@@ -539,7 +594,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(o_empty(ps));
+                if (lane == 0) mbar_arrive(o_empty(L, ps));
 #pragma unroll
                 for (int e = 0; e < kD; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(r[e]));
             }
@@ -547,13 +602,13 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         if (ok) {
             const int ps = (nblk - 1) & 1;
-            if (mbar_wait(o_full(ps), ((nblk - 1) >> 1) & 1u, abort_flag)) {
+            if (mbar_wait(o_full(L, ps), ((nblk - 1) >> 1) & 1u, abort_flag)) {
                 tc_fence_after_sync();
                 uint32_t r[32];
                 tmem_ld32(trow + 128 + ps * kD, r);
                 tmem_ld_wait();
                 const float inv = 1.0f / l;
-                if (qpos < N) {
+                if (qpos < N && line_valid) {
                     uint4* dst = reinterpret_cast<uint4*>(o_out + ((bl * N + qpos) * (long long)kC) + h * kD);
 #pragma unroll
                     for (int v4 = 0; v4 < 4; ++v4) {
@@ -566,7 +621,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                 }
             } else if (lane == 0) {
-                report_wait_failure(status, abort_flag, kKidCore, 7);
+                report_wait_failure(status, abort_flag, kKidCore, 9);
             }
         }
     }
@@ -575,7 +630,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 256);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -842,7 +897,7 @@ int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16*
                float inf, int flags, const of3_triattn_params* p, __nv_bfloat16* q, __nv_bfloat16* k,
                __nv_bfloat16* vt, __nv_bfloat16* tb, __nv_bfloat16* o, int ldn, cudaStream_t st) {
     int rc;
-    CUtensorMap tmZ, tmOut, tmO, tmW[5], tmQ, tmK, tmV;
+    CUtensorMap tmZ, tmOut, tmO, tmW[5], tmQ, tmK, tmV, tmTb;
     if ((rc = z_tmap(&tmZ, z, B, N, kT))) return rc;
     if ((rc = z_tmap(&tmOut, out, B, N, kT))) return rc;
     if ((rc = z_tmap(&tmO, o, B, N, false))) return rc;  // o is [line][pos][128] in view order
@@ -861,11 +916,17 @@ int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16*
         uint64_t strv[2] = {(uint64_t)ldn * 2, (uint64_t)kD * ldn * 2};
         uint32_t boxv[3] = {kBK, kD, 1};
         if ((rc = make_tmap_bf16(&tmV, vt, 3, dimv, strv, boxv, 1))) return rc;
+        // pair bias [b*H + h][q][k], row pitch ldn: tile = 128 queries x 64 keys
+        uint64_t dimt[3] = {(uint64_t)ldn, (uint64_t)N, (uint64_t)B * kH};
+        uint64_t strt[2] = {(uint64_t)ldn * 2, (uint64_t)N * ldn * 2};
+        uint32_t boxt[3] = {kBK, kBQ, 1};
+        if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 1))) return rc;
     }
     static bool attr_done = false;
     if (!attr_done) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_proj_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ProjSmem::kDyn));
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_core_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, CoreSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_core_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            CoreSmem::dyn_bytes(kMaxKeys / kBK)));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_out_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, AOutSmem::kDyn));
         attr_done = true;
     }
@@ -879,12 +940,12 @@ int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16*
         (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, N, ldn, status);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
-    const long long ctas = lines * ceil_div(N, kBQ);
+    const long long ctas = (long long)B * ceil_div(N, kLines) * kH * ceil_div(N, kBQ);
     OF3_REQUIRE(ctas < (1LL << 31), OF3_ERR_SHAPE, "triattn: too many attention tiles");
     {
     LaunchScope scope(kKidCore, st);
-    triattn_core_kernel<kT><<<(unsigned)ctas, 192, CoreSmem::kDyn, st>>>(tmQ, tmK, tmV, tb, mask, o, B, N,
-                                                                        ldn, inf, status);
+    triattn_core_kernel<kT><<<(unsigned)ctas, 320, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
+        tmQ, tmK, tmV, tmTb, mask, o, B, N, inf, status);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     LaunchScope scope(kKidOut, st);

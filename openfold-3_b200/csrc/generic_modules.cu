@@ -213,13 +213,18 @@ int attn_pair_bias(const T* a, const T* z, const T* s, const T* mask, T* out, in
         TRY((layernorm<T, T>(a, (const T*)p->ln_a_w, (const T*)p->ln_a_b, an, rows, c_a, 1e-5f, rows, 0,
                              c_a, st)));
     }
-    for (long long r0 = 0; r0 < zrows; r0 += panel) {
-        const long long nr = zrows - r0 < panel ? zrows - r0 : panel;
-        TRY((layernorm<T, T>(z + r0 * c_z, (const T*)p->ln_z_w, (const T*)p->ln_z_b, zn, nr, c_z, 1e-5f,
-                             nr, 0, c_z, st)));
-        TRY(linear<T>(zn, (const T*)p->w_z, nullptr, zp + r0 * H, nr, H, c_z, st));
+    if (c_z == 128 && H == 16 && ((uintptr_t)z & 15) == 0) {
+        // one pass over z: LayerNorm statistics and all 16 head projections per pair position
+        TRY(pair_bias_c128_h16<T>(z, (const T*)p->ln_z_w, (const T*)p->ln_z_b, (const T*)p->w_z, zb, Bz, N, st));
+    } else {
+        for (long long r0 = 0; r0 < zrows; r0 += panel) {
+            const long long nr = zrows - r0 < panel ? zrows - r0 : panel;
+            TRY((layernorm<T, T>(z + r0 * c_z, (const T*)p->ln_z_w, (const T*)p->ln_z_b, zn, nr, c_z, 1e-5f,
+                                 nr, 0, c_z, st)));
+            TRY(linear<T>(zn, (const T*)p->w_z, nullptr, zp + r0 * H, nr, H, c_z, st));
+        }
+        TRY(permute_bias(zp, zb, Bz, N, H, st));
     }
-    TRY(permute_bias(zp, zb, Bz, N, H, st));
     TRY(linear<T>(an, (const T*)p->w_q, (const T*)p->b_q, q, rows, hd, c_a, st));
     TRY(linear<T>(an, (const T*)p->w_k, nullptr, k, rows, hd, c_a, st));
     TRY(linear<T>(an, (const T*)p->w_v, nullptr, v, rows, hd, c_a, st));

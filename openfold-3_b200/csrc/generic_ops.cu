@@ -192,6 +192,79 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ k,
     }
 }
 
+
+// ------------------------------------------------------------------ fused pair-bias projection
+// LN(x).w_h = rstd * sum_c (x_c - mean) * (gamma_c w_hc) + sum_c beta_c w_hc
+template <typename T>
+__global__ void __launch_bounds__(256) pair_bias_c128_h16_kernel(const T* __restrict__ z,
+                                                                 const T* __restrict__ gamma,
+                                                                 const T* __restrict__ beta,
+                                                                 const T* __restrict__ w,
+                                                                 float* __restrict__ dst, long long rows,
+                                                                 long long nn) {
+    __shared__ float ws[16][128];
+    __shared__ float cs[16];
+    for (int i = threadIdx.x; i < 16 * 128; i += 256) {
+        const int c = i & 127;
+        ws[i >> 7][c] = ld_as_float(w + i) * (gamma ? ld_as_float(gamma + c) : 1.0f);
+    }
+    if (threadIdx.x < 16) {
+        float a = 0.f;
+        if (beta)
+            for (int c = 0; c < 128; ++c) a += ld_as_float(beta + c) * ld_as_float(w + threadIdx.x * 128 + c);
+        cs[threadIdx.x] = a;
+    }
+    __syncthreads();
+    const long long r = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (r >= rows) return;
+    float x[128];
+    const T* zr = z + r * 128;
+    if constexpr (sizeof(T) == 2) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(zr) + i);
+            const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                x[i * 8 + j * 2] = bf16lo(u[j]);
+                x[i * 8 + j * 2 + 1] = bf16hi(u[j]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(zr) + i);
+            x[i * 4] = v.x; x[i * 4 + 1] = v.y; x[i * 4 + 2] = v.z; x[i * 4 + 3] = v.w;
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < 128; ++c) s += x[c];
+    const float mean = s * (1.0f / 128.0f);
+    float var = 0.f;
+#pragma unroll
+    for (int c = 0; c < 128; ++c) {
+        x[c] -= mean;
+        var = fmaf(x[c], x[c], var);
+    }
+    const float rstd = 1.0f / sqrtf(var * (1.0f / 128.0f) + 1e-5f);
+    const long long b = r / nn;
+    const long long qk = r % nn;
+#pragma unroll 1
+    for (int h = 0; h < 16; ++h) {
+        float acc = 0.f;
+#pragma unroll
+        for (int c = 0; c < 128; c += 4) {
+            const float4 wv = *reinterpret_cast<const float4*>(&ws[h][c]);
+            acc = fmaf(x[c], wv.x, acc);
+            acc = fmaf(x[c + 1], wv.y, acc);
+            acc = fmaf(x[c + 2], wv.z, acc);
+            acc = fmaf(x[c + 3], wv.w, acc);
+        }
+        dst[(b * 16 + h) * nn + qk] = fmaf(acc, rstd, cs[h]);
+    }
+}
+
 // ------------------------------------------------------------------ elementwise
 template <typename T>
 __global__ void gate_mul_mask_kernel(const float* __restrict__ g, const float* __restrict__ p,
@@ -398,6 +471,24 @@ template int finalize<float>(const float*, const float*, const float*, const flo
 template int finalize<__nv_bfloat16>(const float*, const float*, const __nv_bfloat16*,
                                      const __nv_bfloat16*, __nv_bfloat16*, long long, int, long long,
                                      long long, long long, cudaStream_t);
+
+
+template <typename T>
+int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, float* dst, long long B, int N,
+                       cudaStream_t stream) {
+    const long long nn = (long long)N * N;
+    const long long rows = B * nn;
+    if (rows <= 0) return OF3_OK;
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "pair_bias: z must be 16-byte aligned");
+    LaunchScope scope(20, stream);
+    pair_bias_c128_h16_kernel<T><<<grid_for(rows, 256), 256, 0, stream>>>(z, gamma, beta, w, dst, rows, nn);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+template int pair_bias_c128_h16<float>(const float*, const float*, const float*, const float*, float*,
+                                       long long, int, cudaStream_t);
+template int pair_bias_c128_h16<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*,
+                                               const __nv_bfloat16*, float*, long long, int, cudaStream_t);
 
 int permute_bias(const float* src, float* dst, long long B, int N, int H, cudaStream_t stream) {
     const long long total = B * H * (long long)N * N;

@@ -62,6 +62,12 @@ template <typename T>
 int finalize(const float* upd, const float* gate, const T* residual, const T* mask, T* out,
              long long rows, int C, long long inner, long long outer_stride,
              long long inner_stride, cudaStream_t stream);
+// Fused pair-bias projection for 128-channel pair tensors and 16 heads:
+// dst[b][h][q][k] = sum_c LN(z[b, q, k, :])[c] * w[h][c], one thread per pair position, one pass over z.
+// gamma/beta may be null. Returns OF3_ERR_SHAPE for other widths (callers fall back to the chain).
+template <typename T>
+int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, float* dst, long long B, int N,
+                       cudaStream_t stream);
 // dst[b][h][q][k] = src[b][q][k][h]
 int permute_bias(const float* src, float* dst, long long B, int N, int H, cudaStream_t stream);
 // dense fp32 copy of a storage-type tensor
