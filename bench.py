@@ -220,8 +220,7 @@ def run_ours(args) -> None:
     z_out_host = torch.empty_like(z_host).pin_memory()
 
     if world > 1:
-        from openfold3_b200 import dap
-        runner = dap.DapPairFormerStack(stack, world, rank)
+        runner = pkg.dap.DapPairFormerStack(stack, world, rank, ops=pkg.dap.CudaOps(dev))
     else:
         runner = None
 

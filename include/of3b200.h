@@ -212,6 +212,35 @@ int of3_cond_transition_forward(const void* a, const void* s, const void* mask, 
                                 const of3_cond_transition_params* p, void* workspace,
                                 size_t workspace_bytes, void* stream);
 
+/* ---- Row-sharded ("DAP") pair stack: phase entry points --------------------------------------
+ * No counterpart in the reference (it has data-parallel DDP / ZeRO only; SURVEY of its
+ * experiment_runner.py:218-246). Each rank owns R = N / P consecutive rows of one sample's pair
+ * tensor (bf16, c_z = c_hidden = 128, 4 heads x 32) and runs every layer as project | exchange |
+ * finish; the exchange (all-gather / all-to-all) is the caller's, between the two calls.
+ * Pitches: ld = of3_dap_pitch(N, 8) for a_t / b_t / x, ldn = of3_dap_pitch(N, 64) for v^T and bias.
+ *   z_rows, out_rows [R, N, 128]; mask_rows [R, N] or NULL; a_t, x_scratch [128, R, ld];
+ *   b_all [128, N, ld]; q, k [R, 4, N, 32]; vt [R, 4, 32, ldn]; bias_rows [4, R, ldn];
+ *   bias_all [4, N, ldn]; o_scratch [R, N, 128]. out_rows may alias z_rows. */
+int of3_dap_pitch(int N, int multiple);
+int of3_dap_trimul_project(const void* z_rows, const void* mask_rows, void* a_t, void* b_t, int R, int N,
+                           const of3_trimul_params* p, void* stream);
+int of3_dap_trimul_finish(const void* z_rows, void* out_rows, const void* a_t, const void* b_all, void* x_scratch,
+                          int R, int N, int flags, const of3_trimul_params* p, void* stream);
+int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N,
+                            const of3_triattn_params* p, void* stream);
+int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_rows, const void* q, const void* k,
+                           const void* vt, const void* bias_all, void* o_scratch, int R, int N, float inf, int flags,
+                           const of3_triattn_params* p, void* stream);
+/* Pair-bias projection of AttentionPairBias (attention_pair_bias.py:154-163) for `positions` pair
+ * positions: bias_rows[h][pos] = linear_z(LayerNorm_z(z))[pos][h], fp32, c_z = 128, 16 heads. */
+int of3_pair_bias_project(const void* z_rows, const void* ln_w, const void* ln_b, const void* w, float* bias_rows,
+                          long long positions, int c_z, int H, int dtype, void* stream);
+/* of3_attn_pair_bias_forward with the pair bias [Bz, H, N, N] (fp32) already projected. */
+int of3_attn_pair_bias_forward_prebias(const void* a, const float* pair_bias, const void* s, const void* mask,
+                                       void* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf,
+                                       int dtype, int flags, const of3_attn_pair_bias_params* p, void* workspace,
+                                       size_t workspace_bytes, void* stream);
+
 /* ---- Building block exported for tests and profiling --------------------------------------
  * X[b][i][j] = sum_k A[b][i][k] * B[b][j][k], bf16 in / fp32 accumulate / bf16 out, the
  * tcgen05 kernel behind the triangle contraction (einsum of

@@ -6,7 +6,7 @@ used for tensors, streams and ``torch.distributed`` only; every forward runs han
 CUDA kernels from the in-tree C-ABI library ``libof3b200.so``.
 """
 
-from . import init_config, lib, weights
+from . import dap, init_config, lib, weights
 from .modules import (
     AdaLN,
     Attention,

@@ -38,23 +38,24 @@ constexpr float kLog2e = 1.4426950408889634f;
 struct LineTile {
     int b, line, t0;
 };
-__device__ __forceinline__ LineTile line_tile(long long t, int N, int tiles_per_line) {
+// R = lines per sample (R == N for a whole pair tensor, N / P for a row shard)
+__device__ __forceinline__ LineTile line_tile(long long t, int R, int tiles_per_line) {
     LineTile c;
     c.t0 = (int)(t % tiles_per_line) * kRows;
     const long long l = t / tiles_per_line;
-    c.line = (int)(l % N);
-    c.b = (int)(l / N);
+    c.line = (int)(l % R);
+    c.b = (int)(l / R);
     return c;
 }
 // z tile of a line: rows (line, t0..t0+127) of the view; transposed view = z[b, t, line, :]
 template <bool kTransposed>
 __device__ __forceinline__ void load_z_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
-                                            const LineTile& c, int N) {
+                                            const LineTile& c, int R) {
     for (int kb = 0; kb < 2; ++kb) {
         if (kTransposed)
             tma_load_4d(dst + kb * kKBlockBytes, tm, bar, kb * 64, c.line, c.t0, c.b);
         else
-            tma_load_3d(dst + kb * kKBlockBytes, tm, bar, kb * 64, c.t0, c.b * N + c.line);
+            tma_load_3d(dst + kb * kKBlockBytes, tm, bar, kb * 64, c.t0, c.b * R + c.line);
     }
 }
 
@@ -80,7 +81,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
                     const __nv_bfloat16* __restrict__ w_bias, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ vt_out,
-                    __nv_bfloat16* __restrict__ tb_out, int B, int N, int ldn, int* status) {
+                    __nv_bfloat16* __restrict__ tb_out, int B, int R, int N, int ldn, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -99,7 +100,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_line = (N + kRows - 1) / kRows;
-    const long long num_tiles = (long long)B * N * tiles_per_line;
+    const long long num_tiles = (long long)B * R * tiles_per_line;
 
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
@@ -144,9 +145,9 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     report_wait_failure(status, abort_flag, kKidProj, 1);
                     break;
                 }
-                const LineTile tc = line_tile(t, N, tiles_per_line);
+                const LineTile tc = line_tile(t, R, tiles_per_line);
                 mbar_arrive_expect_tx(z_full(s), kTileBytes);
-                load_z_tile<kTransposed>(sbase + ProjSmem::kZ + s * kTileBytes, &tmZ, z_full(s), tc, N);
+                load_z_tile<kTransposed>(sbase + ProjSmem::kZ + s * kTileBytes, &tmZ, z_full(s), tc, R);
             }
         }
     } else if (warp == 1) {
@@ -185,7 +186,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 5);
                 break;
             }
-            const LineTile tc = line_tile(t, N, tiles_per_line);
+            const LineTile tc = line_tile(t, R, tiles_per_line);
             const uint32_t tile = sbase + ProjSmem::kZ + s * kTileBytes;
             uint32_t raw[64];
             load_row(tile, row, raw);
@@ -217,7 +218,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             if (pos < ldn) {  // the row padding [N, ldn) is read by the attention kernel: keep it finite
 #pragma unroll
                 for (int h = 0; h < kH; ++h)
-                    tb_out[(((long long)tc.b * kH + h) * N + tc.line) * ldn + pos] =
+                    tb_out[(((long long)tc.b * kH + h) * R + tc.line) * ldn + pos] =
                         __float2bfloat16_rn(pos < N ? tb[h] * kLog2e : 0.f);
             }
         }
@@ -229,10 +230,10 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
         uint32_t it = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-            const LineTile tc = line_tile(t, N, tiles_per_line);
+            const LineTile tc = line_tile(t, R, tiles_per_line);
             const int pos = tc.t0 + row;
             const bool valid = pos < N;
-            const long long lineh = ((long long)tc.b * N + tc.line) * kH;  // (line, head 0)
+            const long long lineh = ((long long)tc.b * R + tc.line) * kH;  // (line, head 0)
             // ---- slot 0: q (columns 0..127) and k (128..255), [line][head][pos][32]
             if (!mbar_wait(slot_full(0), it & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 6);
@@ -327,7 +328,7 @@ __global__ void __launch_bounds__(320, 1)
 triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTb,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
-                    int N, float inf, int* status) {
+                    int R, int N, float inf, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -347,7 +348,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (N + kBQ - 1) / kBQ;
-    const int pairs_per_b = (N + kLines - 1) / kLines;
+    const int pairs_per_b = (R + kLines - 1) / kLines;
     const int qt = blockIdx.x % n_qt;
     const int h = (blockIdx.x / n_qt) % kH;
     const int lp = blockIdx.x / (n_qt * kH);
@@ -357,7 +358,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int nblk = (N + kBK - 1) / kBK;
     const int nkp = nblk * kBK;
     // an odd N leaves the last pair with one line: the second group recomputes the first, unsaved
-    auto line_of = [&](int L) { return (line0 + L < N) ? line0 + L : line0; };
+    auto line_of = [&](int L) { return (line0 + L < R) ? line0 + L : line0; };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -388,7 +389,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             v = 0.f;
             if (mask != nullptr) {
                 const long long mi = kTransposed ? ((long long)b * N + k) * N + line
-                                                 : ((long long)b * N + line) * N + k;
+                                                 : ((long long)b * R + line) * N + k;
                 v = inf * (__bfloat162float(mask[mi]) - 1.0f) * kLog2e;
             }
         }
@@ -417,7 +418,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             mbar_arrive_expect_tx(q_full, kLines * kBQ * 64);
             for (int L = 0; L < kLines; ++L)
                 tma_load_3d(sbase + CoreSmem::kQ + L * 8192, &tmQ, q_full, 0, q0,
-                            (b * N + line_of(L)) * kH + h);
+                            (b * R + line_of(L)) * kH + h);
             for (int j = 0; j < nblk; ++j) {
                 const int s = j & 1;
                 if (!mbar_wait(kv_empty(s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
@@ -426,7 +427,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
                 mbar_arrive_expect_tx(kv_full(s), kLines * 8192 + kKBlockBytes);
                 for (int L = 0; L < kLines; ++L) {
-                    const int lh = (b * N + line_of(L)) * kH + h;
+                    const int lh = (b * R + line_of(L)) * kH + h;
                     tma_load_3d(sbase + CoreSmem::kK + (L * 2 + s) * 4096, &tmK, kv_full(s), 0, j * kBK, lh);
                     tma_load_3d(sbase + CoreSmem::kV + (L * 2 + s) * 4096, &tmV, kv_full(s), j * kBK, 0, lh);
                 }
@@ -490,8 +491,8 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int qpos = q0 + row;
-        const bool line_valid = line0 + L < N;
-        const long long bl = (long long)b * N + line_of(L);
+        const bool line_valid = line0 + L < R;
+        const long long bl = (long long)b * R + line_of(L);
         const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 256;
         const float* mbl = mbs + L * nkp;
         float m = -INFINITY, l = 0.f, corr_prev = 1.f;
@@ -653,7 +654,7 @@ __global__ void __launch_bounds__(320, 1)
 triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmO,
                    const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmWg,
                    const __grid_constant__ CUtensorMap tmWo, const __nv_bfloat16* __restrict__ ln_w,
-                   const __nv_bfloat16* __restrict__ ln_b, int B, int N, int add_residual, int* status) {
+                   const __nv_bfloat16* __restrict__ ln_b, int B, int R, int N, int add_residual, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -671,7 +672,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_line = (N + kRows - 1) / kRows;
-    const long long num_tiles = (long long)B * N * tiles_per_line;
+    const long long num_tiles = (long long)B * R * tiles_per_line;
     const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
     if (threadIdx.x == 0) {
@@ -717,12 +718,12 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                     report_wait_failure(status, abort_flag, kKidOut, 1);
                     break;
                 }
-                const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+                const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
                 mbar_arrive_expect_tx(full(g), 2 * kTileBytes);
-                load_z_tile<kTransposed>(sbase + AOutSmem::kZ + g * kTileBytes, &tmZ, full(g), tc, N);
+                load_z_tile<kTransposed>(sbase + AOutSmem::kZ + g * kTileBytes, &tmZ, full(g), tc, R);
                 const uint32_t odst = sbase + AOutSmem::kO + g * kTileBytes;
                 for (int kb = 0; kb < 2; ++kb)
-                    tma_load_3d(odst + kb * kKBlockBytes, &tmO, full(g), kb * 64, tc.t0, tc.b * N + tc.line);
+                    tma_load_3d(odst + kb * kKBlockBytes, &tmO, full(g), kb * 64, tc.t0, tc.b * R + tc.line);
             }
         }
     } else if (warp == 1) {
@@ -768,7 +769,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
         const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
         for (long long lt = g; lt < my_tiles; lt += 2) {
             const uint32_t use = (uint32_t)(lt >> 1);
-            const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+            const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
             if (!mbar_wait(full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
                 break;
@@ -853,7 +854,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                             "r"(ztile + kb * kKBlockBytes), "r"(kb * 64), "r"(tc.line), "r"(tc.t0), "r"(tc.b)
                             : "memory");
                     } else {
-                        tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * N + tc.line);
+                        tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.line);
                     }
                 }
                 tma_store_commit();
@@ -879,9 +880,9 @@ int weight_tmap128(CUtensorMap* m, const void* w) {
     return make_tmap_bf16(m, w, 2, dims, str, box, 1);
 }
 
-int z_tmap(CUtensorMap* m, const void* z, int B, int N, bool transposed) {
+int z_tmap(CUtensorMap* m, const void* z, int B, int R, int N, bool transposed) {
     if (!transposed) {
-        uint64_t dims[3] = {128, (uint64_t)N, (uint64_t)B * N};
+        uint64_t dims[3] = {128, (uint64_t)N, (uint64_t)B * R};
         uint64_t str[2] = {256, (uint64_t)N * 256};
         uint32_t box[3] = {64, 128, 1};
         return make_tmap_bf16(m, z, 3, dims, str, box, 1);
@@ -893,18 +894,50 @@ int z_tmap(CUtensorMap* m, const void* z, int B, int N, bool transposed) {
 }
 
 template <bool kT>
-int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
-               float inf, int flags, const of3_triattn_params* p, __nv_bfloat16* q, __nv_bfloat16* k,
-               __nv_bfloat16* vt, __nv_bfloat16* tb, __nv_bfloat16* o, int ldn, cudaStream_t st) {
+int set_attrs() {
+    static bool attr_done = false;
+    if (!attr_done) {
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_proj_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ProjSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_core_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            CoreSmem::dyn_bytes(kMaxKeys / kBK)));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_out_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, AOutSmem::kDyn));
+        attr_done = true;
+    }
+    return OF3_OK;
+}
+
+template <bool kT>
+int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
+                 __nv_bfloat16* tb, int B, int R, int N, int ldn, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
-    CUtensorMap tmZ, tmOut, tmO, tmW[5], tmQ, tmK, tmV, tmTb;
-    if ((rc = z_tmap(&tmZ, z, B, N, kT))) return rc;
-    if ((rc = z_tmap(&tmOut, out, B, N, kT))) return rc;
-    if ((rc = z_tmap(&tmO, o, B, N, false))) return rc;  // o is [line][pos][128] in view order
-    const void* w5[5] = {p->w_q, p->w_k, p->w_v, p->w_g, p->w_o};
-    for (int i = 0; i < 5; ++i)
-        if ((rc = weight_tmap128(&tmW[i], w5[i]))) return rc;
-    const long long lines = (long long)B * N * kH;
+    CUtensorMap tmZ, tmW[3];
+    if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
+    const void* w3[3] = {p->w_q, p->w_k, p->w_v};
+    for (int i = 0; i < 3; ++i)
+        if ((rc = weight_tmap128(&tmW[i], w3[i]))) return rc;
+    if ((rc = set_attrs<kT>())) return rc;
+    const long long tiles = (long long)B * R * ceil_div(N, kRows);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    LaunchScope scope(kKidProj, st);
+    triattn_proj_kernel<kT><<<grid, 320, ProjSmem::kDyn, st>>>(
+        tmZ, tmW[0], tmW[1], tmW[2], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
+        (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, R, N, ldn, device_status_ptr());
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+template <bool kT>
+int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, const __nv_bfloat16* q,
+                const __nv_bfloat16* k, const __nv_bfloat16* vt, const __nv_bfloat16* tb, __nv_bfloat16* o, int B,
+                int R, int N, int ldn, float inf, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
+    int rc;
+    CUtensorMap tmZ, tmOut, tmO, tmWg, tmWo, tmQ, tmK, tmV, tmTb;
+    if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
+    if ((rc = z_tmap(&tmOut, out, B, R, N, kT))) return rc;
+    if ((rc = z_tmap(&tmO, o, B, R, N, false))) return rc;  // o is [line][pos][128] in view order
+    if ((rc = weight_tmap128(&tmWg, p->w_g))) return rc;
+    if ((rc = weight_tmap128(&tmWo, p->w_o))) return rc;
+    const long long lines = (long long)B * R * kH;
     {
         uint64_t dims[3] = {kD, (uint64_t)N, (uint64_t)lines};
         uint64_t str[2] = {kD * 2, (uint64_t)N * kD * 2};
@@ -916,42 +949,28 @@ int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16*
         uint64_t strv[2] = {(uint64_t)ldn * 2, (uint64_t)kD * ldn * 2};
         uint32_t boxv[3] = {kBK, kD, 1};
         if ((rc = make_tmap_bf16(&tmV, vt, 3, dimv, strv, boxv, 1))) return rc;
-        // pair bias [b*H + h][q][k], row pitch ldn: tile = 128 queries x 64 keys
+        // pair bias [b*H + h][q][k] for ALL N query positions, row pitch ldn: tile = 128 queries x 64 keys
         uint64_t dimt[3] = {(uint64_t)ldn, (uint64_t)N, (uint64_t)B * kH};
         uint64_t strt[2] = {(uint64_t)ldn * 2, (uint64_t)N * ldn * 2};
         uint32_t boxt[3] = {kBK, kBQ, 1};
         if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 1))) return rc;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_proj_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ProjSmem::kDyn));
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_core_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            CoreSmem::dyn_bytes(kMaxKeys / kBK)));
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_out_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, AOutSmem::kDyn));
-        attr_done = true;
-    }
+    if ((rc = set_attrs<kT>())) return rc;
     int* status = device_status_ptr();
-    const long long tiles = (long long)B * N * ceil_div(N, kRows);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    {
-    LaunchScope scope(kKidProj, st);
-    triattn_proj_kernel<kT><<<grid, 320, ProjSmem::kDyn, st>>>(
-        tmZ, tmW[0], tmW[1], tmW[2], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
-        (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, N, ldn, status);
-    }
-    OF3_CUDA_CHECK(cudaGetLastError());
-    const long long ctas = (long long)B * ceil_div(N, kLines) * kH * ceil_div(N, kBQ);
+    const long long ctas = (long long)B * ceil_div(R, kLines) * kH * ceil_div(N, kBQ);
     OF3_REQUIRE(ctas < (1LL << 31), OF3_ERR_SHAPE, "triattn: too many attention tiles");
     {
-    LaunchScope scope(kKidCore, st);
-    triattn_core_kernel<kT><<<(unsigned)ctas, 320, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
-        tmQ, tmK, tmV, tmTb, mask, o, B, N, inf, status);
+        LaunchScope scope(kKidCore, st);
+        triattn_core_kernel<kT><<<(unsigned)ctas, 320, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
+            tmQ, tmK, tmV, tmTb, mask, o, B, R, N, inf, status);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
+    const long long tiles = (long long)B * R * ceil_div(N, kRows);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     LaunchScope scope(kKidOut, st);
     triattn_out_kernel<kT><<<grid, 320, AOutSmem::kDyn, st>>>(
-        tmZ, tmO, tmOut, tmW[3], tmW[4], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, B, N,
-        (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, status);
+        tmZ, tmO, tmOut, tmWg, tmWo, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, B, R, N,
+        add_residual, status);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
@@ -960,6 +979,31 @@ int launch_all(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16*
 
 bool triattn_supported(int c_z, int H, int d, int N) {
     return c_z == 128 && H == kH && d == kD && N <= kMaxKeys;
+}
+
+// q, k [line][head][pos][32], v transposed, and this shard's rows of the pair bias
+// tb[(b*H + h)][line][ldn] from R lines of N positions. transposed: whole square tensors only.
+int triattn_project(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
+                    __nv_bfloat16* tb, int B, int R, int N, int ldn, bool transposed,
+                    const of3_triattn_params* p, cudaStream_t st) {
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "triattn: z must be 16-byte aligned");
+    OF3_REQUIRE(!transposed || R == N, OF3_ERR_SHAPE, "triattn: transposed view needs the whole tensor");
+    return transposed ? project_impl<true>(z, q, k, vt, tb, B, R, N, ldn, p, st)
+                      : project_impl<false>(z, q, k, vt, tb, B, R, N, ldn, p, st);
+}
+
+// attention over the R lines with the pair bias of all N query rows, gate, output projection, residual.
+int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
+                   const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
+                   const __nv_bfloat16* tb, __nv_bfloat16* o, int B, int R, int N, int ldn, float inf,
+                   bool transposed, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
+                "triattn: z/out must be 16-byte aligned");
+    OF3_REQUIRE(N <= kMaxKeys, OF3_ERR_SHAPE, "triattn: N %d above the %d keys one CTA keeps a mask row for", N,
+                kMaxKeys);
+    OF3_REQUIRE(!transposed || R == N, OF3_ERR_SHAPE, "triattn: transposed view needs the whole tensor");
+    return transposed ? finish_impl<true>(z, mask, out, q, k, vt, tb, o, B, R, N, ldn, inf, add_residual, p, st)
+                      : finish_impl<false>(z, mask, out, q, k, vt, tb, o, B, R, N, ldn, inf, add_residual, p, st);
 }
 
 int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
@@ -973,13 +1017,11 @@ int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* ou
     __nv_bfloat16* tb = (__nv_bfloat16*)ws.take((size_t)B * kH * N * ldn * sizeof(__nv_bfloat16) + 256);
     if (!ws.base) return OF3_OK;
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "triattn: workspace too small (%zu needed)", ws.off);
-    OF3_REQUIRE(N <= kMaxKeys, OF3_ERR_SHAPE, "triattn: N %d above the %d keys one CTA keeps a mask row for",
-                N, kMaxKeys);
-    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
-                "triattn: z/out must be 16-byte aligned");
-    if (flags & OF3_FLAG_TRANSPOSED)
-        return launch_all<true>(z, mask, out, B, N, inf, flags, p, q, k, vt, tb, o, ldn, st);
-    return launch_all<false>(z, mask, out, B, N, inf, flags, p, q, k, vt, tb, o, ldn, st);
+    const bool tr = (flags & OF3_FLAG_TRANSPOSED) != 0;
+    int rc = triattn_project(z, q, k, vt, tb, B, N, N, ldn, tr, p, st);
+    if (rc) return rc;
+    return triattn_finish(z, mask, out, q, k, vt, tb, o, B, N, N, ldn, inf, tr,
+                          (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, st);
 }
 
 }  // namespace fast

@@ -29,12 +29,13 @@ constexpr int kKidOut = 3;
 struct TileCoord {
     int b, fixed, t0;  // sample, fixed index (i), first row of the tile along the walking index
 };
-__device__ __forceinline__ TileCoord tile_coord(long long t, int N, int tiles_per_line) {
+// R = lines per sample (R == N for a whole pair tensor, N / P for a row shard)
+__device__ __forceinline__ TileCoord tile_coord(long long t, int R, int tiles_per_line) {
     TileCoord c;
     c.t0 = (int)(t % tiles_per_line) * kRows;
     const long long line = t / tiles_per_line;
-    c.fixed = (int)(line % N);
-    c.b = (int)(line / N);
+    c.fixed = (int)(line % R);
+    c.b = (int)(line / R);
     return c;
 }
 
@@ -59,8 +60,8 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmWag, const __grid_constant__ CUtensorMap tmWbp,
                  const __grid_constant__ CUtensorMap tmWbg, const __nv_bfloat16* __restrict__ mask,
                  const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
-                 __nv_bfloat16* __restrict__ a_t, __nv_bfloat16* __restrict__ b_t, int B, int N,
-                 int ld, int* status) {
+                 __nv_bfloat16* __restrict__ a_t, __nv_bfloat16* __restrict__ b_t, int B, int R,
+                 int N, int ld, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -78,7 +79,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_line = (N + kRows - 1) / kRows;
-    const long long num_tiles = (long long)B * N * tiles_per_line;
+    const long long num_tiles = (long long)B * R * tiles_per_line;
 
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
@@ -122,13 +123,13 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                     report_wait_failure(status, abort_flag, kKidIn, 1);
                     break;
                 }
-                const TileCoord tc = tile_coord(t, N, tiles_per_line);
+                const TileCoord tc = tile_coord(t, R, tiles_per_line);
                 mbar_arrive_expect_tx(z_full(s), kTileBytes);
                 const uint32_t dst = sbase + InSmem::kZ + s * kTileBytes;
                 for (int kb = 0; kb < 2; ++kb) {
                     if (kOutgoing)
                         tma_load_3d(dst + kb * kKBlockBytes, &tmZ, z_full(s), kb * 64, tc.t0,
-                                    tc.b * N + tc.fixed);
+                                    tc.b * R + tc.fixed);
                     else
                         tma_load_4d(dst + kb * kKBlockBytes, &tmZ, z_full(s), kb * 64, tc.fixed, tc.t0,
                                     tc.b);
@@ -189,12 +190,12 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         uint32_t it = 0;
         bool ok = true;
         for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
-            const TileCoord tc = tile_coord(t, N, tiles_per_line);
+            const TileCoord tc = tile_coord(t, R, tiles_per_line);
             const int k = tc.t0 + row;
             const bool valid = k < N;
             float m = 1.0f;
             if (valid && mask != nullptr) {
-                const long long lin = kOutgoing ? ((long long)(tc.b * N + tc.fixed) * N + k)
+                const long long lin = kOutgoing ? ((long long)(tc.b * R + tc.fixed) * N + k)
                                                 : ((long long)(tc.b * N + k) * N + tc.fixed);
                 m = __bfloat162float(mask[lin]);
             }
@@ -206,7 +207,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 }
                 tc_fence_after_sync();
                 __nv_bfloat16* dst = (q == 0 ? a_t : b_t) +
-                                     ((long long)tc.b * kC * N + tc.fixed) * ld + k;
+                                     ((long long)tc.b * kC * R + tc.fixed) * ld + k;
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + q * 256;
 #pragma unroll 1
                 for (int cb = 0; cb < 4; ++cb) {
@@ -218,7 +219,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
 #pragma unroll
                         for (int e = 0; e < 32; ++e) {
                             const float v = m * __uint_as_float(p[e]) * sigmoid_fast(__uint_as_float(g[e]));
-                            dst[(long long)(cb * 32 + e) * N * ld] = __float2bfloat16_rn(v);
+                            dst[(long long)(cb * 32 + e) * R * ld] = __float2bfloat16_rn(v);
                         }
                     }
                 }
@@ -256,7 +257,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                   const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmWg,
                   const __grid_constant__ CUtensorMap tmWz, const __nv_bfloat16* __restrict__ ln_in_w,
                   const __nv_bfloat16* __restrict__ ln_in_b, const __nv_bfloat16* __restrict__ ln_out_w,
-                  const __nv_bfloat16* __restrict__ ln_out_b, int B, int N, int add_residual,
+                  const __nv_bfloat16* __restrict__ ln_out_b, int B, int R, int N, int add_residual,
                   int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -273,7 +274,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_line = (N + kRows - 1) / kRows;
-    const long long num_tiles = (long long)B * N * tiles_per_line;
+    const long long num_tiles = (long long)B * R * tiles_per_line;
     // tiles of this CTA alternate between the two groups: local tile index lt -> group lt & 1
     const long long my_tiles = (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
 
@@ -321,11 +322,11 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                     report_wait_failure(status, abort_flag, kKidOut, 1);
                     break;
                 }
-                const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+                const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
                 mbar_arrive_expect_tx(full(g), 2 * kTileBytes);
                 const uint32_t zdst = sbase + OutSmem::kZ + g * kTileBytes;
                 for (int kb = 0; kb < 2; ++kb)
-                    tma_load_3d(zdst + kb * kKBlockBytes, &tmZ, full(g), kb * 64, tc.t0, tc.b * N + tc.fixed);
+                    tma_load_3d(zdst + kb * kKBlockBytes, &tmZ, full(g), kb * 64, tc.t0, tc.b * R + tc.fixed);
                 // x tile: all 128 channels of positions (fixed, t0 .. t0+127), layout [c][j]
                 tma_load_3d(sbase + OutSmem::kX + g * kTileBytes, &tmX, full(g), tc.t0, tc.fixed, tc.b * kC);
             }
@@ -362,7 +363,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
         const uint32_t xtile = sbase + OutSmem::kX + g * kTileBytes;
         for (long long lt = g; lt < my_tiles; lt += 2) {
             const uint32_t use = (uint32_t)(lt >> 1);
-            const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, N, tiles_per_line);
+            const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
             if (!mbar_wait(full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 4);
                 break;
@@ -428,7 +429,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
             group_sync(1 + g, 128);
             if (gtid == 0) {
                 for (int kb = 0; kb < 2; ++kb)
-                    tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * N + tc.fixed);
+                    tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.fixed);
                 tma_store_commit();
                 tma_store_wait_read<0>();
                 mbar_arrive(empty(g));
@@ -456,6 +457,95 @@ int weight_tmap(CUtensorMap* m, const void* w, int rows) {
 
 bool trimul_supported(int c_z, int c_h) { return c_z == 128 && c_h == 128; }
 
+static int set_attrs() {
+    static bool attr_done = false;
+    if (!attr_done) {
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, OutSmem::kDyn));
+        attr_done = true;
+    }
+    return OF3_OK;
+}
+
+// z as lines: {c, position, b*R + line}
+static int line_tmap(CUtensorMap* m, const void* z, int B, int R, int N) {
+    uint64_t dims[3] = {128, (uint64_t)N, (uint64_t)B * R};
+    uint64_t str[2] = {256, (uint64_t)N * 256};
+    uint32_t box[3] = {64, 128, 1};
+    return make_tmap_bf16(m, z, 3, dims, str, box, 1);
+}
+
+// a_t[(b*128 + c)][line][k], b_t likewise, from R lines of N positions per sample.
+// transposed_walk (whole square tensors only, R == N): the tile walks z along its first index, which
+// makes the incoming update the same K-major contraction as the outgoing one.
+int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* a_t, __nv_bfloat16* b_t,
+                   int B, int R, int N, int ld, bool transposed_walk, const of3_trimul_params* p,
+                   cudaStream_t st) {
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "trimul: z must be 16-byte aligned");
+    OF3_REQUIRE(!transposed_walk || R == N, OF3_ERR_SHAPE, "trimul: transposed walk needs the whole tensor");
+    int rc;
+    CUtensorMap tmZ, tmW[4];
+    if (!transposed_walk) {
+        if ((rc = line_tmap(&tmZ, z, B, R, N))) return rc;
+    } else {  // {c, second, first, b}
+        uint64_t dims[4] = {128, (uint64_t)N, (uint64_t)N, (uint64_t)B};
+        uint64_t str[3] = {256, (uint64_t)N * 256, (uint64_t)N * N * 256};
+        uint32_t box[4] = {64, 1, 128, 1};
+        if ((rc = make_tmap_bf16(&tmZ, z, 4, dims, str, box, 1))) return rc;
+    }
+    const void* w4[4] = {p->w_a_p, p->w_a_g, p->w_b_p, p->w_b_g};
+    for (int i = 0; i < 4; ++i)
+        if ((rc = weight_tmap(&tmW[i], w4[i], 128))) return rc;
+    if ((rc = set_attrs())) return rc;
+    const long long tiles = (long long)B * R * ceil_div(N, kRows);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    LaunchScope scope(kKidIn, st);
+    if (!transposed_walk)
+        trimul_in_kernel<true><<<grid, 320, InSmem::kDyn, st>>>(
+            tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, device_status_ptr());
+    else
+        trimul_in_kernel<false><<<grid, 320, InSmem::kDyn, st>>>(
+            tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, device_status_ptr());
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+// x = a_t . b_t^T per channel (a_t: R lines, b_t: all N lines), then LN_out / linear_z / gate / residual
+// on the R lines of z -> out (may alias z).
+int trimul_finish(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat16* a_t,
+                  const __nv_bfloat16* b_t, __nv_bfloat16* x_t, int B, int R, int N, int ld, int add_residual,
+                  const of3_trimul_params* p, cudaStream_t st) {
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
+                "trimul: z/out must be 16-byte aligned");
+    int rc = contract_nt_bf16(a_t, b_t, x_t, B * kC, R, N, N, ld, ld, ld, (long long)R * ld, (long long)N * ld,
+                              (long long)R * ld, st);
+    if (rc) return rc;
+    CUtensorMap tmZ, tmOut, tmX, tmWg, tmWz;
+    if ((rc = line_tmap(&tmZ, z, B, R, N))) return rc;
+    if ((rc = line_tmap(&tmOut, out, B, R, N))) return rc;
+    {   // x_t[b*128 + c][line][j], pitch ld: box = 128 positions j x 1 x 128 channels, no swizzle
+        uint64_t dims[3] = {(uint64_t)N, (uint64_t)R, (uint64_t)B * kC};
+        uint64_t str[2] = {(uint64_t)ld * 2, (uint64_t)R * ld * 2};
+        uint32_t box[3] = {128, 1, 128};
+        if ((rc = make_tmap_bf16(&tmX, x_t, 3, dims, str, box, 0))) return rc;
+    }
+    if ((rc = weight_tmap(&tmWg, p->w_g, 128))) return rc;
+    if ((rc = weight_tmap(&tmWz, p->w_z, 128))) return rc;
+    if ((rc = set_attrs())) return rc;
+    const long long tiles = (long long)B * R * ceil_div(N, kRows);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    LaunchScope scope(kKidOut, st);
+    trimul_out_kernel<<<grid, 320, OutSmem::kDyn, st>>>(
+        tmZ, tmX, tmOut, tmWg, tmWz, (const __nv_bfloat16*)p->ln_in_w, (const __nv_bfloat16*)p->ln_in_b,
+        (const __nv_bfloat16*)p->ln_out_w, (const __nv_bfloat16*)p->ln_out_b, B, R, N, add_residual,
+        device_status_ptr());
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
 int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
            int flags, const of3_trimul_params* p, Arena& ws, cudaStream_t st) {
     const int ld = (int)align_up(N, 8);
@@ -465,68 +555,10 @@ int trimul(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out
     __nv_bfloat16* x_t = (__nv_bfloat16*)ws.take(plane);
     if (!ws.base) return OF3_OK;
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "trimul: workspace too small (%zu needed)", ws.off);
-    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
-                "trimul: z/out must be 16-byte aligned");
     const bool outgoing = (flags & OF3_FLAG_OUTGOING) != 0;
-    int rc;
-    CUtensorMap tmZin, tmZrow, tmOut, tmX, tmW[6];
-    {   // z as rows of one line: {c, second index, b*N + first index}
-        uint64_t dims[3] = {128, (uint64_t)N, (uint64_t)B * N};
-        uint64_t str[2] = {256, (uint64_t)N * 256};
-        uint32_t box[3] = {64, 128, 1};
-        if ((rc = make_tmap_bf16(&tmZrow, z, 3, dims, str, box, true))) return rc;
-        if ((rc = make_tmap_bf16(&tmOut, out, 3, dims, str, box, true))) return rc;
-    }
-    if (outgoing) {
-        tmZin = tmZrow;
-    } else {  // walk the first index: {c, second, first, b}
-        uint64_t dims[4] = {128, (uint64_t)N, (uint64_t)N, (uint64_t)B};
-        uint64_t str[3] = {256, (uint64_t)N * 256, (uint64_t)N * N * 256};
-        uint32_t box[4] = {64, 1, 128, 1};
-        if ((rc = make_tmap_bf16(&tmZin, z, 4, dims, str, box, true))) return rc;
-    }
-    {   // x_t[b*128 + c][i][j], pitch ld: box = 128 positions j x 1 x 128 channels, no swizzle
-        uint64_t dims[3] = {(uint64_t)N, (uint64_t)N, (uint64_t)B * kC};
-        uint64_t str[2] = {(uint64_t)ld * 2, (uint64_t)N * ld * 2};
-        uint32_t box[3] = {128, 1, 128};
-        if ((rc = make_tmap_bf16(&tmX, x_t, 3, dims, str, box, false))) return rc;
-    }
-    const void* ws6[6] = {p->w_a_p, p->w_a_g, p->w_b_p, p->w_b_g, p->w_g, p->w_z};
-    for (int i = 0; i < 6; ++i)
-        if ((rc = weight_tmap(&tmW[i], ws6[i], 128))) return rc;
-
-    static bool attr_done = false;
-    if (!attr_done) {
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, OutSmem::kDyn));
-        attr_done = true;
-    }
-    int* status = device_status_ptr();
-    const long long tiles = (long long)B * N * ceil_div(N, kRows);
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
-    {
-    LaunchScope scope(kKidIn, st);
-    if (outgoing)
-        trimul_in_kernel<true><<<grid, 320, InSmem::kDyn, st>>>(
-            tmZin, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, N, ld, status);
-    else
-        trimul_in_kernel<false><<<grid, 320, InSmem::kDyn, st>>>(
-            tmZin, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, N, ld, status);
-    }
-    OF3_CUDA_CHECK(cudaGetLastError());
-    rc = contract_nt_bf16(a_t, b_t, x_t, B * kC, N, N, N, ld, ld, ld, (long long)N * ld,
-                          (long long)N * ld, (long long)N * ld, st);
+    int rc = trimul_project(z, mask, a_t, b_t, B, N, N, ld, !outgoing, p, st);
     if (rc) return rc;
-    LaunchScope scope(kKidOut, st);
-    trimul_out_kernel<<<grid, 320, OutSmem::kDyn, st>>>(
-        tmZrow, tmX, tmOut, tmW[4], tmW[5], (const __nv_bfloat16*)p->ln_in_w,
-        (const __nv_bfloat16*)p->ln_in_b, (const __nv_bfloat16*)p->ln_out_w,
-        (const __nv_bfloat16*)p->ln_out_b, B, N, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, status);
-    OF3_CUDA_CHECK(cudaGetLastError());
-    return OF3_OK;
+    return trimul_finish(z, out, a_t, b_t, x_t, B, N, N, ld, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, st);
 }
 
 }  // namespace fast

@@ -180,7 +180,7 @@ static int ada_ln(const T* a, const T* s, float* dst, float* sn, float* t1, floa
 template <typename T>
 int attn_pair_bias(const T* a, const T* z, const T* s, const T* mask, T* out, int Ba, int Bz, int N,
                    int c_a, int c_s, int c_z, int H, int d, float inf, int flags,
-                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st) {
+                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st, const float* pair_bias) {
     const long long rows = (long long)Ba * N;
     const long long zrows = (long long)Bz * N * N;
     const int hd = H * d;
@@ -213,9 +213,12 @@ int attn_pair_bias(const T* a, const T* z, const T* s, const T* mask, T* out, in
         TRY((layernorm<T, T>(a, (const T*)p->ln_a_w, (const T*)p->ln_a_b, an, rows, c_a, 1e-5f, rows, 0,
                              c_a, st)));
     }
-    if (c_z == 128 && H == 16 && ((uintptr_t)z & 15) == 0) {
+    if (pair_bias != nullptr) {
+        zb = const_cast<float*>(pair_bias);
+    } else if (c_z == 128 && H == 16 && ((uintptr_t)z & 15) == 0) {
         // one pass over z: LayerNorm statistics and all 16 head projections per pair position
-        TRY(pair_bias_c128_h16<T>(z, (const T*)p->ln_z_w, (const T*)p->ln_z_b, (const T*)p->w_z, zb, Bz, N, st));
+        TRY(pair_bias_c128_h16<T>(z, (const T*)p->ln_z_w, (const T*)p->ln_z_b, (const T*)p->w_z, zb, Bz,
+                                      (long long)N * N, st));
     } else {
         for (long long r0 = 0; r0 < zrows; r0 += panel) {
             const long long nr = zrows - r0 < panel ? zrows - r0 : panel;
@@ -284,7 +287,7 @@ int cond_transition(const T* a, const T* s, const T* mask, T* out, long long row
                                const of3_transition_params*, Arena&, cudaStream_t);                  \
     template int attn_pair_bias<T>(const T*, const T*, const T*, const T*, T*, int, int, int, int,   \
                                    int, int, int, int, float, int, const of3_attn_pair_bias_params*, \
-                                   Arena&, cudaStream_t);                                            \
+                                   Arena&, cudaStream_t, const float*);                                          \
     template int cond_transition<T>(const T*, const T*, const T*, T*, long long, int, int, int, int, \
                                     const of3_cond_transition_params*, Arena&, cudaStream_t);
 INSTANTIATE(float)

@@ -474,9 +474,9 @@ template int finalize<__nv_bfloat16>(const float*, const float*, const __nv_bflo
 
 
 template <typename T>
-int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, float* dst, long long B, int N,
-                       cudaStream_t stream) {
-    const long long nn = (long long)N * N;
+int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, float* dst, long long B,
+                       long long positions_per_sample, cudaStream_t stream) {
+    const long long nn = positions_per_sample;
     const long long rows = B * nn;
     if (rows <= 0) return OF3_OK;
     OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "pair_bias: z must be 16-byte aligned");
@@ -486,9 +486,9 @@ int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, fl
     return OF3_OK;
 }
 template int pair_bias_c128_h16<float>(const float*, const float*, const float*, const float*, float*,
-                                       long long, int, cudaStream_t);
+                                       long long, long long, cudaStream_t);
 template int pair_bias_c128_h16<__nv_bfloat16>(const __nv_bfloat16*, const __nv_bfloat16*, const __nv_bfloat16*,
-                                               const __nv_bfloat16*, float*, long long, int, cudaStream_t);
+                                               const __nv_bfloat16*, float*, long long, long long, cudaStream_t);
 
 int permute_bias(const float* src, float* dst, long long B, int N, int H, cudaStream_t stream) {
     const long long total = B * H * (long long)N * N;

@@ -63,11 +63,12 @@ int finalize(const float* upd, const float* gate, const T* residual, const T* ma
              long long rows, int C, long long inner, long long outer_stride,
              long long inner_stride, cudaStream_t stream);
 // Fused pair-bias projection for 128-channel pair tensors and 16 heads:
-// dst[b][h][q][k] = sum_c LN(z[b, q, k, :])[c] * w[h][c], one thread per pair position, one pass over z.
+// dst[b][h][pos] = sum_c LN(z[b, pos, :])[c] * w[h][c] for pos < positions_per_sample (N*N for a whole
+// tensor, R*N for a row shard), one thread per pair position, one pass over z.
 // gamma/beta may be null. Returns OF3_ERR_SHAPE for other widths (callers fall back to the chain).
 template <typename T>
-int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, float* dst, long long B, int N,
-                       cudaStream_t stream);
+int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, float* dst, long long B,
+                       long long positions_per_sample, cudaStream_t stream);
 // dst[b][h][q][k] = src[b][q][k][h]
 int permute_bias(const float* src, float* dst, long long B, int N, int H, cudaStream_t stream);
 // dense fp32 copy of a storage-type tensor

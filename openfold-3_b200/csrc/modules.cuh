@@ -19,7 +19,8 @@ int transition(const T* x, const T* mask, T* out, long long rows, int c, int n, 
 template <typename T>
 int attn_pair_bias(const T* a, const T* z, const T* s, const T* mask, T* out, int Ba, int Bz, int N,
                    int c_a, int c_s, int c_z, int H, int d, float inf, int flags,
-                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st);
+                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st,
+                   const float* pair_bias = nullptr);  // [Bz][H][N][N] already projected (z unused)
 template <typename T>
 int cond_transition(const T* a, const T* s, const T* mask, T* out, long long rows, int c_a, int c_s,
                     int n, int flags, const of3_cond_transition_params* p, Arena& ws,
@@ -36,6 +37,20 @@ bool triattn_supported(int c_z, int H, int d, int N);
 int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
             float inf, int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st);
 // bf16, c = 128, n = 4
+// phases of the two layers above on R lines of N positions (R == N: whole tensor; R = N / P: a row shard)
+int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* a_t, __nv_bfloat16* b_t,
+                   int B, int R, int N, int ld, bool transposed_walk, const of3_trimul_params* p,
+                   cudaStream_t st);
+int trimul_finish(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat16* a_t,
+                  const __nv_bfloat16* b_t, __nv_bfloat16* x_t, int B, int R, int N, int ld, int add_residual,
+                  const of3_trimul_params* p, cudaStream_t st);
+int triattn_project(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
+                    __nv_bfloat16* tb, int B, int R, int N, int ldn, bool transposed,
+                    const of3_triattn_params* p, cudaStream_t st);
+int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
+                   const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
+                   const __nv_bfloat16* tb, __nv_bfloat16* o, int B, int R, int N, int ldn, float inf,
+                   bool transposed, int add_residual, const of3_triattn_params* p, cudaStream_t st);
 bool transition_supported(int c, int n);
 int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows,
                int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);

@@ -68,6 +68,16 @@ SIGNATURES = {
     "of3_cond_transition_forward": (c_int, [c_void_p] * 4 + [c_longlong, c_int, c_int, c_int, c_int, c_int,
                                             ctypes.POINTER(CondTransitionParams), c_void_p, c_size_t,
                                             c_void_p]),
+    "of3_dap_pitch": (c_int, [c_int, c_int]),
+    "of3_dap_trimul_project": (c_int, [c_void_p] * 4 + [c_int, c_int, ctypes.POINTER(TrimulParams), c_void_p]),
+    "of3_dap_trimul_finish": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, ctypes.POINTER(TrimulParams), c_void_p]),
+    "of3_dap_triattn_project": (c_int, [c_void_p] * 5 + [c_int, c_int, ctypes.POINTER(TriattnParams), c_void_p]),
+    "of3_dap_triattn_finish": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_int,
+                                       ctypes.POINTER(TriattnParams), c_void_p]),
+    "of3_pair_bias_project": (c_int, [c_void_p] * 5 + [c_longlong, c_int, c_int, c_int, c_void_p]),
+    "of3_attn_pair_bias_forward_prebias": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_float, c_int, c_int,
+                                                   ctypes.POINTER(AttnPairBiasParams), c_void_p, c_size_t,
+                                                   c_void_p]),
     "of3_contract_nt_bf16": (c_int, [c_void_p] * 3 + [c_int] * 7 + [c_longlong] * 3 + [c_void_p]),
 }
 

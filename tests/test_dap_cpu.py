@@ -1,0 +1,149 @@
+"""Row-sharded (DAP) orchestration on CPU: two gloo ranks with an oracle compute backend.
+
+The exchange logic of ``openfold3_b200.dap`` (row shards, all-gathers of the channel-major b / pair
+bias, all-to-all transposes for the incoming update and the ending-node attention, the replicated
+single track) is backend independent; here the per-phase compute is the CPU oracle, so the test
+checks that sharding + collectives reproduce the unsharded oracle bit-for-rounding, without a GPU.
+"""
+
+import os
+import socket
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+import torch.nn.functional as F
+
+ROOT = Path(__file__).resolve().parent.parent
+for p in (str(ROOT), str(ROOT / "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+
+class OracleOps:
+    """The phase semantics of dap.CudaOps restated with the CPU oracle (fp32)."""
+
+    def __init__(self, oracle):
+        self.o = oracle
+
+    @staticmethod
+    def _P(mod):
+        return {k: v.detach() for k, v in mod.state_dict().items()}
+
+    @staticmethod
+    def _pad(t, ld):
+        return F.pad(t, (0, ld - t.shape[-1]))
+
+    def trimul_project(self, z_loc, mask_rows, mod):
+        P, o = self._P(mod), self.o
+        N = z_loc.shape[1]
+        zn = o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1])
+        m = mask_rows.unsqueeze(-1)
+        a = m * torch.sigmoid(o._lin(zn, P, "linear_a_g.")) * o._lin(zn, P, "linear_a_p.")
+        b = m * torch.sigmoid(o._lin(zn, P, "linear_b_g.")) * o._lin(zn, P, "linear_b_p.")
+        ld = (N + 7) // 8 * 8
+        return self._pad(a.permute(2, 0, 1), ld).contiguous(), self._pad(b.permute(2, 0, 1), ld).contiguous()
+
+    def trimul_finish(self, z_loc, a_t, b_all, mod):
+        P, o = self._P(mod), self.o
+        N = z_loc.shape[1]
+        x = torch.einsum("cik,cjk->ijc", a_t[:, :, :N], b_all[:, :, :N])
+        x = o._lin(o._ln(x, P, "layer_norm_out.", x.shape[-1]), P, "linear_z.")
+        g = torch.sigmoid(o._lin(o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1]), P, "linear_g."))
+        z_loc += x * g
+
+    def triattn_project(self, z_loc, mod):
+        P, o = self._P(mod), self.o
+        N = z_loc.shape[1]
+        xn = o._ln(z_loc, P, "layer_norm.", z_loc.shape[-1])
+        tb = o._lin(xn, P, "linear_z.").permute(2, 0, 1)
+        return (xn,), self._pad(tb, (N + 63) // 64 * 64).contiguous()
+
+    def triattn_finish(self, z_loc, mask_rows, qkv, tb_all, mod):
+        P, o = self._P(mod), self.o
+        N = z_loc.shape[1]
+        (xn,) = qkv
+        mask_bias = (mod.inf * (mask_rows - 1))[:, None, None, :]
+        tb = tb_all[:, :, :N].unsqueeze(0)
+        mha = {k[len("mha."):]: v for k, v in P.items() if k.startswith("mha.")}
+        z_loc += o.attention(xn, xn, [mask_bias, tb], mha, "", mod.no_heads)
+
+    def transition(self, x_rows, mask_rows, mod):
+        x_rows += self.o.swiglu_transition(x_rows, mask_rows, self._P(mod), "")
+
+    def pair_bias_project(self, z_loc, apb):
+        P, o = self._P(apb), self.o
+        return o._lin(o._ln(z_loc, P, "layer_norm_z.", z_loc.shape[-1]), P, "linear_z.").permute(2, 0, 1).contiguous()
+
+    def single_track(self, s, zb_all, single_mask, block, mask_trans=True):
+        apb, o = block.attn_pair_bias, self.o
+        P = self._P(apb)
+        an = o._ln(s, P, "layer_norm_a.", s.shape[-1])
+        mask_bias = (apb.inf * (single_mask - 1))[None, None, None, :]
+        mha = {k[len("mha."):]: v for k, v in P.items() if k.startswith("mha.")}
+        s += o.attention(an, an, [mask_bias, zb_all.unsqueeze(0)], mha, "", apb.no_heads)
+        s += o.swiglu_transition(s, single_mask[None] if mask_trans else None, self._P(block.single_transition), "")
+
+
+def _free_port():
+    with socket.socket() as sk:
+        sk.bind(("127.0.0.1", 0))
+        return sk.getsockname()[1]
+
+
+def _worker(rank, world, port, n_token, n_blocks, result_file):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import cases
+        from oracle import pairformer_oracle as oracle
+
+        pkg = cases.pkg
+        torch.manual_seed(0)
+        g = torch.Generator().manual_seed(5)
+        s = torch.randn(1, n_token, 384, generator=g)
+        z = torch.randn(1, n_token, n_token, 128, generator=g)
+        sm = cases.rand_mask((1, n_token), g)
+        pm = cases.rand_mask((1, n_token, n_token), g)  # not an outer product, not symmetric
+        P = pkg.weights.pairformer_stack_params(seed=3, no_blocks=n_blocks, final_std=None, **cases.OF3)
+        stack = pkg.PairFormerStack(**cases.OF3, no_blocks=n_blocks, transition_type="swiglu", pair_dropout=0.25,
+                                    fuse_projection_weights=False, blocks_per_ckpt=None, inf=1e9)
+        stack.load_state_dict(P, strict=True)
+        stack.eval()
+        runner = pkg.dap.DapPairFormerStack(stack, world, rank, ops=OracleOps(oracle))
+        with torch.no_grad():
+            s_d, z_d = runner(s, z, sm, pm)
+            s_r, z_r = oracle.pairformer_stack(s, z, sm, pm, P, "", n_blocks, 4, 16)
+        es, ez = cases.rel_err(s_d, s_r), cases.rel_err(z_d, z_r)
+        # every rank must hold the same full result
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (float(es), float(ez), float(z_d.double().sum())))
+        if rank == 0:
+            torch.save(gathered, result_file)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,n_token", [(2, 16), (4, 12)])
+def test_dap_orchestration_matches_unsharded_oracle(tmp_path, world, n_token):
+    result = tmp_path / "res.pt"
+    mp.spawn(_worker, args=(world, _free_port(), n_token, 2, str(result)), nprocs=world, join=True)
+    gathered = torch.load(result)
+    assert len(gathered) == world
+    for es, ez, _ in gathered:
+        assert es < 1e-4 and ez < 1e-4, gathered
+    sums = [g[2] for g in gathered]
+    assert max(sums) - min(sums) < 1e-6 * max(1.0, abs(sums[0]))
+
+
+def test_all_to_all_transpose_single_rank():
+    import cases
+
+    dap = cases.pkg.dap
+    x = torch.randn(6, 6, 3)
+    assert torch.equal(dap.all_to_all_transpose(x, 1), x.transpose(0, 1))
+    y = torch.randn(5, 4, 7)
+    assert torch.equal(dap.all_gather_lines(y, 1), y)

@@ -1,0 +1,108 @@
+"""Row-shard phase kernels on one GPU: the DAP orchestration with the CUDA backend, (a) as a single
+rank and (b) with P virtual ranks whose exchanges are done by local concatenation, both against the
+unsharded drop-in stack (same kernels, whole tensor) and the CPU oracle."""
+
+import pytest
+import torch
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _virtual_pair_block(ops, shards, mask, pb, P):
+    """dap.DapPairFormerStack.pair_block for P shards held on one device."""
+    R = shards[0].shape[0]
+    mrow = [mask[r * R:(r + 1) * R].contiguous() for r in range(P)]
+    mcol = [mask[:, r * R:(r + 1) * R].t().contiguous() for r in range(P)]
+
+    def transpose_all(sh):
+        full = torch.cat(sh, 0).transpose(0, 1).contiguous()
+        return [full[r * R:(r + 1) * R].contiguous() for r in range(P)]
+
+    def gather(parts):
+        return torch.cat(parts, 1).contiguous()
+
+    proj = [ops.trimul_project(shards[r], mrow[r], pb.tri_mul_out) for r in range(P)]
+    b_all = gather([p[1] for p in proj])
+    for r in range(P):
+        ops.trimul_finish(shards[r], proj[r][0], b_all, pb.tri_mul_out)
+    zT = transpose_all(shards)
+    proj = [ops.trimul_project(zT[r], mcol[r], pb.tri_mul_in) for r in range(P)]
+    b_all = gather([p[1] for p in proj])
+    for r in range(P):
+        ops.trimul_finish(shards[r], proj[r][0], b_all, pb.tri_mul_in)
+    proj = [ops.triattn_project(shards[r], pb.tri_att_start) for r in range(P)]
+    tb_all = gather([p[1] for p in proj])
+    for r in range(P):
+        ops.triattn_finish(shards[r], mrow[r], proj[r][0], tb_all, pb.tri_att_start)
+    zT = transpose_all(shards)
+    proj = [ops.triattn_project(zT[r], pb.tri_att_end) for r in range(P)]
+    tb_all = gather([p[1] for p in proj])
+    for r in range(P):
+        ops.triattn_finish(zT[r], mcol[r], proj[r][0], tb_all, pb.tri_att_end)
+        ops.transition(zT[r], mcol[r], pb.pair_transition)
+    return transpose_all(zT)
+
+
+@pytest.mark.parametrize("P,N", [(1, 40), (2, 48), (4, 200), (3, 33)])
+def test_row_shard_kernels_match_whole_tensor(pkg, P, N):
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    g = torch.Generator().manual_seed(N)
+    z = torch.randn(1, N, N, 128, generator=g)
+    s = torch.randn(1, N, 384, generator=g)
+    pm = cases.rand_mask((1, N, N), g)
+    sm = cases.rand_mask((1, N), g)
+    Pw = pkg.weights.pairformer_stack_params(seed=4, no_blocks=1, final_std=None, **cases.OF3)
+    stack = pkg.PairFormerStack(**cases.OF3, no_blocks=1, transition_type="swiglu", pair_dropout=0.25,
+                                fuse_projection_weights=False, blocks_per_ckpt=None, inf=1e9)
+    stack.load_state_dict(Pw, strict=True)
+    stack = stack.to(dev, bf).eval()
+    ops = pkg.dap.CudaOps(dev)
+    zd, sd, pmd, smd = z.to(dev, bf), s.to(dev, bf), pm.to(dev, bf), sm.to(dev, bf)
+    with torch.no_grad():
+        s_ref, z_ref = stack(sd, zd, smd, pmd)
+        R = N // P
+        shards = [zd[0, r * R:(r + 1) * R].contiguous().clone() for r in range(P)]
+        block = stack.blocks[0]
+        shards = _virtual_pair_block(ops, shards, pmd[0], block.pair_stack, P)
+        zb = torch.cat([ops.pair_bias_project(shards[r], block.attn_pair_bias) for r in range(P)], 1).contiguous()
+        s_dap = sd.clone()
+        ops.single_track(s_dap, zb, smd[0], block)
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    z_dap = torch.cat(shards, 0).unsqueeze(0)
+    # same kernels on the same values: only the bf16 rounding of intermediates that are summed in a
+    # different tile order may differ
+    assert cases.rel_err(z_dap.float().cpu(), z_ref.float().cpu()) < 2e-2
+    assert cases.rel_err(s_dap.float().cpu(), s_ref.float().cpu()) < 2e-2
+    # and against the fp32 oracle on the rounded inputs
+    Pq = {k: v.to(bf).float() for k, v in Pw.items()}
+    s_o, z_o = cases.oracle.pairformer_stack(s.to(bf).float(), z.to(bf).float(), sm, pm, Pq, "", 1, 4, 16)
+    assert cases.rel_err(z_dap.float().cpu(), z_o) < 6e-2
+    assert cases.rel_err(s_dap.float().cpu(), s_o) < 6e-2
+
+
+def test_single_rank_dap_runner(pkg):
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    N = 64
+    g = torch.Generator().manual_seed(1)
+    z = torch.randn(1, N, N, 128, generator=g).to(dev, bf)
+    s = torch.randn(1, N, 384, generator=g).to(dev, bf)
+    pm = cases.rand_mask((1, N, N), g).to(dev, bf)
+    sm = cases.rand_mask((1, N), g).to(dev, bf)
+    Pw = pkg.weights.pairformer_stack_params(seed=5, no_blocks=2, **cases.OF3)
+    stack = pkg.PairFormerStack(**cases.OF3, no_blocks=2, transition_type="swiglu", pair_dropout=0.25,
+                                fuse_projection_weights=False, blocks_per_ckpt=None, inf=1e9)
+    stack.load_state_dict(Pw, strict=True)
+    stack = stack.to(dev, bf).eval()
+    runner = pkg.dap.DapPairFormerStack(stack, 1, 0, ops=pkg.dap.CudaOps(dev))
+    with torch.no_grad():
+        s_ref, z_ref = stack(s, z, sm, pm)
+        s_d, z_d = runner(s, z, sm, pm)
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    assert cases.rel_err(z_d.float().cpu(), z_ref.float().cpu()) < 2e-2
+    assert cases.rel_err(s_d.float().cpu(), s_ref.float().cpu()) < 2e-2
