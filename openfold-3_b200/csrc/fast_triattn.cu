@@ -302,29 +302,46 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 // =====================================================================================
 // triattn_core
 // =====================================================================================
-// One CTA = one head, 128 queries and TWO lines of the pair tensor. The pair-bias tile
-// [128 q x 64 k] does not depend on the line, so it is fetched once per key block by TMA and read
-// by both lines' softmax warpgroups from shared memory (conflict-free swizzled rows) instead of
-// every thread gathering its own row from L2.
+// One CTA = one head, 128 queries and FOUR lines of the pair tensor, 32 keys per step:
+//  * the pair-bias tile [128 q x 32 k] does not depend on the line: fetched once per step by TMA and
+//    shared by the four lines' softmax warpgroups;
+//  * sixteen softmax warps (four per SM sub-partition) hide the TMEM / barrier latencies that two
+//    warps per sub-partition could not (the earlier 64-key, 2-line version sat at ~40 % issue use);
+//  * O accumulates in TMEM across all key blocks (tcgen05.mma with accumulate), so the softmax
+//    threads hold no output registers and do no per-block read-modify-write. The running maximum
+//    used for scaling is only raised when the true row maximum exceeds it by more than 8 (2^8 head
+//    room in the exponentials): then, and only then, the thread rescales its O row in TMEM
+//    (tcgen05.ld / st) and its running sum. The result is exact: sum and O always share one scale.
 constexpr int kBQ = 128;      // queries per CTA
-constexpr int kBK = 64;       // keys per block
-constexpr int kMaxKeys = 4096;
-constexpr int kLines = 2;     // lines per CTA
+constexpr int kBK = 32;       // keys per step
+constexpr int kMaxKeys = 2048;   // one CTA keeps a mask-bias row per line in shared memory
+constexpr int kKvStages = 4;     // K / V / bias ring: deep enough to cover the TMA round trip
+constexpr int kLines = 4;     // lines per CTA
+constexpr int kCoreThreads = 32 * (2 + 4 * kLines);
+constexpr float kRescaleThreshold = 8.0f;
+#ifdef OF3_CORE_TIMING
+__device__ long long g_core_dbg[64];
+#define DBG_T(var) const long long var = clock64()
+#define DBG_ADD(slot, a, b) do { if (dbg_on) atomicAdd((unsigned long long*)&g_core_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
+#else
+#define DBG_T(var)
+#define DBG_ADD(slot, a, b)
+#endif
 
 struct CoreSmem {
-    static constexpr uint32_t kQ = 0;                               // lines x 8 KB (64-byte swizzle)
-    static constexpr uint32_t kK = kQ + kLines * 8192;              // lines x 2 stages x 4 KB
-    static constexpr uint32_t kV = kK + kLines * 2 * 4096;          // lines x 2 stages x 4 KB
-    static constexpr uint32_t kTb = kV + kLines * 2 * 4096;         // 2 stages x 16 KB
-    static constexpr uint32_t kP = kTb + 2 * kKBlockBytes;          // lines x 2 x 16 KB
-    static constexpr uint32_t kBars = kP + kLines * 2 * kKBlockBytes;
-    static constexpr uint32_t kFlags = kBars + 256;                 // lines x 64 block flags (bytes)
-    static constexpr uint32_t kMb = kFlags + 128;                   // lines x nkeys_pad floats
+    static constexpr uint32_t kQ = 0;                                // lines x 8 KB
+    static constexpr uint32_t kK = kQ + kLines * 8192;               // lines x stages x 2 KB
+    static constexpr uint32_t kV = kK + kLines * kKvStages * 2048;   // lines x stages x 2 KB
+    static constexpr uint32_t kTb = kV + kLines * kKvStages * 2048;  // stages x 8 KB
+    static constexpr uint32_t kP = kTb + kKvStages * 8192;           // lines x 2 x 8 KB
+    static constexpr uint32_t kBars = kP + kLines * 2 * 8192;
+    static constexpr uint32_t kFlags = kBars + 384;                  // lines x 128 block flags (bytes)
+    static constexpr uint32_t kMb = kFlags + kLines * 128;           // lines x nkeys_pad floats
     static uint32_t dyn_bytes(int nblk) { return kMb + kLines * nblk * kBK * 4 + 1024; }
 };
 
 template <bool kTransposed>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(kCoreThreads, 1)
 triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTb,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
@@ -336,41 +353,42 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     volatile uint8_t* mbflag = gbase + CoreSmem::kFlags;
     const uint32_t bars = sbase + CoreSmem::kBars;
     const uint32_t q_full = bars;
+    constexpr int kB0 = 1 + 2 * kKvStages;
     auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-    auto kv_empty = [&](int s) { return bars + 8u * (3 + s); };
-    auto s_full = [&](int L, int s) { return bars + 8u * (5 + L * 2 + s); };
-    auto s_empty = [&](int L, int s) { return bars + 8u * (9 + L * 2 + s); };
-    auto p_ready = [&](int L, int s) { return bars + 8u * (13 + L * 2 + s); };
-    auto o_full = [&](int L, int s) { return bars + 8u * (17 + L * 2 + s); };
-    auto o_empty = [&](int L, int s) { return bars + 8u * (21 + L * 2 + s); };
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 208);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 216);
+    auto kv_empty = [&](int s) { return bars + 8u * (1 + kKvStages + s); };
+    auto s_full = [&](int L, int s) { return bars + 8u * (kB0 + L * 2 + s); };
+    auto s_empty = [&](int L, int s) { return bars + 8u * (kB0 + 2 * kLines + L * 2 + s); };
+    auto p_ready = [&](int L, int s) { return bars + 8u * (kB0 + 4 * kLines + L * 2 + s); };
+    auto pv_done = [&](int L, int s) { return bars + 8u * (kB0 + 6 * kLines + L * 2 + s); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * (kB0 + 8 * kLines));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * (kB0 + 8 * kLines) + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (N + kBQ - 1) / kBQ;
-    const int pairs_per_b = (R + kLines - 1) / kLines;
+    const int groups_per_b = (R + kLines - 1) / kLines;
     const int qt = blockIdx.x % n_qt;
     const int h = (blockIdx.x / n_qt) % kH;
-    const int lp = blockIdx.x / (n_qt * kH);
-    const int b = lp / pairs_per_b;
-    const int line0 = (lp % pairs_per_b) * kLines;
+    const int lg = blockIdx.x / (n_qt * kH);
+    const int b = lg / groups_per_b;
+    const int line0 = (lg % groups_per_b) * kLines;
     const int q0 = qt * kBQ;
     const int nblk = (N + kBK - 1) / kBK;
     const int nkp = nblk * kBK;
-    // an odd N leaves the last pair with one line: the second group recomputes the first, unsaved
+    // lines past the end of the sample recompute the first line of the group and are not stored
     auto line_of = [&](int L) { return (line0 + L < R) ? line0 + L : line0; };
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kKvStages; ++s) {
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1 + 4 * kLines);  // MMA commit + every softmax warp (bias tile read)
+        }
+        for (int s = 0; s < 2; ++s) {
             for (int L = 0; L < kLines; ++L) {
                 mbar_init(s_full(L, s), 1);
                 mbar_init(s_empty(L, s), 4);
                 mbar_init(p_ready(L, s), 4);
-                mbar_init(o_full(L, s), 1);
-                mbar_init(o_empty(L, s), 4);
+                mbar_init(pv_done(L, s), 1);
             }
         }
         *abort_flag = 0;
@@ -407,11 +425,11 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const float* m = mbs + (idx / nblk) * nkp + (idx % nblk) * kBK;
         bool any = false;
         for (int e = 0; e < kBK; ++e) any |= (m[e] != 0.f);
-        mbflag[(idx / nblk) * 64 + (idx % nblk)] = any ? 1 : 0;
+        mbflag[(idx / nblk) * 128 + (idx % nblk)] = any ? 1 : 0;
     }
     __syncthreads();
     const uint32_t tmem_base = *tmem_ptr;
-    // TMEM columns of line L: L*256 + { S0 [0,64)  S1 [64,128)  O0 [128,160)  O1 [160,192) }
+    // TMEM columns of line L: L*128 + { S0 [0,32)  S1 [32,64)  O [64,96) }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -419,34 +437,48 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             for (int L = 0; L < kLines; ++L)
                 tma_load_3d(sbase + CoreSmem::kQ + L * 8192, &tmQ, q_full, 0, q0,
                             (b * R + line_of(L)) * kH + h);
+#ifdef OF3_CORE_TIMING
+            const bool dbg_on = blockIdx.x == 300;
+#endif
             for (int j = 0; j < nblk; ++j) {
-                const int s = j & 1;
-                if (!mbar_wait(kv_empty(s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                const int s = j % kKvStages;
+                DBG_T(p0);
+                if (!mbar_wait(kv_empty(s), ((j / kKvStages) & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidCore, 1);
                     break;
                 }
-                mbar_arrive_expect_tx(kv_full(s), kLines * 8192 + kKBlockBytes);
+                DBG_T(p1);
+                DBG_ADD(16, p0, p1);
+                mbar_arrive_expect_tx(kv_full(s), kLines * 4096 + 8192);
                 for (int L = 0; L < kLines; ++L) {
                     const int lh = (b * R + line_of(L)) * kH + h;
-                    tma_load_3d(sbase + CoreSmem::kK + (L * 2 + s) * 4096, &tmK, kv_full(s), 0, j * kBK, lh);
-                    tma_load_3d(sbase + CoreSmem::kV + (L * 2 + s) * 4096, &tmV, kv_full(s), j * kBK, 0, lh);
+                    tma_load_3d(sbase + CoreSmem::kK + (L * kKvStages + s) * 2048, &tmK, kv_full(s), 0, j * kBK, lh);
+                    tma_load_3d(sbase + CoreSmem::kV + (L * kKvStages + s) * 2048, &tmV, kv_full(s), j * kBK, 0, lh);
                 }
-                tma_load_3d(sbase + CoreSmem::kTb + s * kKBlockBytes, &tmTb, kv_full(s), j * kBK, q0, b * kH + h);
+                tma_load_3d(sbase + CoreSmem::kTb + s * 8192, &tmTb, kv_full(s), j * kBK, q0, b * kH + h);
+                DBG_T(p2);
+                DBG_ADD(17, p1, p2);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);
-            constexpr uint32_t idesc_o = idesc_bf16_f32(128, kD);
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 32);  // both GEMMs are 128 x 32 x 32
             bool ok = mbar_wait(q_full, 0, abort_flag);
             if (!ok) report_wait_failure(status, abort_flag, kKidCore, 2);
+#ifdef OF3_CORE_TIMING
+            const bool dbg_on = blockIdx.x == 300;
+#endif
             for (int j = 0; j <= nblk && ok; ++j) {
-                if (j < nblk) {  // S_j = Q K_j^T for both lines
+                DBG_T(m0);
+                if (j < nblk) {  // S_j = Q K_j^T
                     const int s = j & 1;
-                    if (!mbar_wait(kv_full(s), (j >> 1) & 1u, abort_flag)) {
+                    const int ks = j % kKvStages;
+                    if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
                         report_wait_failure(status, abort_flag, kKidCore, 3);
                         break;
                     }
+                    DBG_T(m1);
+                    DBG_ADD(18, m0, m1);
                     for (int L = 0; L < kLines && ok; ++L) {
                         if (!mbar_wait(s_empty(L, s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
                             report_wait_failure(status, abort_flag, kKidCore, 4);
@@ -455,34 +487,37 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                         }
                         tc_fence_after_sync();
                         const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ + L * 8192);
-                        const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (L * 2 + s) * 4096);
-                        const uint32_t d = tmem_base + L * 256 + s * kBK;
-                        mma_bf16(d, qdesc, kdesc, idesc_s, 0u);
-                        mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
+                        const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (L * kKvStages + ks) * 2048);
+                        const uint32_t d = tmem_base + L * 128 + s * kBK;
+                        mma_bf16(d, qdesc, kdesc, idesc, 0u);
+                        mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc, 1u);
                         mma_commit(s_full(L, s));
                     }
                 }
-                if (j >= 1 && ok) {  // O_{j-1} = P_{j-1} V_{j-1} for both lines
+                DBG_T(m2);
+                DBG_ADD(19, m0, m2);
+                if (j >= 1 && ok) {  // O += P_{j-1} V_{j-1}
                     const int jj = j - 1;
                     const int s = jj & 1;
+                    const int ks = jj % kKvStages;
                     for (int L = 0; L < kLines && ok; ++L) {
-                        if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag) ||
-                            !mbar_wait(o_empty(L, s), ((jj >> 1) & 1u) ^ 1u, abort_flag)) {
+                        if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag)) {
                             report_wait_failure(status, abort_flag, kKidCore, 5);
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint64_t pdesc = smem_desc_k_sw128(sbase + CoreSmem::kP + (L * 2 + s) * kKBlockBytes);
-                        const uint64_t vdesc = smem_desc_k_sw128(sbase + CoreSmem::kV + (L * 2 + s) * 4096);
-#pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4)
-                            mma_bf16(tmem_base + L * 256 + 128 + s * kD, pdesc + 2u * k4, vdesc + 2u * k4,
-                                     idesc_o, k4 != 0 ? 1u : 0u);
-                        mma_commit(o_full(L, s));
+                        const uint64_t pdesc = smem_desc_k_sw64(sbase + CoreSmem::kP + (L * 2 + s) * 8192);
+                        const uint64_t vdesc = smem_desc_k_sw64(sbase + CoreSmem::kV + (L * kKvStages + ks) * 2048);
+                        const uint32_t d = tmem_base + L * 128 + 64;
+                        mma_bf16(d, pdesc, vdesc, idesc, jj != 0 ? 1u : 0u);
+                        mma_bf16(d, pdesc + 2u, vdesc + 2u, idesc, 1u);
+                        mma_commit(pv_done(L, s));
                     }
-                    if (ok) mma_commit(kv_empty(s));
+                    if (ok) mma_commit(kv_empty(ks));
                 }
+                DBG_T(m3);
+                DBG_ADD(20, m2, m3);
             }
         }
     } else {
@@ -493,55 +528,55 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int qpos = q0 + row;
         const bool line_valid = line0 + L < R;
         const long long bl = (long long)b * R + line_of(L);
-        const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 256;
+        const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 128;
         const float* mbl = mbs + L * nkp;
-        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-        float o[kD];
-#pragma unroll
-        for (int e = 0; e < kD; ++e) o[e] = 0.f;
+        float m_used = 0.f, l = 0.f;
         bool ok = true;
+#ifdef OF3_CORE_TIMING
+        const bool dbg_on = (blockIdx.x == 300) && lane == 0 && (warp == 2 || warp == 17);
+#endif
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
+            const int ks = j % kKvStages;
             const int k0 = j * kBK;
-            if (!mbar_wait(kv_full(s), (j >> 1) & 1u, abort_flag)) {
+            DBG_T(t0);
+            if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
                 ok = false;
                 break;
             }
-            // this row's 64 pair-bias values from the shared tile
-            uint4 tbv[8];
+            uint4 tbv[4];  // this row's 32 pair-bias values from the shared tile
             {
-                const uint32_t tbt = sbase + CoreSmem::kTb + s * kKBlockBytes;
+                const uint32_t tbt = sbase + CoreSmem::kTb + ks * 8192;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) tbv[i] = lds128(chunk_addr(tbt, row, i));
+                for (int i = 0; i < 4; ++i) tbv[i] = lds128(chunk_addr64(tbt, row, i));
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(kv_empty(s));
+            if (lane == 0) mbar_arrive(kv_empty(ks));
+            DBG_T(t1);
             if (!mbar_wait(s_full(L, s), (j >> 1) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 7);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
+            DBG_T(t2);
             float sv[kBK];
             {
-                uint32_t r0[32], r1[32];
+                uint32_t r0[32];
                 tmem_ld32(trow + s * kBK, r0);
-                tmem_ld32(trow + s * kBK + 32, r1);
                 tmem_ld_wait();
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    sv[e] = __uint_as_float(r0[e]);
-                    sv[32 + e] = __uint_as_float(r1[e]);
-                }
+                for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r0[e]);
             }
+            DBG_T(t3);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(s_empty(L, s));
             // (q.k + mask bias) + pair bias: the reference's order, in fp32
-            if (mbflag[L * 64 + j]) {
+            if (mbflag[L * 128 + j]) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) {
+                for (int i = 0; i < 8; ++i) {
                     const float4 mb = *reinterpret_cast<const float4*>(mbl + k0 + i * 4);
                     sv[i * 4] += mb.x;
                     sv[i * 4 + 1] += mb.y;
@@ -549,9 +584,9 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     sv[i * 4 + 3] += mb.w;
                 }
             }
-            float mx = m;
+            float mx = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
+            for (int i = 0; i < 4; ++i) {
                 const uint32_t w[4] = {tbv[i].x, tbv[i].y, tbv[i].z, tbv[i].w};
 #pragma unroll
                 for (int jj = 0; jj < 4; ++jj) {
@@ -561,52 +596,73 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     mx = fmaxf(mx, fmaxf(sv[e], sv[e + 1]));
                 }
             }
-            const float corr = ex2_approx(m - mx);
-            m = mx;
-            float sum = 0.f;
-            uint32_t ppk[32];
+            if (j == 0) {
+                m_used = mx;  // finite: block 0 always holds a key < N, masked keys are -1e9-ish, not -inf
+            } else {
+                const bool need = mx - m_used > kRescaleThreshold;
+                if (__any_sync(0xffffffffu, need)) {
+                    // every P V issued so far must have landed in O before it is rescaled
+                    if (!mbar_wait(pv_done(L, (j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) {
+                        if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 8);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const float f = need ? ex2_approx(m_used - mx) : 1.0f;
+                    uint32_t orow[32];
+                    tmem_ld32(trow + 64, orow);
+                    tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < kBK; e += 2) {
-                const float p0 = ex2_approx(sv[e] - mx);
-                const float p1 = ex2_approx(sv[e + 1] - mx);
-                sum += p0 + p1;
-                ppk[e >> 1] = pack_bf16x2(p0, p1);
+                    for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * f);
+                    tmem_st32(trow + 64, orow);
+                    tmem_st_wait();
+                    if (need) {
+                        l *= f;
+                        m_used = mx;
+                    }
+                }
             }
-            l = fmaf(l, corr, sum);
-            const uint32_t ptile = sbase + CoreSmem::kP + (L * 2 + s) * kKBlockBytes;
+            DBG_T(t4);
+            // the P buffer of this parity was last read by the P V of block j-2
+            if (j >= 2 && !mbar_wait(pv_done(L, s), ((j - 2) >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 9);
+                ok = false;
+                break;
+            }
+            DBG_T(t5);
+            const uint32_t ptile = sbase + CoreSmem::kP + (L * 2 + s) * 8192;
+            float sum = 0.f;
 #pragma unroll
-            for (int ch = 0; ch < 8; ++ch)
-                sts128(chunk_addr(ptile, row, ch),
-                       make_uint4(ppk[ch * 4], ppk[ch * 4 + 1], ppk[ch * 4 + 2], ppk[ch * 4 + 3]));
+            for (int ch = 0; ch < 4; ++ch) {
+                uint32_t pk[4];
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int e = ch * 8 + jj * 2;
+                    const float p0 = ex2_approx(sv[e] - m_used);
+                    const float p1 = ex2_approx(sv[e + 1] - m_used);
+                    sum += p0 + p1;
+                    pk[jj] = pack_bf16x2(p0, p1);
+                }
+                sts128(chunk_addr64(ptile, row, ch), make_uint4(pk[0], pk[1], pk[2], pk[3]));
+            }
+            l += sum;
+            DBG_T(t6);
+            tc_fence_before_sync();
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready(L, s));
-            // fold in the previous block's P V while this block's MMA runs
-            if (j >= 1) {
-                const int ps = (j - 1) & 1;
-                if (!mbar_wait(o_full(L, ps), ((j - 1) >> 1) & 1u, abort_flag)) {
-                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 8);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                uint32_t r[32];
-                tmem_ld32(trow + 128 + ps * kD, r);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(o_empty(L, ps));
-#pragma unroll
-                for (int e = 0; e < kD; ++e) o[e] = fmaf(o[e], corr_prev, __uint_as_float(r[e]));
-            }
-            corr_prev = corr;
+            DBG_T(t7);
+#ifdef OF3_CORE_TIMING
+            { const int o8 = (warp == 2) ? 0 : 8;
+              DBG_ADD(o8 + 0, t0, t1); DBG_ADD(o8 + 1, t1, t2); DBG_ADD(o8 + 2, t2, t3); DBG_ADD(o8 + 3, t3, t4);
+              DBG_ADD(o8 + 4, t4, t5); DBG_ADD(o8 + 5, t5, t6); DBG_ADD(o8 + 6, t6, t7); DBG_ADD(o8 + 7, t0, t7); }
+#endif
         }
         if (ok) {
-            const int ps = (nblk - 1) & 1;
-            if (mbar_wait(o_full(L, ps), ((nblk - 1) >> 1) & 1u, abort_flag)) {
+            if (mbar_wait(pv_done(L, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1u, abort_flag)) {
                 tc_fence_after_sync();
                 uint32_t r[32];
-                tmem_ld32(trow + 128 + ps * kD, r);
+                tmem_ld32(trow + 64, r);
                 tmem_ld_wait();
                 const float inv = 1.0f / l;
                 if (qpos < N && line_valid) {
@@ -615,14 +671,13 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     for (int v4 = 0; v4 < 4; ++v4) {
                         float f[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e)
-                            f[e] = fmaf(o[v4 * 8 + e], corr_prev, __uint_as_float(r[v4 * 8 + e])) * inv;
+                        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v4 * 8 + e]) * inv;
                         dst[v4] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
                                              pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
                     }
                 }
             } else if (lane == 0) {
-                report_wait_failure(status, abort_flag, kKidCore, 9);
+                report_wait_failure(status, abort_flag, kKidCore, 10);
             }
         }
     }
@@ -948,12 +1003,12 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
         uint64_t dimv[3] = {(uint64_t)N, kD, (uint64_t)lines};
         uint64_t strv[2] = {(uint64_t)ldn * 2, (uint64_t)kD * ldn * 2};
         uint32_t boxv[3] = {kBK, kD, 1};
-        if ((rc = make_tmap_bf16(&tmV, vt, 3, dimv, strv, boxv, 1))) return rc;
-        // pair bias [b*H + h][q][k] for ALL N query positions, row pitch ldn: tile = 128 queries x 64 keys
+        if ((rc = make_tmap_bf16(&tmV, vt, 3, dimv, strv, boxv, 2))) return rc;
+        // pair bias [b*H + h][q][k] for ALL N query positions, row pitch ldn: tile = 128 queries x 32 keys
         uint64_t dimt[3] = {(uint64_t)ldn, (uint64_t)N, (uint64_t)B * kH};
         uint64_t strt[2] = {(uint64_t)ldn * 2, (uint64_t)N * ldn * 2};
         uint32_t boxt[3] = {kBK, kBQ, 1};
-        if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 1))) return rc;
+        if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 2))) return rc;
     }
     if ((rc = set_attrs<kT>())) return rc;
     int* status = device_status_ptr();
@@ -961,7 +1016,7 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
     OF3_REQUIRE(ctas < (1LL << 31), OF3_ERR_SHAPE, "triattn: too many attention tiles");
     {
         LaunchScope scope(kKidCore, st);
-        triattn_core_kernel<kT><<<(unsigned)ctas, 320, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
+        triattn_core_kernel<kT><<<(unsigned)ctas, kCoreThreads, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
             tmQ, tmK, tmV, tmTb, mask, o, B, R, N, inf, status);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
@@ -976,6 +1031,13 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
 }
 
 }  // namespace
+
+#ifdef OF3_CORE_TIMING
+extern "C" int of3_core_dbg(long long* out, int reset) {
+    if (reset) { long long z[64] = {0}; return (int)cudaMemcpyToSymbol(g_core_dbg, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(out, g_core_dbg, 64 * sizeof(long long));
+}
+#endif
 
 bool triattn_supported(int c_z, int H, int d, int N) {
     return c_z == 128 && H == kH && d == kD && N <= kMaxKeys;

@@ -38,6 +38,10 @@ __device__ __forceinline__ void group_sync(int id, int nthreads) {
 __device__ __forceinline__ uint32_t chunk_addr(uint32_t tile, int row, int chunk) {
     return tile + (uint32_t)((chunk >> 3) * kKBlockBytes + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
 }
+// Same for a tile with 64-byte rows (32 bf16) in the 64-byte swizzle: chunk 0..3, XORed with (row/2)%4.
+__device__ __forceinline__ uint32_t chunk_addr64(uint32_t tile, int row, int chunk) {
+    return tile + (uint32_t)(row * 64 + ((chunk ^ ((row >> 1) & 3)) << 4));
+}
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
     uint4 v;
     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
