@@ -219,9 +219,11 @@ int of3_cond_transition_forward(const void* a, const void* s, const void* mask, 
  * finish; the exchange (all-gather / all-to-all) is the caller's, between the two calls.
  * Pitches: ld = of3_dap_pitch(N, 8) for a_t / b_t / x, ldn = of3_dap_pitch(N, 64) for v^T and bias.
  *   z_rows, out_rows [R, N, 128]; mask_rows [R, N] or NULL; a_t, x_scratch [128, R, ld];
- *   b_all [128, N, ld]; q, k [R, 4, N, 32]; vt [R, 4, 32, ldn]; bias_rows [4, R, ldn];
+ *   b_all [128, N, ld]; q, k, vt: opaque images of of3_dap_triattn_image_elems(R, N) elements each
+ *   (pre-swizzled operand tiles); bias_rows [4, R, ldn];
  *   bias_all [4, N, ldn]; o_scratch [R, N, 128]. out_rows may alias z_rows. */
 int of3_dap_pitch(int N, int multiple);
+long long of3_dap_triattn_image_elems(int R, int N);
 int of3_dap_trimul_project(const void* z_rows, const void* mask_rows, void* a_t, void* b_t, int R, int N,
                            const of3_trimul_params* p, void* stream);
 int of3_dap_trimul_finish(const void* z_rows, void* out_rows, const void* a_t, const void* b_all, void* x_scratch,

@@ -18,6 +18,8 @@ extern "C" {
 
 int of3_dap_pitch(int N, int multiple) { return (int)align_up((size_t)N, (size_t)multiple); }
 
+long long of3_dap_triattn_image_elems(int R, int N) { return (long long)fast::triattn_image_elems(1, R, N); }
+
 int of3_dap_trimul_project(const void* z_rows, const void* mask_rows, void* a_t, void* b_t, int R, int N,
                            const of3_trimul_params* p, void* stream) {
     OF3_REQUIRE(z_rows && a_t && b_t && p, OF3_ERR_ARG, "dap_trimul_project: null pointer argument");

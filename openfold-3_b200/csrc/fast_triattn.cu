@@ -81,7 +81,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
                     const __nv_bfloat16* __restrict__ w_bias, __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ vt_out,
-                    __nv_bfloat16* __restrict__ tb_out, int B, int R, int N, int ldn, int* status) {
+                    __nv_bfloat16* __restrict__ tb_out, int B, int R, int N, int ldn, int npad, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -232,9 +232,17 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
         for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
             const LineTile tc = line_tile(t, R, tiles_per_line);
             const int pos = tc.t0 + row;
-            const bool valid = pos < N;
-            const long long lineh = ((long long)tc.b * R + tc.line) * kH;  // (line, head 0)
-            // ---- slot 0: q (columns 0..127) and k (128..255), [line][head][pos][32]
+            const bool valid = pos < npad;   // positions in [N, npad) are written as zeros (key padding)
+            const bool live = pos < N;
+            // Images are tile-major with the line inside the tile index, so the tiles of four consecutive
+            // lines (one attention CTA) are contiguous and arrive with ONE bulk copy:
+            //   q [b][h][query tile of 128][line < rpad][128][32]
+            //   k [b][h][key block of 32 ][line < rpad][32][32]      v likewise with [32 d][32 keys]
+            const int rpad = (R + 3) & ~3;
+            const int nkb = npad >> 5;
+            // ---- slot 0: q (columns 0..127) and k (128..255), [line][head][pos][32], stored as the
+            // 64-byte-swizzled shared-memory image (16-byte chunk c of row pos at chunk c ^ ((pos/2)%4)),
+            // so that the attention kernel fetches whole tiles with one untiled bulk copy each
             if (!mbar_wait(slot_full(0), it & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 6);
                 break;
@@ -250,16 +258,21 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     uint32_t r[32];
                     tmem_ld32(taddr + qk * 128 + h * 32, r);
                     tmem_ld_wait();
-                    if (valid) {
-                        uint4* dst = reinterpret_cast<uint4*>(base + ((lineh + h) * N + pos) * kD);
+                    if (valid || qk == 0) {
+                        const long long bh = (long long)tc.b * kH + h;
+                        const long long rowidx = qk == 0
+                            ? ((bh * tiles_per_line + (pos >> 7)) * rpad + tc.line) * 128 + (pos & 127)
+                            : ((bh * nkb + (pos >> 5)) * rpad + tc.line) * 32 + (pos & 31);
+                        uint4* dst = reinterpret_cast<uint4*>(base + rowidx * kD);
+                        const float sl = live ? sc : 0.f;
 #pragma unroll
                         for (int v4 = 0; v4 < 4; ++v4) {
                             uint4 v;
-                            v.x = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 0]), sc * __uint_as_float(r[v4 * 8 + 1]));
-                            v.y = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 2]), sc * __uint_as_float(r[v4 * 8 + 3]));
-                            v.z = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 4]), sc * __uint_as_float(r[v4 * 8 + 5]));
-                            v.w = pack_bf16x2(sc * __uint_as_float(r[v4 * 8 + 6]), sc * __uint_as_float(r[v4 * 8 + 7]));
-                            dst[v4] = v;
+                            v.x = pack_bf16x2(sl * __uint_as_float(r[v4 * 8 + 0]), sl * __uint_as_float(r[v4 * 8 + 1]));
+                            v.y = pack_bf16x2(sl * __uint_as_float(r[v4 * 8 + 2]), sl * __uint_as_float(r[v4 * 8 + 3]));
+                            v.z = pack_bf16x2(sl * __uint_as_float(r[v4 * 8 + 4]), sl * __uint_as_float(r[v4 * 8 + 5]));
+                            v.w = pack_bf16x2(sl * __uint_as_float(r[v4 * 8 + 6]), sl * __uint_as_float(r[v4 * 8 + 7]));
+                            dst[v4 ^ ((pos >> 1) & 3)] = v;
                         }
                     }
                 }
@@ -267,7 +280,8 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(0));
-            // ---- slot 1: v, stored transposed [line][head][32][pos]
+            // ---- slot 1: v, stored as tiles [line][head][key block of 32][32 d][32 keys], each tile the
+            // 64-byte-swizzled image of the K-major B operand of P V (row d, chunk (key%32)/8)
             if (!mbar_wait(slot_full(1), it & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 7);
                 ok = false;
@@ -280,9 +294,13 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                 tmem_ld32(taddr + 256 + h * 32, r);
                 tmem_ld_wait();
                 if (valid) {
-                    __nv_bfloat16* dst = vt_out + ((lineh + h) * kD) * ldn + pos;
+                    __nv_bfloat16* tile =
+                        vt_out + (((((long long)tc.b * kH + h) * nkb + (pos >> 5)) * rpad + tc.line) << 10);
+                    const int c = (pos & 31) >> 3, w = pos & 7;
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) dst[(long long)e * ldn] = __float2bfloat16_rn(__uint_as_float(r[e]));
+                    for (int e = 0; e < 32; ++e)
+                        tile[e * 32 + (((c ^ ((e >> 1) & 3)) << 3) | w)] =
+                            __float2bfloat16_rn(live ? __uint_as_float(r[e]) : 0.f);
                 }
             }
             tc_fence_before_sync();
@@ -315,9 +333,9 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 32;       // keys per step
 constexpr int kMaxKeys = 2048;   // one CTA keeps a mask-bias row per line in shared memory
-constexpr int kKvStages = 4;     // K / V / bias ring: deep enough to cover the TMA round trip
+constexpr int kKvStages = 4;     // K / V ring (one untiled bulk copy per tile): covers the load round trip
 constexpr int kLines = 4;     // lines per CTA
-constexpr int kCoreThreads = 32 * (2 + 4 * kLines);
+constexpr int kCoreThreads = 32 * (1 + kLines + 4 * kLines);  // producer, one MMA warp per line, softmax
 constexpr float kRescaleThreshold = 8.0f;
 #ifdef OF3_CORE_TIMING
 __device__ long long g_core_dbg[64];
@@ -332,8 +350,8 @@ struct CoreSmem {
     static constexpr uint32_t kQ = 0;                                // lines x 8 KB
     static constexpr uint32_t kK = kQ + kLines * 8192;               // lines x stages x 2 KB
     static constexpr uint32_t kV = kK + kLines * kKvStages * 2048;   // lines x stages x 2 KB
-    static constexpr uint32_t kTb = kV + kLines * kKvStages * 2048;  // stages x 8 KB
-    static constexpr uint32_t kP = kTb + kKvStages * 8192;           // lines x 2 x 8 KB
+    static constexpr uint32_t kTb = kV + kLines * kKvStages * 2048;  // 2 x 16 KB: bias tiles [128 q x 64 k]
+    static constexpr uint32_t kP = kTb + 2 * kKBlockBytes;           // lines x 2 x 8 KB
     static constexpr uint32_t kBars = kP + kLines * 2 * 8192;
     static constexpr uint32_t kFlags = kBars + 384;                  // lines x 128 block flags (bytes)
     static constexpr uint32_t kMb = kFlags + kLines * 128;           // lines x nkeys_pad floats
@@ -342,10 +360,10 @@ struct CoreSmem {
 
 template <bool kTransposed>
 __global__ void __launch_bounds__(kCoreThreads, 1)
-triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmTb,
+triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16* __restrict__ k_img,
+                    const __nv_bfloat16* __restrict__ v_img, const __grid_constant__ CUtensorMap tmTb,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
-                    int R, int N, float inf, int* status) {
+                    int R, int N, int npad, float inf, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -353,9 +371,11 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     volatile uint8_t* mbflag = gbase + CoreSmem::kFlags;
     const uint32_t bars = sbase + CoreSmem::kBars;
     const uint32_t q_full = bars;
-    constexpr int kB0 = 1 + 2 * kKvStages;
+    constexpr int kB0 = 1 + 2 * kKvStages + 4;
     auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bars + 8u * (1 + kKvStages + s); };
+    auto tb_full = [&](int s) { return bars + 8u * (1 + 2 * kKvStages + s); };
+    auto tb_empty = [&](int s) { return bars + 8u * (3 + 2 * kKvStages + s); };
     auto s_full = [&](int L, int s) { return bars + 8u * (kB0 + L * 2 + s); };
     auto s_empty = [&](int L, int s) { return bars + 8u * (kB0 + 2 * kLines + L * 2 + s); };
     auto p_ready = [&](int L, int s) { return bars + 8u * (kB0 + 4 * kLines + L * 2 + s); };
@@ -381,9 +401,11 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) {
             mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), 1 + 4 * kLines);  // MMA commit + every softmax warp (bias tile read)
+            mbar_init(kv_empty(s), kLines);  // each line's commit after the P V that read the stage
         }
         for (int s = 0; s < 2; ++s) {
+            mbar_init(tb_full(s), 1);
+            mbar_init(tb_empty(s), 4 * kLines);  // every softmax warp has read its rows of the bias tile
             for (int L = 0; L < kLines; ++L) {
                 mbar_init(s_full(L, s), 1);
                 mbar_init(s_empty(L, s), 4);
@@ -393,9 +415,6 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         *abort_flag = 0;
         mbar_fence_init();
-        prefetch_tmap(&tmQ);
-        prefetch_tmap(&tmK);
-        prefetch_tmap(&tmV);
         prefetch_tmap(&tmTb);
     }
     // additive key mask of each line, pre-scaled for exp2: inf * (mask - 1) * log2(e); -inf beyond N
@@ -433,14 +452,25 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (warp == 0) {
         if (lane == 0) {
+            const int nkb = npad / kBK;
+            const int rpad = (R + 3) & ~3;
+            const long long bh = (long long)b * kH + h;
             mbar_arrive_expect_tx(q_full, kLines * kBQ * 64);
-            for (int L = 0; L < kLines; ++L)
-                tma_load_3d(sbase + CoreSmem::kQ + L * 8192, &tmQ, q_full, 0, q0,
-                            (b * R + line_of(L)) * kH + h);
+            bulk_load(sbase + CoreSmem::kQ, q_img + (((bh * n_qt + qt) * rpad + line0) * kBQ) * kD, kLines * kBQ * 64,
+                      q_full);
 #ifdef OF3_CORE_TIMING
             const bool dbg_on = blockIdx.x == 300;
 #endif
             for (int j = 0; j < nblk; ++j) {
+                if ((j & 1) == 0) {  // pair-bias tile for the key blocks j and j+1 (64 keys), shared by all lines
+                    const int t = j >> 1, ts = t & 1;
+                    if (!mbar_wait(tb_empty(ts), ((t >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 11);
+                        break;
+                    }
+                    mbar_arrive_expect_tx(tb_full(ts), kKBlockBytes);
+                    tma_load_3d(sbase + CoreSmem::kTb + ts * kKBlockBytes, &tmTb, tb_full(ts), t * 64, q0, b * kH + h);
+                }
                 const int s = j % kKvStages;
                 DBG_T(p0);
                 if (!mbar_wait(kv_empty(s), ((j / kKvStages) & 1u) ^ 1u, abort_flag)) {
@@ -449,24 +479,27 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 }
                 DBG_T(p1);
                 DBG_ADD(16, p0, p1);
-                mbar_arrive_expect_tx(kv_full(s), kLines * 4096 + 8192);
-                for (int L = 0; L < kLines; ++L) {
-                    const int lh = (b * R + line_of(L)) * kH + h;
-                    tma_load_3d(sbase + CoreSmem::kK + (L * kKvStages + s) * 2048, &tmK, kv_full(s), 0, j * kBK, lh);
-                    tma_load_3d(sbase + CoreSmem::kV + (L * kKvStages + s) * 2048, &tmV, kv_full(s), j * kBK, 0, lh);
-                }
-                tma_load_3d(sbase + CoreSmem::kTb + s * 8192, &tmTb, kv_full(s), j * kBK, q0, b * kH + h);
+                mbar_arrive_expect_tx(kv_full(s), kLines * 4096);
+                const long long tile0 = ((bh * nkb + j) * rpad + line0) << 10;  // first of the 4 lines' tiles
+                bulk_load(sbase + CoreSmem::kK + s * kLines * 2048, k_img + tile0, kLines * 2048, kv_full(s));
+                bulk_load(sbase + CoreSmem::kV + s * kLines * 2048, v_img + tile0, kLines * 2048, kv_full(s));
                 DBG_T(p2);
                 DBG_ADD(17, p1, p2);
             }
         }
-    } else if (warp == 1) {
+    } else if (warp <= kLines) {
+        // ---------------------------------------------------------------- one MMA-issuing warp per line:
+        // a single issuing thread for all lines spent ~3400 cycles per step on its 16 MMAs, 8 commits and
+        // 9 barrier waits and was the critical path; per line it is a quarter of that
         if (lane == 0) {
+            const int L = warp - 1;
             constexpr uint32_t idesc = idesc_bf16_f32(128, 32);  // both GEMMs are 128 x 32 x 32
             bool ok = mbar_wait(q_full, 0, abort_flag);
             if (!ok) report_wait_failure(status, abort_flag, kKidCore, 2);
+            const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ + L * 8192);
+            const uint32_t d_o = tmem_base + L * 128 + 64;
 #ifdef OF3_CORE_TIMING
-            const bool dbg_on = blockIdx.x == 300;
+            const bool dbg_on = blockIdx.x == 300 && L == 0;
 #endif
             for (int j = 0; j <= nblk && ok; ++j) {
                 DBG_T(m0);
@@ -479,42 +512,34 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     }
                     DBG_T(m1);
                     DBG_ADD(18, m0, m1);
-                    for (int L = 0; L < kLines && ok; ++L) {
-                        if (!mbar_wait(s_empty(L, s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
-                            report_wait_failure(status, abort_flag, kKidCore, 4);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ + L * 8192);
-                        const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (L * kKvStages + ks) * 2048);
-                        const uint32_t d = tmem_base + L * 128 + s * kBK;
-                        mma_bf16(d, qdesc, kdesc, idesc, 0u);
-                        mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc, 1u);
-                        mma_commit(s_full(L, s));
+                    if (!mbar_wait(s_empty(L, s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 4);
+                        break;
                     }
+                    tc_fence_after_sync();
+                    const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (ks * kLines + L) * 2048);
+                    const uint32_t d = tmem_base + L * 128 + s * kBK;
+                    mma_bf16(d, qdesc, kdesc, idesc, 0u);
+                    mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc, 1u);
+                    mma_commit(s_full(L, s));
                 }
                 DBG_T(m2);
                 DBG_ADD(19, m0, m2);
-                if (j >= 1 && ok) {  // O += P_{j-1} V_{j-1}
+                if (j >= 1) {  // O += P_{j-1} V_{j-1}
                     const int jj = j - 1;
                     const int s = jj & 1;
                     const int ks = jj % kKvStages;
-                    for (int L = 0; L < kLines && ok; ++L) {
-                        if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag)) {
-                            report_wait_failure(status, abort_flag, kKidCore, 5);
-                            ok = false;
-                            break;
-                        }
-                        tc_fence_after_sync();
-                        const uint64_t pdesc = smem_desc_k_sw64(sbase + CoreSmem::kP + (L * 2 + s) * 8192);
-                        const uint64_t vdesc = smem_desc_k_sw64(sbase + CoreSmem::kV + (L * kKvStages + ks) * 2048);
-                        const uint32_t d = tmem_base + L * 128 + 64;
-                        mma_bf16(d, pdesc, vdesc, idesc, jj != 0 ? 1u : 0u);
-                        mma_bf16(d, pdesc + 2u, vdesc + 2u, idesc, 1u);
-                        mma_commit(pv_done(L, s));
+                    if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 5);
+                        break;
                     }
-                    if (ok) mma_commit(kv_empty(ks));
+                    tc_fence_after_sync();
+                    const uint64_t pdesc = smem_desc_k_sw64(sbase + CoreSmem::kP + (L * 2 + s) * 8192);
+                    const uint64_t vdesc = smem_desc_k_sw64(sbase + CoreSmem::kV + (ks * kLines + L) * 2048);
+                    mma_bf16(d_o, pdesc, vdesc, idesc, jj != 0 ? 1u : 0u);
+                    mma_bf16(d_o, pdesc + 2u, vdesc + 2u, idesc, 1u);
+                    mma_commit(pv_done(L, s));
+                    mma_commit(kv_empty(ks));
                 }
                 DBG_T(m3);
                 DBG_ADD(20, m2, m3);
@@ -522,7 +547,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
     } else {
         // ---------------------------------------------------------------- softmax warpgroups
-        const int L = (warp - 2) >> 2;
+        const int L = (warp - 1 - kLines) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const int qpos = q0 + row;
@@ -533,26 +558,26 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         float m_used = 0.f, l = 0.f;
         bool ok = true;
 #ifdef OF3_CORE_TIMING
-        const bool dbg_on = (blockIdx.x == 300) && lane == 0 && (warp == 2 || warp == 17);
+        const bool dbg_on = (blockIdx.x == 300) && lane == 0 && (warp == 1 + kLines || warp == 4 * kLines + kLines);
 #endif
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
-            const int ks = j % kKvStages;
             const int k0 = j * kBK;
             DBG_T(t0);
-            if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
+            const int tbs = (j >> 1) & 1;
+            if (!mbar_wait(tb_full(tbs), (j >> 2) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
                 ok = false;
                 break;
             }
-            uint4 tbv[4];  // this row's 32 pair-bias values from the shared tile
+            uint4 tbv[4];  // this row's 32 pair-bias values: half of its 128-byte row of the shared tile
             {
-                const uint32_t tbt = sbase + CoreSmem::kTb + ks * 8192;
+                const uint32_t tbt = sbase + CoreSmem::kTb + tbs * kKBlockBytes;
 #pragma unroll
-                for (int i = 0; i < 4; ++i) tbv[i] = lds128(chunk_addr64(tbt, row, i));
+                for (int i = 0; i < 4; ++i) tbv[i] = lds128(chunk_addr(tbt, row, (j & 1) * 4 + i));
             }
             __syncwarp();
-            if (lane == 0) mbar_arrive(kv_empty(ks));
+            if ((j & 1) && lane == 0) mbar_arrive(tb_empty(tbs));
             DBG_T(t1);
             if (!mbar_wait(s_full(L, s), (j >> 1) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 7);
@@ -653,7 +678,7 @@ triattn_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (lane == 0) mbar_arrive(p_ready(L, s));
             DBG_T(t7);
 #ifdef OF3_CORE_TIMING
-            { const int o8 = (warp == 2) ? 0 : 8;
+            { const int o8 = (warp == 1 + kLines) ? 0 : 8;
               DBG_ADD(o8 + 0, t0, t1); DBG_ADD(o8 + 1, t1, t2); DBG_ADD(o8 + 2, t2, t3); DBG_ADD(o8 + 3, t3, t4);
               DBG_ADD(o8 + 4, t4, t5); DBG_ADD(o8 + 5, t5, t6); DBG_ADD(o8 + 6, t6, t7); DBG_ADD(o8 + 7, t0, t7); }
 #endif
@@ -976,7 +1001,7 @@ int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __n
     LaunchScope scope(kKidProj, st);
     triattn_proj_kernel<kT><<<grid, 320, ProjSmem::kDyn, st>>>(
         tmZ, tmW[0], tmW[1], tmW[2], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
-        (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, R, N, ldn, device_status_ptr());
+        (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, R, N, ldn, (int)align_up(N, kBK), device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
@@ -986,29 +1011,17 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
                 const __nv_bfloat16* k, const __nv_bfloat16* vt, const __nv_bfloat16* tb, __nv_bfloat16* o, int B,
                 int R, int N, int ldn, float inf, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
-    CUtensorMap tmZ, tmOut, tmO, tmWg, tmWo, tmQ, tmK, tmV, tmTb;
+    CUtensorMap tmZ, tmOut, tmO, tmWg, tmWo, tmTb;
     if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
     if ((rc = z_tmap(&tmOut, out, B, R, N, kT))) return rc;
     if ((rc = z_tmap(&tmO, o, B, R, N, false))) return rc;  // o is [line][pos][128] in view order
     if ((rc = weight_tmap128(&tmWg, p->w_g))) return rc;
     if ((rc = weight_tmap128(&tmWo, p->w_o))) return rc;
-    const long long lines = (long long)B * R * kH;
-    {
-        uint64_t dims[3] = {kD, (uint64_t)N, (uint64_t)lines};
-        uint64_t str[2] = {kD * 2, (uint64_t)N * kD * 2};
-        uint32_t boxq[3] = {kD, kBQ, 1};
-        uint32_t boxk[3] = {kD, kBK, 1};
-        if ((rc = make_tmap_bf16(&tmQ, q, 3, dims, str, boxq, 2))) return rc;
-        if ((rc = make_tmap_bf16(&tmK, k, 3, dims, str, boxk, 2))) return rc;
-        uint64_t dimv[3] = {(uint64_t)N, kD, (uint64_t)lines};
-        uint64_t strv[2] = {(uint64_t)ldn * 2, (uint64_t)kD * ldn * 2};
-        uint32_t boxv[3] = {kBK, kD, 1};
-        if ((rc = make_tmap_bf16(&tmV, vt, 3, dimv, strv, boxv, 2))) return rc;
-        // pair bias [b*H + h][q][k] for ALL N query positions, row pitch ldn: tile = 128 queries x 32 keys
+    {   // pair bias [b*H + h][q][k] for ALL N query positions, row pitch ldn: tile = 128 queries x 64 keys
         uint64_t dimt[3] = {(uint64_t)ldn, (uint64_t)N, (uint64_t)B * kH};
         uint64_t strt[2] = {(uint64_t)ldn * 2, (uint64_t)N * ldn * 2};
-        uint32_t boxt[3] = {kBK, kBQ, 1};
-        if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 2))) return rc;
+        uint32_t boxt[3] = {64, kBQ, 1};
+        if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 1))) return rc;
     }
     if ((rc = set_attrs<kT>())) return rc;
     int* status = device_status_ptr();
@@ -1017,7 +1030,7 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
     {
         LaunchScope scope(kKidCore, st);
         triattn_core_kernel<kT><<<(unsigned)ctas, kCoreThreads, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
-            tmQ, tmK, tmV, tmTb, mask, o, B, R, N, inf, status);
+            q, k, vt, tmTb, mask, o, B, R, N, (int)align_up(N, kBK), inf, status);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     const long long tiles = (long long)B * R * ceil_div(N, kRows);
@@ -1041,6 +1054,12 @@ extern "C" int of3_core_dbg(long long* out, int reset) {
 
 bool triattn_supported(int c_z, int H, int d, int N) {
     return c_z == 128 && H == kH && d == kD && N <= kMaxKeys;
+}
+
+// Elements of each of the q / k / v image buffers for B samples of R lines and N positions: 4 heads x
+// (query tiles of 128) x (R rounded up to 4 lines) x 128 x 32; the k / v images need no more than that.
+size_t triattn_image_elems(int B, int R, int N) {
+    return (size_t)B * kH * ceil_div(N, kBQ) * align_up(R, kLines) * kBQ * kD;
 }
 
 // q, k [line][head][pos][32], v transposed, and this shard's rows of the pair bias
@@ -1072,9 +1091,10 @@ int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* ou
             float inf, int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st) {
     const int ldn = (int)align_up(N, 64);
     const size_t plane = (size_t)B * N * N * kC * sizeof(__nv_bfloat16);
-    __nv_bfloat16* q = (__nv_bfloat16*)ws.take(plane);
-    __nv_bfloat16* k = (__nv_bfloat16*)ws.take(plane);
-    __nv_bfloat16* vt = (__nv_bfloat16*)ws.take((size_t)B * N * kC * ldn * sizeof(__nv_bfloat16));
+    const size_t img = triattn_image_elems(B, N, N) * sizeof(__nv_bfloat16);
+    __nv_bfloat16* q = (__nv_bfloat16*)ws.take(img);
+    __nv_bfloat16* k = (__nv_bfloat16*)ws.take(img);
+    __nv_bfloat16* vt = (__nv_bfloat16*)ws.take(img);
     __nv_bfloat16* o = (__nv_bfloat16*)ws.take(plane);
     __nv_bfloat16* tb = (__nv_bfloat16*)ws.take((size_t)B * kH * N * ldn * sizeof(__nv_bfloat16) + 256);
     if (!ws.base) return OF3_OK;

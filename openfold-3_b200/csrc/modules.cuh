@@ -44,6 +44,7 @@ int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
 int trimul_finish(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat16* a_t,
                   const __nv_bfloat16* b_t, __nv_bfloat16* x_t, int B, int R, int N, int ld, int add_residual,
                   const of3_trimul_params* p, cudaStream_t st);
+size_t triattn_image_elems(int B, int R, int N);
 int triattn_project(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
                     __nv_bfloat16* tb, int B, int R, int N, int ldn, bool transposed,
                     const of3_triattn_params* p, cudaStream_t st);

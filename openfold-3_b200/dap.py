@@ -89,9 +89,10 @@ class CudaOps:
         R, N, _ = z_loc.shape
         ldn = _pitch(N, 64)
         dt, dev = z_loc.dtype, z_loc.device
-        q = torch.empty((R, 4, N, 32), dtype=dt, device=dev)
-        k = torch.empty((R, 4, N, 32), dtype=dt, device=dev)
-        vt = torch.empty((R, 4, 32, ldn), dtype=dt, device=dev)
+        img = int(self.l.of3_dap_triattn_image_elems(R, N))  # opaque pre-swizzled operand tiles
+        q = torch.empty(img, dtype=dt, device=dev)
+        k = torch.empty(img, dtype=dt, device=dev)
+        vt = torch.empty(img, dtype=dt, device=dev)
         tb = torch.empty((4, R, ldn), dtype=dt, device=dev)
         p = lib.TriattnParams(*[t.data_ptr() for t in mod._params(dt, dev)])
         lib._check(self.l.of3_dap_triattn_project(z_loc.data_ptr(), q.data_ptr(), k.data_ptr(), vt.data_ptr(),

@@ -69,6 +69,7 @@ SIGNATURES = {
                                             ctypes.POINTER(CondTransitionParams), c_void_p, c_size_t,
                                             c_void_p]),
     "of3_dap_pitch": (c_int, [c_int, c_int]),
+    "of3_dap_triattn_image_elems": (c_longlong, [c_int, c_int]),
     "of3_dap_trimul_project": (c_int, [c_void_p] * 4 + [c_int, c_int, ctypes.POINTER(TrimulParams), c_void_p]),
     "of3_dap_trimul_finish": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, ctypes.POINTER(TrimulParams), c_void_p]),
     "of3_dap_triattn_project": (c_int, [c_void_p] * 5 + [c_int, c_int, ctypes.POINTER(TriattnParams), c_void_p]),
