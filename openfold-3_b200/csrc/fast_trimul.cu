@@ -23,6 +23,14 @@ namespace {
 using namespace umma;
 using namespace rowtile;
 
+#ifdef OF3_CORE_TIMING
+__device__ long long g_out_dbg[16];
+#define ODBG_T(var) const long long var = clock64()
+#define ODBG_ADD(slot, a, b) do { if (odbg) atomicAdd((unsigned long long*)&g_out_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
+#else
+#define ODBG_T(var)
+#define ODBG_ADD(slot, a, b)
+#endif
 constexpr int kKidIn = 2;
 constexpr int kKidOut = 3;
 
@@ -361,13 +369,18 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
         const int gtid = (warp - 2 - g * 4) * 32 + lane;  // 0..127 inside the group
         const uint32_t ztile = sbase + OutSmem::kZ + g * kTileBytes;
         const uint32_t xtile = sbase + OutSmem::kX + g * kTileBytes;
+#ifdef OF3_CORE_TIMING
+        const bool odbg = blockIdx.x == 40 && gtid == 0 && g == 0;
+#endif
         for (long long lt = g; lt < my_tiles; lt += 2) {
             const uint32_t use = (uint32_t)(lt >> 1);
             const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
+            ODBG_T(o0);
             if (!mbar_wait(full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 4);
                 break;
             }
+            ODBG_T(o1);
             float mean, rstd;
             // --- x column of this position: 128 channels, [c][j] layout, stride 256 B
             {
@@ -385,6 +398,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                 group_sync(1 + g, 128);  // everyone has read its column before rows overwrite the buffer
                 store_normalized_row(xtile, row, xraw, mean, rstd, prm + 256, prm + 384);
             }
+            ODBG_T(o2);
             // --- z row: keep the raw values for the residual, normalise in place (A operand 1)
             uint32_t zraw[64];
             load_row(ztile, row, zraw);
@@ -393,11 +407,13 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(g));
+            ODBG_T(o3);
             // --- wait for both GEMMs, combine, write the output tile over the z buffer
             if (!mbar_wait(d_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
                 break;
             }
+            ODBG_T(o4);
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
 #pragma unroll
@@ -424,9 +440,11 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                     sts128(chunk_addr(ztile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
                 }
             }
+            ODBG_T(o5);
             tc_fence_before_sync();
             fence_proxy_async_smem();
             group_sync(1 + g, 128);
+            ODBG_T(o6);
             if (gtid == 0) {
                 for (int kb = 0; kb < 2; ++kb)
                     tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.fixed);
@@ -434,6 +452,10 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                 tma_store_wait_read<0>();
                 mbar_arrive(empty(g));
             }
+            ODBG_T(o7);
+            ODBG_ADD(0, o0, o1); ODBG_ADD(1, o1, o2); ODBG_ADD(2, o2, o3); ODBG_ADD(3, o3, o4);
+            ODBG_ADD(4, o4, o5); ODBG_ADD(5, o5, o6); ODBG_ADD(6, o6, o7); ODBG_ADD(7, o0, o7);
+            ODBG_ADD(8, o0, o0 + 1);
         }
         if (gtid == 0) tma_store_wait_all<0>();
     }
@@ -454,6 +476,13 @@ int weight_tmap(CUtensorMap* m, const void* w, int rows) {
 }
 
 }  // namespace
+
+#ifdef OF3_CORE_TIMING
+extern "C" int of3_out_dbg(long long* out, int reset) {
+    if (reset) { long long z[16] = {0}; return (int)cudaMemcpyToSymbol(g_out_dbg, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(out, g_out_dbg, 16 * sizeof(long long));
+}
+#endif
 
 bool trimul_supported(int c_z, int c_h) { return c_z == 128 && c_h == 128; }
 

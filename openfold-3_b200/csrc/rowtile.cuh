@@ -67,35 +67,55 @@ __device__ __forceinline__ void load_row(uint32_t tile, int row, uint32_t (&raw)
     }
 }
 
-// LayerNorm statistics of 128 packed bf16 values (fp32, two-pass on registers).
+// LayerNorm statistics of 128 packed bf16 values (fp32, two-pass on registers). Eight independent
+// partial sums: a single accumulator is a 128-deep dependent chain, which with two warps per
+// scheduler is pure latency.
 __device__ __forceinline__ void row_stats(const uint32_t (&raw)[64], float& mean, float& rstd) {
-    float s = 0.f;
+    float s[8];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) s += bf16lo(raw[i]) + bf16hi(raw[i]);
-    mean = s * (1.0f / kC);
-    float v = 0.f;
+    for (int a = 0; a < 8; ++a) s[a] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 64; ++i) {
-        const float a = bf16lo(raw[i]) - mean, b = bf16hi(raw[i]) - mean;
-        v = fmaf(a, a, v);
-        v = fmaf(b, b, v);
+    for (int i = 0; i < 64; i += 8) {
+#pragma unroll
+        for (int a = 0; a < 8; ++a) s[a] += bf16lo(raw[i + a]) + bf16hi(raw[i + a]);
     }
-    rstd = rsqrtf(v * (1.0f / kC) + kLnEps);
+    mean = (((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]))) * (1.0f / kC);
+    float v[8];
+#pragma unroll
+    for (int a = 0; a < 8; ++a) v[a] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 64; i += 8) {
+#pragma unroll
+        for (int a = 0; a < 8; ++a) {
+            const float x0 = bf16lo(raw[i + a]) - mean, x1 = bf16hi(raw[i + a]) - mean;
+            v[a] = fmaf(x0, x0, v[a]);
+            v[a] = fmaf(x1, x1, v[a]);
+        }
+    }
+    const float var = (((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]))) * (1.0f / kC);
+    rstd = rsqrtf(var + kLnEps);
 }
 
 // Writes LN(raw) * gamma + beta (bf16) as this thread's row of a swizzled tile.
-// gamma/beta: fp32 arrays of 128 in shared memory (broadcast reads).
+// gamma/beta: fp32 arrays of 128 in shared memory, 16-byte aligned (broadcast vector reads).
 __device__ __forceinline__ void store_normalized_row(uint32_t tile, int row, const uint32_t (&raw)[64],
                                                      float mean, float rstd, const float* gamma,
                                                      const float* beta) {
+    const float nm = -mean * rstd;
 #pragma unroll
     for (int ch = 0; ch < 16; ++ch) {
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + ch * 8);
+        const float4 g1 = *reinterpret_cast<const float4*>(gamma + ch * 8 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(beta + ch * 8);
+        const float4 b1 = *reinterpret_cast<const float4*>(beta + ch * 8 + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            const int c = ch * 8 + j * 2;
-            const float a = (bf16lo(raw[ch * 4 + j]) - mean) * rstd * gamma[c] + beta[c];
-            const float b = (bf16hi(raw[ch * 4 + j]) - mean) * rstd * gamma[c + 1] + beta[c + 1];
+            // (x - mean) * rstd as one fma: x * rstd + (-mean * rstd)
+            const float a = fmaf(fmaf(bf16lo(raw[ch * 4 + j]), rstd, nm), gg[j * 2], bb[j * 2]);
+            const float b = fmaf(fmaf(bf16hi(raw[ch * 4 + j]), rstd, nm), gg[j * 2 + 1], bb[j * 2 + 1]);
             o[j] = pack_bf16x2(a, b);
         }
         sts128(chunk_addr(tile, row, ch), make_uint4(o[0], o[1], o[2], o[3]));
