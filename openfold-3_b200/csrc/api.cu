@@ -45,6 +45,9 @@ int transition_dispatch(const void* x, const void* mask, void* out, long long ro
     if (use_fast(dtype, flags) && fast::transition_supported(c, n))
         return fast::transition((const __nv_bfloat16*)x, (const __nv_bfloat16*)mask,
                                 (__nv_bfloat16*)out, rows, flags, p, ws, st);
+    if (use_fast(dtype, flags) && fast::transition_wide_supported(c, n))
+        return fast::transition_wide((const __nv_bfloat16*)x, (const __nv_bfloat16*)mask, (__nv_bfloat16*)out, rows,
+                                     c, n, flags, p, ws, st);
     if (dtype == OF3_DTYPE_BF16)
         return generic::transition<__nv_bfloat16>((const __nv_bfloat16*)x, (const __nv_bfloat16*)mask,
                                                   (__nv_bfloat16*)out, rows, c, n, flags, p, ws, st);
@@ -55,6 +58,9 @@ int transition_dispatch(const void* x, const void* mask, void* out, long long ro
 int apb_dispatch(const void* a, const void* z, const void* s, const void* mask, void* out, int Ba,
                  int Bz, int N, int c_a, int c_s, int c_z, int H, int d, float inf, int dtype,
                  int flags, const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st) {
+    if (dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, c_z, H, d, flags))
+        return fast::attn_pair_bias((const __nv_bfloat16*)a, (const __nv_bfloat16*)z, (const __nv_bfloat16*)mask,
+                                    (__nv_bfloat16*)out, Ba, Bz, N, c_a, H, d, inf, flags, p, ws, st, nullptr);
     if (dtype == OF3_DTYPE_BF16)
         return generic::attn_pair_bias<__nv_bfloat16>(
             (const __nv_bfloat16*)a, (const __nv_bfloat16*)z, (const __nv_bfloat16*)s,

@@ -80,6 +80,9 @@ int of3_attn_pair_bias_forward_prebias(const void* a, const float* pair_bias, co
     OF3_REQUIRE(a && pair_bias && out && p && workspace, OF3_ERR_ARG, "attn_pair_bias_prebias: null pointer argument");
     OF3_REQUIRE(Ba > 0 && Bz > 0 && Ba % Bz == 0 && N > 0, OF3_ERR_ARG, "attn_pair_bias_prebias: bad sizes");
     Arena ws(workspace, workspace_bytes);
+    if (dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, 128, H, d, flags))
+        return fast::attn_pair_bias((const __nv_bfloat16*)a, nullptr, (const __nv_bfloat16*)mask, (__nv_bfloat16*)out,
+                                    Ba, Bz, N, c_a, H, d, inf, flags, p, ws, (cudaStream_t)stream, pair_bias);
     if (dtype == OF3_DTYPE_BF16)
         return generic::attn_pair_bias<__nv_bfloat16>((const __nv_bfloat16*)a, nullptr, (const __nv_bfloat16*)s,
                                                       (const __nv_bfloat16*)mask, (__nv_bfloat16*)out, Ba, Bz, N, c_a,

@@ -1,0 +1,295 @@
+// Single-track layers of the Pairformer block in bf16 (c_s = 384 in OpenFold3): attention with pair bias
+// (LayerNorm variant) and the SwiGLU transition for widths without a fused row-tile kernel.
+//
+// The token dimension is tiny next to the pair tensor (N x 384 against N x N x 128), so these are
+// launch/latency-bound chains, not roofline kernels. The linears run on the tcgen05 contraction
+// kernel (activation rows x weight rows, both K-major), the attention keeps one head's K and V
+// resident in shared memory, and everything in between is bf16 in HBM with fp32 arithmetic.
+// Reference: openfold3/core/model/layers/attention_pair_bias.py:123-227,
+//            openfold3/core/model/primitives/attention.py:94-135, 270-310,
+//            openfold3/core/model/layers/transition.py:225-271.
+#include "generic_ops.cuh"
+#include "modules.cuh"
+#include "runtime.cuh"
+
+namespace of3 {
+namespace fast {
+namespace {
+
+typedef __nv_bfloat16 bf16;
+constexpr int kKidSingle = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// ---------------------------------------------------------------- LayerNorm rows -> bf16
+__global__ void __launch_bounds__(256) ln_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
+                                                      const bf16* __restrict__ beta, bf16* __restrict__ y,
+                                                      long long rows, int C) {
+    const int lane = threadIdx.x & 31;
+    const long long r = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (r >= rows) return;
+    const bf16* xr = x + r * C;
+    float s = 0.f;
+    for (int c = lane; c < C; c += 32) s += __bfloat162float(xr[c]);
+    const float mean = warp_sum(s) / (float)C;
+    float v = 0.f;
+    for (int c = lane; c < C; c += 32) {
+        const float d = __bfloat162float(xr[c]) - mean;
+        v += d * d;
+    }
+    const float rstd = rsqrtf(warp_sum(v) / (float)C + 1e-5f);
+    for (int c = lane; c < C; c += 32) {
+        float o = (__bfloat162float(xr[c]) - mean) * rstd;
+        if (gamma) o *= __bfloat162float(gamma[c]);
+        if (beta) o += __bfloat162float(beta[c]);
+        y[r * C + c] = __float2bfloat16_rn(o);
+    }
+}
+
+// ---------------------------------------------------------------- attention, one head resident
+// grid (query chunks, H, BB); 8 warps; each warp takes queries chunk*QPB + warp, + 8, ...
+// K and V of (bb, h) sit in shared memory as bf16 with an odd word pitch (conflict-free row reads).
+constexpr int kQPB = 32;  // queries per block
+
+template <int D>
+__global__ void __launch_bounds__(256)
+single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
+                   const bf16* __restrict__ g, const bf16* __restrict__ q_bias, const float* __restrict__ pair_bias,
+                   const bf16* __restrict__ mask, bf16* __restrict__ out, int N, int H, float scale, float inf,
+                   long long rows_per_bias) {
+    constexpr int P = D + 2;  // pitch in bf16: (D + 2) / 2 words, odd for D = 24, 48 -> conflict-free
+    extern __shared__ uint8_t smem[];
+    bf16* Ks = reinterpret_cast<bf16*>(smem);
+    bf16* Vs = Ks + (size_t)N * P;
+    float* mb = reinterpret_cast<float*>(Vs + (size_t)N * P);  // additive key mask
+    float* Qs = mb + ((N + 31) & ~31);                          // [8 warps][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long bb = blockIdx.z;
+    const int h = blockIdx.y;
+    const int HD = H * D;
+    for (int idx = threadIdx.x; idx < N * (D / 2); idx += 256) {
+        const int kk = idx / (D / 2), c2 = idx % (D / 2);
+        const long long off = (bb * N + kk) * HD + h * D + c2 * 2;
+        *reinterpret_cast<uint32_t*>(Ks + kk * P + c2 * 2) = *reinterpret_cast<const uint32_t*>(k + off);
+        *reinterpret_cast<uint32_t*>(Vs + kk * P + c2 * 2) = *reinterpret_cast<const uint32_t*>(v + off);
+    }
+    for (int kk = threadIdx.x; kk < ((N + 31) & ~31); kk += 256)
+        mb[kk] = kk < N ? (mask ? inf * (__bfloat162float(mask[bb * N + kk]) - 1.0f) : 0.f) : -INFINITY;
+    __syncthreads();
+    const float* pb_base = pair_bias + ((bb / rows_per_bias) * H + h) * (long long)N * N;
+    for (int qi = blockIdx.x * kQPB + warp; qi < min(N, (int)(blockIdx.x + 1) * kQPB); qi += 8) {
+        const long long qoff = (bb * N + qi) * HD + h * D;
+        for (int c = lane; c < D; c += 32)
+            Qs[warp * D + c] = (__bfloat162float(q[qoff + c]) + (q_bias ? __bfloat162float(q_bias[h * D + c]) : 0.f)) * scale;
+        __syncwarp();
+        float qr[D];
+#pragma unroll
+        for (int c = 0; c < D; ++c) qr[c] = Qs[warp * D + c];
+        const float* pb = pb_base + (long long)qi * N;
+        float m = -INFINITY, l = 0.f;
+        float o0 = 0.f, o1 = 0.f;  // this lane owns output dims lane and lane + 32
+        for (int k0 = 0; k0 < N; k0 += 32) {
+            const int kk = k0 + lane;
+            float s = -INFINITY;
+            if (kk < N) {
+                float dot = 0.f;
+                const uint32_t* kr = reinterpret_cast<const uint32_t*>(Ks + kk * P);
+#pragma unroll
+                for (int c2 = 0; c2 < D / 2; ++c2) {
+                    const uint32_t w = kr[c2];
+                    dot = fmaf(qr[c2 * 2], bf16lo(w), dot);
+                    dot = fmaf(qr[c2 * 2 + 1], bf16hi(w), dot);
+                }
+                s = (dot + mb[kk]) + pb[kk];
+            }
+            const float m_new = fmaxf(m, warp_max(s));
+            const float p = (kk < N) ? __expf(s - m_new) : 0.f;
+            const float corr = __expf(m - m_new);
+            l = l * corr + warp_sum(p);
+            o0 *= corr;
+            o1 *= corr;
+            const int kmax = min(32, N - k0);
+            for (int j = 0; j < kmax; ++j) {
+                const float pj = __shfl_sync(0xffffffffu, p, j);
+                const bf16* vr = Vs + (k0 + j) * P;
+                if (lane < D) o0 = fmaf(pj, __bfloat162float(vr[lane]), o0);
+                if (D > 32 && lane + 32 < D) o1 = fmaf(pj, __bfloat162float(vr[lane + 32]), o1);
+            }
+            m = m_new;
+        }
+        const float inv = 1.0f / l;
+        if (lane < D) {
+            float r = o0 * inv;
+            if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[qoff + lane])));
+            out[qoff + lane] = __float2bfloat16_rn(r);
+        }
+        if (D > 32 && lane + 32 < D) {
+            float r = o1 * inv;
+            if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[qoff + lane + 32])));
+            out[qoff + lane + 32] = __float2bfloat16_rn(r);
+        }
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------- elementwise
+__global__ void silu_mul_bf16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ b, bf16* __restrict__ dst,
+                                     long long n) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    const uint32_t av = *reinterpret_cast<const uint32_t*>(a + i), bv = *reinterpret_cast<const uint32_t*>(b + i);
+    const float a0 = bf16lo(av), a1 = bf16hi(av);
+    const float h0 = a0 / (1.0f + __expf(-a0)) * bf16lo(bv);
+    const float h1 = a1 / (1.0f + __expf(-a1)) * bf16hi(bv);
+    *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16x2(h0, h1);
+}
+// out[r, :] = (residual ? residual[r, :] : 0) + upd[r, :] * (mask ? mask[r] : 1)
+__global__ void residual_bf16_kernel(const bf16* __restrict__ upd, const bf16* residual, const bf16* __restrict__ mask,
+                                     bf16* out, long long rows, int C) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= rows * C) return;
+    const long long r = i / C;
+    const float mk = mask ? __bfloat162float(mask[r]) : 1.0f;
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(upd + i);
+    float v0 = bf16lo(u) * mk, v1 = bf16hi(u) * mk;
+    if (residual) {
+        const uint32_t z = *reinterpret_cast<const uint32_t*>(residual + i);
+        v0 += bf16lo(z);
+        v1 += bf16hi(z);
+    }
+    *reinterpret_cast<uint32_t*>(out + i) = pack_bf16x2(v0, v1);
+}
+
+int linear_bf16(const bf16* x, const bf16* w, bf16* y, long long rows, int out_dim, int in_dim, cudaStream_t st) {
+    return contract_nt_bf16(x, w, y, 1, (int)rows, out_dim, in_dim, in_dim, in_dim, out_dim, rows * in_dim,
+                            (long long)out_dim * in_dim, rows * out_dim, st);
+}
+
+template <int D>
+int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias, const float* pb,
+                const bf16* mask, bf16* out, int BB, int N, int H, float inf, long long rows_per_bias,
+                cudaStream_t st) {
+    const size_t smem = (size_t)N * (D + 2) * 2 * 2 + (size_t)((N + 31) & ~31) * 4 + 8 * D * 4;
+    static size_t configured = 0;
+    if (smem > configured) {
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(single_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                            (int)smem));
+        configured = smem;
+    }
+    dim3 grid(ceil_div(N, kQPB), H, BB);
+    LaunchScope scope(kKidSingle, st);
+    single_attn_kernel<D><<<grid, 256, smem, st>>>(q, k, v, g, q_bias, pb, mask, out, N, H, rsqrtf((float)D), inf,
+                                                   rows_per_bias);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+}  // namespace
+
+// bf16, LayerNorm variant, one pair tensor per sample; c_a = H * d a multiple of 64; d in {24, 48};
+// K and V of one head must fit in shared memory.
+bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_z, int H, int d, int flags) {
+    if (flags & (OF3_FLAG_ADA_LN | OF3_FLAG_FORCE_GENERIC)) return false;
+    if (!(d == 24 || d == 48) || H * d != c_a || c_a % 64 != 0) return false;
+    if (c_z != 128 || H != 16 || Bz <= 0 || Ba % Bz != 0) return false;
+    return (size_t)N * (d + 2) * 4 + (size_t)N * 4 + 8192 <= 200 * 1024;
+}
+
+int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, int Ba, int Bz, int N, int c_a, int H,
+                   int d, float inf, int flags, const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st,
+                   const float* pair_bias) {
+    const long long rows = (long long)Ba * N;
+    bf16* an = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* q = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* k = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* v = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* g = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* og = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* y = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    float* zb = (float*)ws.take((size_t)Bz * H * N * N * sizeof(float));
+    if (!ws.base) return OF3_OK;
+    OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "attn_pair_bias: workspace too small (%zu needed)", ws.off);
+    int rc;
+    if (pair_bias == nullptr) {
+        if ((rc = generic::pair_bias_c128_h16<bf16>(z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b,
+                                                    (const bf16*)p->w_z, zb, Bz, (long long)N * N, st)))
+            return rc;
+        pair_bias = zb;
+    }
+    {
+        LaunchScope scope(kKidSingle, st);
+        ln_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(a, (const bf16*)p->ln_a_w, (const bf16*)p->ln_a_b,
+                                                                   an, rows, c_a);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    if ((rc = linear_bf16(an, (const bf16*)p->w_q, q, rows, c_a, c_a, st))) return rc;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_k, k, rows, c_a, c_a, st))) return rc;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_v, v, rows, c_a, c_a, st))) return rc;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_g, g, rows, c_a, c_a, st))) return rc;
+    const long long rpb = Ba / Bz;
+    if (d == 24)
+        rc = launch_attn<24>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, H, inf, rpb, st);
+    else
+        rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, H, inf, rpb, st);
+    if (rc) return rc;
+    if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * c_a / 2;
+        residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
+            y, (flags & OF3_FLAG_ADD_RESIDUAL) ? a : nullptr, nullptr, out, rows, c_a);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+// SwiGLU transition for widths without the fused row-tile kernel (bf16, c and n*c multiples of 64).
+bool transition_wide_supported(int c, int n) { return c % 64 == 0 && !(c == 128 && n == 4); }
+
+int transition_wide(const bf16* x, const bf16* mask, bf16* out, long long rows, int c, int n, int flags,
+                    const of3_transition_params* p, Arena& ws, cudaStream_t st) {
+    const int hid = n * c;
+    bf16* xn = (bf16*)ws.take(rows * c * sizeof(bf16));
+    bf16* ha = (bf16*)ws.take(rows * hid * sizeof(bf16));
+    bf16* hb = (bf16*)ws.take(rows * hid * sizeof(bf16));
+    bf16* y = (bf16*)ws.take(rows * c * sizeof(bf16));
+    if (!ws.base) return OF3_OK;
+    OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "transition: workspace too small (%zu needed)", ws.off);
+    OF3_REQUIRE(rows < (1LL << 31), OF3_ERR_SHAPE, "transition: too many rows");
+    int rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        ln_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(x, (const bf16*)p->ln_w, (const bf16*)p->ln_b, xn,
+                                                                   rows, c);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    if ((rc = linear_bf16(xn, (const bf16*)p->w_a, ha, rows, hid, c, st))) return rc;
+    if ((rc = linear_bf16(xn, (const bf16*)p->w_b, hb, rows, hid, c, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * hid / 2;
+        silu_mul_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(ha, hb, ha, rows * hid);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    if ((rc = linear_bf16(ha, (const bf16*)p->w_out, y, rows, c, hid, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * c / 2;
+        residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
+            y, (flags & OF3_FLAG_ADD_RESIDUAL) ? x : nullptr, mask, out, rows, c);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+}  // namespace fast
+}  // namespace of3

@@ -55,6 +55,14 @@ int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
 bool transition_supported(int c, int n);
 int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows,
                int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
+// single-track layers (bf16): linears on the tcgen05 contraction kernel, one head of K/V resident per CTA
+bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_z, int H, int d, int flags);
+int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
+                   int Ba, int Bz, int N, int c_a, int H, int d, float inf, int flags,
+                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st, const float* pair_bias);
+bool transition_wide_supported(int c, int n);
+int transition_wide(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows, int c,
+                    int n, int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
 }  // namespace fast
 
 int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
