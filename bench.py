@@ -64,9 +64,16 @@ def kernel_flops(n: int) -> dict:
     }
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the committed ncu
-# summaries under profiles/, scaled to N = 768 where the capture was taken at a smaller N.
-KERNEL_DRAM_TRAFFIC = {}
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at N = 768 from the committed ncu
+# summaries under profiles/ (captured at N = 768 itself, one block).
+KERNEL_DRAM_TRAFFIC = {
+    "triattn_core": 597.3e6,
+    "trimul_in": 400e6,
+    "contract": 417e6,
+    "trimul_out": 412e6,
+    "triattn_proj": 552e6,
+    "triattn_out": 412e6,
+}
 
 
 def peaks() -> tuple[float, float, str]:
@@ -313,7 +320,7 @@ def run_ours(args) -> None:
             achieved = kf[top] / world / (per_launch_ms * 1e-3) / 1e12
             roofline = {"kernel": top, "bound": "tensor", "achieved": round(achieved, 1), "peak": tensor_peak,
                         "unit": "TFLOP/s", "frac": round(achieved / tensor_peak, 4),
-                        "traffic": KERNEL_DRAM_TRAFFIC.get(top), "peak_kind": f"bf16 sustained, {peak_kind}",
+                        "traffic": KERNEL_DRAM_TRAFFIC.get(top) if n == 768 else None, "peak_kind": f"bf16 sustained, {peak_kind}",
                         "algorithmic_flop_per_launch": kf[top] / world}
         cpu_s, cores = oracle_block_seconds(n) if world == 1 and not args.no_cpu_baseline else (None, 0)
         cpu_baseline = None
