@@ -213,21 +213,40 @@ int of3_cond_transition_forward(const void* a, const void* s, const void* mask, 
                                 size_t workspace_bytes, void* stream);
 
 /* ---- Row-sharded ("DAP") pair stack: phase entry points --------------------------------------
- * No counterpart in the reference (it has data-parallel DDP / ZeRO only; SURVEY of its
- * experiment_runner.py:218-246). Each rank owns R = N / P consecutive rows of one sample's pair
- * tensor (bf16, c_z = c_hidden = 128, 4 heads x 32) and runs every layer as project | exchange |
- * finish; the exchange (all-gather / all-to-all) is the caller's, between the two calls.
- * Pitches: ld = of3_dap_pitch(N, 8) for a_t / b_t / x, ldn = of3_dap_pitch(N, 64) for v^T and bias.
- *   z_rows, out_rows [R, N, 128]; mask_rows [R, N] or NULL; a_t, x_scratch [128, R, ld];
- *   b_all [128, N, ld]; q, k, vt: opaque images of of3_dap_triattn_image_elems(R, N) elements each
- *   (pre-swizzled operand tiles); bias_rows [4, R, ldn];
+ * No counterpart in the reference (it has data-parallel DDP / ZeRO only;
+ * openfold3/entry_points/experiment_runner.py:218-246). Each of the P ranks (P = 1, 2, 4, 8) owns
+ * R = N / P consecutive rows of one sample's pair tensor (bf16, c_z = c_hidden = 128, 4 heads x 32)
+ * and runs every layer as phases around the exchanges the layer needs; the exchanges (all-to-all /
+ * all-gather) are the caller's, between the calls. Pitches: ld(n) = of3_dap_pitch(n, 8) for the
+ * triangle update's planes, ldn = of3_dap_pitch(N, 64) for the attention bias.
+ *
+ * Triangle update (triangular_multiplicative_update.py:421-503), C = 128 / P channels per rank:
+ *   project   z_rows -> ab [P][2][C][lines][ld(positions)]: the gated projections a (index 0) and b
+ *             (index 1), channel-major, grouped by the rank that will contract each channel.
+ *             outgoing: transposed = 0, z_rows [lines = R][positions = N][128], mask [R][N];
+ *             incoming: transposed = 1, the same memory read as [positions = R][lines = N][128]
+ *             (a line runs along the local rows), mask [R][N] likewise.
+ *   (all-to-all of the P blocks, then regroup to ab_all [2][C][N][ld(N)]: of3_copy_rows_3d)
+ *   contract  x[c][i][j] = sum_k a[c][i][k] b[c][j][k] for this rank's C channels and ALL i, j, written as
+ *             x_blocks [P][C][R][ld(N)]: block q holds rows q*R .. q*R + R - 1, i.e. what rank q needs
+ *   (all-to-all of the P blocks: x_t [128][R][ld(N)] = this rank's rows of every channel)
+ *   output    LayerNorm_out(x) -> linear_z, sigmoid(linear_g(LayerNorm_in(z))) gate, residual, on z_rows.
+ * Attention: z_rows, out_rows [R, N, 128]; mask_rows [R, N] or NULL; q, k, vt: opaque images of
+ *   of3_dap_triattn_image_elems(R, N) elements each (pre-swizzled operand tiles); bias_rows [4, R, ldn];
  *   bias_all [4, N, ldn]; o_scratch [R, N, 128]. out_rows may alias z_rows. */
 int of3_dap_pitch(int N, int multiple);
 long long of3_dap_triattn_image_elems(int R, int N);
-int of3_dap_trimul_project(const void* z_rows, const void* mask_rows, void* a_t, void* b_t, int R, int N,
-                           const of3_trimul_params* p, void* stream);
-int of3_dap_trimul_finish(const void* z_rows, void* out_rows, const void* a_t, const void* b_all, void* x_scratch,
-                          int R, int N, int flags, const of3_trimul_params* p, void* stream);
+int of3_dap_trimul_project(const void* z_rows, const void* mask, void* ab, int lines, int positions, int transposed,
+                           int world, const of3_trimul_params* p, void* stream);
+int of3_dap_trimul_contract(const void* ab_all, void* x_blocks, int N, int channels, int rows_per_rank,
+                            void* stream);
+int of3_dap_trimul_output(const void* z_rows, void* out_rows, const void* x_t, int R, int N, int flags,
+                          const of3_trimul_params* p, void* stream);
+/* Strided copy of n0*n1*n2 rows of row_bytes bytes; row (i0, i1, i2) is read at src + i0*s0 + i1*s1 +
+ * i2*s2 and written at dst + i0*t0 + i1*t1 + i2*t2 (byte strides). The repacks between an
+ * all-to-all's rank-major blocks and the layouts the kernels read. */
+int of3_copy_rows_3d(const void* src, void* dst, int n0, int n1, int n2, long long s0, long long s1, long long s2,
+                     long long t0, long long t1, long long t2, int row_bytes, void* stream);
 int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N,
                             const of3_triattn_params* p, void* stream);
 int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_rows, const void* q, const void* k,
@@ -242,6 +261,15 @@ int of3_attn_pair_bias_forward_prebias(const void* a, const float* pair_bias, co
                                        void* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf,
                                        int dtype, int flags, const of3_attn_pair_bias_params* p, void* workspace,
                                        size_t workspace_bytes, void* stream);
+
+/* The AttentionPairBias layer (attention_pair_bias.py:123-227, LayerNorm variant) for a window of R
+ * query rows [row0, row0 + R) of one sample: keys / values from all N rows of a [N, c_a], the pair bias
+ * of exactly those rows (pair_bias_rows [H, R, N], fp32), out_rows [R, c_a]. bf16, 16 heads of 24 / 48. */
+size_t of3_attn_pair_bias_rows_workspace_bytes(int N, int R, int c_a);
+int of3_attn_pair_bias_forward_rows(const void* a, const float* pair_bias_rows, const void* mask, void* out_rows,
+                                    int N, int row0, int R, int c_a, int H, int d, float inf, int dtype, int flags,
+                                    const of3_attn_pair_bias_params* p, void* workspace, size_t workspace_bytes,
+                                    void* stream);
 
 /* ---- Building block exported for tests and profiling --------------------------------------
  * X[b][i][j] = sum_k A[b][i][k] * B[b][j][k], bf16 in / fp32 accumulate / bf16 out, the

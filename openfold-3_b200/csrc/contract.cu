@@ -37,7 +37,8 @@ template <int BN>
 __global__ void __launch_bounds__(192, 1)
 contract_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    __nv_bfloat16* __restrict__ out, int M, int N, int K, int batch,
-                   long long out_batch_stride, int ldo, int* status) {
+                   long long out_batch_stride, int ldo, int rows_per_block, long long row_block_stride,
+                   int* status) {
     using Cfg = ContractCfg<BN>;
     constexpr int S = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -166,7 +167,14 @@ contract_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             }
             tc_fence_after_sync();
             const int row = mt * kBM + quad * 32 + lane;
-            __nv_bfloat16* orow = out + (long long)b * out_batch_stride + (long long)row * ldo;
+            // rows_per_block > 0: output rows are grouped in blocks of that many rows and block q starts
+            // at q * row_block_stride (the layout a row-sharding all-to-all sends without a repack)
+            long long roff = (long long)row * ldo;
+            if (rows_per_block > 0) {
+                const int q = row / rows_per_block;
+                roff = (long long)q * row_block_stride + (long long)(row - q * rows_per_block) * ldo;
+            }
+            __nv_bfloat16* orow = out + (long long)b * out_batch_stride + roff;
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
@@ -207,7 +215,7 @@ contract_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 template <int BN>
 int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
                     int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
-                    long long o_bs, cudaStream_t stream) {
+                    long long o_bs, int rows_per_block, long long row_block_stride, cudaStream_t stream) {
     using Cfg = ContractCfg<BN>;
     CUtensorMap tmA, tmB;
     {
@@ -236,7 +244,8 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
     int* status = device_status_ptr();
     LaunchScope scope(kKernelIdContract, stream);
     contract_nt_kernel<BN><<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, batch,
-                                                                   o_bs, ldo, status);
+                                                                   o_bs, ldo, rows_per_block, row_block_stride,
+                                                                   status);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
@@ -245,7 +254,7 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
 
 int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
                      int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
-                     long long o_bs, cudaStream_t stream) {
+                     long long o_bs, cudaStream_t stream, int rows_per_block, long long row_block_stride) {
     OF3_REQUIRE(a && b && out, OF3_ERR_ARG, "contract: null pointer");
     OF3_REQUIRE(batch > 0 && M > 0 && N > 0 && K > 0, OF3_ERR_ARG, "contract: non-positive size");
     OF3_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0 && a_bs % 8 == 0 && b_bs % 8 == 0 &&
@@ -253,9 +262,13 @@ int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat
                 OF3_ERR_ALIGN, "contract: pitches must be multiples of 8 elements");
     OF3_REQUIRE(ldo >= (int)align_up(N, 8), OF3_ERR_ALIGN, "contract: ldo < round_up(N, 8)");
     OF3_REQUIRE(((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN, "contract: out not 16-byte aligned");
+    OF3_REQUIRE(rows_per_block >= 0 && row_block_stride % 8 == 0, OF3_ERR_ALIGN,
+                "contract: row block stride must be a multiple of 8 elements");
     if (N > 128)
-        return launch_contract<256>(a, b, out, batch, M, N, K, lda, ldb, ldo, a_bs, b_bs, o_bs, stream);
-    return launch_contract<128>(a, b, out, batch, M, N, K, lda, ldb, ldo, a_bs, b_bs, o_bs, stream);
+        return launch_contract<256>(a, b, out, batch, M, N, K, lda, ldb, ldo, a_bs, b_bs, o_bs, rows_per_block,
+                                    row_block_stride, stream);
+    return launch_contract<128>(a, b, out, batch, M, N, K, lda, ldb, ldo, a_bs, b_bs, o_bs, rows_per_block,
+                                row_block_stride, stream);
 }
 
 }  // namespace of3
@@ -267,5 +280,5 @@ extern "C" int of3_contract_nt_bf16(const void* a, const void* b, void* out, int
                                     void* stream) {
     return of3::contract_nt_bf16((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                  (__nv_bfloat16*)out, batch, M, N, K, lda, ldb, ldo, a_batch_stride,
-                                 b_batch_stride, out_batch_stride, (cudaStream_t)stream);
+                                 b_batch_stride, out_batch_stride, (cudaStream_t)stream, 0, 0);
 }

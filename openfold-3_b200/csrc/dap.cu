@@ -4,38 +4,130 @@
 // torch.distributed) is done by the caller between the phases; remote data always lands in this
 // GPU's own memory first and the kernels only ever read local memory.
 //
-//   triangle update  project: local rows -> a_t, b_t (channel-major) | all-gather b_t | finish:
-//                    contraction of the local rows of a against ALL rows of b, LN / gate / residual
+//   triangle update  project: local rows -> a_t, b_t (channel-major, one group of 128 / P channels per
+//                    destination rank) | all-to-all: rows -> channels | contract: this rank's channels
+//                    over ALL rows, output grouped by the rank that owns each row | all-to-all back |
+//                    output: LN / linear / gate / residual on the local rows
 //   triangle attn    project: q, k, v^T and the local rows of the pair bias | all-gather bias |
 //                    finish: attention over the local lines, gate, output projection, residual
-//   incoming update / ending-node attention run the same phases on the all-to-all-transposed shard.
+//   The incoming update projects with a transposed walk over the local rows (no transposed copy of
+//   z); ending-node attention runs the same phases on the all-to-all-transposed shard.
 #include "generic_ops.cuh"
 #include "modules.cuh"
+#include "runtime.cuh"
 
 using namespace of3;
 
+namespace {
+// Rows of `row_bytes` bytes indexed by (i0, i1, i2); byte strides per index on both sides. One warp per
+// row chunk of 512 B (16-byte vectors) when everything is 16-byte aligned, else 2-byte elements.
+template <typename V>
+__global__ void __launch_bounds__(256)
+copy_rows_3d_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long n_rows, int n1, int n2,
+                    long long s0, long long s1, long long s2, long long t0, long long t1, long long t2,
+                    int vec_per_row) {
+    const int chunks = (vec_per_row + 31) / 32;
+    const long long total = n_rows * chunks;
+    const int lane = threadIdx.x & 31;
+    for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total;
+         w += ((long long)gridDim.x * blockDim.x) >> 5) {
+        const long long row = w / chunks;
+        const int v = (int)(w % chunks) * 32 + lane;
+        if (v >= vec_per_row) continue;
+        const int i2 = (int)(row % n2);
+        const long long r1 = row / n2;
+        const int i1 = (int)(r1 % n1);
+        const long long i0 = r1 / n1;
+        const V* sp = reinterpret_cast<const V*>(src + i0 * s0 + i1 * s1 + i2 * s2);
+        V* dp = reinterpret_cast<V*>(dst + i0 * t0 + i1 * t1 + i2 * t2);
+        dp[v] = sp[v];
+    }
+}
+}  // namespace
+
 extern "C" {
+
+int of3_copy_rows_3d(const void* src, void* dst, int n0, int n1, int n2, long long s0, long long s1, long long s2,
+                     long long t0, long long t1, long long t2, int row_bytes, void* stream) {
+    OF3_REQUIRE(src && dst, OF3_ERR_ARG, "copy_rows_3d: null pointer argument");
+    OF3_REQUIRE(n0 > 0 && n1 > 0 && n2 > 0 && row_bytes > 0 && row_bytes % 2 == 0, OF3_ERR_ARG,
+                "copy_rows_3d: bad sizes");
+    const long long n_rows = (long long)n0 * n1 * n2;
+    const bool vec = (((uintptr_t)src | (uintptr_t)dst | (uintptr_t)s0 | (uintptr_t)s1 | (uintptr_t)s2 |
+                       (uintptr_t)t0 | (uintptr_t)t1 | (uintptr_t)t2 | (uintptr_t)row_bytes) & 15) == 0;
+    const int vpr = vec ? row_bytes / 16 : row_bytes / 2;
+    const long long warps = n_rows * ((vpr + 31) / 32);
+    long long blocks = (warps + 7) / 8;
+    const long long cap = (long long)sm_count() * 16;
+    if (blocks > cap) blocks = cap;
+    LaunchScope scope(20, (cudaStream_t)stream);
+    if (vec)
+        copy_rows_3d_kernel<uint4><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+            (const uint8_t*)src, (uint8_t*)dst, n_rows, n1, n2, s0, s1, s2, t0, t1, t2, vpr);
+    else
+        copy_rows_3d_kernel<uint16_t><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+            (const uint8_t*)src, (uint8_t*)dst, n_rows, n1, n2, s0, s1, s2, t0, t1, t2, vpr);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+size_t of3_attn_pair_bias_rows_workspace_bytes(int N, int R, int c_a) {
+    Arena ws(nullptr, 0);
+    fast::attn_pair_bias_rows(nullptr, nullptr, nullptr, nullptr, N, 0, R, c_a, 16, c_a / 16, 0.f, 0, nullptr, ws, 0);
+    return ws.off + 256;
+}
+
+int of3_attn_pair_bias_forward_rows(const void* a, const float* pair_bias_rows, const void* mask, void* out_rows,
+                                    int N, int row0, int R, int c_a, int H, int d, float inf, int dtype, int flags,
+                                    const of3_attn_pair_bias_params* p, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
+    OF3_REQUIRE(a && pair_bias_rows && out_rows && p && workspace, OF3_ERR_ARG,
+                "attn_pair_bias_rows: null pointer argument");
+    OF3_REQUIRE(dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(1, 1, N, c_a, 128, H, d, flags),
+                OF3_ERR_SHAPE, "attn_pair_bias_rows: bf16, 16 heads of 24 or 48 only");
+    Arena ws(workspace, workspace_bytes);
+    return fast::attn_pair_bias_rows((const __nv_bfloat16*)a, pair_bias_rows, (const __nv_bfloat16*)mask,
+                                     (__nv_bfloat16*)out_rows, N, row0, R, c_a, H, d, inf, flags, p, ws,
+                                     (cudaStream_t)stream);
+}
 
 int of3_dap_pitch(int N, int multiple) { return (int)align_up((size_t)N, (size_t)multiple); }
 
 long long of3_dap_triattn_image_elems(int R, int N) { return (long long)fast::triattn_image_elems(1, R, N); }
 
-int of3_dap_trimul_project(const void* z_rows, const void* mask_rows, void* a_t, void* b_t, int R, int N,
-                           const of3_trimul_params* p, void* stream) {
-    OF3_REQUIRE(z_rows && a_t && b_t && p, OF3_ERR_ARG, "dap_trimul_project: null pointer argument");
-    OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_trimul_project: non-positive size");
-    return fast::trimul_project((const __nv_bfloat16*)z_rows, (const __nv_bfloat16*)mask_rows, (__nv_bfloat16*)a_t,
-                                (__nv_bfloat16*)b_t, 1, R, N, (int)align_up(N, 8), false, p, (cudaStream_t)stream);
+int of3_dap_trimul_project(const void* z_rows, const void* mask, void* ab, int lines, int positions, int transposed,
+                           int world, const of3_trimul_params* p, void* stream) {
+    OF3_REQUIRE(z_rows && ab && p, OF3_ERR_ARG, "dap_trimul_project: null pointer argument");
+    OF3_REQUIRE(lines > 0 && positions > 0, OF3_ERR_ARG, "dap_trimul_project: non-positive size");
+    OF3_REQUIRE(world == 1 || world == 2 || world == 4 || world == 8, OF3_ERR_ARG,
+                "dap_trimul_project: world must be 1, 2, 4 or 8 (got %d)", world);
+    const int ld = (int)align_up(positions, 8);
+    const long long plane = (long long)(128 / world) * lines * ld;  // one rank's channels of a (or b)
+    __nv_bfloat16* a_t = (__nv_bfloat16*)ab;
+    return fast::trimul_project((const __nv_bfloat16*)z_rows, (const __nv_bfloat16*)mask, a_t, a_t + plane, 1, lines,
+                                positions, ld, transposed != 0, p, (cudaStream_t)stream, world, 2 * plane);
 }
 
-int of3_dap_trimul_finish(const void* z_rows, void* out_rows, const void* a_t, const void* b_all, void* x_scratch,
-                          int R, int N, int flags, const of3_trimul_params* p, void* stream) {
-    OF3_REQUIRE(z_rows && out_rows && a_t && b_all && x_scratch && p, OF3_ERR_ARG,
-                "dap_trimul_finish: null pointer argument");
-    OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_trimul_finish: non-positive size");
-    return fast::trimul_finish((const __nv_bfloat16*)z_rows, (__nv_bfloat16*)out_rows, (const __nv_bfloat16*)a_t,
-                               (const __nv_bfloat16*)b_all, (__nv_bfloat16*)x_scratch, 1, R, N, (int)align_up(N, 8),
-                               (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, (cudaStream_t)stream);
+int of3_dap_trimul_contract(const void* ab_all, void* x_blocks, int N, int channels, int rows_per_rank,
+                            void* stream) {
+    OF3_REQUIRE(ab_all && x_blocks, OF3_ERR_ARG, "dap_trimul_contract: null pointer argument");
+    OF3_REQUIRE(N > 0 && channels > 0 && rows_per_rank > 0 && N % rows_per_rank == 0, OF3_ERR_ARG,
+                "dap_trimul_contract: bad sizes N=%d channels=%d rows_per_rank=%d", N, channels, rows_per_rank);
+    const int ld = (int)align_up(N, 8);
+    const __nv_bfloat16* a = (const __nv_bfloat16*)ab_all;
+    const long long plane = (long long)N * ld;
+    return contract_nt_bf16(a, a + (long long)channels * plane, (__nv_bfloat16*)x_blocks, channels, N, N, N, ld, ld, ld,
+                            plane, plane, (long long)rows_per_rank * ld, (cudaStream_t)stream, rows_per_rank,
+                            (long long)channels * rows_per_rank * ld);
+}
+
+int of3_dap_trimul_output(const void* z_rows, void* out_rows, const void* x_t, int R, int N, int flags,
+                          const of3_trimul_params* p, void* stream) {
+    OF3_REQUIRE(z_rows && out_rows && x_t && p, OF3_ERR_ARG, "dap_trimul_output: null pointer argument");
+    OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_trimul_output: non-positive size");
+    return fast::trimul_output((const __nv_bfloat16*)z_rows, (__nv_bfloat16*)out_rows, (const __nv_bfloat16*)x_t, 1, R,
+                               N, (int)align_up(N, 8), (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p,
+                               (cudaStream_t)stream);
 }
 
 int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N,

@@ -57,6 +57,8 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const bf16* __restrict__ x
 
 // ---------------------------------------------------------------- attention, one head resident
 // grid (query chunks, H, BB); 8 warps; each warp takes queries chunk*QPB + warp, + 8, ...
+// q, g, out and the pair bias hold nq query rows per sample (nq = N, or a window of the rows when the
+// queries are split over ranks); k, v and the mask always hold all N keys.
 // K and V of (bb, h) sit in shared memory as bf16 with an odd word pitch (conflict-free row reads).
 constexpr int kQPB = 32;  // queries per block
 
@@ -64,7 +66,7 @@ template <int D>
 __global__ void __launch_bounds__(256)
 single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                    const bf16* __restrict__ g, const bf16* __restrict__ q_bias, const float* __restrict__ pair_bias,
-                   const bf16* __restrict__ mask, bf16* __restrict__ out, int N, int H, float scale, float inf,
+                   const bf16* __restrict__ mask, bf16* __restrict__ out, int N, int nq, int H, float scale, float inf,
                    long long rows_per_bias) {
     constexpr int P = D + 2;  // pitch in bf16: (D + 2) / 2 words, odd for D = 24, 48 -> conflict-free
     extern __shared__ uint8_t smem[];
@@ -85,9 +87,9 @@ single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
     for (int kk = threadIdx.x; kk < ((N + 31) & ~31); kk += 256)
         mb[kk] = kk < N ? (mask ? inf * (__bfloat162float(mask[bb * N + kk]) - 1.0f) : 0.f) : -INFINITY;
     __syncthreads();
-    const float* pb_base = pair_bias + ((bb / rows_per_bias) * H + h) * (long long)N * N;
-    for (int qi = blockIdx.x * kQPB + warp; qi < min(N, (int)(blockIdx.x + 1) * kQPB); qi += 8) {
-        const long long qoff = (bb * N + qi) * HD + h * D;
+    const float* pb_base = pair_bias + ((bb / rows_per_bias) * H + h) * (long long)nq * N;
+    for (int qi = blockIdx.x * kQPB + warp; qi < min(nq, (int)(blockIdx.x + 1) * kQPB); qi += 8) {
+        const long long qoff = (bb * nq + qi) * HD + h * D;
         for (int c = lane; c < D; c += 32)
             Qs[warp * D + c] = (__bfloat162float(q[qoff + c]) + (q_bias ? __bfloat162float(q_bias[h * D + c]) : 0.f)) * scale;
         __syncwarp();
@@ -176,7 +178,7 @@ int linear_bf16(const bf16* x, const bf16* w, bf16* y, long long rows, int out_d
 
 template <int D>
 int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias, const float* pb,
-                const bf16* mask, bf16* out, int BB, int N, int H, float inf, long long rows_per_bias,
+                const bf16* mask, bf16* out, int BB, int N, int nq, int H, float inf, long long rows_per_bias,
                 cudaStream_t st) {
     const size_t smem = (size_t)N * (D + 2) * 2 * 2 + (size_t)((N + 31) & ~31) * 4 + 8 * D * 4;
     static size_t configured = 0;
@@ -185,10 +187,10 @@ int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, cons
                                             (int)smem));
         configured = smem;
     }
-    dim3 grid(ceil_div(N, kQPB), H, BB);
+    dim3 grid(ceil_div(nq, kQPB), H, BB);
     LaunchScope scope(kKidSingle, st);
-    single_attn_kernel<D><<<grid, 256, smem, st>>>(q, k, v, g, q_bias, pb, mask, out, N, H, rsqrtf((float)D), inf,
-                                                   rows_per_bias);
+    single_attn_kernel<D><<<grid, 256, smem, st>>>(q, k, v, g, q_bias, pb, mask, out, N, nq, H, rsqrtf((float)D),
+                                                   inf, rows_per_bias);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
@@ -237,9 +239,9 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, in
     if ((rc = linear_bf16(an, (const bf16*)p->w_g, g, rows, c_a, c_a, st))) return rc;
     const long long rpb = Ba / Bz;
     if (d == 24)
-        rc = launch_attn<24>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, H, inf, rpb, st);
+        rc = launch_attn<24>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, inf, rpb, st);
     else
-        rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, H, inf, rpb, st);
+        rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, inf, rpb, st);
     if (rc) return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
     {
@@ -247,6 +249,52 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, in
         const long long n2 = rows * c_a / 2;
         residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
             y, (flags & OF3_FLAG_ADD_RESIDUAL) ? a : nullptr, nullptr, out, rows, c_a);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+// The same layer for a window of R query rows [row0, row0 + R) of one sample: keys and values come from
+// all N rows of `a`, queries / gate / output only from the window; pair_bias_rows is [H][R][N] (the
+// projected pair bias of exactly those rows) and out_rows is [R][c_a]. Used when the pair tensor, and
+// with it the pair bias, is split by rows over several GPUs.
+int attn_pair_bias_rows(const bf16* a, const float* pair_bias_rows, const bf16* mask, bf16* out_rows, int N, int row0,
+                        int R, int c_a, int H, int d, float inf, int flags, const of3_attn_pair_bias_params* p,
+                        Arena& ws, cudaStream_t st) {
+    bf16* an = (bf16*)ws.take((size_t)N * c_a * sizeof(bf16));
+    bf16* k = (bf16*)ws.take((size_t)N * c_a * sizeof(bf16));
+    bf16* v = (bf16*)ws.take((size_t)N * c_a * sizeof(bf16));
+    bf16* q = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
+    bf16* g = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
+    bf16* og = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
+    bf16* y = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
+    if (!ws.base) return OF3_OK;
+    OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "attn_pair_bias_rows: workspace too small (%zu needed)", ws.off);
+    OF3_REQUIRE(row0 >= 0 && R > 0 && row0 + R <= N, OF3_ERR_ARG, "attn_pair_bias_rows: window [%d, %d) outside %d rows",
+                row0, row0 + R, N);
+    int rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        ln_rows_kernel<<<(unsigned)((N + 7) / 8), 256, 0, st>>>(a, (const bf16*)p->ln_a_w, (const bf16*)p->ln_a_b, an, N,
+                                                                c_a);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    const bf16* an_w = an + (long long)row0 * c_a;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_k, k, N, c_a, c_a, st))) return rc;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_v, v, N, c_a, c_a, st))) return rc;
+    if ((rc = linear_bf16(an_w, (const bf16*)p->w_q, q, R, c_a, c_a, st))) return rc;
+    if ((rc = linear_bf16(an_w, (const bf16*)p->w_g, g, R, c_a, c_a, st))) return rc;
+    if (d == 24)
+        rc = launch_attn<24>(q, k, v, g, (const bf16*)p->b_q, pair_bias_rows, mask, og, 1, N, R, H, inf, 1, st);
+    else
+        rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias_rows, mask, og, 1, N, R, H, inf, 1, st);
+    if (rc) return rc;
+    if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, R, c_a, c_a, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = (long long)R * c_a / 2;
+        residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
+            y, (flags & OF3_FLAG_ADD_RESIDUAL) ? a + (long long)row0 * c_a : nullptr, nullptr, out_rows, R, c_a);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;

@@ -69,7 +69,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmWbg, const __nv_bfloat16* __restrict__ mask,
                  const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
                  __nv_bfloat16* __restrict__ a_t, __nv_bfloat16* __restrict__ b_t, int B, int R,
-                 int N, int ld, int* status) {
+                 int N, int ld, int group_shift, long long group_stride, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -204,7 +204,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             float m = 1.0f;
             if (valid && mask != nullptr) {
                 const long long lin = kOutgoing ? ((long long)(tc.b * R + tc.fixed) * N + k)
-                                                : ((long long)(tc.b * N + k) * N + tc.fixed);
+                                                : ((long long)(tc.b * N + k) * R + tc.fixed);
                 m = __bfloat162float(mask[lin]);
             }
             for (int q = 0; q < 2; ++q) {
@@ -214,8 +214,13 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                     break;
                 }
                 tc_fence_after_sync();
+                // channel c lives at (c >> group_shift) * group_stride + (c & group_mask) * R * ld: one
+                // contiguous plane [128][R][ld] by default, or one group of channels per destination
+                // rank when the planes are about to be exchanged
+                const long long cs = (long long)R * ld;
                 __nv_bfloat16* dst = (q == 0 ? a_t : b_t) +
-                                     ((long long)tc.b * kC * R + tc.fixed) * ld + k;
+                                     (long long)tc.b * ((kC >> group_shift) * group_stride) +
+                                     (long long)tc.fixed * ld + k;
                 const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + q * 256;
 #pragma unroll 1
                 for (int cb = 0; cb < 4; ++cb) {
@@ -225,9 +230,16 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                     tmem_ld_wait();
                     if (valid) {
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) {
-                            const float v = m * __uint_as_float(p[e]) * sigmoid_fast(__uint_as_float(g[e]));
-                            dst[(long long)(cb * 32 + e) * R * ld] = __float2bfloat16_rn(v);
+                        for (int hf = 0; hf < 2; ++hf) {  // groups hold >= 16 channels: no boundary inside a half
+                            const int c0 = cb * 32 + hf * 16;
+                            __nv_bfloat16* d0 = dst + (long long)(c0 >> group_shift) * group_stride +
+                                                (long long)(c0 & ((1 << group_shift) - 1)) * cs;
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                const float v = m * __uint_as_float(p[hf * 16 + e]) *
+                                                sigmoid_fast(__uint_as_float(g[hf * 16 + e]));
+                                d0[(long long)e * cs] = __float2bfloat16_rn(v);
+                            }
                         }
                     }
                 }
@@ -505,21 +517,28 @@ static int line_tmap(CUtensorMap* m, const void* z, int B, int R, int N) {
     return make_tmap_bf16(m, z, 3, dims, str, box, 1);
 }
 
-// a_t[(b*128 + c)][line][k], b_t likewise, from R lines of N positions per sample.
-// transposed_walk (whole square tensors only, R == N): the tile walks z along its first index, which
-// makes the incoming update the same K-major contraction as the outgoing one.
+// a_t[(b*128 + c)][line][k], b_t likewise, from R lines of N positions per sample: z is [B][R][N][128].
+// transposed_walk: z is [B][N][R][128] and a line runs along its FIRST index (line = second index),
+// which makes the incoming update the same K-major contraction as the outgoing one; with R != N this
+// is a row shard of N rows seen as R lines of N positions each.
+// groups > 1: the 128 channels are written as `groups` equal groups, group q of a_t at
+// a_t + q * group_stride (b_t likewise), so that each group can be sent to another rank as one block.
 int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* a_t, __nv_bfloat16* b_t,
                    int B, int R, int N, int ld, bool transposed_walk, const of3_trimul_params* p,
-                   cudaStream_t st) {
+                   cudaStream_t st, int groups, long long group_stride) {
     OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "trimul: z must be 16-byte aligned");
-    OF3_REQUIRE(!transposed_walk || R == N, OF3_ERR_SHAPE, "trimul: transposed walk needs the whole tensor");
+    OF3_REQUIRE(groups == 1 || groups == 2 || groups == 4 || groups == 8, OF3_ERR_ARG,
+                "trimul: channel groups must be 1, 2, 4 or 8 (got %d)", groups);
+    int group_shift = 7;
+    for (int g = groups; g > 1; g >>= 1) --group_shift;
+    if (groups == 1) group_stride = (long long)kC * R * ld;
     int rc;
     CUtensorMap tmZ, tmW[4];
     if (!transposed_walk) {
         if ((rc = line_tmap(&tmZ, z, B, R, N))) return rc;
-    } else {  // {c, second, first, b}
-        uint64_t dims[4] = {128, (uint64_t)N, (uint64_t)N, (uint64_t)B};
-        uint64_t str[3] = {256, (uint64_t)N * 256, (uint64_t)N * N * 256};
+    } else {  // {c, second (line), first (position), b}
+        uint64_t dims[4] = {128, (uint64_t)R, (uint64_t)N, (uint64_t)B};
+        uint64_t str[3] = {256, (uint64_t)R * 256, (uint64_t)N * R * 256};
         uint32_t box[4] = {64, 1, 128, 1};
         if ((rc = make_tmap_bf16(&tmZ, z, 4, dims, str, box, 1))) return rc;
     }
@@ -533,11 +552,11 @@ int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
     if (!transposed_walk)
         trimul_in_kernel<true><<<grid, 320, InSmem::kDyn, st>>>(
             tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, device_status_ptr());
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, device_status_ptr());
     else
         trimul_in_kernel<false><<<grid, 320, InSmem::kDyn, st>>>(
             tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, device_status_ptr());
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
@@ -552,6 +571,16 @@ int trimul_finish(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat1
     int rc = contract_nt_bf16(a_t, b_t, x_t, B * kC, R, N, N, ld, ld, ld, (long long)R * ld, (long long)N * ld,
                               (long long)R * ld, st);
     if (rc) return rc;
+    return trimul_output(z, out, x_t, B, R, N, ld, add_residual, p, st);
+}
+
+// LN_out(x) -> linear_z, gate from LN_in(z), residual: the part of the update after the contraction,
+// on R lines of z with x_t[b*128 + c][line][j] (pitch ld)
+int trimul_output(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat16* x_t, int B, int R, int N, int ld,
+                  int add_residual, const of3_trimul_params* p, cudaStream_t st) {
+    OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)x_t & 15) == 0, OF3_ERR_ALIGN,
+                "trimul: z/out/x must be 16-byte aligned");
+    int rc;
     CUtensorMap tmZ, tmOut, tmX, tmWg, tmWz;
     if ((rc = line_tmap(&tmZ, z, B, R, N))) return rc;
     if ((rc = line_tmap(&tmOut, out, B, R, N))) return rc;

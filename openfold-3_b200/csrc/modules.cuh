@@ -40,7 +40,9 @@ int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* ou
 // phases of the two layers above on R lines of N positions (R == N: whole tensor; R = N / P: a row shard)
 int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* a_t, __nv_bfloat16* b_t,
                    int B, int R, int N, int ld, bool transposed_walk, const of3_trimul_params* p,
-                   cudaStream_t st);
+                   cudaStream_t st, int groups = 1, long long group_stride = 0);
+int trimul_output(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat16* x_t, int B, int R, int N, int ld,
+                  int add_residual, const of3_trimul_params* p, cudaStream_t st);
 int trimul_finish(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat16* a_t,
                   const __nv_bfloat16* b_t, __nv_bfloat16* x_t, int B, int R, int N, int ld, int add_residual,
                   const of3_trimul_params* p, cudaStream_t st);
@@ -60,6 +62,9 @@ bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_z, int H, in
 int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
                    int Ba, int Bz, int N, int c_a, int H, int d, float inf, int flags,
                    const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st, const float* pair_bias);
+int attn_pair_bias_rows(const __nv_bfloat16* a, const float* pair_bias_rows, const __nv_bfloat16* mask,
+                        __nv_bfloat16* out_rows, int N, int row0, int R, int c_a, int H, int d, float inf, int flags,
+                        const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st);
 bool transition_wide_supported(int c, int n);
 int transition_wide(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows, int c,
                     int n, int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
@@ -67,6 +72,6 @@ int transition_wide(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bflo
 
 int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
                      int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
-                     long long o_bs, cudaStream_t stream);
+                     long long o_bs, cudaStream_t stream, int rows_per_block = 0, long long row_block_stride = 0);
 
 }  // namespace of3

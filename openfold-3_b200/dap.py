@@ -1,16 +1,24 @@
 """Row-sharded ("DAP") Pairformer trunk over the GPUs of one node.
 
-The pair tensor z[N, N, C] is split by rows over P ranks (N divisible by P); the single
-representation and the masks are replicated. Per block (reference order,
+The pair tensor z[N, N, C] is split by rows over P ranks (P in 1, 2, 4, 8; N divisible by P); the
+single representation and the masks are replicated. Per block (reference order,
 openfold3/core/model/latent/base_blocks.py:453-478 and pairformer.py:177-211):
 
-  tri_mul_out    project local rows -> a, b (channel-major) | ALL-GATHER b | contract + finish
-  tri_mul_in     ALL-TO-ALL transpose of z (copy) -> project on the transposed shard
-                 (a'[i,k] = a[k,i]) | ALL-GATHER b' | contract + finish on the ORIGINAL rows
-  tri_att_start  project q,k,v + local rows of the pair bias | ALL-GATHER bias | attention + finish
+  tri_mul_out    project local rows -> a, b, channel-major, one group of 128/P channels per rank
+                 | ALL-TO-ALL rows -> channels | contract this rank's channels over all rows
+                 | ALL-TO-ALL channels -> rows | LayerNorm / linear / gate / residual on the local rows
+  tri_mul_in     the same with a transposed walk of the projection kernel over the local rows
+                 (a'[i, k] = a[k, i]): no transposed copy of z is needed
+  tri_att_start  project q, k, v + local rows of the pair bias | ALL-GATHER bias | attention + finish
   tri_att_end    ALL-TO-ALL transpose of z -> the same on the transposed shard, in place there,
   transition     pointwise, still on the transposed shard | ALL-TO-ALL transpose back
-  single track   pair-bias projection of the local rows | ALL-GATHER | (replicated, small) update of s
+  single track   pair-bias projection of the local rows (main stream), then on a SIDE stream:
+                 attention of the local query rows against all keys, single transition on those rows,
+                 ALL-GATHER of the updated rows of s. z never depends on s, so the side stream runs
+                 concurrently with the next block's pair stack.
+
+Exchanging channel groups (each rank sends/receives ~3 N^2 C / P elements per update) replaces an
+all-gather of b (N^2 C elements received by every rank, independent of P).
 
 The reference has no model-parallel path (only data-parallel DDP / ZeRO), so this is new design
 judged against the single-GPU result. Collectives go through ``torch.distributed`` (NCCL on GPUs,
@@ -21,6 +29,7 @@ backend with the same phase semantics, which lets the exchange logic be checked 
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 
 import torch
@@ -44,15 +53,62 @@ def all_gather_lines(x_loc: torch.Tensor, world: int, group=None) -> torch.Tenso
     return buf.view(world, G, R, L).permute(1, 0, 2, 3).reshape(G, world * R, L).contiguous()
 
 
-def all_to_all_transpose(x_loc: torch.Tensor, world: int, group=None) -> torch.Tensor:
+def exchange_blocks(x: torch.Tensor, world: int, group=None) -> torch.Tensor:
+    """x [world, ...]: block q goes to rank q; returns [world, ...] with block q received from rank q."""
+    if world == 1:
+        return x
+    recv = torch.empty_like(x)
+    dist.all_to_all_single(recv, x.contiguous(), group=group)
+    return recv
+
+
+def all_to_all_transpose(x_loc: torch.Tensor, world: int, group=None, ops=None) -> torch.Tensor:
     """Row shard [R, N, C] of X[N, N, C] -> row shard [R, N, C] of X^T (y[i, k] = X[k, r*R + i])."""
     if world == 1:
         return x_loc.transpose(0, 1).contiguous()
     R, N, C = x_loc.shape
-    send = x_loc.view(R, world, R, C).permute(1, 0, 2, 3).contiguous()  # [dest][k_loc][i_loc][C]
-    recv = torch.empty_like(send)
-    dist.all_to_all_single(recv, send, group=group)                    # [src][k_loc][i_loc][C]
-    return recv.permute(2, 0, 1, 3).reshape(R, N, C).contiguous()
+    copy = getattr(ops, "copy_rows", None)
+    e = x_loc.element_size()
+    if copy is None:
+        send = x_loc.view(R, world, R, C).permute(1, 0, 2, 3).contiguous()  # [dest][k_loc][i_loc][C]
+    else:
+        send = torch.empty((world, R, R, C), dtype=x_loc.dtype, device=x_loc.device)
+        copy(x_loc, send, (1, world, R), (0, R * C * e, N * C * e), (0, R * R * C * e, R * C * e), R * C * e)
+    recv = exchange_blocks(send, world, group)                              # [src][k_loc][i_loc][C]
+    if copy is None:
+        return recv.permute(2, 0, 1, 3).reshape(R, N, C).contiguous()
+    out = torch.empty_like(x_loc)
+    copy(recv, out, (world, R, R), (R * R * C * e, R * C * e, C * e), (R * C * e, C * e, N * C * e), C * e)
+    return out
+
+
+def regroup_ab(recv: torch.Tensor, N: int, R: int, incoming: bool, copy=None) -> torch.Tensor:
+    """The received blocks of the rows -> channels exchange as the contraction's operands.
+
+    outgoing: recv [P, 2, C, R, ld(N)]  (block = a source rank's R lines)      -> [2, C, N, ld(N)]
+    incoming: recv [P, 2, C, N, ld(R)]  (block = a source rank's R positions k) -> [2, C, N, ld(N)]
+    """
+    P, _, C = recv.shape[:3]
+    ldn = _pitch(N, 8)
+    if P == 1:
+        return recv.view(2, C, N, ldn)
+    out = torch.empty((2, C, N, ldn), dtype=recv.dtype, device=recv.device)
+    e = recv.element_size()
+    if not incoming:
+        if copy is None:
+            out.view(2 * C, P, R, ldn).copy_(recv.view(P, 2 * C, R, ldn).permute(1, 0, 2, 3))
+        else:
+            copy(recv, out, (P, 2 * C, R), (2 * C * R * ldn * e, R * ldn * e, ldn * e),
+                 (R * ldn * e, N * ldn * e, ldn * e), ldn * e)
+    else:
+        ldr = recv.shape[-1]
+        if copy is None:
+            src = recv.view(P, 2 * C, N, ldr)[..., :R].permute(1, 2, 0, 3).reshape(2 * C, N, N)
+            out.view(2 * C, N, ldn)[:, :, :N].copy_(src)
+        else:
+            copy(recv, out, (P, 2 * C, N), (2 * C * N * ldr * e, N * ldr * e, ldr * e),
+                 (R * e, N * ldn * e, ldn * e), R * e)
+    return out
 
 
 # ----------------------------------------------------------------------------- CUDA backend
@@ -62,29 +118,68 @@ class CudaOps:
     def __init__(self, device):
         self.device = device
         self.l = lib.load()
+        self._side = None
 
     def _st(self):
         return torch.cuda.current_stream(self.device).cuda_stream
 
-    def trimul_project(self, z_loc, mask_rows, mod):
+    # ---- streams: the single track runs on a side stream, ordered against the main one by events
+    @contextlib.contextmanager
+    def side(self):
+        """Run the body on the side stream, after everything queued so far on the current stream."""
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.device)
+        self._side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(self._side):
+            yield
+
+    def mark_side(self):
+        """An event after everything queued so far on the side stream."""
+        ev = torch.cuda.Event()
+        ev.record(self._side)
+        return ev
+
+    def wait_mark(self, ev):
+        if ev is not None:
+            torch.cuda.current_stream(self.device).wait_event(ev)
+
+    # ---- repack
+    def copy_rows(self, src, dst, n, s, t, row_bytes):
+        lib._check(self.l.of3_copy_rows_3d(src.data_ptr(), dst.data_ptr(), n[0], n[1], n[2], s[0], s[1], s[2], t[0],
+                                           t[1], t[2], row_bytes, self._st()), "of3_copy_rows_3d")
+
+    # ---- triangle update
+    def trimul_project(self, z_loc, mask_rows, mod, world, incoming):
+        """-> ab [world, 2, 128 / world, lines, ld]; see of3_dap_trimul_project."""
         R, N, _ = z_loc.shape
-        ld = _pitch(N, 8)
-        a_t = torch.empty((128, R, ld), dtype=z_loc.dtype, device=z_loc.device)
-        b_t = torch.empty((128, R, ld), dtype=z_loc.dtype, device=z_loc.device)
+        lines, positions = (N, R) if incoming else (R, N)
+        ld = _pitch(positions, 8)
+        ab = torch.empty((world, 2, 128 // world, lines, ld), dtype=z_loc.dtype, device=z_loc.device)
         p = lib.TrimulParams(*[t.data_ptr() for t in mod._params(z_loc.dtype, z_loc.device)])
-        lib._check(self.l.of3_dap_trimul_project(z_loc.data_ptr(), lib._ptr(mask_rows), a_t.data_ptr(),
-                                                 b_t.data_ptr(), R, N, ctypes.byref(p), self._st()),
+        lib._check(self.l.of3_dap_trimul_project(z_loc.data_ptr(), lib._ptr(mask_rows), ab.data_ptr(), lines,
+                                                 positions, 1 if incoming else 0, world, ctypes.byref(p), self._st()),
                    "of3_dap_trimul_project")
-        return a_t, b_t
+        return ab
 
-    def trimul_finish(self, z_loc, a_t, b_all, mod):
+    def regroup_ab(self, recv, N, R, incoming):
+        return regroup_ab(recv, N, R, incoming, copy=self.copy_rows)
+
+    def trimul_contract(self, ab_all, N, R):
+        """ab_all [2, C, N, ld] -> x_blocks [N / R, C, R, ld]."""
+        C = ab_all.shape[1]
+        xb = torch.empty((N // R, C, R, ab_all.shape[-1]), dtype=ab_all.dtype, device=ab_all.device)
+        lib._check(self.l.of3_dap_trimul_contract(ab_all.data_ptr(), xb.data_ptr(), N, C, R, self._st()),
+                   "of3_dap_trimul_contract")
+        return xb
+
+    def trimul_output(self, z_loc, x_t, mod):
         R, N, _ = z_loc.shape
-        x = torch.empty_like(a_t)
         p = lib.TrimulParams(*[t.data_ptr() for t in mod._params(z_loc.dtype, z_loc.device)])
-        lib._check(self.l.of3_dap_trimul_finish(z_loc.data_ptr(), z_loc.data_ptr(), a_t.data_ptr(), b_all.data_ptr(),
-                                                x.data_ptr(), R, N, lib.FLAG_ADD_RESIDUAL, ctypes.byref(p),
-                                                self._st()), "of3_dap_trimul_finish")
+        lib._check(self.l.of3_dap_trimul_output(z_loc.data_ptr(), z_loc.data_ptr(), x_t.data_ptr(), R, N,
+                                                lib.FLAG_ADD_RESIDUAL, ctypes.byref(p), self._st()),
+                   "of3_dap_trimul_output")
 
+    # ---- triangle attention
     def triattn_project(self, z_loc, mod):
         R, N, _ = z_loc.shape
         ldn = _pitch(N, 64)
@@ -113,34 +208,37 @@ class CudaOps:
     def transition(self, x_rows, mask_rows, mod):
         mod._run(x_rows, mask_rows, in_place=True)
 
-    def pair_bias_project(self, z_loc, apb):
+    # ---- single track
+    def pair_bias_project(self, z_loc, apb, out=None):
         R, N, _ = z_loc.shape
         dt, dev = z_loc.dtype, z_loc.device
         prm = apb._params(dt, dev)
         ln_w, ln_b, w = prm[8], prm[9], prm[10]
-        out = torch.empty((16, R, N), dtype=torch.float32, device=dev)
+        if out is None:
+            out = torch.empty((16, R, N), dtype=torch.float32, device=dev)
         lib._check(self.l.of3_pair_bias_project(z_loc.data_ptr(), lib._ptr(ln_w), lib._ptr(ln_b), w.data_ptr(),
                                                 out.data_ptr(), R * N, 128, 16, lib.dtype_code(dt), self._st()),
                    "of3_pair_bias_project")
         return out
 
-    def single_track(self, s, zb_all, single_mask, block, mask_trans=True):
-        """s [1, N, c_s] updated in place with the already projected pair bias [16, N, N] (fp32)."""
+    def single_rows(self, s_full, zb_rows, single_mask, block, row0, R, mask_trans=True):
+        """Rows [row0, row0 + R) of the updated single representation: s_full [N, c_s] (all rows, for the
+        keys and values), zb_rows [16, R, N] the projected pair bias of those rows (fp32) -> [R, c_s]."""
         apb = block.attn_pair_bias
-        N = s.shape[-2]
-        dt, dev = s.dtype, s.device
-        a = s.view(1, N, apb.c_q)
-        m = None if single_mask is None else single_mask.to(dt).reshape(1, N).contiguous()
+        N = s_full.shape[0]
+        dt, dev = s_full.dtype, s_full.device
+        m = None if single_mask is None else single_mask.to(dt).reshape(N).contiguous()
         p = lib.AttnPairBiasParams(*[lib._ptr(t) for t in apb._params(dt, dev)])
-        flags = lib.FLAG_ADD_RESIDUAL
-        nbytes = self.l.of3_attn_pair_bias_workspace_bytes(1, 1, N, apb.c_q, 0, 128, apb.no_heads, apb.c_hidden,
-                                                           lib.dtype_code(dt), flags)
-        ws = lib.workspace(nbytes, dev)
-        lib._check(self.l.of3_attn_pair_bias_forward_prebias(
-            a.data_ptr(), zb_all.data_ptr(), None, lib._ptr(m), a.data_ptr(), 1, 1, N, apb.c_q, 0, apb.no_heads,
-            apb.c_hidden, float(apb.inf), lib.dtype_code(dt), flags, ctypes.byref(p), ws.data_ptr(), ws.numel(),
-            self._st()), "of3_attn_pair_bias_forward_prebias")
-        block.single_transition._run(s, single_mask if mask_trans else None, in_place=True)
+        nbytes = self.l.of3_attn_pair_bias_rows_workspace_bytes(N, R, apb.c_q)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+        out = torch.empty((R, apb.c_q), dtype=dt, device=dev)
+        lib._check(self.l.of3_attn_pair_bias_forward_rows(
+            s_full.data_ptr(), zb_rows.data_ptr(), lib._ptr(m), out.data_ptr(), N, row0, R, apb.c_q, apb.no_heads,
+            apb.c_hidden, float(apb.inf), lib.dtype_code(dt), lib.FLAG_ADD_RESIDUAL, ctypes.byref(p), ws.data_ptr(),
+            ws.numel(), self._st()), "of3_attn_pair_bias_forward_rows")
+        mrows = None if (m is None or not mask_trans) else m[row0:row0 + R]
+        block.single_transition._run(out, mrows, in_place=True)
+        return out
 
 
 # ----------------------------------------------------------------------------- orchestration
@@ -149,57 +247,89 @@ class DapPairFormerStack:
 
     ``__call__(s, z, single_mask, pair_mask)`` takes the full (replicated) tensors of ONE sample
     ([1, N, C] / [1, N, N, C]) and returns the full updated (s, z) on every rank.
+    ``side_group``: a second process group (its own communicator) for the single track's all-gather,
+    which is issued from the side stream while the main stream's exchanges are in flight; created
+    here when ``world > 1`` and none is given (every rank must construct the runner at the same point).
     """
 
-    def __init__(self, stack, world: int, rank: int, group=None, ops=None):
+    def __init__(self, stack, world: int, rank: int, group=None, ops=None, side_group=None):
+        assert world in (1, 2, 4, 8), "the triangle update splits its 128 channels over 1, 2, 4 or 8 ranks"
         self.stack, self.world, self.rank, self.group = stack, world, rank, group
         self.ops = ops
+        self.side_group = side_group
+        if world > 1 and side_group is None:
+            self.side_group = dist.new_group(ranks=None if group is None else dist.get_process_group_ranks(group))
 
     def shard(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
         R = t.shape[dim] // self.world
         return t.narrow(dim, self.rank * R, R)
 
+    def _trimul(self, z_loc, mask_rows, mod, incoming: bool):
+        ops, P, g = self.ops, self.world, self.group
+        R, N, _ = z_loc.shape
+        ab = ops.trimul_project(z_loc, mask_rows, mod, P, incoming)           # [P, 2, C, lines, ld]
+        ab_all = ops.regroup_ab(exchange_blocks(ab, P, g), N, R, incoming)    # [2, C, N, ld]
+        xb = ops.trimul_contract(ab_all, N, R)                                # [P, C, R, ld]
+        x_t = exchange_blocks(xb, P, g)                                       # = [128, R, ld]
+        ops.trimul_output(z_loc, x_t, mod)
+
     def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):
         """One PairBlock on the local row shard (in place); returns the shard."""
         ops, P, g = self.ops, self.world, self.group
-        # outgoing
-        a_t, b_loc = ops.trimul_project(z_loc, mask_rows, pb.tri_mul_out)
-        ops.trimul_finish(z_loc, a_t, all_gather_lines(b_loc, P, g), pb.tri_mul_out)
-        # incoming: the projections come from the transposed shard, the update lands on the original rows
-        zT = all_to_all_transpose(z_loc, P, g)
-        a_t, b_loc = ops.trimul_project(zT, maskT_rows, pb.tri_mul_in)
-        ops.trimul_finish(z_loc, a_t, all_gather_lines(b_loc, P, g), pb.tri_mul_in)
+        self._trimul(z_loc, mask_rows, pb.tri_mul_out, incoming=False)
+        self._trimul(z_loc, mask_rows, pb.tri_mul_in, incoming=True)
         # starting node
         qkv, tb_loc = ops.triattn_project(z_loc, pb.tri_att_start)
         ops.triattn_finish(z_loc, mask_rows, qkv, all_gather_lines(tb_loc, P, g), pb.tri_att_start)
         # ending node and transition on the transposed shard, then back
-        zT = all_to_all_transpose(z_loc, P, g)
+        zT = all_to_all_transpose(z_loc, P, g, ops)
         qkv, tb_loc = ops.triattn_project(zT, pb.tri_att_end)
         ops.triattn_finish(zT, maskT_rows, qkv, all_gather_lines(tb_loc, P, g), pb.tri_att_end)
         ops.transition(zT, maskT_rows if mask_trans else None, pb.pair_transition)
-        z_new = all_to_all_transpose(zT, P, g)
+        z_new = all_to_all_transpose(zT, P, g, ops)
         z_loc.copy_(z_new)
         return z_loc
+
+    def _gather_rows(self, s_rows):
+        if self.world == 1:
+            return s_rows
+        full = torch.empty((self.world * s_rows.shape[0], s_rows.shape[1]), dtype=s_rows.dtype, device=s_rows.device)
+        dist.all_gather_into_tensor(full, s_rows.contiguous(), group=self.side_group)
+        return full
 
     def __call__(self, s, z, single_mask, pair_mask, _mask_trans=True):
         assert z.shape[0] == 1 and z.dim() == 4, "DAP runs one sample: z [1, N, N, C]"
         N = z.shape[1]
         assert N % self.world == 0, f"N_token {N} must be divisible by the {self.world} ranks"
+        ops = self.ops
+        R = N // self.world
         z_loc = self.shard(z[0]).contiguous().clone()
-        s = s.clone(memory_format=torch.contiguous_format)
+        s_full = s[0].clone(memory_format=torch.contiguous_format)
         pm = pair_mask[0].to(z.dtype)
         mask_rows = self.shard(pm, 0).contiguous()
         maskT_rows = self.shard(pm, 1).transpose(0, 1).contiguous()
         sm = None if single_mask is None else single_mask[0]
-        for block in self.stack.blocks:
+        side = getattr(ops, "side", contextlib.nullcontext)
+        mark = getattr(ops, "mark_side", lambda: None)
+        wait = getattr(ops, "wait_mark", lambda ev: None)
+        zb_buf, zb_free = [None, None], [None, None]
+        for i, block in enumerate(self.stack.blocks):
             self.pair_block(z_loc, mask_rows, maskT_rows, block.pair_stack, _mask_trans)
-            zb_loc = self.ops.pair_bias_project(z_loc, block.attn_pair_bias)          # [H, R, N]
-            zb_all = all_gather_lines(zb_loc, self.world, self.group)                  # [H, N, N]
-            self.ops.single_track(s, zb_all, sm, block, _mask_trans)
+            slot = i & 1
+            wait(zb_free[slot])  # the side stream has finished with this buffer (two blocks ago)
+            zb_buf[slot] = ops.pair_bias_project(z_loc, block.attn_pair_bias, out=zb_buf[slot])   # [H, R, N]
+            with side():
+                s_rows = ops.single_rows(s_full, zb_buf[slot], sm, block, self.rank * R, R, _mask_trans)
+                s_full = self._gather_rows(s_rows)
+                zb_free[slot] = mark()
+        wait(zb_free[0])
+        wait(zb_free[1])
+        if s_full.is_cuda:
+            s_full.record_stream(torch.cuda.current_stream(s_full.device))
         if self.world > 1:
             z_full = torch.empty((N,) + tuple(z_loc.shape[1:]), dtype=z_loc.dtype, device=z_loc.device)
             dist.all_gather_into_tensor(z_full, z_loc, group=self.group)
             z_full = z_full.reshape(1, N, N, z_loc.shape[-1])
         else:
             z_full = z_loc.unsqueeze(0)
-        return s, z_full
+        return s_full.unsqueeze(0), z_full

@@ -70,8 +70,13 @@ SIGNATURES = {
                                             c_void_p]),
     "of3_dap_pitch": (c_int, [c_int, c_int]),
     "of3_dap_triattn_image_elems": (c_longlong, [c_int, c_int]),
-    "of3_dap_trimul_project": (c_int, [c_void_p] * 4 + [c_int, c_int, ctypes.POINTER(TrimulParams), c_void_p]),
-    "of3_dap_trimul_finish": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, ctypes.POINTER(TrimulParams), c_void_p]),
+    "of3_dap_trimul_project": (c_int, [c_void_p] * 3 + [c_int] * 4 + [ctypes.POINTER(TrimulParams), c_void_p]),
+    "of3_dap_trimul_contract": (c_int, [c_void_p] * 2 + [c_int] * 3 + [c_void_p]),
+    "of3_dap_trimul_output": (c_int, [c_void_p] * 3 + [c_int] * 3 + [ctypes.POINTER(TrimulParams), c_void_p]),
+    "of3_copy_rows_3d": (c_int, [c_void_p] * 2 + [c_int] * 3 + [c_longlong] * 6 + [c_int, c_void_p]),
+    "of3_attn_pair_bias_rows_workspace_bytes": (c_size_t, [c_int] * 3),
+    "of3_attn_pair_bias_forward_rows": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_float, c_int, c_int,
+                                                ctypes.POINTER(AttnPairBiasParams), c_void_p, c_size_t, c_void_p]),
     "of3_dap_triattn_project": (c_int, [c_void_p] * 5 + [c_int, c_int, ctypes.POINTER(TriattnParams), c_void_p]),
     "of3_dap_triattn_finish": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_int,
                                        ctypes.POINTER(TriattnParams), c_void_p]),

@@ -1,8 +1,8 @@
 """Row-sharded (DAP) orchestration on CPU: two gloo ranks with an oracle compute backend.
 
-The exchange logic of ``openfold3_b200.dap`` (row shards, all-gathers of the channel-major b / pair
-bias, all-to-all transposes for the incoming update and the ending-node attention, the replicated
-single track) is backend independent; here the per-phase compute is the CPU oracle, so the test
+The exchange logic of ``openfold3_b200.dap`` (row shards, the rows <-> channels all-to-alls around the
+triangle contraction, all-gathers of the attention bias, all-to-all transposes for the ending-node
+attention, the query-sharded single track) is backend independent; here the per-phase compute is the CPU oracle, so the test
 checks that sharding + collectives reproduce the unsharded oracle bit-for-rounding, without a GPU.
 """
 
@@ -37,20 +37,34 @@ class OracleOps:
     def _pad(t, ld):
         return F.pad(t, (0, ld - t.shape[-1]))
 
-    def trimul_project(self, z_loc, mask_rows, mod):
+    def trimul_project(self, z_loc, mask_rows, mod, world, incoming):
         P, o = self._P(mod), self.o
-        N = z_loc.shape[1]
         zn = o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1])
         m = mask_rows.unsqueeze(-1)
         a = m * torch.sigmoid(o._lin(zn, P, "linear_a_g.")) * o._lin(zn, P, "linear_a_p.")
         b = m * torch.sigmoid(o._lin(zn, P, "linear_b_g.")) * o._lin(zn, P, "linear_b_p.")
-        ld = (N + 7) // 8 * 8
-        return self._pad(a.permute(2, 0, 1), ld).contiguous(), self._pad(b.permute(2, 0, 1), ld).contiguous()
+        # channel-major planes [c][line][position]; incoming: a line runs along the local rows
+        perm = (2, 1, 0) if incoming else (2, 0, 1)
+        a, b = a.permute(*perm), b.permute(*perm)
+        ld = (a.shape[-1] + 7) // 8 * 8
+        ab = torch.stack([self._pad(a, ld), self._pad(b, ld)])                       # [2, 128, lines, ld]
+        C = 128 // world
+        return ab.view(2, world, C, ab.shape[2], ld).permute(1, 0, 2, 3, 4).contiguous()  # [P, 2, C, lines, ld]
 
-    def trimul_finish(self, z_loc, a_t, b_all, mod):
+    def regroup_ab(self, recv, N, R, incoming):
+        import cases
+        return cases.pkg.dap.regroup_ab(recv, N, R, incoming)
+
+    def trimul_contract(self, ab_all, N, R):
+        x = torch.einsum("cik,cjk->cij", ab_all[0][:, :, :N], ab_all[1][:, :, :N])    # [C, N, N]
+        x = self._pad(x, ab_all.shape[-1])
+        C = x.shape[0]
+        return x.view(C, N // R, R, x.shape[-1]).permute(1, 0, 2, 3).contiguous()     # [P, C, R, ld]
+
+    def trimul_output(self, z_loc, x_t, mod):
         P, o = self._P(mod), self.o
-        N = z_loc.shape[1]
-        x = torch.einsum("cik,cjk->ijc", a_t[:, :, :N], b_all[:, :, :N])
+        R, N, _ = z_loc.shape
+        x = x_t.reshape(128, R, -1)[:, :, :N].permute(1, 2, 0)
         x = o._lin(o._ln(x, P, "layer_norm_out.", x.shape[-1]), P, "linear_z.")
         g = torch.sigmoid(o._lin(o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1]), P, "linear_g."))
         z_loc += x * g
@@ -74,18 +88,19 @@ class OracleOps:
     def transition(self, x_rows, mask_rows, mod):
         x_rows += self.o.swiglu_transition(x_rows, mask_rows, self._P(mod), "")
 
-    def pair_bias_project(self, z_loc, apb):
+    def pair_bias_project(self, z_loc, apb, out=None):
         P, o = self._P(apb), self.o
         return o._lin(o._ln(z_loc, P, "layer_norm_z.", z_loc.shape[-1]), P, "linear_z.").permute(2, 0, 1).contiguous()
 
-    def single_track(self, s, zb_all, single_mask, block, mask_trans=True):
+    def single_rows(self, s_full, zb_rows, single_mask, block, row0, R, mask_trans=True):
         apb, o = block.attn_pair_bias, self.o
         P = self._P(apb)
-        an = o._ln(s, P, "layer_norm_a.", s.shape[-1])
-        mask_bias = (apb.inf * (single_mask - 1))[None, None, None, :]
+        an = o._ln(s_full, P, "layer_norm_a.", s_full.shape[-1])
+        mask_bias = (apb.inf * (single_mask - 1))[None, None, :]
         mha = {k[len("mha."):]: v for k, v in P.items() if k.startswith("mha.")}
-        s += o.attention(an, an, [mask_bias, zb_all.unsqueeze(0)], mha, "", apb.no_heads)
-        s += o.swiglu_transition(s, single_mask[None] if mask_trans else None, self._P(block.single_transition), "")
+        rows = s_full[row0:row0 + R] + o.attention(an[row0:row0 + R], an, [mask_bias, zb_rows], mha, "", apb.no_heads)
+        m = single_mask[row0:row0 + R] if mask_trans else None
+        return rows + o.swiglu_transition(rows, m, self._P(block.single_transition), "")
 
 
 def _free_port():

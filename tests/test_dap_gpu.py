@@ -10,9 +10,15 @@ import cases
 pytestmark = pytest.mark.gpu
 
 
+def _exchange(blocks):
+    """all_to_all_single among virtual ranks: blocks[r][q] goes to rank q as its block r."""
+    P = len(blocks)
+    return [torch.stack([blocks[src][dst] for src in range(P)]) for dst in range(P)]
+
+
 def _virtual_pair_block(ops, shards, mask, pb, P):
     """dap.DapPairFormerStack.pair_block for P shards held on one device."""
-    R = shards[0].shape[0]
+    R, N = shards[0].shape[0], shards[0].shape[1]
     mrow = [mask[r * R:(r + 1) * R].contiguous() for r in range(P)]
     mcol = [mask[:, r * R:(r + 1) * R].t().contiguous() for r in range(P)]
 
@@ -23,15 +29,13 @@ def _virtual_pair_block(ops, shards, mask, pb, P):
     def gather(parts):
         return torch.cat(parts, 1).contiguous()
 
-    proj = [ops.trimul_project(shards[r], mrow[r], pb.tri_mul_out) for r in range(P)]
-    b_all = gather([p[1] for p in proj])
-    for r in range(P):
-        ops.trimul_finish(shards[r], proj[r][0], b_all, pb.tri_mul_out)
-    zT = transpose_all(shards)
-    proj = [ops.trimul_project(zT[r], mcol[r], pb.tri_mul_in) for r in range(P)]
-    b_all = gather([p[1] for p in proj])
-    for r in range(P):
-        ops.trimul_finish(shards[r], proj[r][0], b_all, pb.tri_mul_in)
+    for mod, incoming in ((pb.tri_mul_out, False), (pb.tri_mul_in, True)):
+        ab = [ops.trimul_project(shards[r], mrow[r], mod, P, incoming) for r in range(P)]
+        recv = _exchange(ab) if P > 1 else ab
+        xb = [ops.trimul_contract(ops.regroup_ab(recv[r], N, R, incoming), N, R) for r in range(P)]
+        x_t = _exchange(xb) if P > 1 else xb
+        for r in range(P):
+            ops.trimul_output(shards[r], x_t[r], mod)
     proj = [ops.triattn_project(shards[r], pb.tri_att_start) for r in range(P)]
     tb_all = gather([p[1] for p in proj])
     for r in range(P):
@@ -45,7 +49,7 @@ def _virtual_pair_block(ops, shards, mask, pb, P):
     return transpose_all(zT)
 
 
-@pytest.mark.parametrize("P,N", [(1, 40), (2, 48), (4, 200), (3, 33)])
+@pytest.mark.parametrize("P,N", [(1, 40), (2, 48), (4, 200), (8, 96), (2, 66)])
 def test_row_shard_kernels_match_whole_tensor(pkg, P, N):
     dev = torch.device("cuda:0")
     bf = torch.bfloat16
@@ -67,9 +71,9 @@ def test_row_shard_kernels_match_whole_tensor(pkg, P, N):
         shards = [zd[0, r * R:(r + 1) * R].contiguous().clone() for r in range(P)]
         block = stack.blocks[0]
         shards = _virtual_pair_block(ops, shards, pmd[0], block.pair_stack, P)
-        zb = torch.cat([ops.pair_bias_project(shards[r], block.attn_pair_bias) for r in range(P)], 1).contiguous()
-        s_dap = sd.clone()
-        ops.single_track(s_dap, zb, smd[0], block)
+        rows = [ops.single_rows(sd[0], ops.pair_bias_project(shards[r], block.attn_pair_bias), smd[0], block,
+                                r * R, R) for r in range(P)]
+        s_dap = torch.cat(rows, 0).unsqueeze(0)
     torch.cuda.synchronize()
     pkg.lib.check_device_status()
     z_dap = torch.cat(shards, 0).unsqueeze(0)
@@ -106,3 +110,17 @@ def test_single_rank_dap_runner(pkg):
     pkg.lib.check_device_status()
     assert cases.rel_err(z_d.float().cpu(), z_ref.float().cpu()) < 2e-2
     assert cases.rel_err(s_d.float().cpu(), s_ref.float().cpu()) < 2e-2
+
+
+def test_copy_rows_3d_matches_torch_permute(pkg):
+    """The repack kernel against torch indexing: 16-byte vector path and the 2-byte path."""
+    dev = torch.device("cuda:0")
+    ops = pkg.dap.CudaOps(dev)
+    for P, C, R, ld in ((4, 3, 5, 24), (2, 2, 3, 6)):
+        src = torch.randn(P, C, R, ld, device=dev).to(torch.bfloat16)
+        dst = torch.zeros(C, P * R, ld, device=dev, dtype=torch.bfloat16)
+        e = 2
+        ops.copy_rows(src, dst, (P, C, R), (C * R * ld * e, R * ld * e, ld * e), (R * ld * e, P * R * ld * e, ld * e),
+                      ld * e)
+        torch.cuda.synchronize()
+        assert torch.equal(dst, src.permute(1, 0, 2, 3).reshape(C, P * R, ld))
