@@ -19,28 +19,38 @@
 using namespace of3;
 
 namespace {
-// Rows of `row_bytes` bytes indexed by (i0, i1, i2); byte strides per index on both sides. One warp per
-// row chunk of 512 B (16-byte vectors) when everything is 16-byte aligned, else 2-byte elements.
+// Rows of `row_bytes` bytes indexed by (i0, i1, i2); byte strides per index on both sides. The rows are
+// cut into vectors V (16 bytes when everything is 16-byte aligned, else 2 bytes) and the vectors are
+// dealt to threads in flat order, so short rows still fill a warp; four independent vectors per thread
+// and step keep enough loads in flight.
 template <typename V>
 __global__ void __launch_bounds__(256)
 copy_rows_3d_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, long long n_rows, int n1, int n2,
                     long long s0, long long s1, long long s2, long long t0, long long t1, long long t2,
                     int vec_per_row) {
-    const int chunks = (vec_per_row + 31) / 32;
-    const long long total = n_rows * chunks;
-    const int lane = threadIdx.x & 31;
-    for (long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5; w < total;
-         w += ((long long)gridDim.x * blockDim.x) >> 5) {
-        const long long row = w / chunks;
-        const int v = (int)(w % chunks) * 32 + lane;
-        if (v >= vec_per_row) continue;
-        const int i2 = (int)(row % n2);
-        const long long r1 = row / n2;
-        const int i1 = (int)(r1 % n1);
-        const long long i0 = r1 / n1;
-        const V* sp = reinterpret_cast<const V*>(src + i0 * s0 + i1 * s1 + i2 * s2);
-        V* dp = reinterpret_cast<V*>(dst + i0 * t0 + i1 * t1 + i2 * t2);
-        dp[v] = sp[v];
+    const long long total = n_rows * vec_per_row;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long base = (long long)blockIdx.x * blockDim.x + threadIdx.x; base < total; base += 4 * stride) {
+        V val[4];
+        long long doff[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long idx = base + u * stride;
+            doff[u] = -1;
+            if (idx < total) {
+                const long long row = idx / vec_per_row;
+                const int v = (int)(idx - row * vec_per_row);
+                const int i2 = (int)(row % n2);
+                const long long r1 = row / n2;
+                const int i1 = (int)(r1 % n1);
+                const long long i0 = r1 / n1;
+                val[u] = reinterpret_cast<const V*>(src + i0 * s0 + i1 * s1 + i2 * s2)[v];
+                doff[u] = i0 * t0 + i1 * t1 + i2 * t2 + (long long)v * (long long)sizeof(V);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (doff[u] >= 0) *reinterpret_cast<V*>(dst + doff[u]) = val[u];
     }
 }
 }  // namespace
@@ -56,9 +66,8 @@ int of3_copy_rows_3d(const void* src, void* dst, int n0, int n1, int n2, long lo
     const bool vec = (((uintptr_t)src | (uintptr_t)dst | (uintptr_t)s0 | (uintptr_t)s1 | (uintptr_t)s2 |
                        (uintptr_t)t0 | (uintptr_t)t1 | (uintptr_t)t2 | (uintptr_t)row_bytes) & 15) == 0;
     const int vpr = vec ? row_bytes / 16 : row_bytes / 2;
-    const long long warps = n_rows * ((vpr + 31) / 32);
-    long long blocks = (warps + 7) / 8;
-    const long long cap = (long long)sm_count() * 16;
+    long long blocks = (n_rows * vpr + 4 * 256 - 1) / (4 * 256);
+    const long long cap = (long long)sm_count() * 8;
     if (blocks > cap) blocks = cap;
     LaunchScope scope(20, (cudaStream_t)stream);
     if (vec)

@@ -13,9 +13,9 @@ openfold3/core/model/latent/base_blocks.py:453-478 and pairformer.py:177-211):
   tri_att_end    ALL-TO-ALL transpose of z -> the same on the transposed shard, in place there,
   transition     pointwise, still on the transposed shard | ALL-TO-ALL transpose back
   single track   pair-bias projection of the local rows (main stream), then on a SIDE stream:
-                 attention of the local query rows against all keys, single transition on those rows,
-                 ALL-GATHER of the updated rows of s. z never depends on s, so the side stream runs
-                 concurrently with the next block's pair stack.
+                 attention of the local query rows against all keys, single transition on those rows.
+                 z never depends on s, so the side stream runs concurrently with the next block's pair
+                 stack; the updated rows of s are ALL-GATHERed on the main stream one block later.
 
 Exchanging channel groups (each rank sends/receives ~3 N^2 C / P elements per update) replaces an
 all-gather of b (N^2 C elements received by every rank, independent of P).
@@ -247,18 +247,15 @@ class DapPairFormerStack:
 
     ``__call__(s, z, single_mask, pair_mask)`` takes the full (replicated) tensors of ONE sample
     ([1, N, C] / [1, N, N, C]) and returns the full updated (s, z) on every rank.
-    ``side_group``: a second process group (its own communicator) for the single track's all-gather,
-    which is issued from the side stream while the main stream's exchanges are in flight; created
-    here when ``world > 1`` and none is given (every rank must construct the runner at the same point).
+    Every collective is issued from the main stream on the one process group, in program order: the
+    side stream carries kernels only, so no two communicators ever have to make progress at once (their
+    relative order inside a CUDA graph is not ours to fix, and a different order on two ranks deadlocks).
     """
 
-    def __init__(self, stack, world: int, rank: int, group=None, ops=None, side_group=None):
+    def __init__(self, stack, world: int, rank: int, group=None, ops=None):
         assert world in (1, 2, 4, 8), "the triangle update splits its 128 channels over 1, 2, 4 or 8 ranks"
         self.stack, self.world, self.rank, self.group = stack, world, rank, group
         self.ops = ops
-        self.side_group = side_group
-        if world > 1 and side_group is None:
-            self.side_group = dist.new_group(ranks=None if group is None else dist.get_process_group_ranks(group))
 
     def shard(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
         R = t.shape[dim] // self.world
@@ -274,7 +271,8 @@ class DapPairFormerStack:
         ops.trimul_output(z_loc, x_t, mod)
 
     def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):
-        """One PairBlock on the local row shard (in place); returns the shard."""
+        """One PairBlock on the local row shard; returns the updated shard (a new tensor: the result of
+        the transpose back; z_loc itself holds an intermediate state afterwards)."""
         ops, P, g = self.ops, self.world, self.group
         self._trimul(z_loc, mask_rows, pb.tri_mul_out, incoming=False)
         self._trimul(z_loc, mask_rows, pb.tri_mul_in, incoming=True)
@@ -286,15 +284,13 @@ class DapPairFormerStack:
         qkv, tb_loc = ops.triattn_project(zT, pb.tri_att_end)
         ops.triattn_finish(zT, maskT_rows, qkv, all_gather_lines(tb_loc, P, g), pb.tri_att_end)
         ops.transition(zT, maskT_rows if mask_trans else None, pb.pair_transition)
-        z_new = all_to_all_transpose(zT, P, g, ops)
-        z_loc.copy_(z_new)
-        return z_loc
+        return all_to_all_transpose(zT, P, g, ops)
 
     def _gather_rows(self, s_rows):
         if self.world == 1:
             return s_rows
         full = torch.empty((self.world * s_rows.shape[0], s_rows.shape[1]), dtype=s_rows.dtype, device=s_rows.device)
-        dist.all_gather_into_tensor(full, s_rows.contiguous(), group=self.side_group)
+        dist.all_gather_into_tensor(full, s_rows.contiguous(), group=self.group)
         return full
 
     def __call__(self, s, z, single_mask, pair_mask, _mask_trans=True):
@@ -313,18 +309,23 @@ class DapPairFormerStack:
         mark = getattr(ops, "mark_side", lambda: None)
         wait = getattr(ops, "wait_mark", lambda ev: None)
         zb_buf, zb_free = [None, None], [None, None]
+        pending = None  # (rows of s updated on the side stream, event after them)
         for i, block in enumerate(self.stack.blocks):
-            self.pair_block(z_loc, mask_rows, maskT_rows, block.pair_stack, _mask_trans)
+            z_loc = self.pair_block(z_loc, mask_rows, maskT_rows, block.pair_stack, _mask_trans)
             slot = i & 1
             wait(zb_free[slot])  # the side stream has finished with this buffer (two blocks ago)
             zb_buf[slot] = ops.pair_bias_project(z_loc, block.attn_pair_bias, out=zb_buf[slot])   # [H, R, N]
+            if pending is not None:  # the previous block's rows: long finished; gathered on the main stream
+                wait(pending[1])
+                s_full = self._gather_rows(pending[0])
             with side():
                 s_rows = ops.single_rows(s_full, zb_buf[slot], sm, block, self.rank * R, R, _mask_trans)
-                s_full = self._gather_rows(s_rows)
                 zb_free[slot] = mark()
-        wait(zb_free[0])
-        wait(zb_free[1])
-        if s_full.is_cuda:
+            pending = (s_rows, zb_free[slot])
+        if pending is not None:
+            wait(pending[1])
+            s_full = self._gather_rows(pending[0])
+        if s_full.is_cuda and not torch.cuda.is_current_stream_capturing():
             s_full.record_stream(torch.cuda.current_stream(s_full.device))
         if self.world > 1:
             z_full = torch.empty((N,) + tuple(z_loc.shape[1:]), dtype=z_loc.dtype, device=z_loc.device)
@@ -333,3 +334,45 @@ class DapPairFormerStack:
         else:
             z_full = z_loc.unsqueeze(0)
         return s_full.unsqueeze(0), z_full
+
+
+class GraphedDapRunner:
+    """A ``DapPairFormerStack`` step captured once into a CUDA graph and replayed.
+
+    A block is ~100 short launches and collectives; issued one by one from Python the host cannot keep
+    P >= 2 GPUs busy (the per-rank kernels shrink with P, the host work does not). The graph holds the
+    kernels of both streams and the NCCL collectives; replaying it costs one launch. Inputs are copied into the static buffers the graph reads; the returned tensors are the
+    graph's static outputs (overwritten by the next replay). Every rank must capture and replay at
+    the same points.
+    """
+
+    def __init__(self, runner: DapPairFormerStack, s, z, single_mask, pair_mask, warmup: int = 2):
+        self.runner = runner
+        self.s_in, self.z_in = s.clone(), z.clone()
+        self.sm_in = None if single_mask is None else single_mask.clone()
+        self.pm_in = pair_mask.clone()
+        dev = z.device
+        cur = torch.cuda.current_stream(dev)
+        st = torch.cuda.Stream(dev)
+        st.wait_stream(cur)
+        with torch.cuda.stream(st), torch.no_grad():  # communicators, kernel attributes, workspaces: all set up eagerly
+            for _ in range(max(1, warmup)):
+                runner(self.s_in, self.z_in, self.sm_in, self.pm_in)
+        cur.wait_stream(st)
+        torch.cuda.synchronize(dev)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.s_out, self.z_out = runner(self.s_in, self.z_in, self.sm_in, self.pm_in)
+
+    def __call__(self, s, z, single_mask, pair_mask):
+        for dst, src in ((self.s_in, s), (self.z_in, z), (self.sm_in, single_mask), (self.pm_in, pair_mask)):
+            if dst is not None and src is not None and dst.data_ptr() != src.data_ptr():
+                dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        return self.s_out, self.z_out
+
+    def release(self):
+        """Drops the graph (and with it its hold on the communicator) and the static buffers."""
+        self.graph.reset()
+        self.graph = None
+        self.s_out = self.z_out = self.s_in = self.z_in = self.sm_in = self.pm_in = None

@@ -124,3 +124,34 @@ def test_copy_rows_3d_matches_torch_permute(pkg):
                       ld * e)
         torch.cuda.synchronize()
         assert torch.equal(dst, src.permute(1, 0, 2, 3).reshape(C, P * R, ld))
+
+
+def test_graphed_runner_replays_the_eager_result(pkg):
+    """One rank: the captured step (both streams, all phase kernels) equals the eager step, twice."""
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    N = 64
+    g = torch.Generator().manual_seed(2)
+    z = torch.randn(1, N, N, 128, generator=g).to(dev, bf)
+    s = torch.randn(1, N, 384, generator=g).to(dev, bf)
+    pm = cases.rand_mask((1, N, N), g).to(dev, bf)
+    sm = cases.rand_mask((1, N), g).to(dev, bf)
+    Pw = pkg.weights.pairformer_stack_params(seed=6, no_blocks=2, **cases.OF3)
+    stack = pkg.PairFormerStack(**cases.OF3, no_blocks=2, transition_type="swiglu", pair_dropout=0.25,
+                                fuse_projection_weights=False, blocks_per_ckpt=None, inf=1e9)
+    stack.load_state_dict(Pw, strict=True)
+    stack = stack.to(dev, bf).eval()
+    runner = pkg.dap.DapPairFormerStack(stack, 1, 0, ops=pkg.dap.CudaOps(dev))
+    with torch.no_grad():
+        s_e, z_e = runner(s, z, sm, pm)
+        graphed = pkg.dap.GraphedDapRunner(runner, s, z, sm, pm)
+        for _ in range(2):
+            s_g, z_g = graphed(s, z, sm, pm)
+            torch.cuda.synchronize()
+            assert torch.equal(s_g, s_e) and torch.equal(z_g, z_e)
+        z2 = (z * 0.5).contiguous()
+        s_e2, z_e2 = runner(s, z2, sm, pm)
+        s_g, z_g = graphed(s, z2, sm, pm)
+        torch.cuda.synchronize()
+        assert torch.equal(s_g, s_e2) and torch.equal(z_g, z_e2)
+    pkg.lib.check_device_status()
