@@ -228,8 +228,14 @@ def run_ours(args) -> None:
     s_out_host = torch.empty_like(s_host).pin_memory()
     z_out_host = torch.empty_like(z_host).pin_memory()
 
+    heap = None
     if world > 1:
-        runner = pkg.dap.DapPairFormerStack(stack, world, rank, ops=pkg.dap.CudaOps(dev))
+        ops = pkg.dap.CudaOps(dev)
+        xchg = None  # default: torch.distributed collectives (NCCL)
+        if args.exchange == "peer":
+            heap = pkg.dap.PeerHeap(pkg.dap.PeerExchange.heap_bytes(n, world), world, rank, dev)
+            xchg = pkg.dap.PeerExchange(heap, ops)
+        runner = pkg.dap.DapPairFormerStack(stack, world, rank, ops=ops, exchange=xchg)
     else:
         runner = None
 
@@ -367,6 +373,9 @@ def run_ours(args) -> None:
                                    "seeded random weights",
                        "parallelism": "single GPU" if world == 1 else f"DAP row-sharded over {world} GPUs",
                        "launch": graph_note,
+                       "exchange": ("none" if world == 1 else
+                                    "barrier + pull kernels over NVLink peer memory" if args.exchange == "peer"
+                                    else "NCCL all-to-all / all-gather"),
                        "l2": "inputs and per-layer working set (>1 GB) exceed the 126 MB L2; no explicit flush"},
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -384,6 +393,9 @@ def run_ours(args) -> None:
             graphed.release()
         torch.cuda.synchronize(dev)
         dist.barrier()
+        if heap is not None:
+            runner = None
+            heap.close()
         dist.destroy_process_group()
 
 
@@ -396,6 +408,8 @@ def main():
     ap.add_argument("--blocks", type=int, default=48)
     ap.add_argument("--n-token", type=int, default=768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="nccl",
+                    help="N > 1: how shards move between GPUs")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -271,6 +271,26 @@ int of3_attn_pair_bias_forward_rows(const void* a, const float* pair_bias_rows, 
                                     const of3_attn_pair_bias_params* p, void* workspace, size_t workspace_bytes,
                                     void* stream);
 
+/* ---- Exchanges over NVLink peer memory (no counterpart in the reference) --------------------
+ * One "peer heap" per rank: device memory of this process that the other ranks of the node map into
+ * their own address space (CUDA IPC). alloc returns the local pointer and a 64-byte handle to pass to
+ * the other processes (any host transport); open maps a peer's heap; close / free undo them.
+ * of3_peer_barrier: a one-warp kernel; returns (on the stream) once every rank has launched the same
+ *   barrier. flag_blocks[r] = address IN THIS PROCESS of a zero-initialised 64-byte block inside rank r's
+ *   heap (the same offset on every rank). Waits are bounded (2 s), then of3_device_status reports kernel 30.
+ * of3_peer_pull_rows: world*n1*n2 rows of row_bytes; row (r, i1, i2) is read from rank r's heap at
+ *   srcs[r] + src_off + i1*s1 + i2*s2 and written to dst + r*t0 + i1*t1 + i2*t2 (byte strides):
+ *   all-to-all, all-gather and the repack into the consumer's layout in one pass. Call it after a
+ *   barrier that follows the producers; a buffer may be rewritten once a later barrier has passed. */
+int of3_peer_heap_alloc(size_t bytes, void** ptr, void* handle64);
+int of3_peer_heap_open(const void* handle64, void** ptr);
+int of3_peer_heap_close(void* ptr);
+int of3_peer_heap_free(void* ptr);
+int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream);
+int of3_peer_pull_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
+                       long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
+                       void* stream);
+
 /* ---- Building block exported for tests and profiling --------------------------------------
  * X[b][i][j] = sum_k A[b][i][k] * B[b][j][k], bf16 in / fp32 accumulate / bf16 out, the
  * tcgen05 kernel behind the triangle contraction (einsum of

@@ -149,12 +149,13 @@ class CudaOps:
                                            t[1], t[2], row_bytes, self._st()), "of3_copy_rows_3d")
 
     # ---- triangle update
-    def trimul_project(self, z_loc, mask_rows, mod, world, incoming):
+    def trimul_project(self, z_loc, mask_rows, mod, world, incoming, out=None):
         """-> ab [world, 2, 128 / world, lines, ld]; see of3_dap_trimul_project."""
         R, N, _ = z_loc.shape
         lines, positions = (N, R) if incoming else (R, N)
         ld = _pitch(positions, 8)
-        ab = torch.empty((world, 2, 128 // world, lines, ld), dtype=z_loc.dtype, device=z_loc.device)
+        shape = (world, 2, 128 // world, lines, ld)
+        ab = torch.empty(shape, dtype=z_loc.dtype, device=z_loc.device) if out is None else out.view(shape)
         p = lib.TrimulParams(*[t.data_ptr() for t in mod._params(z_loc.dtype, z_loc.device)])
         lib._check(self.l.of3_dap_trimul_project(z_loc.data_ptr(), lib._ptr(mask_rows), ab.data_ptr(), lines,
                                                  positions, 1 if incoming else 0, world, ctypes.byref(p), self._st()),
@@ -164,10 +165,11 @@ class CudaOps:
     def regroup_ab(self, recv, N, R, incoming):
         return regroup_ab(recv, N, R, incoming, copy=self.copy_rows)
 
-    def trimul_contract(self, ab_all, N, R):
+    def trimul_contract(self, ab_all, N, R, out=None):
         """ab_all [2, C, N, ld] -> x_blocks [N / R, C, R, ld]."""
         C = ab_all.shape[1]
-        xb = torch.empty((N // R, C, R, ab_all.shape[-1]), dtype=ab_all.dtype, device=ab_all.device)
+        shape = (N // R, C, R, ab_all.shape[-1])
+        xb = torch.empty(shape, dtype=ab_all.dtype, device=ab_all.device) if out is None else out.view(shape)
         lib._check(self.l.of3_dap_trimul_contract(ab_all.data_ptr(), xb.data_ptr(), N, C, R, self._st()),
                    "of3_dap_trimul_contract")
         return xb
@@ -180,7 +182,7 @@ class CudaOps:
                    "of3_dap_trimul_output")
 
     # ---- triangle attention
-    def triattn_project(self, z_loc, mod):
+    def triattn_project(self, z_loc, mod, out=None):
         R, N, _ = z_loc.shape
         ldn = _pitch(N, 64)
         dt, dev = z_loc.dtype, z_loc.device
@@ -188,7 +190,7 @@ class CudaOps:
         q = torch.empty(img, dtype=dt, device=dev)
         k = torch.empty(img, dtype=dt, device=dev)
         vt = torch.empty(img, dtype=dt, device=dev)
-        tb = torch.empty((4, R, ldn), dtype=dt, device=dev)
+        tb = torch.empty((4, R, ldn), dtype=dt, device=dev) if out is None else out.view(4, R, ldn)
         p = lib.TriattnParams(*[t.data_ptr() for t in mod._params(dt, dev)])
         lib._check(self.l.of3_dap_triattn_project(z_loc.data_ptr(), q.data_ptr(), k.data_ptr(), vt.data_ptr(),
                                                   tb.data_ptr(), R, N, ctypes.byref(p), self._st()),
@@ -221,7 +223,7 @@ class CudaOps:
                    "of3_pair_bias_project")
         return out
 
-    def single_rows(self, s_full, zb_rows, single_mask, block, row0, R, mask_trans=True):
+    def single_rows(self, s_full, zb_rows, single_mask, block, row0, R, mask_trans=True, out=None):
         """Rows [row0, row0 + R) of the updated single representation: s_full [N, c_s] (all rows, for the
         keys and values), zb_rows [16, R, N] the projected pair bias of those rows (fp32) -> [R, c_s]."""
         apb = block.attn_pair_bias
@@ -231,7 +233,7 @@ class CudaOps:
         p = lib.AttnPairBiasParams(*[lib._ptr(t) for t in apb._params(dt, dev)])
         nbytes = self.l.of3_attn_pair_bias_rows_workspace_bytes(N, R, apb.c_q)
         ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
-        out = torch.empty((R, apb.c_q), dtype=dt, device=dev)
+        out = torch.empty((R, apb.c_q), dtype=dt, device=dev) if out is None else out.view(R, apb.c_q)
         lib._check(self.l.of3_attn_pair_bias_forward_rows(
             s_full.data_ptr(), zb_rows.data_ptr(), lib._ptr(m), out.data_ptr(), N, row0, R, apb.c_q, apb.no_heads,
             apb.c_hidden, float(apb.inf), lib.dtype_code(dt), lib.FLAG_ADD_RESIDUAL, ctypes.byref(p), ws.data_ptr(),
@@ -241,65 +243,279 @@ class CudaOps:
         return out
 
 
-# ----------------------------------------------------------------------------- orchestration
-class DapPairFormerStack:
-    """Runs a ``PairFormerStack`` with z row-sharded over ``world`` ranks.
+# ----------------------------------------------------------------------------- exchange strategies
+class NcclExchange:
+    """The exchanges as torch.distributed collectives (NCCL on GPUs, gloo in the CPU tests)."""
 
-    ``__call__(s, z, single_mask, pair_mask)`` takes the full (replicated) tensors of ONE sample
-    ([1, N, C] / [1, N, N, C]) and returns the full updated (s, z) on every rank.
-    Every collective is issued from the main stream on the one process group, in program order: the
-    side stream carries kernels only, so no two communicators ever have to make progress at once (their
-    relative order inside a CUDA graph is not ours to fix, and a different order on two ranks deadlocks).
-    """
+    def __init__(self, world: int, rank: int, group=None, ops=None):
+        self.world, self.rank, self.group, self.ops = world, rank, group, ops
 
-    def __init__(self, stack, world: int, rank: int, group=None, ops=None):
-        assert world in (1, 2, 4, 8), "the triangle update splits its 128 channels over 1, 2, 4 or 8 ranks"
-        self.stack, self.world, self.rank, self.group = stack, world, rank, group
-        self.ops = ops
+    def buf(self, name, shape, dtype, device):
+        return None  # producers allocate their own outputs
 
-    def shard(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
-        R = t.shape[dim] // self.world
-        return t.narrow(dim, self.rank * R, R)
+    def begin(self):
+        pass
 
-    def _trimul(self, z_loc, mask_rows, mod, incoming: bool):
-        ops, P, g = self.ops, self.world, self.group
-        R, N, _ = z_loc.shape
-        ab = ops.trimul_project(z_loc, mask_rows, mod, P, incoming)           # [P, 2, C, lines, ld]
-        ab_all = ops.regroup_ab(exchange_blocks(ab, P, g), N, R, incoming)    # [2, C, N, ld]
-        xb = ops.trimul_contract(ab_all, N, R)                                # [P, C, R, ld]
-        x_t = exchange_blocks(xb, P, g)                                       # = [128, R, ld]
-        ops.trimul_output(z_loc, x_t, mod)
+    def ab_all(self, ab, N, R, incoming):
+        return self.ops.regroup_ab(exchange_blocks(ab, self.world, self.group), N, R, incoming)
 
-    def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):
-        """One PairBlock on the local row shard; returns the updated shard (a new tensor: the result of
-        the transpose back; z_loc itself holds an intermediate state afterwards)."""
-        ops, P, g = self.ops, self.world, self.group
-        self._trimul(z_loc, mask_rows, pb.tri_mul_out, incoming=False)
-        self._trimul(z_loc, mask_rows, pb.tri_mul_in, incoming=True)
-        # starting node
-        qkv, tb_loc = ops.triattn_project(z_loc, pb.tri_att_start)
-        ops.triattn_finish(z_loc, mask_rows, qkv, all_gather_lines(tb_loc, P, g), pb.tri_att_start)
-        # ending node and transition on the transposed shard, then back
-        zT = all_to_all_transpose(z_loc, P, g, ops)
-        qkv, tb_loc = ops.triattn_project(zT, pb.tri_att_end)
-        ops.triattn_finish(zT, maskT_rows, qkv, all_gather_lines(tb_loc, P, g), pb.tri_att_end)
-        ops.transition(zT, maskT_rows if mask_trans else None, pb.pair_transition)
-        return all_to_all_transpose(zT, P, g, ops)
+    def x_rows(self, xb):
+        P, C, R, ld = xb.shape
+        return exchange_blocks(xb, self.world, self.group).view(P * C, R, ld)
 
-    def _gather_rows(self, s_rows):
+    def transpose(self, z_loc, dst_name):
+        return all_to_all_transpose(z_loc, self.world, self.group, self.ops)
+
+    def gather_lines(self, x_loc):
+        return all_gather_lines(x_loc, self.world, self.group)
+
+    def gather_rows(self, s_rows):
         if self.world == 1:
             return s_rows
         full = torch.empty((self.world * s_rows.shape[0], s_rows.shape[1]), dtype=s_rows.dtype, device=s_rows.device)
         dist.all_gather_into_tensor(full, s_rows.contiguous(), group=self.group)
         return full
 
+
+class _RawDeviceMemory:
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerHeap:
+    """This rank's peer heap and the mapped heaps of the other ranks of the node (see csrc/peer.cu).
+
+    ``bases[r]`` is the address, in this process, of rank r's heap. Regions are handed out by a bump
+    allocator keyed by name; every rank requests the same names and sizes in the same order, so a name
+    has the same offset everywhere.
+    """
+
+    def __init__(self, nbytes: int, world: int, rank: int, device, group=None):
+        self.l = lib.load()
+        self.world, self.rank, self.device, self.nbytes = world, rank, device, int(nbytes)
+        ptr = ctypes.c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        lib._check(self.l.of3_peer_heap_alloc(self.nbytes, ctypes.byref(ptr), handle), "of3_peer_heap_alloc")
+        self._own = ptr.value
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(handle.raw), group=group)
+        self.bases = []
+        for r in range(world):
+            if r == rank:
+                self.bases.append(self._own)
+            else:
+                q = ctypes.c_void_p()
+                lib._check(self.l.of3_peer_heap_open(ctypes.create_string_buffer(handles[r], 64), ctypes.byref(q)),
+                           "of3_peer_heap_open")
+                self.bases.append(q.value)
+        self._finish_init()
+
+    def _finish_init(self):
+        self.local = torch.as_tensor(_RawDeviceMemory(self.bases[self.rank], self.nbytes), device=self.device)
+        self.regions, self.top = {}, 256  # bytes [0, 64) are the barrier's flag block
+        self.c_bases = (ctypes.c_void_p * self.world)(*self.bases)
+
+    def region(self, name: str, nbytes: int) -> int:
+        if name not in self.regions:
+            off = self.top
+            self.top = (off + nbytes + 255) // 256 * 256
+            if self.top > self.nbytes:
+                raise RuntimeError(f"peer heap of {self.nbytes} bytes is too small for region {name!r} ({nbytes} bytes)")
+            self.regions[name] = (off, nbytes)
+        off, size = self.regions[name]
+        if nbytes > size:
+            raise RuntimeError(f"peer heap region {name!r} holds {size} bytes, {nbytes} requested")
+        return off
+
+    def tensor(self, name: str, shape, dtype) -> torch.Tensor:
+        n = 1
+        for d in shape:
+            n *= int(d)
+        nbytes = n * torch.empty((), dtype=dtype).element_size()
+        off = self.region(name, nbytes)
+        return self.local[off:off + nbytes].view(dtype).view(*shape)
+
+    def offset_of(self, t: torch.Tensor) -> int:
+        off = t.data_ptr() - self.bases[self.rank]
+        assert 0 <= off < self.nbytes, "tensor does not live in the peer heap"
+        return off
+
+    def close(self):
+        for r, b in enumerate(self.bases):
+            if r != self.rank and b is not None:
+                self.l.of3_peer_heap_close(ctypes.c_void_p(b))
+        if getattr(self, "_own", None):
+            self.l.of3_peer_heap_free(ctypes.c_void_p(self._own))
+            self._own = None
+        self.bases = []
+
+
+class LocalPeerHeaps:
+    """P heaps inside ONE process (virtual ranks on one GPU, for tests): ``view(r)`` is rank r's PeerHeap-like
+    object. The barrier between production and pulls is the host's program order, not a kernel."""
+
+    def __init__(self, nbytes: int, world: int, device):
+        self.store = [torch.zeros(int(nbytes), dtype=torch.uint8, device=device) for _ in range(world)]
+        self.world, self.device, self.nbytes = world, device, int(nbytes)
+
+    def view(self, rank: int) -> PeerHeap:
+        h = PeerHeap.__new__(PeerHeap)
+        h.l = lib.load()
+        h.world, h.rank, h.device, h.nbytes = self.world, rank, self.device, self.nbytes
+        h.bases = [t.data_ptr() for t in self.store]
+        h._own = None
+        h._finish_init()
+        return h
+
+
+class PeerExchange:
+    """The exchanges as barrier + pull over NVLink peer memory: one kernel moves the data from the peers'
+    heaps into the layout the next kernel reads (all-to-all / all-gather and repack fused)."""
+
+    def __init__(self, heap: PeerHeap, ops, barrier: bool = True):
+        self.heap, self.ops, self.world, self.rank = heap, ops, heap.world, heap.rank
+        self.use_barrier = barrier
+        self.l = lib.load()
+
+    def buf(self, name, shape, dtype, device):
+        return self.heap.tensor(name, shape, dtype)
+
+    def begin(self):
+        """Start of a step: the peers have finished reading the previous step's buffers."""
+        self.barrier()
+
+    def barrier(self):
+        if self.use_barrier and self.world > 1:
+            lib._check(self.l.of3_peer_barrier(self.heap.c_bases, self.world, self.rank, self.ops._st()),
+                       "of3_peer_barrier")
+
+    def _pull(self, src_off, dst, n1, n2, s1, s2, t0, t1, t2, row_bytes):
+        lib._check(self.l.of3_peer_pull_rows(self.heap.c_bases, src_off, dst.data_ptr(), self.world, self.rank, n1, n2,
+                                             s1, s2, t0, t1, t2, row_bytes, self.ops._st()), "of3_peer_pull_rows")
+
+    def ab_all(self, ab, N, R, incoming):
+        P, _, C, lines, ld = ab.shape
+        e = ab.element_size()
+        ldn = _pitch(N, 8)
+        out = torch.empty((2, C, N, ldn), dtype=ab.dtype, device=ab.device)
+        self.barrier()
+        off = self.heap.offset_of(ab) + self.rank * (2 * C * lines * ld * e)  # the block each source holds for me
+        if not incoming:   # source block [2C][R][ldn] -> out[2C][src*R + r][ldn]
+            self._pull(off, out, 2 * C, R, R * ldn * e, ldn * e, R * ldn * e, N * ldn * e, ldn * e, ldn * e)
+        else:              # source block [2C][N][ld(R)] -> out[2C][i][src*R + k]
+            self._pull(off, out, 2 * C, N, N * ld * e, ld * e, R * e, N * ldn * e, ldn * e, R * e)
+        return out
+
+    def x_rows(self, xb):
+        P, C, R, ld = xb.shape
+        e = xb.element_size()
+        out = torch.empty((P * C, R, ld), dtype=xb.dtype, device=xb.device)
+        blk = C * R * ld * e
+        self.barrier()
+        self._pull(self.heap.offset_of(xb) + self.rank * blk, out, 1, 1, 0, 0, blk, 0, 0, blk)
+        return out
+
+    def transpose(self, z_loc, dst_name):
+        R, N, C = z_loc.shape
+        e = z_loc.element_size()
+        out = self.heap.tensor(dst_name, (R, N, C), z_loc.dtype)
+        self.barrier()
+        # out[i_loc][src*R + k_loc][:] = z_src[k_loc][rank*R + i_loc][:]; rows (src, k_loc, i_loc) of C elements
+        self._pull(self.heap.offset_of(z_loc) + self.rank * R * C * e, out, R, R, N * C * e, C * e, R * C * e, C * e,
+                   N * C * e, C * e)
+        return out
+
+    def gather_lines(self, x_loc):
+        G, R, L = x_loc.shape
+        e = x_loc.element_size()
+        out = torch.empty((G, self.world * R, L), dtype=x_loc.dtype, device=x_loc.device)
+        self.barrier()
+        self._pull(self.heap.offset_of(x_loc), out, G, R, R * L * e, L * e, R * L * e, self.world * R * L * e, L * e,
+                   L * e)
+        return out
+
+    def gather_rows(self, s_rows):
+        R, c = s_rows.shape
+        e = s_rows.element_size()
+        out = torch.empty((self.world * R, c), dtype=s_rows.dtype, device=s_rows.device)
+        self.barrier()
+        self._pull(self.heap.offset_of(s_rows), out, 1, 1, 0, 0, R * c * e, 0, 0, R * c * e)
+        return out
+
+    @staticmethod
+    def heap_bytes(N: int, world: int, c_s: int = 384) -> int:
+        """Bytes of peer heap one rank needs for a Pairformer trunk at N tokens (bf16)."""
+        R = N // world
+        ld, ldn = _pitch(N, 8), _pitch(N, 64)
+        ab = 2 * 128 * max(R * ld, N * _pitch(R, 8)) * 2
+        return 2 * R * N * 128 * 2 + ab + 128 * R * ld * 2 + 4 * R * ldn * 2 + 2 * R * c_s * 2 + 16 * 256 + 4096
+
+
+# ----------------------------------------------------------------------------- orchestration
+class DapPairFormerStack:
+    """Runs a ``PairFormerStack`` with z row-sharded over ``world`` ranks.
+
+    ``__call__(s, z, single_mask, pair_mask)`` takes the full (replicated) tensors of ONE sample
+    ([1, N, C] / [1, N, N, C]) and returns the full updated (s, z) on every rank.
+    ``exchange``: how shards move between ranks -- ``NcclExchange`` (default) or ``PeerExchange``.
+    Every exchange is issued from the main stream, in program order: the side stream carries kernels
+    only, so no two communicators (or barriers) ever have to make progress at once.
+    """
+
+    def __init__(self, stack, world: int, rank: int, group=None, ops=None, exchange=None):
+        assert world in (1, 2, 4, 8), "the triangle update splits its 128 channels over 1, 2, 4 or 8 ranks"
+        self.stack, self.world, self.rank, self.group = stack, world, rank, group
+        self.ops = ops
+        self.x = exchange if exchange is not None else NcclExchange(world, rank, group, ops)
+
+    def shard(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
+        R = t.shape[dim] // self.world
+        return t.narrow(dim, self.rank * R, R)
+
+    def _trimul(self, z_loc, mask_rows, mod, incoming: bool):
+        ops, P, X = self.ops, self.world, self.x
+        R, N, _ = z_loc.shape
+        lines, pos = (N, R) if incoming else (R, N)
+        C, dt, dev = 128 // P, z_loc.dtype, z_loc.device
+        ld = _pitch(pos, 8)
+        # one region serves both directions: lines x pitch differs between them
+        ab_buf = X.buf("ab", (2 * 128 * max(R * _pitch(N, 8), N * _pitch(R, 8)),), dt, dev)
+        ab_out = None if ab_buf is None else ab_buf[:2 * 128 * lines * ld].view(P, 2, C, lines, ld)
+        ab = ops.trimul_project(z_loc, mask_rows, mod, P, incoming, out=ab_out)              # [P, 2, C, lines, ld]
+        ab_all = X.ab_all(ab, N, R, incoming)                                                # [2, C, N, ld]
+        xb = ops.trimul_contract(ab_all, N, R, out=X.buf("xb", (P, C, R, _pitch(N, 8)), dt, dev))  # [P, C, R, ld]
+        ops.trimul_output(z_loc, X.x_rows(xb), mod)                                          # x_t [128, R, ld]
+
+    def _triattn(self, z_loc, mask_rows, mod):
+        ops, X = self.ops, self.x
+        R, N, _ = z_loc.shape
+        qkv, tb_loc = ops.triattn_project(z_loc, mod, out=X.buf("tb", (4, R, _pitch(N, 64)), z_loc.dtype, z_loc.device))
+        ops.triattn_finish(z_loc, mask_rows, qkv, X.gather_lines(tb_loc), mod)
+
+    def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):
+        """One PairBlock on the local row shard; returns the updated shard (the result of the transpose
+        back: with collectives a new tensor, z_loc itself then holds an intermediate state)."""
+        self._trimul(z_loc, mask_rows, pb.tri_mul_out, incoming=False)
+        self._trimul(z_loc, mask_rows, pb.tri_mul_in, incoming=True)
+        self._triattn(z_loc, mask_rows, pb.tri_att_start)
+        # ending node and transition on the transposed shard, then back
+        zT = self.x.transpose(z_loc, "z1")
+        self._triattn(zT, maskT_rows, pb.tri_att_end)
+        self.ops.transition(zT, maskT_rows if mask_trans else None, pb.pair_transition)
+        return self.x.transpose(zT, "z0")
+
     def __call__(self, s, z, single_mask, pair_mask, _mask_trans=True):
         assert z.shape[0] == 1 and z.dim() == 4, "DAP runs one sample: z [1, N, N, C]"
         N = z.shape[1]
         assert N % self.world == 0, f"N_token {N} must be divisible by the {self.world} ranks"
-        ops = self.ops
+        ops, X = self.ops, self.x
         R = N // self.world
-        z_loc = self.shard(z[0]).contiguous().clone()
+        X.begin()
+        z_loc = X.buf("z0", (R, N, z.shape[-1]), z.dtype, z.device)
+        if z_loc is None:
+            z_loc = self.shard(z[0]).contiguous().clone()
+        else:
+            z_loc.copy_(self.shard(z[0]))
         s_full = s[0].clone(memory_format=torch.contiguous_format)
         pm = pair_mask[0].to(z.dtype)
         mask_rows = self.shard(pm, 0).contiguous()
@@ -317,22 +533,18 @@ class DapPairFormerStack:
             zb_buf[slot] = ops.pair_bias_project(z_loc, block.attn_pair_bias, out=zb_buf[slot])   # [H, R, N]
             if pending is not None:  # the previous block's rows: long finished; gathered on the main stream
                 wait(pending[1])
-                s_full = self._gather_rows(pending[0])
+                s_full = X.gather_rows(pending[0])
             with side():
-                s_rows = ops.single_rows(s_full, zb_buf[slot], sm, block, self.rank * R, R, _mask_trans)
+                s_rows = ops.single_rows(s_full, zb_buf[slot], sm, block, self.rank * R, R, _mask_trans,
+                                         out=X.buf(f"s{slot}", (R, s.shape[-1]), s.dtype, s.device))
                 zb_free[slot] = mark()
             pending = (s_rows, zb_free[slot])
         if pending is not None:
             wait(pending[1])
-            s_full = self._gather_rows(pending[0])
+            s_full = X.gather_rows(pending[0])
         if s_full.is_cuda and not torch.cuda.is_current_stream_capturing():
             s_full.record_stream(torch.cuda.current_stream(s_full.device))
-        if self.world > 1:
-            z_full = torch.empty((N,) + tuple(z_loc.shape[1:]), dtype=z_loc.dtype, device=z_loc.device)
-            dist.all_gather_into_tensor(z_full, z_loc, group=self.group)
-            z_full = z_full.reshape(1, N, N, z_loc.shape[-1])
-        else:
-            z_full = z_loc.unsqueeze(0)
+        z_full = X.gather_rows(z_loc.view(R, -1)).view(1, N, N, z_loc.shape[-1])
         return s_full.unsqueeze(0), z_full
 
 

@@ -84,6 +84,13 @@ SIGNATURES = {
     "of3_attn_pair_bias_forward_prebias": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_float, c_int, c_int,
                                                    ctypes.POINTER(AttnPairBiasParams), c_void_p, c_size_t,
                                                    c_void_p]),
+    "of3_peer_heap_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
+    "of3_peer_heap_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "of3_peer_heap_close": (c_int, [c_void_p]),
+    "of3_peer_heap_free": (c_int, [c_void_p]),
+    "of3_peer_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "of3_peer_pull_rows": (c_int, [ctypes.POINTER(c_void_p), c_longlong, c_void_p, c_int, c_int, c_int, c_int]
+                           + [c_longlong] * 5 + [c_int, c_void_p]),
     "of3_contract_nt_bf16": (c_int, [c_void_p] * 3 + [c_int] * 7 + [c_longlong] * 3 + [c_void_p]),
 }
 
@@ -128,7 +135,8 @@ def check_device_status():
 
 
 KERNEL_NAMES = {1: "trimul_contract", 2: "trimul_in", 3: "trimul_out", 4: "transition", 5: "triattn_proj",
-                6: "triattn_core", 7: "triattn_out", 8: "single_track", 20: "generic"}
+                6: "triattn_core", 7: "triattn_out", 8: "single_track", 20: "generic", 30: "peer_barrier",
+                31: "peer_pull"}
 
 
 def profile_begin(timing: bool = True):

@@ -37,7 +37,7 @@ class OracleOps:
     def _pad(t, ld):
         return F.pad(t, (0, ld - t.shape[-1]))
 
-    def trimul_project(self, z_loc, mask_rows, mod, world, incoming):
+    def trimul_project(self, z_loc, mask_rows, mod, world, incoming, out=None):
         P, o = self._P(mod), self.o
         zn = o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1])
         m = mask_rows.unsqueeze(-1)
@@ -55,7 +55,7 @@ class OracleOps:
         import cases
         return cases.pkg.dap.regroup_ab(recv, N, R, incoming)
 
-    def trimul_contract(self, ab_all, N, R):
+    def trimul_contract(self, ab_all, N, R, out=None):
         x = torch.einsum("cik,cjk->cij", ab_all[0][:, :, :N], ab_all[1][:, :, :N])    # [C, N, N]
         x = self._pad(x, ab_all.shape[-1])
         C = x.shape[0]
@@ -69,7 +69,7 @@ class OracleOps:
         g = torch.sigmoid(o._lin(o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1]), P, "linear_g."))
         z_loc += x * g
 
-    def triattn_project(self, z_loc, mod):
+    def triattn_project(self, z_loc, mod, out=None):
         P, o = self._P(mod), self.o
         N = z_loc.shape[1]
         xn = o._ln(z_loc, P, "layer_norm.", z_loc.shape[-1])
@@ -92,7 +92,7 @@ class OracleOps:
         P, o = self._P(apb), self.o
         return o._lin(o._ln(z_loc, P, "layer_norm_z.", z_loc.shape[-1]), P, "linear_z.").permute(2, 0, 1).contiguous()
 
-    def single_rows(self, s_full, zb_rows, single_mask, block, row0, R, mask_trans=True):
+    def single_rows(self, s_full, zb_rows, single_mask, block, row0, R, mask_trans=True, out=None):
         apb, o = block.attn_pair_bias, self.o
         P = self._P(apb)
         an = o._ln(s_full, P, "layer_norm_a.", s_full.shape[-1])

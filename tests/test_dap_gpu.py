@@ -155,3 +155,81 @@ def test_graphed_runner_replays_the_eager_result(pkg):
         torch.cuda.synchronize()
         assert torch.equal(s_g, s_e2) and torch.equal(z_g, z_e2)
     pkg.lib.check_device_status()
+
+
+def _virtual_pair_block_peer(ops, X, z, mask, pb, P):
+    """The same block with the PeerExchange strategy: P virtual ranks whose heaps live in this process;
+    the host's program order (all ranks produce, then all ranks pull) stands in for the barrier kernel."""
+    dap = cases.pkg.dap
+    R, N = z[0].shape[0], z[0].shape[1]
+    C = 128 // P
+    bf, dev = z[0].dtype, z[0].device
+    mrow = [mask[r * R:(r + 1) * R].contiguous() for r in range(P)]
+    mcol = [mask[:, r * R:(r + 1) * R].t().contiguous() for r in range(P)]
+    nab = 2 * 128 * max(R * dap._pitch(N, 8), N * dap._pitch(R, 8))
+    for mod, incoming in ((pb.tri_mul_out, False), (pb.tri_mul_in, True)):
+        lines, pos = (N, R) if incoming else (R, N)
+        ld = dap._pitch(pos, 8)
+        ab = [ops.trimul_project(z[r], mrow[r], mod, P, incoming,
+                                 out=X[r].buf("ab", (nab,), bf, dev)[:2 * 128 * lines * ld].view(P, 2, C, lines, ld))
+              for r in range(P)]
+        ab_all = [X[r].ab_all(ab[r], N, R, incoming) for r in range(P)]
+        xb = [ops.trimul_contract(ab_all[r], N, R, out=X[r].buf("xb", (P, C, R, dap._pitch(N, 8)), bf, dev))
+              for r in range(P)]
+        x_t = [X[r].x_rows(xb[r]) for r in range(P)]
+        for r in range(P):
+            ops.trimul_output(z[r], x_t[r], mod)
+
+    def attn(zz, mm, mod):
+        proj = [ops.triattn_project(zz[r], mod, out=X[r].buf("tb", (4, R, dap._pitch(N, 64)), bf, dev)) for r in range(P)]
+        tb_all = [X[r].gather_lines(proj[r][1]) for r in range(P)]
+        for r in range(P):
+            ops.triattn_finish(zz[r], mm[r], proj[r][0], tb_all[r], mod)
+
+    attn(z, mrow, pb.tri_att_start)
+    zT = [X[r].transpose(z[r], "z1") for r in range(P)]
+    attn(zT, mcol, pb.tri_att_end)
+    for r in range(P):
+        ops.transition(zT[r], mcol[r], pb.pair_transition)
+    return [X[r].transpose(zT[r], "z0") for r in range(P)]
+
+
+@pytest.mark.parametrize("P,N", [(2, 48), (4, 200), (8, 96), (2, 66)])
+def test_peer_exchange_matches_whole_tensor(pkg, P, N):
+    """Pull kernels + heap layout: the block through PeerExchange equals the unsharded drop-in stack."""
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    g = torch.Generator().manual_seed(N + 1)
+    z = torch.randn(1, N, N, 128, generator=g)
+    s = torch.randn(1, N, 384, generator=g)
+    pm = cases.rand_mask((1, N, N), g)
+    sm = cases.rand_mask((1, N), g)
+    Pw = pkg.weights.pairformer_stack_params(seed=4, no_blocks=1, final_std=None, **cases.OF3)
+    stack = pkg.PairFormerStack(**cases.OF3, no_blocks=1, transition_type="swiglu", pair_dropout=0.25,
+                                fuse_projection_weights=False, blocks_per_ckpt=None, inf=1e9)
+    stack.load_state_dict(Pw, strict=True)
+    stack = stack.to(dev, bf).eval()
+    ops = pkg.dap.CudaOps(dev)
+    zd, sd, pmd, smd = z.to(dev, bf), s.to(dev, bf), pm.to(dev, bf), sm.to(dev, bf)
+    R = N // P
+    heaps = pkg.dap.LocalPeerHeaps(pkg.dap.PeerExchange.heap_bytes(N, P), P, dev)
+    X = [pkg.dap.PeerExchange(heaps.view(r), ops, barrier=False) for r in range(P)]
+    with torch.no_grad():
+        s_ref, z_ref = stack(sd, zd, smd, pmd)
+        shards = []
+        for r in range(P):
+            t = X[r].buf("z0", (R, N, 128), bf, dev)
+            t.copy_(zd[0, r * R:(r + 1) * R])
+            shards.append(t)
+        block = stack.blocks[0]
+        shards = _virtual_pair_block_peer(ops, X, shards, pmd[0], block.pair_stack, P)
+        rows = [ops.single_rows(sd[0], ops.pair_bias_project(shards[r], block.attn_pair_bias), smd[0], block, r * R, R,
+                                out=X[r].buf("s0", (R, 384), bf, dev)) for r in range(P)]
+        s_all = [X[r].gather_rows(rows[r]) for r in range(P)]
+        z_all = [X[r].gather_rows(shards[r].view(R, -1)).view(1, N, N, 128) for r in range(P)]
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    for r in range(P):
+        assert torch.equal(s_all[r], s_all[0]) and torch.equal(z_all[r], z_all[0])
+    assert cases.rel_err(z_all[0].float().cpu(), z_ref.float().cpu()) < 2e-2
+    assert cases.rel_err(s_all[0].unsqueeze(0).float().cpu(), s_ref.float().cpu()) < 2e-2
