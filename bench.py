@@ -231,10 +231,22 @@ def run_ours(args) -> None:
     heap = None
     if world > 1:
         ops = pkg.dap.CudaOps(dev)
-        xchg = None  # default: torch.distributed collectives (NCCL)
+        xchg = None  # None: torch.distributed collectives (NCCL)
         if args.exchange == "peer":
-            heap = pkg.dap.PeerHeap(pkg.dap.PeerExchange.heap_bytes(n, world), world, rank, dev)
-            xchg = pkg.dap.PeerExchange(heap, ops)
+            try:
+                heap = pkg.dap.PeerHeap(pkg.dap.PeerExchange.heap_bytes(n, world), world, rank, dev)
+            except Exception as exc:  # e.g. CUDA IPC not permitted between the ranks' processes
+                print(f"[bench] rank {rank}: no peer heap ({exc}); falling back to NCCL", file=sys.stderr, flush=True)
+                heap = None
+            agreed = torch.tensor([1 if heap is not None else 0], device=dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if int(agreed.item()) == 1:
+                xchg = pkg.dap.PeerExchange(heap, ops)
+            else:
+                if heap is not None:
+                    heap.close()
+                    heap = None
+                args.exchange = "nccl"
         runner = pkg.dap.DapPairFormerStack(stack, world, rank, ops=ops, exchange=xchg)
     else:
         runner = None
@@ -408,7 +420,7 @@ def main():
     ap.add_argument("--blocks", type=int, default=48)
     ap.add_argument("--n-token", type=int, default=768)
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--exchange", choices=["peer", "nccl"], default="nccl",
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how shards move between GPUs")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()

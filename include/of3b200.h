@@ -290,6 +290,11 @@ int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream
 int of3_peer_pull_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
                        long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
                        void* stream);
+/* The same index space with the roles swapped: row (r, i1, i2) is read from the local src + r*t0 + i1*t1 +
+ * i2*t2 and written into rank r's heap at dsts[r] + dst_off + i1*s1 + i2*s2. Follow it with a barrier. */
+int of3_peer_push_rows(void* const* dsts, long long dst_off, const void* src, int world, int rank, int n1, int n2,
+                       long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
+                       void* stream);
 
 /* ---- Building block exported for tests and profiling --------------------------------------
  * X[b][i][j] = sum_k A[b][i][k] * B[b][j][k], bf16 in / fp32 accumulate / bf16 out, the

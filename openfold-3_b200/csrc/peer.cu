@@ -79,7 +79,9 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs flags, int wo
 // srcs.p[i0] + src_off + i1*s1 + i2*s2 and written at dst + i0*t0 + i1*t1 + i2*t2. Vectors are dealt
 // to threads in flat order with the source index rotated by this rank, so that at any moment the ranks
 // read from different peers.
-template <typename V>
+// kPush: the same index space with the roles swapped -- the row is read from the LOCAL buffer `dst` and
+// written into rank i0's heap (posted writes instead of read round trips).
+template <typename V, bool kPush>
 __global__ void __launch_bounds__(256)
 peer_pull_rows_kernel(PeerPtrs srcs, long long src_off, uint8_t* __restrict__ dst, int n0, int n1, int n2,
                       long long s1, long long s2, long long t0, long long t1, long long t2, int vec_per_row,
@@ -100,14 +102,26 @@ peer_pull_rows_kernel(PeerPtrs srcs, long long src_off, uint8_t* __restrict__ ds
                 const long long r1 = row / n2;
                 const int i1 = (int)(r1 % n1);
                 const int i0 = ((int)(r1 / n1) + rank) % n0;
-                const uint8_t* sp = reinterpret_cast<const uint8_t*>(srcs.p[i0]) + src_off + i1 * s1 + i2 * s2;
-                val[u] = reinterpret_cast<const V*>(sp)[v];
-                doff[u] = i0 * t0 + i1 * t1 + i2 * t2 + (long long)v * (long long)sizeof(V);
+                uint8_t* remote = reinterpret_cast<uint8_t*>(srcs.p[i0]) + src_off + i1 * s1 + i2 * s2 +
+                                  (long long)v * (long long)sizeof(V);
+                const long long loff = i0 * t0 + i1 * t1 + i2 * t2 + (long long)v * (long long)sizeof(V);
+                if (kPush) {
+                    val[u] = *reinterpret_cast<const V*>(dst + loff);
+                    doff[u] = reinterpret_cast<long long>(remote);
+                } else {
+                    val[u] = *reinterpret_cast<const V*>(remote);
+                    doff[u] = loff;
+                }
             }
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-            if (doff[u] >= 0) *reinterpret_cast<V*>(dst + doff[u]) = val[u];
+        for (int u = 0; u < 4; ++u) {
+            if (doff[u] < 0) continue;
+            if (kPush)
+                *reinterpret_cast<V*>(doff[u]) = val[u];
+            else
+                *reinterpret_cast<V*>(dst + doff[u]) = val[u];
+        }
     }
 }
 
@@ -159,9 +173,9 @@ int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream
     return OF3_OK;
 }
 
-int of3_peer_pull_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
-                       long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
-                       void* stream) {
+static int peer_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
+                     long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
+                     void* stream, bool push) {
     OF3_REQUIRE(srcs && dst && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, OF3_ERR_ARG,
                 "peer_pull_rows: bad argument (world %d, rank %d)", world, rank);
     OF3_REQUIRE(n1 > 0 && n2 > 0 && row_bytes > 0 && row_bytes % 2 == 0 && src_off >= 0, OF3_ERR_ARG,
@@ -181,14 +195,35 @@ int of3_peer_pull_rows(void* const* srcs, long long src_off, void* dst, int worl
     const long long cap = (long long)sm_count() * 8;
     if (blocks > cap) blocks = cap;
     LaunchScope scope(31, (cudaStream_t)stream);
-    if (vec)
-        peer_pull_rows_kernel<uint4><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-            s, src_off, (uint8_t*)dst, world, n1, n2, s1, s2, t0, t1, t2, vpr, rank);
+    cudaStream_t st = (cudaStream_t)stream;
+    uint8_t* d = (uint8_t*)dst;
+    if (vec && push)
+        peer_pull_rows_kernel<uint4, true><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2, t0, t1,
+                                                                             t2, vpr, rank);
+    else if (vec)
+        peer_pull_rows_kernel<uint4, false><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2, t0,
+                                                                              t1, t2, vpr, rank);
+    else if (push)
+        peer_pull_rows_kernel<uint16_t, true><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2, t0,
+                                                                                t1, t2, vpr, rank);
     else
-        peer_pull_rows_kernel<uint16_t><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
-            s, src_off, (uint8_t*)dst, world, n1, n2, s1, s2, t0, t1, t2, vpr, rank);
+        peer_pull_rows_kernel<uint16_t, false><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2,
+                                                                                 t0, t1, t2, vpr, rank);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
+}
+
+int of3_peer_pull_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
+                       long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
+                       void* stream) {
+    return peer_rows(srcs, src_off, dst, world, rank, n1, n2, s1, s2, t0, t1, t2, row_bytes, stream, false);
+}
+
+int of3_peer_push_rows(void* const* dsts, long long dst_off, const void* src, int world, int rank, int n1, int n2,
+                       long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
+                       void* stream) {
+    return peer_rows(dsts, dst_off, const_cast<void*>(src), world, rank, n1, n2, s1, s2, t0, t1, t2, row_bytes, stream,
+                     true);
 }
 
 }  // extern "C"

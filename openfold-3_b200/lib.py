@@ -91,6 +91,8 @@ SIGNATURES = {
     "of3_peer_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
     "of3_peer_pull_rows": (c_int, [ctypes.POINTER(c_void_p), c_longlong, c_void_p, c_int, c_int, c_int, c_int]
                            + [c_longlong] * 5 + [c_int, c_void_p]),
+    "of3_peer_push_rows": (c_int, [ctypes.POINTER(c_void_p), c_longlong, c_void_p, c_int, c_int, c_int, c_int]
+                           + [c_longlong] * 5 + [c_int, c_void_p]),
     "of3_contract_nt_bf16": (c_int, [c_void_p] * 3 + [c_int] * 7 + [c_longlong] * 3 + [c_void_p]),
 }
 
