@@ -383,6 +383,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * (kB0 + 8 * kLines));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * (kB0 + 8 * kLines) + 8);
 
+    DBG_T(t_entry);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (N + kBQ - 1) / kBQ;
     const int groups_per_b = (R + kLines - 1) / kLines;
@@ -462,15 +463,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             const bool dbg_on = blockIdx.x == 300;
 #endif
             for (int j = 0; j < nblk; ++j) {
-                if ((j & 1) == 0) {  // pair-bias tile for the key blocks j and j+1 (64 keys), shared by all lines
-                    const int t = j >> 1, ts = t & 1;
-                    if (!mbar_wait(tb_empty(ts), ((t >> 1) & 1u) ^ 1u, abort_flag)) {
-                        report_wait_failure(status, abort_flag, kKidCore, 11);
-                        break;
-                    }
-                    mbar_arrive_expect_tx(tb_full(ts), kKBlockBytes);
-                    tma_load_3d(sbase + CoreSmem::kTb + ts * kKBlockBytes, &tmTb, tb_full(ts), t * 64, q0, b * kH + h);
-                }
+                // K / V first: their stage is free once block j-4 has been consumed, while the bias tile
+                // below has to wait for block j-3 -- issued in the other order, that wait also held back
+                // the K / V copy and left it a single step of lead over the MMA that needs it
                 const int s = j % kKvStages;
                 DBG_T(p0);
                 if (!mbar_wait(kv_empty(s), ((j / kKvStages) & 1u) ^ 1u, abort_flag)) {
@@ -485,6 +480,15 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                 bulk_load(sbase + CoreSmem::kV + s * kLines * 2048, v_img + tile0, kLines * 2048, kv_full(s));
                 DBG_T(p2);
                 DBG_ADD(17, p1, p2);
+                if ((j & 1) == 0) {  // pair-bias tile for the key blocks j and j+1 (64 keys), shared by all lines
+                    const int t = j >> 1, ts = t & 1;
+                    if (!mbar_wait(tb_empty(ts), ((t >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 11);
+                        break;
+                    }
+                    mbar_arrive_expect_tx(tb_full(ts), kKBlockBytes);
+                    tma_load_3d(sbase + CoreSmem::kTb + ts * kKBlockBytes, &tmTb, tb_full(ts), t * 64, q0, b * kH + h);
+                }
             }
         }
     } else if (warp <= kLines) {
@@ -560,6 +564,8 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
 #ifdef OF3_CORE_TIMING
         const bool dbg_on = (blockIdx.x == 300) && lane == 0 && (warp == 1 + kLines || warp == 4 * kLines + kLines);
 #endif
+        DBG_T(t_loop);
+        DBG_ADD(24, t_entry, t_loop);
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
             const int k0 = j * kBK;
@@ -683,6 +689,8 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
               DBG_ADD(o8 + 4, t4, t5); DBG_ADD(o8 + 5, t5, t6); DBG_ADD(o8 + 6, t6, t7); DBG_ADD(o8 + 7, t0, t7); }
 #endif
         }
+        DBG_T(t_loop_end);
+        DBG_ADD(25, t_loop, t_loop_end);
         if (ok) {
             if (mbar_wait(pv_done(L, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1u, abort_flag)) {
                 tc_fence_after_sync();
@@ -713,6 +721,12 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, 512);
     }
+#ifdef OF3_CORE_TIMING
+    if (blockIdx.x == 300 && threadIdx.x == 32 * (1 + kLines)) {
+        const long long t_exit = clock64();
+        atomicAdd((unsigned long long*)&g_core_dbg[26], (unsigned long long)(t_exit - t_entry));
+    }
+#endif
 }
 
 // =====================================================================================
