@@ -56,90 +56,164 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const bf16* __restrict__ x
 }
 
 // ---------------------------------------------------------------- attention, one head resident
-// grid (query chunks, H, BB); 8 warps; each warp takes queries chunk*QPB + warp, + 8, ...
+// grid (query chunks of 16, H, BB); 8 warps, each warp owns TWO queries (they share every K / V read).
+// K and V of (bb, h) sit in shared memory as bf16 rows at a 16-byte-aligned pitch chosen so that eight
+// lanes reading eight consecutive rows with 128-bit loads touch all 32 banks once (48 B for d = 24,
+// 112 B for d = 48). A lane owns the keys lane, lane + 32, ...: logits, exponentials and the P V
+// accumulation are lane-private (no shuffles per key); per chunk of 256 keys the warp agrees on the
+// running maximum (one max-reduction), and the 2 x d partial outputs are summed over lanes once at the end.
 // q, g, out and the pair bias hold nq query rows per sample (nq = N, or a window of the rows when the
 // queries are split over ranks); k, v and the mask always hold all N keys.
-// K and V of (bb, h) sit in shared memory as bf16 with an odd word pitch (conflict-free row reads).
-constexpr int kQPB = 32;  // queries per block
+constexpr int kQPB = 16;  // queries per block
 
 template <int D>
-__global__ void __launch_bounds__(256)
+struct AttnCfg {
+    static constexpr int kPitch = (D == 24) ? 48 : 112;  // bytes per K / V row in shared memory
+    static constexpr int kVec = D / 8;                    // 16-byte vectors per row
+};
+
+__device__ __forceinline__ void unpack8(const uint4& w, float* f) {
+    f[0] = bf16lo(w.x); f[1] = bf16hi(w.x); f[2] = bf16lo(w.y); f[3] = bf16hi(w.y);
+    f[4] = bf16lo(w.z); f[5] = bf16hi(w.z); f[6] = bf16lo(w.w); f[7] = bf16hi(w.w);
+}
+
+template <int D>
+__global__ void __launch_bounds__(256, (D <= 24) ? 2 : 1)
 single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                    const bf16* __restrict__ g, const bf16* __restrict__ q_bias, const float* __restrict__ pair_bias,
                    const bf16* __restrict__ mask, bf16* __restrict__ out, int N, int nq, int H, float scale, float inf,
                    long long rows_per_bias) {
-    constexpr int P = D + 2;  // pitch in bf16: (D + 2) / 2 words, odd for D = 24, 48 -> conflict-free
-    extern __shared__ uint8_t smem[];
-    bf16* Ks = reinterpret_cast<bf16*>(smem);
-    bf16* Vs = Ks + (size_t)N * P;
-    float* mb = reinterpret_cast<float*>(Vs + (size_t)N * P);  // additive key mask
-    float* Qs = mb + ((N + 31) & ~31);                          // [8 warps][D]
+    constexpr int PB = AttnCfg<D>::kPitch, NV = AttnCfg<D>::kVec;
+    constexpr int kChunk = 8;  // keys per lane between two agreements on the running maximum
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint8_t* Ks = smem;
+    uint8_t* Vs = Ks + (size_t)N * PB;
+    float* mb = reinterpret_cast<float*>(Vs + (size_t)N * PB);  // additive key mask
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long bb = blockIdx.z;
     const int h = blockIdx.y;
     const int HD = H * D;
-    for (int idx = threadIdx.x; idx < N * (D / 2); idx += 256) {
-        const int kk = idx / (D / 2), c2 = idx % (D / 2);
-        const long long off = (bb * N + kk) * HD + h * D + c2 * 2;
-        *reinterpret_cast<uint32_t*>(Ks + kk * P + c2 * 2) = *reinterpret_cast<const uint32_t*>(k + off);
-        *reinterpret_cast<uint32_t*>(Vs + kk * P + c2 * 2) = *reinterpret_cast<const uint32_t*>(v + off);
+    for (int idx = threadIdx.x; idx < N * NV; idx += 256) {
+        const int kk = idx / NV, c = idx % NV;
+        const long long off = (bb * N + kk) * HD + h * D + c * 8;
+        *reinterpret_cast<uint4*>(Ks + kk * PB + c * 16) = *reinterpret_cast<const uint4*>(k + off);
+        *reinterpret_cast<uint4*>(Vs + kk * PB + c * 16) = *reinterpret_cast<const uint4*>(v + off);
     }
-    for (int kk = threadIdx.x; kk < ((N + 31) & ~31); kk += 256)
+    const int npad = (N + 31) & ~31;
+    for (int kk = threadIdx.x; kk < npad; kk += 256)
         mb[kk] = kk < N ? (mask ? inf * (__bfloat162float(mask[bb * N + kk]) - 1.0f) : 0.f) : -INFINITY;
     __syncthreads();
+
+    const int qa = blockIdx.x * kQPB + warp * 2;  // this warp's queries qa, qa + 1
+    if (qa >= nq) return;
+    const bool has_b = qa + 1 < nq;
+    const int qb = has_b ? qa + 1 : qa;
     const float* pb_base = pair_bias + ((bb / rows_per_bias) * H + h) * (long long)nq * N;
-    for (int qi = blockIdx.x * kQPB + warp; qi < min(nq, (int)(blockIdx.x + 1) * kQPB); qi += 8) {
-        const long long qoff = (bb * nq + qi) * HD + h * D;
-        for (int c = lane; c < D; c += 32)
-            Qs[warp * D + c] = (__bfloat162float(q[qoff + c]) + (q_bias ? __bfloat162float(q_bias[h * D + c]) : 0.f)) * scale;
-        __syncwarp();
-        float qr[D];
+    const float* pba = pb_base + (long long)qa * N;
+    const float* pbb = pb_base + (long long)qb * N;
+    const long long offa = (bb * nq + qa) * HD + h * D, offb = (bb * nq + qb) * HD + h * D;
+    float fa[D], fb[D];
 #pragma unroll
-        for (int c = 0; c < D; ++c) qr[c] = Qs[warp * D + c];
-        const float* pb = pb_base + (long long)qi * N;
-        float m = -INFINITY, l = 0.f;
-        float o0 = 0.f, o1 = 0.f;  // this lane owns output dims lane and lane + 32
-        for (int k0 = 0; k0 < N; k0 += 32) {
-            const int kk = k0 + lane;
-            float s = -INFINITY;
+    for (int c = 0; c < D; ++c) {
+        const float bq = q_bias ? __bfloat162float(q_bias[h * D + c]) : 0.f;
+        fa[c] = (__bfloat162float(q[offa + c]) + bq) * scale;
+        fb[c] = (__bfloat162float(q[offb + c]) + bq) * scale;
+    }
+    float oa[D], ob[D];
+#pragma unroll
+    for (int c = 0; c < D; ++c) oa[c] = ob[c] = 0.f;
+    float ma = -INFINITY, mbq = -INFINITY, la = 0.f, lb = 0.f;
+
+    for (int k0 = 0; k0 < npad; k0 += 32 * kChunk) {
+        float sa[kChunk], sb[kChunk];
+        float cma = -INFINITY, cmb = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) {
+            const int kk = k0 + i * 32 + lane;
+            sa[i] = sb[i] = -INFINITY;
             if (kk < N) {
-                float dot = 0.f;
-                const uint32_t* kr = reinterpret_cast<const uint32_t*>(Ks + kk * P);
+                float da = 0.f, db = 0.f;
 #pragma unroll
-                for (int c2 = 0; c2 < D / 2; ++c2) {
-                    const uint32_t w = kr[c2];
-                    dot = fmaf(qr[c2 * 2], bf16lo(w), dot);
-                    dot = fmaf(qr[c2 * 2 + 1], bf16hi(w), dot);
+                for (int c8 = 0; c8 < NV; ++c8) {
+                    float kf[8];
+                    unpack8(*reinterpret_cast<const uint4*>(Ks + kk * PB + c8 * 16), kf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        da = fmaf(fa[c8 * 8 + e], kf[e], da);
+                        db = fmaf(fb[c8 * 8 + e], kf[e], db);
+                    }
                 }
-                s = (dot + mb[kk]) + pb[kk];
+                const float m = mb[kk];
+                sa[i] = (da + m) + pba[kk];  // the reference's order: (q.k + mask bias) + pair bias
+                sb[i] = (db + m) + pbb[kk];
             }
-            const float m_new = fmaxf(m, warp_max(s));
-            const float p = (kk < N) ? __expf(s - m_new) : 0.f;
-            const float corr = __expf(m - m_new);
-            l = l * corr + warp_sum(p);
-            o0 *= corr;
-            o1 *= corr;
-            const int kmax = min(32, N - k0);
-            for (int j = 0; j < kmax; ++j) {
-                const float pj = __shfl_sync(0xffffffffu, p, j);
-                const bf16* vr = Vs + (k0 + j) * P;
-                if (lane < D) o0 = fmaf(pj, __bfloat162float(vr[lane]), o0);
-                if (D > 32 && lane + 32 < D) o1 = fmaf(pj, __bfloat162float(vr[lane + 32]), o1);
+            cma = fmaxf(cma, sa[i]);
+            cmb = fmaxf(cmb, sb[i]);
+        }
+        const float na = fmaxf(ma, warp_max(cma)), nb = fmaxf(mbq, warp_max(cmb));  // finite: key k0 exists
+        const float ca = __expf(ma - na), cb = __expf(mbq - nb);                     // 0 on the first chunk
+        ma = na;
+        mbq = nb;
+        la *= ca;
+        lb *= cb;
+#pragma unroll
+        for (int c = 0; c < D; ++c) {
+            oa[c] *= ca;
+            ob[c] *= cb;
+        }
+#pragma unroll
+        for (int i = 0; i < kChunk; ++i) {
+            const int kk = k0 + i * 32 + lane;
+            if (kk < N) {
+                const float pa = __expf(sa[i] - ma), pq = __expf(sb[i] - mbq);
+                la += pa;
+                lb += pq;
+#pragma unroll
+                for (int c8 = 0; c8 < NV; ++c8) {
+                    float vf[8];
+                    unpack8(*reinterpret_cast<const uint4*>(Vs + kk * PB + c8 * 16), vf);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        oa[c8 * 8 + e] = fmaf(pa, vf[e], oa[c8 * 8 + e]);
+                        ob[c8 * 8 + e] = fmaf(pq, vf[e], ob[c8 * 8 + e]);
+                    }
+                }
             }
-            m = m_new;
         }
-        const float inv = 1.0f / l;
-        if (lane < D) {
-            float r = o0 * inv;
-            if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[qoff + lane])));
-            out[qoff + lane] = __float2bfloat16_rn(r);
+    }
+    la = warp_sum(la);
+    lb = warp_sum(lb);
+    float ra = 0.f, rb = 0.f;  // lane c keeps output dim c (and c + 32 for d = 48)
+    float ra2 = 0.f, rb2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < D; ++c) {
+        const float ta = warp_sum(oa[c]), tb = warp_sum(ob[c]);
+        if (c < 32) {
+            if (lane == c) { ra = ta; rb = tb; }
+        } else {
+            if (lane == c - 32) { ra2 = ta; rb2 = tb; }
         }
-        if (D > 32 && lane + 32 < D) {
-            float r = o1 * inv;
-            if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[qoff + lane + 32])));
-            out[qoff + lane + 32] = __float2bfloat16_rn(r);
+    }
+    const float ia = 1.0f / la, ib = 1.0f / lb;
+    if (lane < D) {
+        float r = ra * ia;
+        if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offa + lane])));
+        out[offa + lane] = __float2bfloat16_rn(r);
+        if (has_b) {
+            float r2 = rb * ib;
+            if (g) r2 *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offb + lane])));
+            out[offb + lane] = __float2bfloat16_rn(r2);
         }
-        __syncwarp();
+    }
+    if (D > 32 && lane + 32 < D) {
+        float r = ra2 * ia;
+        if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offa + lane + 32])));
+        out[offa + lane + 32] = __float2bfloat16_rn(r);
+        if (has_b) {
+            float r2 = rb2 * ib;
+            if (g) r2 *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offb + lane + 32])));
+            out[offb + lane + 32] = __float2bfloat16_rn(r2);
+        }
     }
 }
 
@@ -180,7 +254,7 @@ template <int D>
 int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias, const float* pb,
                 const bf16* mask, bf16* out, int BB, int N, int nq, int H, float inf, long long rows_per_bias,
                 cudaStream_t st) {
-    const size_t smem = (size_t)N * (D + 2) * 2 * 2 + (size_t)((N + 31) & ~31) * 4 + 8 * D * 4;
+    const size_t smem = (size_t)N * AttnCfg<D>::kPitch * 2 + (size_t)((N + 31) & ~31) * 4;
     static size_t configured = 0;
     if (smem > configured) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(single_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -203,7 +277,7 @@ bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_z, int H, in
     if (flags & (OF3_FLAG_ADA_LN | OF3_FLAG_FORCE_GENERIC)) return false;
     if (!(d == 24 || d == 48) || H * d != c_a || c_a % 64 != 0) return false;
     if (c_z != 128 || H != 16 || Bz <= 0 || Ba % Bz != 0) return false;
-    return (size_t)N * (d + 2) * 4 + (size_t)N * 4 + 8192 <= 200 * 1024;
+    return (size_t)N * (d == 24 ? 48 : 112) * 2 + (size_t)N * 4 + 1024 <= 200 * 1024;
 }
 
 int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, int Ba, int Bz, int N, int c_a, int H,
