@@ -333,8 +333,9 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 32;       // keys per step
 constexpr int kMaxKeys = 2048;   // one CTA keeps a mask-bias row per line in shared memory
-constexpr int kKvStages = 4;     // K / V ring (one untiled bulk copy per tile): covers the load round trip
-constexpr int kLines = 4;     // lines per CTA
+constexpr int kKvStages = 3;     // K / V ring (one untiled bulk copy per tile): covers the load round trip
+constexpr int kLines = 2;     // lines per CTA; two CTAs share an SM (their prologues, epilogues and waits interleave)
+constexpr int kLinePad = 4;   // the operand images pad the line count of a sample to a multiple of this
 constexpr int kCoreThreads = 32 * (1 + kLines + 4 * kLines);  // producer, one MMA warp per line, softmax
 constexpr float kRescaleThreshold = 8.0f;
 #ifdef OF3_CORE_TIMING
@@ -359,7 +360,7 @@ struct CoreSmem {
 };
 
 template <bool kTransposed>
-__global__ void __launch_bounds__(kCoreThreads, 1)
+__global__ void __launch_bounds__(kCoreThreads, 2)
 triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16* __restrict__ k_img,
                     const __nv_bfloat16* __restrict__ v_img, const __grid_constant__ CUtensorMap tmTb,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
@@ -434,7 +435,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         mbs[idx] = v;
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
+        tmem_alloc(smem_u32((const void*)tmem_ptr), kLines * 128);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -454,7 +455,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     if (warp == 0) {
         if (lane == 0) {
             const int nkb = npad / kBK;
-            const int rpad = (R + 3) & ~3;
+            const int rpad = (R + kLinePad - 1) / kLinePad * kLinePad;
             const long long bh = (long long)b * kH + h;
             mbar_arrive_expect_tx(q_full, kLines * kBQ * 64);
             bulk_load(sbase + CoreSmem::kQ, q_img + (((bh * n_qt + qt) * rpad + line0) * kBQ) * kD, kLines * kBQ * 64,
@@ -719,7 +720,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     __syncthreads();
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem_base, 512);
+        tmem_dealloc(tmem_base, kLines * 128);
     }
 #ifdef OF3_CORE_TIMING
     if (blockIdx.x == 300 && threadIdx.x == 32 * (1 + kLines)) {
@@ -1073,7 +1074,7 @@ bool triattn_supported(int c_z, int H, int d, int N) {
 // Elements of each of the q / k / v image buffers for B samples of R lines and N positions: 4 heads x
 // (query tiles of 128) x (R rounded up to 4 lines) x 128 x 32; the k / v images need no more than that.
 size_t triattn_image_elems(int B, int R, int N) {
-    return (size_t)B * kH * ceil_div(N, kBQ) * align_up(R, kLines) * kBQ * kD;
+    return (size_t)B * kH * ceil_div(N, kBQ) * align_up(R, kLinePad) * kBQ * kD;
 }
 
 // q, k [line][head][pos][32], v transposed, and this shard's rows of the pair bias
