@@ -261,7 +261,7 @@ def run_ours(args) -> None:
         if graphed is not None:
             return graphed(s_d, z_d, sm_d, pm_d)
         if runner is not None:
-            return runner(s_d, z_d, sm_d, pm_d)
+            return runner(s_d, z_d, sm_d, pm_d, sharded=True)
         return stack(s_d, z_d, sm_d, pm_d)  # clones the inputs, then updates the clones in place
 
     def sync():
@@ -270,9 +270,21 @@ def run_ours(args) -> None:
             dist.barrier()
             torch.cuda.synchronize(dev)
 
+    if world > 1:
+        # N > 1: the job's input and output are row-sharded -- a rank moves only its R = N / world rows of z and
+        # of the pair mask (and of the mask's transpose) between host and device; s and the token mask are whole
+        R = n // world
+        rows = slice(rank * R, (rank + 1) * R)
+        z_host = z_host[:, rows].contiguous().pin_memory()
+        pm_host = (pm_host[0, rows].contiguous().pin_memory(), pm_host[0][:, rows].t().contiguous().pin_memory())
+        z_out_host = torch.empty_like(z_host).pin_memory()
+
+    def to_dev(t, **kw):
+        return tuple(x.to(dev, **kw) for x in t) if isinstance(t, tuple) else t.to(dev, **kw)
+
     with torch.no_grad():
         s_d, z_d = s_host.to(dev), z_host.to(dev)
-        sm_d, pm_d = sm_host.to(dev), pm_host.to(dev)
+        sm_d, pm_d = sm_host.to(dev), to_dev(pm_host)
         for _ in range(args.warmup):
             step_resident(s_d, z_d, sm_d, pm_d)
         sync()
@@ -280,7 +292,7 @@ def run_ours(args) -> None:
         graph_note = "eager launches"
         stage(f"eager warm-up done ({args.warmup} steps)")
         if runner is not None and not args.no_graph:
-            graphed = pkg.dap.GraphedDapRunner(runner, s_d, z_d, sm_d, pm_d, warmup=1)
+            graphed = pkg.dap.GraphedDapRunner(runner, s_d, z_d, sm_d, pm_d, warmup=1, sharded=True)
             stage("graph captured")
             graph_note = "one CUDA graph per step (kernels of both streams and the NCCL collectives)"
             for _ in range(args.warmup):
@@ -304,14 +316,18 @@ def run_ours(args) -> None:
         assert torch.isfinite(z_o.float()).all() and torch.isfinite(s_o.float()).all(), "non-finite trunk output"
 
         # ---- end to end through the public API with host buffers
-        h2d = sum(t.numel() * t.element_size() for t in (s_host, z_host, sm_host, pm_host))
-        d2h = sum(t.numel() * t.element_size() for t in (s_out_host, z_out_host))
+        def nbytes(*ts):
+            return sum(x.numel() * x.element_size() for t in ts for x in (t if isinstance(t, tuple) else (t,)))
+
+        # whole-job bytes per step: every rank copies its own shard (and the small replicated tensors)
+        h2d = nbytes(s_host, z_host, sm_host, pm_host) * world
+        d2h = nbytes(s_out_host, z_out_host) * world
 
         def step_e2e():
             s_in = s_host.to(dev, non_blocking=True)
             z_in = z_host.to(dev, non_blocking=True)
             sm_in = sm_host.to(dev, non_blocking=True)
-            pm_in = pm_host.to(dev, non_blocking=True)
+            pm_in = to_dev(pm_host, non_blocking=True)
             if runner is not None:
                 s_r, z_r = step_resident(s_in, z_in, sm_in, pm_in)
             else:
@@ -333,7 +349,7 @@ def run_ours(args) -> None:
         if graphed is not None:
             # per-kernel breakdown and launch count of a step: one eager, profiled step outside the timed region
             lib.profile_begin(timing=True)
-            runner(s_d, z_d, sm_d, pm_d)
+            runner(s_d, z_d, sm_d, pm_d, sharded=True)
             sync()
             prof = lib.profile_end()
             launches_in_timed_region = int(sum(l for l, _ in prof.values())) * args.steps
@@ -367,7 +383,7 @@ def run_ours(args) -> None:
             achieved = kf[top] / world / (per_launch_ms * 1e-3) / 1e12
             roofline = {"kernel": top, "bound": "tensor", "achieved": round(achieved, 1), "peak": tensor_peak,
                         "unit": "TFLOP/s", "frac": round(achieved / tensor_peak, 4),
-                        "traffic": KERNEL_DRAM_TRAFFIC.get(top) if n == 768 else None, "peak_kind": f"bf16 sustained, {peak_kind}",
+                        "traffic": KERNEL_DRAM_TRAFFIC.get(top) if (n == 768 and world == 1) else None, "peak_kind": f"bf16 sustained, {peak_kind}",
                         "algorithmic_flop_per_launch": kf[top] / world}
         cpu_s, cores = oracle_block_seconds(n) if world == 1 and not args.no_cpu_baseline else (None, 0)
         cpu_baseline = None
@@ -385,6 +401,8 @@ def run_ours(args) -> None:
                                    "seeded random weights",
                        "parallelism": "single GPU" if world == 1 else f"DAP row-sharded over {world} GPUs",
                        "launch": graph_note,
+                       "io": ("whole tensors" if world == 1 else
+                              "row-sharded: each rank holds, uploads and downloads its N/world rows of z; s replicated"),
                        "exchange": ("none" if world == 1 else
                                     "barrier + pull kernels over NVLink peer memory" if args.exchange == "peer"
                                     else "NCCL all-to-all / all-gather"),

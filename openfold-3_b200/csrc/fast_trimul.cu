@@ -62,8 +62,10 @@ struct InSmem {
 };
 
 // outgoing: tmZ is 3-D {c, second index, b*N + first index}; incoming: 4-D {c, second, first, b}
+constexpr int kInThreads = 448;  // producer, MMA, 4 LayerNorm warps, 2 x 4 epilogue warps
+
 template <bool kOutgoing>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(kInThreads, 1)
 trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWap,
                  const __grid_constant__ CUtensorMap tmWag, const __grid_constant__ CUtensorMap tmWbp,
                  const __grid_constant__ CUtensorMap tmWbg, const __nv_bfloat16* __restrict__ mask,
@@ -192,7 +194,11 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             if (lane == 0) mbar_arrive(a_ready(s));
         }
     } else {
-        // ---------------------------------------------------------------- epilogue warps (6..9)
+        // ---------------------------------------------------------------- epilogue warps: 6..9 take the a
+        // projection (TMEM slot 0), 10..13 the b projection (slot 1). One set of four warps doing both
+        // (2 x 128 sigmoid / multiply / convert / store per row and tile on one thread) was the longest
+        // chain of the kernel.
+        const int qset = (warp - 6) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         uint32_t it = 0;
@@ -207,7 +213,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                                                 : ((long long)(tc.b * N + k) * R + tc.fixed);
                 m = __bfloat162float(mask[lin]);
             }
-            for (int q = 0; q < 2; ++q) {
+            for (int q = qset; q <= qset; ++q) {
                 if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
                     ok = false;
@@ -550,11 +556,11 @@ int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     LaunchScope scope(kKidIn, st);
     if (!transposed_walk)
-        trimul_in_kernel<true><<<grid, 320, InSmem::kDyn, st>>>(
+        trimul_in_kernel<true><<<grid, kInThreads, InSmem::kDyn, st>>>(
             tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
             (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, device_status_ptr());
     else
-        trimul_in_kernel<false><<<grid, 320, InSmem::kDyn, st>>>(
+        trimul_in_kernel<false><<<grid, kInThreads, InSmem::kDyn, st>>>(
             tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
             (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());

@@ -196,7 +196,7 @@ attention_kernel(const float* __restrict__ q, const float* __restrict__ k,
 // ------------------------------------------------------------------ fused pair-bias projection
 // LN(x).w_h = rstd * sum_c (x_c - mean) * (gamma_c w_hc) + sum_c beta_c w_hc
 template <typename T>
-__global__ void __launch_bounds__(256) pair_bias_c128_h16_kernel(const T* __restrict__ z,
+__global__ void __launch_bounds__(128) pair_bias_c128_h16_kernel(const T* __restrict__ z,
                                                                  const T* __restrict__ gamma,
                                                                  const T* __restrict__ beta,
                                                                  const T* __restrict__ w,
@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256) pair_bias_c128_h16_kernel(const T* __rest
                                                                  long long nn) {
     __shared__ float ws[16][128];
     __shared__ float cs[16];
-    for (int i = threadIdx.x; i < 16 * 128; i += 256) {
+    for (int i = threadIdx.x; i < 16 * 128; i += 128) {
         const int c = i & 127;
         ws[i >> 7][c] = ld_as_float(w + i) * (gamma ? ld_as_float(gamma + c) : 1.0f);
     }
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(256) pair_bias_c128_h16_kernel(const T* __rest
         cs[threadIdx.x] = a;
     }
     __syncthreads();
-    const long long r = (long long)blockIdx.x * 256 + threadIdx.x;
+    const long long r = (long long)blockIdx.x * 128 + threadIdx.x;
     if (r >= rows) return;
     float x[128];
     const T* zr = z + r * 128;
@@ -237,31 +237,42 @@ __global__ void __launch_bounds__(256) pair_bias_c128_h16_kernel(const T* __rest
             x[i * 4] = v.x; x[i * 4 + 1] = v.y; x[i * 4 + 2] = v.z; x[i * 4 + 3] = v.w;
         }
     }
-    float s = 0.f;
+    // four independent partial sums / four heads at a time: the single chains of 128 dependent
+    // operations were the critical path at the 8-12 warps per SM that 128 row registers allow
+    float s4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int c = 0; c < 128; ++c) s += x[c];
-    const float mean = s * (1.0f / 128.0f);
-    float var = 0.f;
-#pragma unroll
-    for (int c = 0; c < 128; ++c) {
-        x[c] -= mean;
-        var = fmaf(x[c], x[c], var);
+    for (int c = 0; c < 128; c += 4) {
+        s4[0] += x[c]; s4[1] += x[c + 1]; s4[2] += x[c + 2]; s4[3] += x[c + 3];
     }
-    const float rstd = 1.0f / sqrtf(var * (1.0f / 128.0f) + 1e-5f);
+    const float mean = ((s4[0] + s4[1]) + (s4[2] + s4[3])) * (1.0f / 128.0f);
+    float v4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int c = 0; c < 128; c += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            x[c + e] -= mean;
+            v4[e] = fmaf(x[c + e], x[c + e], v4[e]);
+        }
+    }
+    const float rstd = 1.0f / sqrtf(((v4[0] + v4[1]) + (v4[2] + v4[3])) * (1.0f / 128.0f) + 1e-5f);
     const long long b = r / nn;
     const long long qk = r % nn;
 #pragma unroll 1
-    for (int h = 0; h < 16; ++h) {
-        float acc = 0.f;
+    for (int h = 0; h < 16; h += 4) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < 128; c += 4) {
-            const float4 wv = *reinterpret_cast<const float4*>(&ws[h][c]);
-            acc = fmaf(x[c], wv.x, acc);
-            acc = fmaf(x[c + 1], wv.y, acc);
-            acc = fmaf(x[c + 2], wv.z, acc);
-            acc = fmaf(x[c + 3], wv.w, acc);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float4 wv = *reinterpret_cast<const float4*>(&ws[h + e][c]);
+                acc[e] = fmaf(x[c], wv.x, acc[e]);
+                acc[e] = fmaf(x[c + 1], wv.y, acc[e]);
+                acc[e] = fmaf(x[c + 2], wv.z, acc[e]);
+                acc[e] = fmaf(x[c + 3], wv.w, acc[e]);
+            }
         }
-        dst[(b * 16 + h) * nn + qk] = fmaf(acc, rstd, cs[h]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) dst[(b * 16 + h + e) * nn + qk] = fmaf(acc[e], rstd, cs[h + e]);
     }
 }
 
@@ -481,7 +492,7 @@ int pair_bias_c128_h16(const T* z, const T* gamma, const T* beta, const T* w, fl
     if (rows <= 0) return OF3_OK;
     OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "pair_bias: z must be 16-byte aligned");
     LaunchScope scope(20, stream);
-    pair_bias_c128_h16_kernel<T><<<grid_for(rows, 256), 256, 0, stream>>>(z, gamma, beta, w, dst, rows, nn);
+    pair_bias_c128_h16_kernel<T><<<grid_for(rows, 128), 128, 0, stream>>>(z, gamma, beta, w, dst, rows, nn);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }

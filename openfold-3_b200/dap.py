@@ -504,22 +504,32 @@ class DapPairFormerStack:
         self.ops.transition(zT, maskT_rows if mask_trans else None, pb.pair_transition)
         return self.x.transpose(zT, "z0")
 
-    def __call__(self, s, z, single_mask, pair_mask, _mask_trans=True):
+    def __call__(self, s, z, single_mask, pair_mask, _mask_trans=True, sharded: bool = False):
+        """Replicated interface (default): z [1, N, N, C] and pair_mask [1, N, N] whole on every rank; returns the
+        whole updated (s, z) on every rank.
+        ``sharded=True``: z is this rank's rows [1, R, N, C], pair_mask a pair (rows [R, N] of the mask, rows
+        [R, N] of its transpose); returns (s, this rank's rows of z [1, R, N, C]) -- nothing of size N^2 is
+        replicated or gathered."""
         assert z.shape[0] == 1 and z.dim() == 4, "DAP runs one sample: z [1, N, N, C]"
-        N = z.shape[1]
+        N = z.shape[2]
         assert N % self.world == 0, f"N_token {N} must be divisible by the {self.world} ranks"
         ops, X = self.ops, self.x
         R = N // self.world
+        assert z.shape[1] == (R if sharded else N)
         X.begin()
+        z_in = z[0] if sharded else self.shard(z[0])
         z_loc = X.buf("z0", (R, N, z.shape[-1]), z.dtype, z.device)
         if z_loc is None:
-            z_loc = self.shard(z[0]).contiguous().clone()
+            z_loc = z_in.contiguous().clone()
         else:
-            z_loc.copy_(self.shard(z[0]))
+            z_loc.copy_(z_in)
         s_full = s[0].clone(memory_format=torch.contiguous_format)
-        pm = pair_mask[0].to(z.dtype)
-        mask_rows = self.shard(pm, 0).contiguous()
-        maskT_rows = self.shard(pm, 1).transpose(0, 1).contiguous()
+        if sharded:
+            mask_rows, maskT_rows = (m.to(z.dtype).contiguous() for m in pair_mask)
+        else:
+            pm = pair_mask[0].to(z.dtype)
+            mask_rows = self.shard(pm, 0).contiguous()
+            maskT_rows = self.shard(pm, 1).transpose(0, 1).contiguous()
         sm = None if single_mask is None else single_mask[0]
         side = getattr(ops, "side", contextlib.nullcontext)
         mark = getattr(ops, "mark_side", lambda: None)
@@ -544,6 +554,8 @@ class DapPairFormerStack:
             s_full = X.gather_rows(pending[0])
         if s_full.is_cuda and not torch.cuda.is_current_stream_capturing():
             s_full.record_stream(torch.cuda.current_stream(s_full.device))
+        if sharded:
+            return s_full.unsqueeze(0), z_loc.unsqueeze(0)
         z_full = X.gather_rows(z_loc.view(R, -1)).view(1, N, N, z_loc.shape[-1])
         return s_full.unsqueeze(0), z_full
 
@@ -558,26 +570,29 @@ class GraphedDapRunner:
     the same points.
     """
 
-    def __init__(self, runner: DapPairFormerStack, s, z, single_mask, pair_mask, warmup: int = 2):
-        self.runner = runner
+    def __init__(self, runner: DapPairFormerStack, s, z, single_mask, pair_mask, warmup: int = 2,
+                 sharded: bool = False):
+        self.runner, self.sharded = runner, sharded
         self.s_in, self.z_in = s.clone(), z.clone()
         self.sm_in = None if single_mask is None else single_mask.clone()
-        self.pm_in = pair_mask.clone()
+        self.pm_in = tuple(m.clone() for m in pair_mask) if sharded else pair_mask.clone()
         dev = z.device
         cur = torch.cuda.current_stream(dev)
         st = torch.cuda.Stream(dev)
         st.wait_stream(cur)
         with torch.cuda.stream(st), torch.no_grad():  # communicators, kernel attributes, workspaces: all set up eagerly
             for _ in range(max(1, warmup)):
-                runner(self.s_in, self.z_in, self.sm_in, self.pm_in)
+                runner(self.s_in, self.z_in, self.sm_in, self.pm_in, sharded=sharded)
         cur.wait_stream(st)
         torch.cuda.synchronize(dev)
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph), torch.no_grad():
-            self.s_out, self.z_out = runner(self.s_in, self.z_in, self.sm_in, self.pm_in)
+            self.s_out, self.z_out = runner(self.s_in, self.z_in, self.sm_in, self.pm_in, sharded=sharded)
 
     def __call__(self, s, z, single_mask, pair_mask):
-        for dst, src in ((self.s_in, s), (self.z_in, z), (self.sm_in, single_mask), (self.pm_in, pair_mask)):
+        pairs = [(self.s_in, s), (self.z_in, z), (self.sm_in, single_mask)]
+        pairs += list(zip(self.pm_in, pair_mask)) if self.sharded else [(self.pm_in, pair_mask)]
+        for dst, src in pairs:
             if dst is not None and src is not None and dst.data_ptr() != src.data_ptr():
                 dst.copy_(src, non_blocking=True)
         self.graph.replay()

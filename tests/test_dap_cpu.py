@@ -132,6 +132,11 @@ def _worker(rank, world, port, n_token, n_blocks, result_file):
         with torch.no_grad():
             s_d, z_d = runner(s, z, sm, pm)
             s_r, z_r = oracle.pairformer_stack(s, z, sm, pm, P, "", n_blocks, 4, 16)
+            # sharded interface: only this rank's rows go in and come out
+            R = n_token // world
+            rows = slice(rank * R, (rank + 1) * R)
+            s_s, z_s = runner(s, z[:, rows].contiguous(), sm, (pm[0, rows], pm[0][:, rows].t()), sharded=True)
+            assert torch.equal(s_s, s_d) and torch.equal(z_s, z_d[:, rows])
         es, ez = cases.rel_err(s_d, s_r), cases.rel_err(z_d, z_r)
         # every rank must hold the same full result
         gathered = [None] * world
