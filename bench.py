@@ -67,12 +67,13 @@ def kernel_flops(n: int) -> dict:
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at N = 768 from the committed ncu
 # summaries under profiles/ (captured at N = 768 itself, one block).
 KERNEL_DRAM_TRAFFIC = {
-    "triattn_core": 597.3e6,
-    "trimul_in": 400e6,
+    "triattn_core": 593.1e6,
+    "trimul_in": 411e6,
     "contract": 417e6,
-    "trimul_out": 412e6,
+    "trimul_out": 411e6,
     "triattn_proj": 552e6,
-    "triattn_out": 412e6,
+    "triattn_out": 413e6,
+    "transition": 268e6,
 }
 
 
