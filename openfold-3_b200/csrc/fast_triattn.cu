@@ -625,7 +625,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                     const int e = i * 8 + jj * 2;
                     sv[e] += bf16lo(w[jj]);
                     sv[e + 1] += bf16hi(w[jj]);
-                    mx = fmaxf(mx, fmaxf(sv[e], sv[e + 1]));
+                    mx = max3(mx, sv[e], sv[e + 1]);
                 }
             }
             if (j == 0) {

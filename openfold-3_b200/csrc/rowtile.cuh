@@ -23,6 +23,12 @@ __device__ __forceinline__ float tanh_approx(float x) {
 __device__ __forceinline__ float sigmoid_fast(float x) {
     return fmaf(0.5f, tanh_approx(0.5f * x), 0.5f);
 }
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
