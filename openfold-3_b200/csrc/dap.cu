@@ -166,9 +166,9 @@ int of3_pair_bias_project(const void* z_rows, const void* ln_w, const void* ln_b
     OF3_REQUIRE(z_rows && w && bias_rows, OF3_ERR_ARG, "pair_bias_project: null pointer argument");
     OF3_REQUIRE(c_z == 128 && H == 16, OF3_ERR_SHAPE, "pair_bias_project: only c_z = 128, 16 heads");
     if (dtype == OF3_DTYPE_BF16)
-        return generic::pair_bias_c128_h16<__nv_bfloat16>((const __nv_bfloat16*)z_rows, (const __nv_bfloat16*)ln_w,
-                                                          (const __nv_bfloat16*)ln_b, (const __nv_bfloat16*)w,
-                                                          bias_rows, 1, positions, (cudaStream_t)stream);
+        return fast::pair_bias_c128_h16((const __nv_bfloat16*)z_rows, (const __nv_bfloat16*)ln_w,
+                                        (const __nv_bfloat16*)ln_b, (const __nv_bfloat16*)w, bias_rows, 1, positions,
+                                        (cudaStream_t)stream);
     OF3_REQUIRE(dtype == OF3_DTYPE_F32, OF3_ERR_ARG, "pair_bias_project: bad dtype %d", dtype);
     return generic::pair_bias_c128_h16<float>((const float*)z_rows, (const float*)ln_w, (const float*)ln_b,
                                               (const float*)w, bias_rows, 1, positions, (cudaStream_t)stream);

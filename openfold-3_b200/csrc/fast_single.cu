@@ -296,8 +296,8 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, in
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "attn_pair_bias: workspace too small (%zu needed)", ws.off);
     int rc;
     if (pair_bias == nullptr) {
-        if ((rc = generic::pair_bias_c128_h16<bf16>(z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b,
-                                                    (const bf16*)p->w_z, zb, Bz, (long long)N * N, st)))
+        if ((rc = fast::pair_bias_c128_h16(z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b, (const bf16*)p->w_z, zb,
+                                           Bz, (long long)N * N, st)))
             return rc;
         pair_bias = zb;
     }

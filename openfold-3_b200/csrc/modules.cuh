@@ -65,6 +65,9 @@ int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bf
 int attn_pair_bias_rows(const __nv_bfloat16* a, const float* pair_bias_rows, const __nv_bfloat16* mask,
                         __nv_bfloat16* out_rows, int N, int row0, int R, int c_a, int H, int d, float inf, int flags,
                         const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st);
+// pair-bias projection of the single track on the tensor pipe: dst [B][16][nn] fp32 from z [B*nn][128] bf16
+int pair_bias_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
+                       const __nv_bfloat16* w, float* dst, long long B, long long nn, cudaStream_t st);
 bool transition_wide_supported(int c, int n);
 int transition_wide(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows, int c,
                     int n, int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
