@@ -68,18 +68,25 @@ struct ProjSmem {
     static constexpr uint32_t kZ = 2 * kWKb;                  // 2 stages x 32768
     static constexpr uint32_t kGamma = kZ + 2 * kTileBytes;
     static constexpr uint32_t kBeta = kGamma + 512;
-    static constexpr uint32_t kWb = kBeta + 512;              // float [4][128]
-    static constexpr uint32_t kBars = kWb + 2048;
+    static constexpr uint32_t kWb = kBeta + 512;              // bias weight as a B operand: 2 k-blocks x [16 x 128 B]
+    static constexpr uint32_t kBars = kWb + 4096;
     static constexpr uint32_t kTotal = kBars + 128;
     static constexpr uint32_t kDyn = kTotal + 1024;
 };
 
+// warps: 0 producer, 1 MMA issuer, 2..5 LayerNorm (one thread per row), 6..9 epilogue of TMEM slot 0 (q, k),
+// 10..13 epilogue of slot 1 (v and the 4-wide triangle bias). The bias projection is a fourth GEMM (N = 16
+// with 12 zero rows) instead of 1024 FMAs per row inside the LayerNorm pass.
+constexpr bool kProjSplitEpilogue = false;  // second epilogue warp set: measured slower (128-register cap)
+constexpr int kProjThreads = kProjSplitEpilogue ? 448 : 320;
+
 template <bool kTransposed>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(kProjThreads, 1)
 triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWq,
                     const __grid_constant__ CUtensorMap tmWk, const __grid_constant__ CUtensorMap tmWv,
+                    const __grid_constant__ CUtensorMap tmWb,
                     const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
-                    const __nv_bfloat16* __restrict__ w_bias, __nv_bfloat16* __restrict__ q_out,
+                    __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ vt_out,
                     __nv_bfloat16* __restrict__ tb_out, int B, int R, int N, int ldn, int npad, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -87,7 +94,6 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
     float* gamma = reinterpret_cast<float*>(gbase + ProjSmem::kGamma);
     float* beta = reinterpret_cast<float*>(gbase + ProjSmem::kBeta);
-    float* wb = reinterpret_cast<float*>(gbase + ProjSmem::kWb);
     const uint32_t bars = sbase + ProjSmem::kBars;
     const uint32_t w_full = bars;
     auto z_full = [&](int s) { return bars + 8u * (1 + s); };
@@ -119,7 +125,6 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
         gamma[threadIdx.x] = __bfloat162float(ln_w[threadIdx.x]);
         beta[threadIdx.x] = __bfloat162float(ln_b[threadIdx.x]);
     }
-    for (int i = threadIdx.x; i < kH * kC; i += blockDim.x) wb[i] = __bfloat162float(w_bias[i]);
     if (warp == 1) {
         tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
         tmem_relinquish();
@@ -128,16 +133,18 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_ptr;
-    // TMEM: slot 0 = [q|k] columns [0,256), slot 1 = v columns [256,384)
+    // TMEM: slot 0 = [q|k] columns [0,256), slot 1 = v columns [256,384) + triangle bias [384,400)
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_arrive_expect_tx(w_full, 2 * ProjSmem::kWKb);
+            mbar_arrive_expect_tx(w_full, 2 * ProjSmem::kWKb + 4096);
             const CUtensorMap* wm[3] = {&tmWq, &tmWk, &tmWv};
             for (int w = 0; w < 3; ++w)
                 for (int kb = 0; kb < 2; ++kb)
                     tma_load_2d(sbase + ProjSmem::kW + kb * ProjSmem::kWKb + w * 128 * 128, wm[w], w_full,
                                 kb * 64, 0);
+            // rows 4..15 of the box lie outside the [4 x 128] weight: the copy fills them with zeros
+            for (int kb = 0; kb < 2; ++kb) tma_load_2d(sbase + ProjSmem::kWb + kb * 2048, &tmWb, w_full, kb * 64, 0);
             uint32_t it = 0;
             for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
                 const int s = it & 1;
@@ -171,13 +178,16 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     mma_k128(tmem_base + q * 256, sbase + ProjSmem::kZ + s * kTileBytes,
                              sbase + ProjSmem::kW + q * 256 * 128, ProjSmem::kWKb,
                              q == 0 ? idesc_bf16_f32(128, 256) : idesc_bf16_f32(128, 128), false);
+                    if (q == 1)
+                        mma_k128(tmem_base + 384, sbase + ProjSmem::kZ + s * kTileBytes, sbase + ProjSmem::kWb, 2048,
+                                 idesc_bf16_f32(128, 16), false);
                     mma_commit(slot_full(q));
                 }
                 if (ok) mma_commit(z_empty(s));
             }
         }
     } else if (warp < 6) {
-        // LayerNorm warps: normalise in place and project the triangle bias in fp32
+        // LayerNorm warps: normalise in place (the A operand of all four GEMMs)
         const int row = (warp - 2) * 32 + lane;
         uint32_t it = 0;
         for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
@@ -186,44 +196,19 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 5);
                 break;
             }
-            const LineTile tc = line_tile(t, R, tiles_per_line);
             const uint32_t tile = sbase + ProjSmem::kZ + s * kTileBytes;
             uint32_t raw[64];
             load_row(tile, row, raw);
             float mean, rstd;
             row_stats(raw, mean, rstd);
-            float tb[kH] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ch = 0; ch < 16; ++ch) {
-                uint32_t o[4];
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int c = ch * 8 + j * 2;
-                    const float a = (bf16lo(raw[ch * 4 + j]) - mean) * rstd * gamma[c] + beta[c];
-                    const float bb = (bf16hi(raw[ch * 4 + j]) - mean) * rstd * gamma[c + 1] + beta[c + 1];
-#pragma unroll
-                    for (int h = 0; h < kH; ++h) {
-                        const float2 w2 = *reinterpret_cast<const float2*>(wb + h * kC + c);
-                        tb[h] = fmaf(a, w2.x, tb[h]);
-                        tb[h] = fmaf(bb, w2.y, tb[h]);
-                    }
-                    o[j] = pack_bf16x2(a, bb);
-                }
-                sts128(chunk_addr(tile, row, ch), make_uint4(o[0], o[1], o[2], o[3]));
-            }
+            store_normalized_row(tile, row, raw, mean, rstd, gamma, beta);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(s));
-            const int pos = tc.t0 + row;
-            if (pos < ldn) {  // the row padding [N, ldn) is read by the attention kernel: keep it finite
-#pragma unroll
-                for (int h = 0; h < kH; ++h)
-                    tb_out[(((long long)tc.b * kH + h) * R + tc.line) * ldn + pos] =
-                        __float2bfloat16_rn(pos < N ? tb[h] * kLog2e : 0.f);
-            }
         }
     } else {
         // epilogue warps
+        const int qset = (warp - 6) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const float qscale = kLog2e * rsqrtf((float)kD);
@@ -243,12 +228,13 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             // ---- slot 0: q (columns 0..127) and k (128..255), [line][head][pos][32], stored as the
             // 64-byte-swizzled shared-memory image (16-byte chunk c of row pos at chunk c ^ ((pos/2)%4)),
             // so that the attention kernel fetches whole tiles with one untiled bulk copy each
+            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
+            if (!kProjSplitEpilogue || qset == 0) {
             if (!mbar_wait(slot_full(0), it & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 6);
                 break;
             }
             tc_fence_after_sync();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
 #pragma unroll 1
             for (int qk = 0; qk < 2; ++qk) {
                 __nv_bfloat16* base = qk == 0 ? q_out : k_out;
@@ -280,6 +266,8 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(0));
+            }
+            if (!kProjSplitEpilogue || qset == 1) {
             // ---- slot 1: v, stored as tiles [line][head][key block of 32][32 d][32 keys], each tile the
             // 64-byte-swizzled image of the K-major B operand of P V (row d, chunk (key%32)/8)
             if (!mbar_wait(slot_full(1), it & 1u, abort_flag)) {
@@ -303,9 +291,19 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                             __float2bfloat16_rn(live ? __uint_as_float(r[e]) : 0.f);
                 }
             }
+            uint32_t tbr[16];  // triangle bias of this position: columns 384..387, pre-scaled for exp2
+            tmem_ld16(taddr + 384, tbr);
+            tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(1));
+            if (pos < ldn) {  // the row padding [N, ldn) is read by the attention kernel: keep it finite
+#pragma unroll
+                for (int h = 0; h < kH; ++h)
+                    tb_out[(((long long)tc.b * kH + h) * R + tc.line) * ldn + pos] =
+                        __float2bfloat16_rn(live ? __uint_as_float(tbr[h]) * kLog2e : 0.f);
+            }
+            }
         }
     }
 
@@ -1005,18 +1003,25 @@ template <bool kT>
 int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
                  __nv_bfloat16* tb, int B, int R, int N, int ldn, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
-    CUtensorMap tmZ, tmW[3];
+    CUtensorMap tmZ, tmW[3], tmWb;
     if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
     const void* w3[3] = {p->w_q, p->w_k, p->w_v};
     for (int i = 0; i < 3; ++i)
         if ((rc = weight_tmap128(&tmW[i], w3[i]))) return rc;
+    {   // linear_z.weight [4, 128]: box of 16 rows, the 12 rows past the end are zero-filled
+        OF3_REQUIRE(((uintptr_t)p->w_bias & 15) == 0, OF3_ERR_ALIGN, "triattn: linear_z.weight must be 16-byte aligned");
+        uint64_t dims[2] = {128, (uint64_t)kH};
+        uint64_t str[1] = {256};
+        uint32_t box[2] = {64, 16};
+        if ((rc = make_tmap_bf16(&tmWb, p->w_bias, 2, dims, str, box, 1))) return rc;
+    }
     if ((rc = set_attrs<kT>())) return rc;
     const long long tiles = (long long)B * R * ceil_div(N, kRows);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     LaunchScope scope(kKidProj, st);
-    triattn_proj_kernel<kT><<<grid, 320, ProjSmem::kDyn, st>>>(
-        tmZ, tmW[0], tmW[1], tmW[2], (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
-        (const __nv_bfloat16*)p->w_bias, q, k, vt, tb, B, R, N, ldn, (int)align_up(N, kBK), device_status_ptr());
+    triattn_proj_kernel<kT><<<grid, kProjThreads, ProjSmem::kDyn, st>>>(
+        tmZ, tmW[0], tmW[1], tmW[2], tmWb, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, q, k, vt,
+        tb, B, R, N, ldn, (int)align_up(N, kBK), device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
