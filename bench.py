@@ -386,6 +386,13 @@ def run_ours(args) -> None:
                         "unit": "TFLOP/s", "frac": round(achieved / tensor_peak, 4),
                         "traffic": KERNEL_DRAM_TRAFFIC.get(top) if (n == 768 and world == 1) else None, "peak_kind": f"bf16 sustained, {peak_kind}",
                         "algorithmic_flop_per_launch": kf[top] / world}
+            if top == "triattn_core":
+                # second ceiling of this kernel: one exp2 per logit on the MUFU pipe (16 per clock and SM)
+                exps = 4.0 * n * n * n / world
+                sm_hz = (clocks.summary().get("sm_mhz") or 1965.0) * 1e6
+                exp_peak = 16.0 * 148 * sm_hz
+                roofline["exp_bound"] = {"exps_per_launch": exps, "peak_exps_per_s": exp_peak,
+                                         "frac": round(exps / (per_launch_ms * 1e-3) / exp_peak, 4)}
         cpu_s, cores = oracle_block_seconds(n) if world == 1 and not args.no_cpu_baseline else (None, 0)
         cpu_baseline = None
         if cpu_s is not None:
