@@ -58,9 +58,10 @@ int transition_dispatch(const void* x, const void* mask, void* out, long long ro
 int apb_dispatch(const void* a, const void* z, const void* s, const void* mask, void* out, int Ba,
                  int Bz, int N, int c_a, int c_s, int c_z, int H, int d, float inf, int dtype,
                  int flags, const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st) {
-    if (dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, c_z, H, d, flags))
-        return fast::attn_pair_bias((const __nv_bfloat16*)a, (const __nv_bfloat16*)z, (const __nv_bfloat16*)mask,
-                                    (__nv_bfloat16*)out, Ba, Bz, N, c_a, H, d, inf, flags, p, ws, st, nullptr);
+    if (dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, c_s, c_z, H, d, flags))
+        return fast::attn_pair_bias((const __nv_bfloat16*)a, (const __nv_bfloat16*)z, (const __nv_bfloat16*)s,
+                                    (const __nv_bfloat16*)mask, (__nv_bfloat16*)out, Ba, Bz, N, c_a, c_s, H, d, inf,
+                                    flags, p, ws, st, nullptr);
     if (dtype == OF3_DTYPE_BF16)
         return generic::attn_pair_bias<__nv_bfloat16>(
             (const __nv_bfloat16*)a, (const __nv_bfloat16*)z, (const __nv_bfloat16*)s,
@@ -74,6 +75,9 @@ int apb_dispatch(const void* a, const void* z, const void* s, const void* mask, 
 int cond_dispatch(const void* a, const void* s, const void* mask, void* out, long long rows, int c_a,
                   int c_s, int n, int dtype, int flags, const of3_cond_transition_params* p,
                   Arena& ws, cudaStream_t st) {
+    if (dtype == OF3_DTYPE_BF16 && fast::cond_transition_supported(c_a, c_s, n, flags))
+        return fast::cond_transition((const __nv_bfloat16*)a, (const __nv_bfloat16*)s, (const __nv_bfloat16*)mask,
+                                     (__nv_bfloat16*)out, rows, c_a, c_s, n, flags, p, ws, st);
     if (dtype == OF3_DTYPE_BF16)
         return generic::cond_transition<__nv_bfloat16>(
             (const __nv_bfloat16*)a, (const __nv_bfloat16*)s, (const __nv_bfloat16*)mask,

@@ -92,7 +92,8 @@ int of3_attn_pair_bias_forward_rows(const void* a, const float* pair_bias_rows, 
                                     void* stream) {
     OF3_REQUIRE(a && pair_bias_rows && out_rows && p && workspace, OF3_ERR_ARG,
                 "attn_pair_bias_rows: null pointer argument");
-    OF3_REQUIRE(dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(1, 1, N, c_a, 128, H, d, flags),
+    OF3_REQUIRE(dtype == OF3_DTYPE_BF16 && !(flags & OF3_FLAG_ADA_LN) &&
+                    fast::attn_pair_bias_supported(1, 1, N, c_a, 0, 128, H, d, flags),
                 OF3_ERR_SHAPE, "attn_pair_bias_rows: bf16, 16 heads of 24 or 48 only");
     Arena ws(workspace, workspace_bytes);
     return fast::attn_pair_bias_rows((const __nv_bfloat16*)a, pair_bias_rows, (const __nv_bfloat16*)mask,
@@ -181,9 +182,10 @@ int of3_attn_pair_bias_forward_prebias(const void* a, const float* pair_bias, co
     OF3_REQUIRE(a && pair_bias && out && p && workspace, OF3_ERR_ARG, "attn_pair_bias_prebias: null pointer argument");
     OF3_REQUIRE(Ba > 0 && Bz > 0 && Ba % Bz == 0 && N > 0, OF3_ERR_ARG, "attn_pair_bias_prebias: bad sizes");
     Arena ws(workspace, workspace_bytes);
-    if (dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, 128, H, d, flags))
-        return fast::attn_pair_bias((const __nv_bfloat16*)a, nullptr, (const __nv_bfloat16*)mask, (__nv_bfloat16*)out,
-                                    Ba, Bz, N, c_a, H, d, inf, flags, p, ws, (cudaStream_t)stream, pair_bias);
+    if (dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, c_s, 128, H, d, flags))
+        return fast::attn_pair_bias((const __nv_bfloat16*)a, nullptr, (const __nv_bfloat16*)s,
+                                    (const __nv_bfloat16*)mask, (__nv_bfloat16*)out, Ba, Bz, N, c_a, c_s, H, d, inf,
+                                    flags, p, ws, (cudaStream_t)stream, pair_bias);
     if (dtype == OF3_DTYPE_BF16)
         return generic::attn_pair_bias<__nv_bfloat16>((const __nv_bfloat16*)a, nullptr, (const __nv_bfloat16*)s,
                                                       (const __nv_bfloat16*)mask, (__nv_bfloat16*)out, Ba, Bz, N, c_a,

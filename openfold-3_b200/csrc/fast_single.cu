@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(256, (D <= 24) ? 2 : 1)
 single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
                    const bf16* __restrict__ g, const bf16* __restrict__ q_bias, const float* __restrict__ pair_bias,
                    const bf16* __restrict__ mask, bf16* __restrict__ out, int N, int nq, int H, float scale, float inf,
-                   long long rows_per_bias) {
+                   long long rows_per_bias, int passes) {
     constexpr int PB = AttnCfg<D>::kPitch, NV = AttnCfg<D>::kVec;
     constexpr int kChunk = 8;  // keys per lane between two agreements on the running maximum
     extern __shared__ __align__(16) uint8_t smem[];
@@ -104,8 +104,10 @@ single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
         mb[kk] = kk < N ? (mask ? inf * (__bfloat162float(mask[bb * N + kk]) - 1.0f) : 0.f) : -INFINITY;
     __syncthreads();
 
-    const int qa = blockIdx.x * kQPB + warp * 2;  // this warp's queries qa, qa + 1
-    if (qa >= nq) return;
+    // a block serves `passes` groups of 16 queries with one load of the head's K and V
+    for (int pass = 0; pass < passes; ++pass) {
+    const int qa = (blockIdx.x * passes + pass) * kQPB + warp * 2;  // this warp's queries qa, qa + 1
+    if (qa >= nq) break;
     const bool has_b = qa + 1 < nq;
     const int qb = has_b ? qa + 1 : qa;
     const float* pb_base = pair_bias + ((bb / rows_per_bias) * H + h) * (long long)nq * N;
@@ -215,6 +217,7 @@ single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const
             out[offb + lane + 32] = __float2bfloat16_rn(r2);
         }
     }
+    }  // passes
 }
 
 // ---------------------------------------------------------------- elementwise
@@ -245,6 +248,40 @@ __global__ void residual_bf16_kernel(const bf16* __restrict__ upd, const bf16* r
     *reinterpret_cast<uint32_t*>(out + i) = pack_bf16x2(v0, v1);
 }
 
+// AdaLN combine (normalization.py:121-140): dst = sigmoid(g_lin + b_g[c]) * ln_a + s_lin
+__global__ void ada_combine_bf16_kernel(const bf16* __restrict__ g_lin, const bf16* __restrict__ b_g,
+                                        const bf16* __restrict__ ln_a, const bf16* __restrict__ s_lin,
+                                        bf16* __restrict__ dst, long long n, int C) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= n) return;
+    const int c = (int)(i % C);
+    const uint32_t gv = *reinterpret_cast<const uint32_t*>(g_lin + i), av = *reinterpret_cast<const uint32_t*>(ln_a + i);
+    const uint32_t sv = *reinterpret_cast<const uint32_t*>(s_lin + i), bv = *reinterpret_cast<const uint32_t*>(b_g + c);
+    const float r0 = bf16lo(av) / (1.0f + __expf(-(bf16lo(gv) + bf16lo(bv)))) + bf16lo(sv);
+    const float r1 = bf16hi(av) / (1.0f + __expf(-(bf16hi(gv) + bf16hi(bv)))) + bf16hi(sv);
+    *reinterpret_cast<uint32_t*>(dst + i) = pack_bf16x2(r0, r1);
+}
+// out[r, c] = (residual ? residual[r, c] : 0) + sigmoid(gate_lin[r, c] + gate_b[c]) * upd[r, c] * (mask ? mask[r] : 1)
+__global__ void gate_residual_bf16_kernel(const bf16* __restrict__ upd, const bf16* __restrict__ gate_lin,
+                                          const bf16* __restrict__ gate_b, const bf16* residual,
+                                          const bf16* __restrict__ mask, bf16* out, long long rows, int C) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i >= rows * C) return;
+    const long long r = i / C;
+    const int c = (int)(i - r * C);
+    const float mk = mask ? __bfloat162float(mask[r]) : 1.0f;
+    const uint32_t u = *reinterpret_cast<const uint32_t*>(upd + i), gv = *reinterpret_cast<const uint32_t*>(gate_lin + i);
+    const uint32_t bv = *reinterpret_cast<const uint32_t*>(gate_b + c);
+    float v0 = bf16lo(u) * mk / (1.0f + __expf(-(bf16lo(gv) + bf16lo(bv))));
+    float v1 = bf16hi(u) * mk / (1.0f + __expf(-(bf16hi(gv) + bf16hi(bv))));
+    if (residual) {
+        const uint32_t z = *reinterpret_cast<const uint32_t*>(residual + i);
+        v0 += bf16lo(z);
+        v1 += bf16hi(z);
+    }
+    *reinterpret_cast<uint32_t*>(out + i) = pack_bf16x2(v0, v1);
+}
+
 int linear_bf16(const bf16* x, const bf16* w, bf16* y, long long rows, int out_dim, int in_dim, cudaStream_t st) {
     return contract_nt_bf16(x, w, y, 1, (int)rows, out_dim, in_dim, in_dim, in_dim, out_dim, rows * in_dim,
                             (long long)out_dim * in_dim, rows * out_dim, st);
@@ -261,10 +298,38 @@ int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, cons
                                             (int)smem));
         configured = smem;
     }
-    dim3 grid(ceil_div(nq, kQPB), H, BB);
+    // enough blocks for a few waves, as few loads of K / V as that allows
+    int passes = 1;
+    while (passes < 8 && (long long)ceil_div(nq, kQPB * passes * 2) * H * BB >= 4LL * sm_count()) passes *= 2;
+    dim3 grid(ceil_div(nq, kQPB * passes), H, BB);
     LaunchScope scope(kKidSingle, st);
     single_attn_kernel<D><<<grid, 256, smem, st>>>(q, k, v, g, q_bias, pb, mask, out, N, nq, H, rsqrtf((float)D),
-                                                   inf, rows_per_bias);
+                                                   inf, rows_per_bias, passes);
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+// an = AdaLN(a, s) (normalization.py:89-140): LN(a) without affine, LN_s(s) with scale only, two linears
+// from it, combine. t_ln / t_sn / t_g / t_s: scratch [rows, c_a], [rows, c_s], [rows, c_a], [rows, c_a].
+int ada_ln_bf16(const bf16* a, const bf16* s, bf16* an, bf16* t_sn, bf16* t_g, bf16* t_s, long long rows, int c_a,
+                int c_s, const bf16* ln_s_w, const bf16* w_g, const bf16* b_g, const bf16* w_s, cudaStream_t st) {
+    {
+        LaunchScope scope(kKidSingle, st);
+        ln_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(a, nullptr, nullptr, an, rows, c_a);
+    }
+    {
+        LaunchScope scope(kKidSingle, st);
+        ln_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(s, ln_s_w, nullptr, t_sn, rows, c_s);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    int rc;
+    if ((rc = linear_bf16(t_sn, w_g, t_g, rows, c_a, c_s, st))) return rc;
+    if ((rc = linear_bf16(t_sn, w_s, t_s, rows, c_a, c_s, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * c_a / 2;
+        ada_combine_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(t_g, b_g, an, t_s, an, rows * c_a, c_a);
+    }
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
@@ -273,17 +338,22 @@ int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, cons
 
 // bf16, LayerNorm variant, one pair tensor per sample; c_a = H * d a multiple of 64; d in {24, 48};
 // K and V of one head must fit in shared memory.
-bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_z, int H, int d, int flags) {
-    if (flags & (OF3_FLAG_ADA_LN | OF3_FLAG_FORCE_GENERIC)) return false;
+bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H, int d, int flags) {
+    if (flags & OF3_FLAG_FORCE_GENERIC) return false;
+    if ((flags & OF3_FLAG_ADA_LN) && (c_s <= 0 || c_s % 64 != 0)) return false;
     if (!(d == 24 || d == 48) || H * d != c_a || c_a % 64 != 0) return false;
     if (c_z != 128 || H != 16 || Bz <= 0 || Ba % Bz != 0) return false;
     return (size_t)N * (d == 24 ? 48 : 112) * 2 + (size_t)N * 4 + 1024 <= 200 * 1024;
 }
 
-int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, int Ba, int Bz, int N, int c_a, int H,
-                   int d, float inf, int flags, const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st,
-                   const float* pair_bias) {
+int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask, bf16* out, int Ba, int Bz, int N,
+                   int c_a, int c_s, int H, int d, float inf, int flags, const of3_attn_pair_bias_params* p, Arena& ws,
+                   cudaStream_t st, const float* pair_bias) {
     const long long rows = (long long)Ba * N;
+    const bool ada = (flags & OF3_FLAG_ADA_LN) != 0;
+    bf16* t_sn = ada ? (bf16*)ws.take(rows * c_s * sizeof(bf16)) : nullptr;
+    bf16* t_g = ada ? (bf16*)ws.take(rows * c_a * sizeof(bf16)) : nullptr;
+    bf16* t_s = ada ? (bf16*)ws.take(rows * c_a * sizeof(bf16)) : nullptr;
     bf16* an = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     bf16* q = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     bf16* k = (bf16*)ws.take(rows * c_a * sizeof(bf16));
@@ -301,7 +371,11 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, in
             return rc;
         pair_bias = zb;
     }
-    {
+    if (ada) {
+        if ((rc = ada_ln_bf16(a, s, an, t_sn, t_g, t_s, rows, c_a, c_s, (const bf16*)p->ada_ln_s_w,
+                              (const bf16*)p->ada_w_g, (const bf16*)p->ada_b_g, (const bf16*)p->ada_w_s, st)))
+            return rc;
+    } else {
         LaunchScope scope(kKidSingle, st);
         ln_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(a, (const bf16*)p->ln_a_w, (const bf16*)p->ln_a_b,
                                                                    an, rows, c_a);
@@ -318,11 +392,56 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* mask, bf16* out, in
         rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, inf, rpb, st);
     if (rc) return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
-    {
+    if (ada) {  // output gate from the raw conditioning: sigmoid(linear_ada_out(s)) * y
+        if ((rc = linear_bf16(s, (const bf16*)p->w_ada_out, t_g, rows, c_a, c_s, st))) return rc;
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * c_a / 2;
+        gate_residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
+            y, t_g, (const bf16*)p->b_ada_out, (flags & OF3_FLAG_ADD_RESIDUAL) ? a : nullptr, nullptr, out, rows, c_a);
+    } else {
         LaunchScope scope(kKidSingle, st);
         const long long n2 = rows * c_a / 2;
         residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
             y, (flags & OF3_FLAG_ADD_RESIDUAL) ? a : nullptr, nullptr, out, rows, c_a);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    return OF3_OK;
+}
+
+// ConditionedTransitionBlock (transition.py:325-339): AdaLN -> SwiGLU -> linear_out, gated by sigmoid(linear_g(s)).
+bool cond_transition_supported(int c_a, int c_s, int n, int flags) {
+    return !(flags & OF3_FLAG_FORCE_GENERIC) && c_a % 64 == 0 && c_s % 64 == 0 && (n * c_a) % 64 == 0;
+}
+int cond_transition(const bf16* a, const bf16* s, const bf16* mask, bf16* out, long long rows, int c_a, int c_s, int n,
+                    int flags, const of3_cond_transition_params* p, Arena& ws, cudaStream_t st) {
+    const int hid = n * c_a;
+    bf16* an = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* t_sn = (bf16*)ws.take(rows * c_s * sizeof(bf16));
+    bf16* t_g = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* t_s = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* ha = (bf16*)ws.take(rows * hid * sizeof(bf16));
+    bf16* hb = (bf16*)ws.take(rows * hid * sizeof(bf16));
+    if (!ws.base) return OF3_OK;
+    OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "cond_transition: workspace too small (%zu needed)", ws.off);
+    int rc;
+    if ((rc = ada_ln_bf16(a, s, an, t_sn, t_g, t_s, rows, c_a, c_s, (const bf16*)p->ada_ln_s_w, (const bf16*)p->ada_w_g,
+                          (const bf16*)p->ada_b_g, (const bf16*)p->ada_w_s, st)))
+        return rc;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_a, ha, rows, hid, c_a, st))) return rc;
+    if ((rc = linear_bf16(an, (const bf16*)p->w_b, hb, rows, hid, c_a, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * hid / 2;
+        silu_mul_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(ha, hb, ha, rows * hid);
+    }
+    OF3_CUDA_CHECK(cudaGetLastError());
+    if ((rc = linear_bf16(ha, (const bf16*)p->w_out, t_s, rows, c_a, hid, st))) return rc;
+    if ((rc = linear_bf16(s, (const bf16*)p->w_g, t_g, rows, c_a, c_s, st))) return rc;
+    {
+        LaunchScope scope(kKidSingle, st);
+        const long long n2 = rows * c_a / 2;
+        gate_residual_bf16_kernel<<<(unsigned)((n2 + 255) / 256), 256, 0, st>>>(
+            t_s, t_g, (const bf16*)p->b_g, (flags & OF3_FLAG_ADD_RESIDUAL) ? a : nullptr, mask, out, rows, c_a);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;

@@ -58,10 +58,15 @@ bool transition_supported(int c, int n);
 int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows,
                int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
 // single-track layers (bf16): linears on the tcgen05 contraction kernel, one head of K/V resident per CTA
-bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_z, int H, int d, int flags);
-int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
-                   int Ba, int Bz, int N, int c_a, int H, int d, float inf, int flags,
+// (LayerNorm variant of the trunk, or with OF3_FLAG_ADA_LN the conditioned variant of the diffusion stack)
+bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H, int d, int flags);
+int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bfloat16* s, const __nv_bfloat16* mask,
+                   __nv_bfloat16* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf, int flags,
                    const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st, const float* pair_bias);
+bool cond_transition_supported(int c_a, int c_s, int n, int flags);
+int cond_transition(const __nv_bfloat16* a, const __nv_bfloat16* s, const __nv_bfloat16* mask, __nv_bfloat16* out,
+                    long long rows, int c_a, int c_s, int n, int flags, const of3_cond_transition_params* p, Arena& ws,
+                    cudaStream_t st);
 int attn_pair_bias_rows(const __nv_bfloat16* a, const float* pair_bias_rows, const __nv_bfloat16* mask,
                         __nv_bfloat16* out_rows, int N, int row0, int R, int c_a, int H, int d, float inf, int flags,
                         const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st);
