@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) pieces the kernels use:
-// mbarrier with bounded waits, TMA tiled loads/stores (never cluster multicast),
+// mbarrier with bounded waits, TMA tiled loads/stores (every copy lands in the issuing CTA only),
 // TMEM allocation, tcgen05.mma (kind::f16, cta_group::1), tcgen05.commit/ld.
 //
 // Every wait is bounded by wall-clock (%globaltimer): when it runs out the caller
@@ -90,7 +90,7 @@ __device__ __forceinline__ void tc_fence_after_sync() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
 
-// ---------------------------------------------------------------- TMA (tiled, no multicast)
+// ---------------------------------------------------------------- TMA (tiled; destination = the issuing CTA)
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap* m) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }
