@@ -167,3 +167,32 @@ def test_all_to_all_transpose_single_rank():
     assert torch.equal(dap.all_to_all_transpose(x, 1), x.transpose(0, 1))
     y = torch.randn(5, 4, 7)
     assert torch.equal(dap.all_gather_lines(y, 1), y)
+
+
+@pytest.mark.parametrize("world,n_token", [(2, 768), (4, 768), (8, 768), (8, 2048), (2, 66)])
+def test_peer_heap_layout_fits_and_is_deterministic(world, n_token):
+    """The named regions a step requests (same order on every rank) fit the size PeerExchange.heap_bytes
+    promises, do not overlap, and get the same offsets on every rank. No GPU: only the bump allocator."""
+    import cases
+
+    dap = cases.pkg.dap
+    R = n_token // world
+    ld, ldn = dap._pitch(n_token, 8), dap._pitch(n_token, 64)
+    requests = [("z0", R * n_token * 128 * 2), ("ab", 2 * 128 * max(R * ld, n_token * dap._pitch(R, 8)) * 2),
+                ("xb", 128 * R * ld * 2), ("tb", 4 * R * ldn * 2), ("z1", R * n_token * 128 * 2),
+                ("s0", R * 384 * 2), ("s1", R * 384 * 2)]
+    layouts = []
+    for rank in range(world):
+        h = dap.PeerHeap.__new__(dap.PeerHeap)
+        h.nbytes, h.regions, h.top = dap.PeerExchange.heap_bytes(n_token, world), {}, 256
+        offs = [h.region(name, nbytes) for name, nbytes in requests]
+        assert [h.region(name, nbytes) for name, nbytes in requests] == offs  # asking again returns the same region
+        spans = sorted((o, o + n) for o, (_, n) in zip(offs, requests))
+        assert spans[0][0] >= 64 and all(a[1] <= b[0] for a, b in zip(spans, spans[1:])) and spans[-1][1] <= h.nbytes
+        assert all(o % 256 == 0 for o in offs)
+        layouts.append(offs)
+    assert all(l == layouts[0] for l in layouts)
+    h = dap.PeerHeap.__new__(dap.PeerHeap)
+    h.nbytes, h.regions, h.top = 4096, {}, 256
+    with pytest.raises(RuntimeError, match="too small"):
+        h.region("big", 1 << 20)
