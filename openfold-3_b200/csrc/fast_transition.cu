@@ -26,6 +26,15 @@ constexpr int kHidden = 512;
 constexpr int kChunk = 64;
 constexpr int kNumChunks = kHidden / kChunk;  // 8
 
+#ifdef OF3_CORE_TIMING
+__device__ long long g_tr_dbg[32];
+#define TDBG_T(var) const long long var = clock64()
+#define TDBG_ADD(slot, a, b) do { if (tdbg) atomicAdd((unsigned long long*)&g_tr_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
+#else
+#define TDBG_T(var)
+#define TDBG_ADD(slot, a, b)
+#endif
+
 struct TrSmem {
     static constexpr uint32_t kWStage = 49152;                 // [Wa|Wb] slab 32 KB + Wout chunk 16 KB
     static constexpr uint32_t kW = 0;                          // 2 stages
@@ -37,7 +46,13 @@ struct TrSmem {
     static constexpr uint32_t kDyn = kTotal + 1024;
 };
 
-__global__ void __launch_bounds__(320, 1)
+// warps: 0 producer, 1 and 2 the MMA issuers of row group 0 and 1, 3..6 and 7..10 the two row groups.
+// One issuing thread for both groups was the critical path (in-kernel clock64 phases: 5000 cycles per hidden
+// chunk for 1536 cycles of tensor work -- it waited for one group's silu pass while the other group's next
+// GEMM was ready to go); each group now has its own issuer and the tensor pipe interleaves the two chains.
+constexpr int kTrThreads = 32 * 11;
+
+__global__ void __launch_bounds__(kTrThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmOut,
                   const __grid_constant__ CUtensorMap tmWa, const __grid_constant__ CUtensorMap tmWb,
                   const __grid_constant__ CUtensorMap tmWo, const __nv_bfloat16* __restrict__ mask,
@@ -59,8 +74,10 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     auto h_free = [&](int g) { return bars + 8u * (16 + g); };
     auto d2_full = [&](int g) { return bars + 8u * (18 + g); };
     auto d2_empty = [&](int g) { return bars + 8u * (20 + g); };
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + TrSmem::kBars + 192);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + TrSmem::kBars + 200);
+    auto wo_full = [&](int s) { return bars + 8u * (22 + s); };   // W_out chunk of a weight stage (its own ring:
+    auto wo_empty = [&](int s) { return bars + 8u * (24 + s); };  // the slab is free long before the chunk's 2nd GEMM)
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + TrSmem::kBars + 224);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + TrSmem::kBars + 232);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long num_tiles = (rows + kRows - 1) / kRows;
@@ -70,7 +87,9 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     if (threadIdx.x == 0) {
         for (int i = 0; i < 2; ++i) {
             mbar_init(w_full(i), 1);
-            mbar_init(w_empty(i), 1);
+            mbar_init(w_empty(i), 2);  // both groups' issuers have consumed the [W_a|W_b] slab
+            mbar_init(wo_full(i), 1);
+            mbar_init(wo_empty(i), 2);
             mbar_init(x_full(i), 1);
             mbar_init(x_empty(i), 1);
             mbar_init(a_ready(i), 4);
@@ -130,20 +149,27 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         ok = false;
                         break;
                     }
-                    mbar_arrive_expect_tx(w_full(s), TrSmem::kWStage);
+                    mbar_arrive_expect_tx(w_full(s), 2 * kKBlockBytes);
                     const uint32_t w = sbase + TrSmem::kW + s * TrSmem::kWStage;
                     for (int kb = 0; kb < 2; ++kb) {
                         // slab k-block kb: rows [0,64) = W_a chunk, rows [64,128) = W_b chunk
                         tma_load_2d(w + kb * kKBlockBytes, &tmWa, w_full(s), kb * 64, c * kChunk);
                         tma_load_2d(w + kb * kKBlockBytes + 64 * 128, &tmWb, w_full(s), kb * 64, c * kChunk);
                     }
-                    tma_load_2d(w + 2 * kKBlockBytes, &tmWo, w_full(s), c * kChunk, 0);
+                    if (!mbar_wait(wo_empty(s), ((wi >> 1) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidTrans, 12);
+                        ok = false;
+                        break;
+                    }
+                    mbar_arrive_expect_tx(wo_full(s), kKBlockBytes);
+                    tma_load_2d(w + 2 * kKBlockBytes, &tmWo, wo_full(s), c * kChunk, 0);
                 }
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------------- MMA issuer
+    } else if (warp <= 2) {
+        // ---------------------------------------------------------------- MMA issuer of row group g
         if (lane == 0) {
+            const int g = warp - 1;
             constexpr uint32_t idesc = idesc_bf16_f32(128, 128);
             uint32_t wi = 0;
             bool ok = true;
@@ -151,58 +177,88 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 report_wait_failure(status, abort_flag, kKidTrans, site);
                 ok = false;
             };
+#ifdef OF3_CORE_TIMING
+            const bool tdbg = blockIdx.x == 40 && g == 0;
+#endif
+            // Software-pipelined per tile: G1 of chunk c+1 is issued as soon as the row group has read D1 of
+            // chunk c, BEFORE waiting for that chunk's silu pass and its G2, so the row group finds its next
+            // accumulator ready when it comes back (the serial G2 -> weights -> G1 hop cost ~1900 cycles per chunk).
+            auto issue_g1 = [&](uint32_t widx, uint32_t c) -> bool {
+                const int s = widx & 1;
+                if (!mbar_wait(w_full(s), (widx >> 1) & 1u, abort_flag)) { fail(3); return false; }
+                if (!mbar_wait(d1_empty(g), (c & 1u) ^ 1u, abort_flag)) { fail(5); return false; }
+                tc_fence_after_sync();
+                mma_k128(tmem_base + g * 256, sbase + TrSmem::kX + g * kTileBytes,
+                         sbase + TrSmem::kW + s * TrSmem::kWStage, kKBlockBytes, idesc, false);
+                mma_commit(d1_full(g));
+                mma_commit(w_empty(s));
+                return true;
+            };
             for (long long pi = 0; pi < my_pairs && ok; ++pi) {
-                const int ng = (pi * 2 + 1 < my_tiles) ? 2 : 1;
+                const bool have_tile = pi * 2 + g < my_tiles;  // the last pair may hold one tile only
                 const uint32_t ppar = (uint32_t)pi & 1u;
+                if (!have_tile) {  // keep both weight rings moving
+                    for (int c = 0; c < kNumChunks && ok; ++c, ++wi) {
+                        const int s = wi & 1;
+                        if (!mbar_wait(w_full(s), (wi >> 1) & 1u, abort_flag)) { fail(3); break; }
+                        mbar_arrive(w_empty(s));
+                        if (!mbar_wait(wo_full(s), (wi >> 1) & 1u, abort_flag)) { fail(13); break; }
+                        mbar_arrive(wo_empty(s));
+                    }
+                    continue;
+                }
+                if (!mbar_wait(a_ready(g), ppar, abort_flag)) { fail(4); break; }
+                if (!issue_g1(wi, 0)) break;
                 for (int c = 0; c < kNumChunks && ok; ++c, ++wi) {
                     const int s = wi & 1;
                     const uint32_t cpar = (uint32_t)c & 1u;  // 8 chunks per tile: chunk parity is global
-                    const uint32_t w = sbase + TrSmem::kW + s * TrSmem::kWStage;
-                    if (!mbar_wait(w_full(s), (wi >> 1) & 1u, abort_flag)) { fail(3); break; }
-                    for (int g = 0; g < ng && ok; ++g) {
-                        if (c == 0 && !mbar_wait(a_ready(g), ppar, abort_flag)) { fail(4); break; }
-                        if (!mbar_wait(d1_empty(g), cpar ^ 1u, abort_flag)) { fail(5); break; }
-                        tc_fence_after_sync();
-                        mma_k128(tmem_base + g * 256, sbase + TrSmem::kX + g * kTileBytes, w, kKBlockBytes,
-                                 idesc, false);
-                        mma_commit(d1_full(g));
-                    }
-                    for (int g = 0; g < ng && ok; ++g) {
-                        if (c == 0 && !mbar_wait(d2_empty(g), ppar ^ 1u, abort_flag)) { fail(6); break; }
-                        if (!mbar_wait(h_ready(g), cpar, abort_flag)) { fail(7); break; }
-                        tc_fence_after_sync();
-                        const uint64_t ad = smem_desc_k_sw128(sbase + TrSmem::kH + g * kKBlockBytes);
-                        const uint64_t bd = smem_desc_k_sw128(w + 2 * kKBlockBytes);
+                    TDBG_T(m0);
+                    if (c + 1 < kNumChunks && !issue_g1(wi + 1, c + 1)) break;
+                    TDBG_T(m2);
+                    TDBG_ADD(17, m0, m2);
+                    if (c == 0 && !mbar_wait(d2_empty(g), ppar ^ 1u, abort_flag)) { fail(6); break; }
+                    if (!mbar_wait(wo_full(s), (wi >> 1) & 1u, abort_flag)) { fail(13); break; }
+                    if (!mbar_wait(h_ready(g), cpar, abort_flag)) { fail(7); break; }
+                    tc_fence_after_sync();
+                    const uint64_t ad = smem_desc_k_sw128(sbase + TrSmem::kH + g * kKBlockBytes);
+                    const uint64_t bd = smem_desc_k_sw128(sbase + TrSmem::kW + s * TrSmem::kWStage + 2 * kKBlockBytes);
 #pragma unroll
-                        for (int k4 = 0; k4 < 4; ++k4)
-                            mma_bf16(tmem_base + g * 256 + 128, ad + 2u * k4, bd + 2u * k4, idesc,
-                                     (c != 0 || k4 != 0) ? 1u : 0u);
-                        mma_commit(h_free(g));
-                        if (c == kNumChunks - 1) mma_commit(d2_full(g));
-                    }
-                    if (ok) mma_commit(w_empty(s));
+                    for (int k4 = 0; k4 < 4; ++k4)
+                        mma_bf16(tmem_base + g * 256 + 128, ad + 2u * k4, bd + 2u * k4, idesc,
+                                 (c != 0 || k4 != 0) ? 1u : 0u);
+                    mma_commit(h_free(g));
+                    if (c == kNumChunks - 1) mma_commit(d2_full(g));
+                    mma_commit(wo_empty(s));
+                    TDBG_T(m3);
+                    TDBG_ADD(18, m2, m3);
+                    TDBG_ADD(19, m0, m0 + 1);
                 }
             }
         }
     } else {
         // ---------------------------------------------------------------- two row groups
-        const int g = (warp - 2) >> 2;
+        const int g = (warp - 3) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
-        const int gtid = (warp - 2 - g * 4) * 32 + lane;
+        const int gtid = (warp - 3 - g * 4) * 32 + lane;
         const uint32_t xtile = sbase + TrSmem::kX + g * kTileBytes;
         const uint32_t htile = sbase + TrSmem::kH + g * kKBlockBytes;
         const uint32_t t_d1 = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
         const uint32_t t_d2 = t_d1 + 128;
         bool ok = true;
+#ifdef OF3_CORE_TIMING
+        const bool tdbg = blockIdx.x == 40 && gtid == 0 && g == 0;
+#endif
         for (long long pi = 0; pi * 2 + g < my_tiles && ok; ++pi) {
             const uint32_t ppar = (uint32_t)pi & 1u;
             const long long tile = blockIdx.x + (pi * 2 + g) * gridDim.x;
             const long long grow = tile * kRows + row;
+            TDBG_T(r0);
             if (!mbar_wait(x_full(g), ppar, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 8);
                 break;
             }
+            TDBG_T(r1);
             uint32_t raw[64];
             load_row(xtile, row, raw);
             {
@@ -213,17 +269,22 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(g));
+            TDBG_T(r2);
+            TDBG_ADD(0, r0, r1);
+            TDBG_ADD(1, r1, r2);
             float m = 1.0f;
             if (mask != nullptr && grow < rows) m = __bfloat162float(mask[grow]);
 
             for (int c = 0; c < kNumChunks; ++c) {
                 const uint32_t cpar = (uint32_t)c & 1u;
+                TDBG_T(c0);
                 if (!mbar_wait(d1_full(g), cpar, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 9);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
+                TDBG_T(c1);
                 uint32_t hpk[32];  // 64 hidden values of this row, packed bf16x2
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -242,6 +303,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(d1_empty(g));
+                TDBG_T(c2);
                 // the previous chunk's G2 must have consumed the H buffer before it is overwritten
                 if (!mbar_wait(h_free(g), cpar ^ 1u, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 10);
@@ -252,11 +314,18 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 for (int ch = 0; ch < 8; ++ch)
                     sts128(chunk_addr(htile, row, ch),
                            make_uint4(hpk[ch * 4], hpk[ch * 4 + 1], hpk[ch * 4 + 2], hpk[ch * 4 + 3]));
+                TDBG_T(c3);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(h_ready(g));
+                TDBG_T(c4);
+                TDBG_ADD(2, c0, c1);
+                TDBG_ADD(3, c1, c2);
+                TDBG_ADD(4, c2, c3);
+                TDBG_ADD(5, c3, c4);
             }
             if (!ok) break;
+            TDBG_T(r3);
             if (!mbar_wait(d2_full(g), ppar, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 11);
                 break;
@@ -297,6 +366,10 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 tma_store_wait_read<0>();
                 mbar_arrive(x_empty(g));
             }
+            TDBG_T(r4);
+            TDBG_ADD(6, r3, r4);
+            TDBG_ADD(7, r0, r4);
+            TDBG_ADD(8, r0, r0 + 1);
         }
         if (gtid == 0) tma_store_wait_all<0>();
     }
@@ -310,6 +383,13 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 }
 
 }  // namespace
+
+#ifdef OF3_CORE_TIMING
+extern "C" int of3_tr_dbg(long long* out, int reset) {
+    if (reset) { long long z[32] = {0}; return (int)cudaMemcpyToSymbol(g_tr_dbg, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(out, g_tr_dbg, 32 * sizeof(long long));
+}
+#endif
 
 bool transition_supported(int c, int n) { return c == 128 && n == 4; }
 
@@ -354,7 +434,7 @@ int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16*
     if (tiles < 2 * grid) grid = (tiles + 1) / 2;
     if (grid < 1) grid = 1;
     LaunchScope scope(kKidTrans, st);
-    transition_kernel<<<(int)grid, 320, TrSmem::kDyn, st>>>(
+    transition_kernel<<<(int)grid, kTrThreads, TrSmem::kDyn, st>>>(
         tmX, tmOut, tmWa, tmWb, tmWo, mask, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b,
         rows, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
