@@ -291,12 +291,18 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
     float* prm = reinterpret_cast<float*>(gbase + OutSmem::kParams);
     const uint32_t bars = sbase + OutSmem::kBars;
     const uint32_t w_full = bars;
-    auto full = [&](int g) { return bars + 8u * (1 + g); };     // TMA landed (z + x tiles)
-    auto empty = [&](int g) { return bars + 8u * (3 + g); };    // group released its buffers
+    // The x buffer is free as soon as the group's GEMMs have read it (the result goes over the z buffer), so
+    // the next x tile is fetched during the epilogue; the z buffer is free once the output store has read it,
+    // and its next tile lands while the group gathers and normalises x. Fetched together after the store,
+    // the two loads cost every tile 2200 cycles of waiting.
+    auto x_full = [&](int g) { return bars + 8u * (1 + g); };   // TMA landed: x tile
+    auto z_empty = [&](int g) { return bars + 8u * (3 + g); };  // output store has read the z buffer
     auto a_ready = [&](int g) { return bars + 8u * (5 + g); };  // both A operands written
     auto d_full = [&](int g) { return bars + 8u * (7 + g); };   // MMAs of the group's tile done
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + OutSmem::kBars + 96);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OutSmem::kBars + 104);
+    auto z_full = [&](int g) { return bars + 8u * (9 + g); };   // TMA landed: z tile
+    auto x_empty = [&](int g) { return bars + 8u * (11 + g); };  // MMAs have read the x buffer
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + OutSmem::kBars + 112);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + OutSmem::kBars + 116);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_line = (N + kRows - 1) / kRows;
@@ -307,8 +313,10 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
         for (int g = 0; g < 2; ++g) {
-            mbar_init(full(g), 1);
-            mbar_init(empty(g), 1);
+            mbar_init(x_full(g), 1);
+            mbar_init(z_full(g), 1);
+            mbar_init(x_empty(g), 1);
+            mbar_init(z_empty(g), 1);
             mbar_init(a_ready(g), 4);
             mbar_init(d_full(g), 1);
         }
@@ -344,17 +352,22 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
             for (long long lt = 0; lt < my_tiles; ++lt) {
                 const int g = (int)(lt & 1);
                 const uint32_t use = (uint32_t)(lt >> 1);
-                if (!mbar_wait(empty(g), (use & 1u) ^ 1u, abort_flag)) {
+                const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
+                if (!mbar_wait(x_empty(g), (use & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidOut, 1);
                     break;
                 }
-                const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
-                mbar_arrive_expect_tx(full(g), 2 * kTileBytes);
+                // x tile: all 128 channels of positions (fixed, t0 .. t0+127), layout [c][j]
+                mbar_arrive_expect_tx(x_full(g), kTileBytes);
+                tma_load_3d(sbase + OutSmem::kX + g * kTileBytes, &tmX, x_full(g), tc.t0, tc.fixed, tc.b * kC);
+                if (!mbar_wait(z_empty(g), (use & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidOut, 6);
+                    break;
+                }
+                mbar_arrive_expect_tx(z_full(g), kTileBytes);
                 const uint32_t zdst = sbase + OutSmem::kZ + g * kTileBytes;
                 for (int kb = 0; kb < 2; ++kb)
-                    tma_load_3d(zdst + kb * kKBlockBytes, &tmZ, full(g), kb * 64, tc.t0, tc.b * R + tc.fixed);
-                // x tile: all 128 channels of positions (fixed, t0 .. t0+127), layout [c][j]
-                tma_load_3d(sbase + OutSmem::kX + g * kTileBytes, &tmX, full(g), tc.t0, tc.fixed, tc.b * kC);
+                    tma_load_3d(zdst + kb * kKBlockBytes, &tmZ, z_full(g), kb * 64, tc.t0, tc.b * R + tc.fixed);
             }
         }
     } else if (warp == 1) {
@@ -377,6 +390,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                 mma_k128(tmem_base + g * 256 + 128, sbase + OutSmem::kX + g * kTileBytes,
                          sbase + OutSmem::kWz, kKBlockBytes, idesc, false);
                 mma_commit(d_full(g));
+                mma_commit(x_empty(g));
             }
         }
     } else {
@@ -394,7 +408,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
             const uint32_t use = (uint32_t)(lt >> 1);
             const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
             ODBG_T(o0);
-            if (!mbar_wait(full(g), use & 1u, abort_flag)) {
+            if (!mbar_wait(x_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 4);
                 break;
             }
@@ -418,6 +432,10 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
             }
             ODBG_T(o2);
             // --- z row: keep the raw values for the residual, normalise in place (A operand 1)
+            if (!mbar_wait(z_full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 7);
+                break;
+            }
             uint32_t zraw[64];
             load_row(ztile, row, zraw);
             row_stats(zraw, mean, rstd);
@@ -468,7 +486,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                     tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.fixed);
                 tma_store_commit();
                 tma_store_wait_read<0>();
-                mbar_arrive(empty(g));
+                mbar_arrive(z_empty(g));
             }
             ODBG_T(o7);
             ODBG_ADD(0, o0, o1); ODBG_ADD(1, o1, o2); ODBG_ADD(2, o2, o3); ODBG_ADD(3, o3, o4);
