@@ -754,14 +754,19 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
     float* prm = reinterpret_cast<float*>(gbase + AOutSmem::kParams);
     const uint32_t bars = sbase + AOutSmem::kBars;
     const uint32_t w_full = bars;
-    auto full = [&](int g) { return bars + 8u * (1 + g); };
-    auto empty = [&](int g) { return bars + 8u * (3 + g); };
+    // The z buffer is free once the gate GEMM has read it (the result goes over the o buffer), so the next
+    // z tile is fetched while this one is still being gated and projected; the o buffer is free once the output
+    // store has read it, and its next tile lands during the next LayerNorm + gate GEMM.
+    auto z_full = [&](int g) { return bars + 8u * (1 + g); };
+    auto o_empty = [&](int g) { return bars + 8u * (3 + g); };
+    auto o_full = [&](int g) { return bars + 8u * (13 + g); };
+    auto z_empty = [&](int g) { return bars + 8u * (15 + g); };
     auto a1_ready = [&](int g) { return bars + 8u * (5 + g); };
     auto g_full = [&](int g) { return bars + 8u * (7 + g); };
     auto a2_ready = [&](int g) { return bars + 8u * (9 + g); };
     auto d_full = [&](int g) { return bars + 8u * (11 + g); };
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + AOutSmem::kBars + 128);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + AOutSmem::kBars + 136);
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + AOutSmem::kBars + 144);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + AOutSmem::kBars + 148);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_per_line = (N + kRows - 1) / kRows;
@@ -771,8 +776,10 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
         for (int g = 0; g < 2; ++g) {
-            mbar_init(full(g), 1);
-            mbar_init(empty(g), 1);
+            mbar_init(z_full(g), 1);
+            mbar_init(o_full(g), 1);
+            mbar_init(z_empty(g), 1);
+            mbar_init(o_empty(g), 1);
             mbar_init(a1_ready(g), 4);
             mbar_init(g_full(g), 1);
             mbar_init(a2_ready(g), 4);
@@ -807,16 +814,21 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
             for (long long lt = 0; lt < my_tiles; ++lt) {
                 const int g = (int)(lt & 1);
                 const uint32_t use = (uint32_t)(lt >> 1);
-                if (!mbar_wait(empty(g), (use & 1u) ^ 1u, abort_flag)) {
+                const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
+                if (!mbar_wait(z_empty(g), (use & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidOut, 1);
                     break;
                 }
-                const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
-                mbar_arrive_expect_tx(full(g), 2 * kTileBytes);
-                load_z_tile<kTransposed>(sbase + AOutSmem::kZ + g * kTileBytes, &tmZ, full(g), tc, R);
+                mbar_arrive_expect_tx(z_full(g), kTileBytes);
+                load_z_tile<kTransposed>(sbase + AOutSmem::kZ + g * kTileBytes, &tmZ, z_full(g), tc, R);
+                if (!mbar_wait(o_empty(g), (use & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidOut, 8);
+                    break;
+                }
+                mbar_arrive_expect_tx(o_full(g), kTileBytes);
                 const uint32_t odst = sbase + AOutSmem::kO + g * kTileBytes;
                 for (int kb = 0; kb < 2; ++kb)
-                    tma_load_3d(odst + kb * kKBlockBytes, &tmO, full(g), kb * 64, tc.t0, tc.b * R + tc.line);
+                    tma_load_3d(odst + kb * kKBlockBytes, &tmO, o_full(g), kb * 64, tc.t0, tc.b * R + tc.line);
             }
         }
     } else if (warp == 1) {
@@ -837,6 +849,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                     mma_k128(tmem_base + g * 256, sbase + AOutSmem::kZ + g * kTileBytes, sbase + AOutSmem::kWg,
                              kKBlockBytes, idesc, false);
                     mma_commit(g_full(g));
+                    mma_commit(z_empty(g));
                 }
                 if (lt >= 1) {
                     const long long pt = lt - 1;
@@ -863,7 +876,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
         for (long long lt = g; lt < my_tiles; lt += 2) {
             const uint32_t use = (uint32_t)(lt >> 1);
             const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
-            if (!mbar_wait(full(g), use & 1u, abort_flag)) {
+            if (!mbar_wait(z_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
                 break;
             }
@@ -883,6 +896,10 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                 break;
             }
             tc_fence_after_sync();
+            if (!mbar_wait(o_full(g), use & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 9);
+                break;
+            }
 #pragma unroll
             for (int cb = 0; cb < 8; ++cb) {
                 uint32_t gate[16];
@@ -907,7 +924,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a2_ready(g));
-            // ---- output projection + residual, written over the z tile and TMA-stored
+            // ---- output projection + residual, written over the o tile (its GEMM is done) and TMA-stored
             if (!mbar_wait(d_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 7);
                 break;
@@ -932,7 +949,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                         }
                         o[j] = pack_bf16x2(v0, v1);
                     }
-                    sts128(chunk_addr(ztile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
+                    sts128(chunk_addr(otile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
                 }
             }
             tc_fence_before_sync();
@@ -944,15 +961,15 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                         asm volatile(
                             "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::
                                 "l"(reinterpret_cast<uint64_t>(&tmOut)),
-                            "r"(ztile + kb * kKBlockBytes), "r"(kb * 64), "r"(tc.line), "r"(tc.t0), "r"(tc.b)
+                            "r"(otile + kb * kKBlockBytes), "r"(kb * 64), "r"(tc.line), "r"(tc.t0), "r"(tc.b)
                             : "memory");
                     } else {
-                        tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.line);
+                        tma_store_3d(&tmOut, otile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.line);
                     }
                 }
                 tma_store_commit();
                 tma_store_wait_read<0>();
-                mbar_arrive(empty(g));
+                mbar_arrive(o_empty(g));
             }
         }
         if (gtid == 0) tma_store_wait_all<0>();
