@@ -90,26 +90,37 @@ class ClockSampler:
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    PERIOD_S = 0.05
 
     def __init__(self, index: int):
         self.index = index
         self.proc = None
-        self.lines = []
+        self.lines = []   # (host time of arrival, csv line)
+        self.t_start = self.t_end = None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 5.0:  # nvidia-smi needs a moment before its first sample:
+                time.sleep(0.02)                               # be sampling before the timed region starts
         except OSError:
             self.proc = None
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def region_start(self):
+        self.t_start = time.time()
+
+    def region_end(self):
+        self.t_end = time.time()
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -122,7 +133,14 @@ class ClockSampler:
     def summary(self) -> dict:
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        lines = self.lines
+        if self.t_start is not None and self.t_end is not None and lines:
+            # samples taken while the timed region ran (a sample is printed up to one period after it was read);
+            # a region shorter than the period keeps the sample nearest to it
+            inside = [x for x in lines if self.t_start <= x[0] <= self.t_end + self.PERIOD_S]
+            mid = 0.5 * (self.t_start + self.t_end)
+            lines = inside or [min(lines, key=lambda x: abs(x[0] - mid))]
+        for _, line in lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
                 continue
@@ -305,11 +323,13 @@ def run_ours(args) -> None:
         with ClockSampler(local_rank) as clocks:
             lib.profile_begin(timing=graphed is None)
             sync()
+            clocks.region_start()
             e0.record()
             for _ in range(args.steps):
                 s_o, z_o = step_resident(s_d, z_d, sm_d, pm_d)
             e1.record()
             sync()
+            clocks.region_end()
             prof = lib.profile_end()
         ms_resident = e0.elapsed_time(e1) / args.steps
         stage(f"resident timing done: {ms_resident:.2f} ms per step")
