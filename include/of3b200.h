@@ -218,7 +218,7 @@ int of3_cond_transition_forward(const void* a, const void* s, const void* mask, 
  * R = N / P consecutive rows of one sample's pair tensor (bf16, c_z = c_hidden = 128, 4 heads x 32)
  * and runs every layer as phases around the exchanges the layer needs; the exchanges (all-to-all /
  * all-gather) are the caller's, between the calls. Pitches: ld(n) = of3_dap_pitch(n, 8) for the
- * triangle update's planes, ldn = of3_dap_pitch(N, 64) for the attention bias.
+ * triangle update's planes.
  *
  * Triangle update (triangular_multiplicative_update.py:421-503), C = 128 / P channels per rank:
  *   project   z_rows -> ab [P][2][C][lines][ld(positions)]: the gated projections a (index 0) and b
@@ -232,10 +232,14 @@ int of3_cond_transition_forward(const void* a, const void* s, const void* mask, 
  *   (all-to-all of the P blocks: x_t [128][R][ld(N)] = this rank's rows of every channel)
  *   output    LayerNorm_out(x) -> linear_z, sigmoid(linear_g(LayerNorm_in(z))) gate, residual, on z_rows.
  * Attention: z_rows, out_rows [R, N, 128]; mask_rows [R, N] or NULL; q, k, vt: opaque images of
- *   of3_dap_triattn_image_elems(R, N) elements each (pre-swizzled operand tiles); bias_rows [4, R, ldn];
- *   bias_all [4, N, ldn]; o_scratch [R, N, 128]. out_rows may alias z_rows. */
+ *   of3_dap_triattn_image_elems(R, N) elements each (pre-swizzled operand tiles); the pair bias is an
+ *   fp32 image, pre-scaled by log2(e): bias_rows [4 heads][nkb = ceil(N / 32) key blocks][R query rows][36]
+ *   (of3_dap_triattn_bias_elems(R, N) floats; 32 keys + 4 floats of row padding), bias_all the same with
+ *   all N query rows [4][nkb][N][36]: an all-gather of the ranks' rows along the third index;
+ *   o_scratch [R, N, 128]. out_rows may alias z_rows. */
 int of3_dap_pitch(int N, int multiple);
 long long of3_dap_triattn_image_elems(int R, int N);
+long long of3_dap_triattn_bias_elems(int R, int N);
 int of3_dap_trimul_project(const void* z_rows, const void* mask, void* ab, int lines, int positions, int transposed,
                            int world, const of3_trimul_params* p, void* stream);
 int of3_dap_trimul_contract(const void* ab_all, void* x_blocks, int N, int channels, int rows_per_rank,

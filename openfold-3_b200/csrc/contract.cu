@@ -232,12 +232,12 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
         int rc = make_tmap_bf16(&tmB, b, 3, dims, str, box, true);
         if (rc) return rc;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
+    constexpr int kAttrKey = BN == 256 ? 0 : (BN == 128 ? 1 : 2);  // per-device function attributes
+    if (!device_configured(kAttrKey)) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(contract_nt_kernel<BN>,
                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             Cfg::kSmemBytes));
-        attr_set = true;
+        device_mark_configured(kAttrKey);
     }
     const long long tiles = (long long)batch * ceil_div(M, kBM) * ceil_div(N, BN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());

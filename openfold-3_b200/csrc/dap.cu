@@ -105,6 +105,8 @@ int of3_dap_pitch(int N, int multiple) { return (int)align_up((size_t)N, (size_t
 
 long long of3_dap_triattn_image_elems(int R, int N) { return (long long)fast::triattn_image_elems(1, R, N); }
 
+long long of3_dap_triattn_bias_elems(int R, int N) { return (long long)fast::triattn_bias_elems(1, R, N); }
+
 int of3_dap_trimul_project(const void* z_rows, const void* mask, void* ab, int lines, int positions, int transposed,
                            int world, const of3_trimul_params* p, void* stream) {
     OF3_REQUIRE(z_rows && ab && p, OF3_ERR_ARG, "dap_trimul_project: null pointer argument");
@@ -145,8 +147,7 @@ int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void
     OF3_REQUIRE(z_rows && q && k && vt && bias_rows && p, OF3_ERR_ARG, "dap_triattn_project: null pointer argument");
     OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_triattn_project: non-positive size");
     return fast::triattn_project((const __nv_bfloat16*)z_rows, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-                                 (__nv_bfloat16*)vt, (__nv_bfloat16*)bias_rows, 1, R, N, (int)align_up(N, 64), false, p,
-                                 (cudaStream_t)stream);
+                                 (__nv_bfloat16*)vt, (float*)bias_rows, 1, R, N, false, p, (cudaStream_t)stream);
 }
 
 int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_rows, const void* q, const void* k,
@@ -157,9 +158,8 @@ int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_
     OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_triattn_finish: non-positive size");
     return fast::triattn_finish((const __nv_bfloat16*)z_rows, (const __nv_bfloat16*)mask_rows,
                                 (__nv_bfloat16*)out_rows, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-                                (const __nv_bfloat16*)vt, (const __nv_bfloat16*)bias_all, (__nv_bfloat16*)o_scratch, 1, R,
-                                N, (int)align_up(N, 64), inf, false, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p,
-                                (cudaStream_t)stream);
+                                (const __nv_bfloat16*)vt, (const float*)bias_all, (__nv_bfloat16*)o_scratch, 1, R,
+                                N, inf, false, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, (cudaStream_t)stream);
 }
 
 int of3_pair_bias_project(const void* z_rows, const void* ln_w, const void* ln_b, const void* w, float* bias_rows,

@@ -204,11 +204,10 @@ int pair_bias_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const 
         uint32_t box[2] = {64, (uint32_t)kHeads};
         if ((rc = make_tmap_bf16(&tmW, w, 2, dims, str, box, 1))) return rc;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
+    if (!device_configured(3)) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(pair_bias_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             PbSmem::kDyn));
-        attr_done = true;
+        device_mark_configured(3);
     }
     const long long tiles = (rows + kRows - 1) / kRows;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());

@@ -292,12 +292,9 @@ int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, cons
                 const bf16* mask, bf16* out, int BB, int N, int nq, int H, float inf, long long rows_per_bias,
                 cudaStream_t st) {
     const size_t smem = (size_t)N * AttnCfg<D>::kPitch * 2 + (size_t)((N + 31) & ~31) * 4;
-    static size_t configured = 0;
-    if (smem > configured) {
-        OF3_CUDA_CHECK(cudaFuncSetAttribute(single_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                            (int)smem));
-        configured = smem;
-    }
+    // the limit depends on N and function attributes are per device: set on every launch (a host-side store)
+    OF3_CUDA_CHECK(cudaFuncSetAttribute(single_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        (int)smem));
     // enough blocks for a few waves, as few loads of K / V as that allows
     int passes = 1;
     while (passes < 8 && (long long)ceil_div(nq, kQPB * passes * 2) * H * BB >= 4LL * sm_count()) passes *= 2;

@@ -422,11 +422,10 @@ int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16*
         uint32_t boxo[2] = {kChunk, 128};
         if ((rc = make_tmap_bf16(&tmWo, p->w_out, 2, dimo, stro, boxo, true))) return rc;
     }
-    static bool attr_done = false;
-    if (!attr_done) {
+    if (!device_configured(4)) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(transition_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             TrSmem::kDyn));
-        attr_done = true;
+        device_mark_configured(4);
     }
     const long long tiles = (rows + kRows - 1) / kRows;
     // two tiles per CTA pass share each weight chunk: aim for an even number of tiles per CTA

@@ -1,15 +1,15 @@
 // Triangle attention, bf16 / tcgen05 family (c_z = 128, 4 heads x 32).
 //
 //   triattn_proj   z tile -> LayerNorm (in place in the A operand) -> [q|k|v] projection on
-//                  tcgen05; the 4-wide triangle-bias projection is folded into the LayerNorm
-//                  pass (fp32 dot products). q is stored pre-scaled by log2(e)/sqrt(d), the bias
-//                  pre-scaled by log2(e), so the softmax runs on exp2. Layouts:
-//                  q,k [line][head][pos][32] (K-major operands of Q K^T), v transposed
-//                  [line][head][32][pos] (K-major operand of P V), bias [head][q][k].
-//   triattn_core   streaming attention for one (line, head, 128 queries): S = Q K^T and
-//                  O_blk = P V on tcgen05 with S/O accumulators double-buffered in TMEM, online
-//                  softmax (fp32, exp2) by one thread per query row, mask + pair bias added in
-//                  fp32 exactly in the reference's order; N^3 logits are never materialised.
+//                  tcgen05; the 4-wide triangle-bias projection is a fourth small GEMM. q is
+//                  stored pre-scaled by log2(e)/sqrt(d), the bias pre-scaled by log2(e), so the
+//                  softmax runs on exp2. Layouts: q, k, v as pre-swizzled operand tiles (see the
+//                  epilogue), bias as fp32 tiles [head][key block of 32][q][36].
+//   triattn_core   streaming attention for (2 lines, head, 128 queries): S = Q K^T on tcgen05 into
+//                  TMEM, online softmax (fp32, exp2) by one thread per query row, P written back
+//                  to TMEM as bf16 over S and used from there as the A operand of O += P V; the row
+//                  sums of P come out of the same GEMM (a constant row of ones appended to V). Mask
+//                  and pair bias are added in fp32; N^3 logits are never materialised.
 //   triattn_out    z tile -> LayerNorm -> linear_g (gate recomputed instead of stored), o tile
 //                  * sigmoid(gate) -> linear_o -> + z, TMA-stored.
 // "line" is the leading index of the (possibly transposed) pair tensor: with kTransposed the
@@ -74,11 +74,14 @@ struct ProjSmem {
     static constexpr uint32_t kDyn = kTotal + 1024;
 };
 
-// warps: 0 producer, 1 MMA issuer, 2..5 LayerNorm (one thread per row), 6..9 epilogue of TMEM slot 0 (q, k),
-// 10..13 epilogue of slot 1 (v and the 4-wide triangle bias). The bias projection is a fourth GEMM (N = 16
-// with 12 zero rows) instead of 1024 FMAs per row inside the LayerNorm pass.
-constexpr bool kProjSplitEpilogue = false;  // second epilogue warp set: measured slower (128-register cap)
-constexpr int kProjThreads = kProjSplitEpilogue ? 448 : 320;
+// warps: 0 producer, 1 MMA issuer, 2..5 LayerNorm (one thread per row), 6..9 epilogue (TMEM slot 0: q, k;
+// slot 1: v and the 4-wide triangle bias). The bias projection is a fourth GEMM (N = 16 with 12 zero rows)
+// instead of 1024 FMAs per row inside the LayerNorm pass.
+constexpr int kProjThreads = 320;
+// Pair-bias image: fp32, pre-scaled by log2(e), [b*4 + head][key block of 32][query row][kTbPitch]. A query
+// tile's 128 rows of one key block are contiguous (one untiled bulk copy), and with a row pitch of 36 floats
+// (144 B) the 16-byte reads of eight consecutive rows fall into distinct shared-memory banks.
+constexpr int kTbPitch = 36;
 
 template <bool kTransposed>
 __global__ void __launch_bounds__(kProjThreads, 1)
@@ -88,7 +91,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
                     __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ vt_out,
-                    __nv_bfloat16* __restrict__ tb_out, int B, int R, int N, int ldn, int npad, int* status) {
+                    float* __restrict__ tb_out, int B, int R, int N, int npad, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -208,7 +211,6 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
         }
     } else {
         // epilogue warps
-        const int qset = (warp - 6) >> 2;
         const int quad = warp & 3;
         const int row = quad * 32 + lane;
         const float qscale = kLog2e * rsqrtf((float)kD);
@@ -229,7 +231,6 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             // 64-byte-swizzled shared-memory image (16-byte chunk c of row pos at chunk c ^ ((pos/2)%4)),
             // so that the attention kernel fetches whole tiles with one untiled bulk copy each
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16);
-            if (!kProjSplitEpilogue || qset == 0) {
             if (!mbar_wait(slot_full(0), it & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidProj, 6);
                 break;
@@ -266,8 +267,6 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(0));
-            }
-            if (!kProjSplitEpilogue || qset == 1) {
             // ---- slot 1: v, stored as tiles [line][head][key block of 32][32 d][32 keys], each tile the
             // 64-byte-swizzled image of the K-major B operand of P V (row d, chunk (key%32)/8)
             if (!mbar_wait(slot_full(1), it & 1u, abort_flag)) {
@@ -297,12 +296,11 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(1));
-            if (pos < ldn) {  // the row padding [N, ldn) is read by the attention kernel: keep it finite
+            if (valid) {  // key padding [N, npad) is read by the attention kernel: zeros
 #pragma unroll
                 for (int h = 0; h < kH; ++h)
-                    tb_out[(((long long)tc.b * kH + h) * R + tc.line) * ldn + pos] =
-                        __float2bfloat16_rn(live ? __uint_as_float(tbr[h]) * kLog2e : 0.f);
-            }
+                    tb_out[((((long long)tc.b * kH + h) * nkb + (pos >> 5)) * R + tc.line) * kTbPitch + (pos & 31)] =
+                        live ? __uint_as_float(tbr[h]) * kLog2e : 0.f;
             }
         }
     }
@@ -318,49 +316,77 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 // =====================================================================================
 // triattn_core
 // =====================================================================================
-// One CTA = one head, 128 queries and FOUR lines of the pair tensor, 32 keys per step:
-//  * the pair-bias tile [128 q x 32 k] does not depend on the line: fetched once per step by TMA and
-//    shared by the four lines' softmax warpgroups;
-//  * sixteen softmax warps (four per SM sub-partition) hide the TMEM / barrier latencies that two
-//    warps per sub-partition could not (the earlier 64-key, 2-line version sat at ~40 % issue use);
-//  * O accumulates in TMEM across all key blocks (tcgen05.mma with accumulate), so the softmax
-//    threads hold no output registers and do no per-block read-modify-write. The running maximum
-//    used for scaling is only raised when the true row maximum exceeds it by more than 8 (2^8 head
-//    room in the exponentials): then, and only then, the thread rescales its O row in TMEM
-//    (tcgen05.ld / st) and its running sum. The result is exact: sum and O always share one scale.
+// One CTA = one head, 128 queries and TWO lines of the pair tensor, 32 keys per step; two CTAs share an SM
+// (their prologues, epilogues and waits interleave). Per line and step:
+//   MMA warp      S = Q K^T (128 x 32, K = 32) into one of two TMEM slots
+//   softmax warps thread = query row = TMEM lane: S -> registers, + pair bias (fp32 tile in shared memory,
+//                 one tile per step shared by both lines) [+ mask bias where the block has masked keys],
+//                 row maximum, P = exp2(S - m) rounded to bf16 and written back to TMEM over the S slot
+//   MMA warp      O[128 x 48] += P V' with P read from TMEM as the A operand; V' is the V tile [32 d x 32 keys]
+//                 followed by 16 constant rows, the first of them all ones: column 32 of O is the row sum of
+//                 exactly the bf16 values of P that entered the product, so the softmax threads keep no sum.
+// The slot of S_j is next written by S_{j+2}, which the MMA thread issues after P_j V_j: tcgen05 operations of
+// one thread execute in issue order, so neither the S slots nor P need an "empty" barrier.
+// The running maximum m used for scaling is only raised when the row maximum exceeds it by more than 8
+// (2^8 head room in P): then, and only then, the thread rescales its O row (sum column included) in TMEM.
+// The result is exact: numerator and denominator always share one scale.
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 32;       // keys per step
 constexpr int kMaxKeys = 2048;   // one CTA keeps a mask-bias row per line in shared memory
-constexpr int kKvStages = 3;     // K / V ring (one untiled bulk copy per tile): covers the load round trip
-constexpr int kLines = 2;     // lines per CTA; two CTAs share an SM (their prologues, epilogues and waits interleave)
+constexpr int kKvStages = 3;     // K / V ring (untiled bulk copies of pre-swizzled tiles): covers the load round trip
+constexpr int kLines = 2;     // lines per CTA
 constexpr int kLinePad = 4;   // the operand images pad the line count of a sample to a multiple of this
 constexpr int kCoreThreads = 32 * (1 + kLines + 4 * kLines);  // producer, one MMA warp per line, softmax
 constexpr float kRescaleThreshold = 8.0f;
-#ifdef OF3_CORE_TIMING
-__device__ long long g_core_dbg[64];
-#define DBG_T(var) const long long var = clock64()
-#define DBG_ADD(slot, a, b) do { if (dbg_on) atomicAdd((unsigned long long*)&g_core_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
-#else
-#define DBG_T(var)
-#define DBG_ADD(slot, a, b)
-#endif
+constexpr uint32_t kTbTileBytes = kBQ * kTbPitch * 4;  // 18432
+constexpr uint32_t kVSlot = 3072;                      // V tile (2 KB) + 16 constant rows of 64 B
+constexpr int kON = 48;                                // N of the P V GEMM: 32 output channels + the row-sum column (+ 15 unused)
 
 struct CoreSmem {
-    static constexpr uint32_t kQ = 0;                                // lines x 8 KB
-    static constexpr uint32_t kK = kQ + kLines * 8192;               // lines x stages x 2 KB
-    static constexpr uint32_t kV = kK + kLines * kKvStages * 2048;   // lines x stages x 2 KB
-    static constexpr uint32_t kTb = kV + kLines * kKvStages * 2048;  // 2 x 16 KB: bias tiles [128 q x 64 k]
-    static constexpr uint32_t kP = kTb + 2 * kKBlockBytes;           // lines x 2 x 8 KB
-    static constexpr uint32_t kBars = kP + kLines * 2 * 8192;
-    static constexpr uint32_t kFlags = kBars + 384;                  // lines x 128 block flags (bytes)
-    static constexpr uint32_t kMb = kFlags + kLines * 128;           // lines x nkeys_pad floats
+    static constexpr uint32_t kQ = 0;                                   // lines x 8 KB
+    static constexpr uint32_t kK = kQ + kLines * 8192;                  // stages x lines x 2 KB
+    static constexpr uint32_t kV = kK + kKvStages * kLines * 2048;      // stages x lines x 3 KB
+    static constexpr uint32_t kTb = kV + kKvStages * kLines * kVSlot;   // 2 x 18 KB: bias tiles [128 q][36] fp32
+    static constexpr uint32_t kBars = kTb + 2 * kTbTileBytes;
+    static constexpr uint32_t kFlags = kBars + 256;                     // lines x 128 block flags (bytes)
+    static constexpr uint32_t kMb = kFlags + kLines * 128;              // lines x nkeys_pad floats
     static uint32_t dyn_bytes(int nblk) { return kMb + kLines * nblk * kBK * 4 + 1024; }
 };
+
+// D[tmem] (+)= A[tmem] * B[smem]^T: A = 128 lanes x 16 bf16 (8 columns of packed pairs), issued by ONE thread.
+__device__ __forceinline__ void mma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Stores 16 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+// (x0, x1) += (y0, y1) as one packed instruction (half the issue slots of two scalar adds)
+__device__ __forceinline__ void add2(float& x0, float& x1, float y0, float y1) {
+    unsigned long long a, b;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x0), "f"(x1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(y0), "f"(y1));
+    asm("add.rn.f32x2 %0, %0, %1;" : "+l"(a) : "l"(b));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(a));
+}
 
 template <bool kTransposed>
 __global__ void __launch_bounds__(kCoreThreads, 2)
 triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16* __restrict__ k_img,
-                    const __nv_bfloat16* __restrict__ v_img, const __grid_constant__ CUtensorMap tmTb,
+                    const __nv_bfloat16* __restrict__ v_img, const float* __restrict__ tb_img,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
                     int R, int N, int npad, float inf, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -376,13 +402,12 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     auto tb_full = [&](int s) { return bars + 8u * (1 + 2 * kKvStages + s); };
     auto tb_empty = [&](int s) { return bars + 8u * (3 + 2 * kKvStages + s); };
     auto s_full = [&](int L, int s) { return bars + 8u * (kB0 + L * 2 + s); };
-    auto s_empty = [&](int L, int s) { return bars + 8u * (kB0 + 2 * kLines + L * 2 + s); };
-    auto p_ready = [&](int L, int s) { return bars + 8u * (kB0 + 4 * kLines + L * 2 + s); };
-    auto pv_done = [&](int L, int s) { return bars + 8u * (kB0 + 6 * kLines + L * 2 + s); };
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * (kB0 + 8 * kLines));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * (kB0 + 8 * kLines) + 8);
+    auto p_ready = [&](int L, int s) { return bars + 8u * (kB0 + 2 * kLines + L * 2 + s); };
+    auto pv_done = [&](int L, int s) { return bars + 8u * (kB0 + 4 * kLines + L * 2 + s); };
+    static_assert(8 * (kB0 + 6 * kLines) + 16 <= 256, "barrier block");
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * (kB0 + 6 * kLines));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * (kB0 + 6 * kLines) + 8);
 
-    DBG_T(t_entry);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (N + kBQ - 1) / kBQ;
     const int groups_per_b = (R + kLines - 1) / kLines;
@@ -408,14 +433,12 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             mbar_init(tb_empty(s), 4 * kLines);  // every softmax warp has read its rows of the bias tile
             for (int L = 0; L < kLines; ++L) {
                 mbar_init(s_full(L, s), 1);
-                mbar_init(s_empty(L, s), 4);
                 mbar_init(p_ready(L, s), 4);
                 mbar_init(pv_done(L, s), 1);
             }
         }
         *abort_flag = 0;
         mbar_fence_init();
-        prefetch_tmap(&tmTb);
     }
     // additive key mask of each line, pre-scaled for exp2: inf * (mask - 1) * log2(e); -inf beyond N
     for (int idx = threadIdx.x; idx < kLines * nkp; idx += blockDim.x) {
@@ -432,6 +455,14 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         }
         mbs[idx] = v;
     }
+    // constant rows 32..47 of every V slot: row 32 = ones (bf16 1.0), the rest zeros; the swizzle permutes
+    // 16-byte chunks inside a row only, and every chunk of a row holds the same value
+    for (int idx = threadIdx.x; idx < kKvStages * kLines * 64; idx += blockDim.x) {
+        const int slot = idx >> 6, w16 = idx & 63;  // 64 chunks of 16 B per slot tail
+        const uint32_t v = (w16 < 4) ? 0x3F803F80u : 0u;
+        *reinterpret_cast<uint4*>(gbase + CoreSmem::kV + slot * kVSlot + 2048 + w16 * 16) = make_uint4(v, v, v, v);
+    }
+    fence_proxy_async_smem();
     if (warp == 1) {
         tmem_alloc(smem_u32((const void*)tmem_ptr), kLines * 128);
         tmem_relinquish();
@@ -448,7 +479,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     }
     __syncthreads();
     const uint32_t tmem_base = *tmem_ptr;
-    // TMEM columns of line L: L*128 + { S0 [0,32)  S1 [32,64)  O [64,96) }
+    // TMEM columns of line L: L*128 + { S0 / P0 [0,32)  S1 / P1 [32,64)  O [64,96)  row sum 96 }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -458,77 +489,58 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             mbar_arrive_expect_tx(q_full, kLines * kBQ * 64);
             bulk_load(sbase + CoreSmem::kQ, q_img + (((bh * n_qt + qt) * rpad + line0) * kBQ) * kD, kLines * kBQ * 64,
                       q_full);
-#ifdef OF3_CORE_TIMING
-            const bool dbg_on = blockIdx.x == 300;
-#endif
+            const int q_rows = (N - q0 < kBQ) ? N - q0 : kBQ;  // rows of the bias tile that exist
+            const uint32_t tb_bytes = (uint32_t)q_rows * kTbPitch * 4;
             for (int j = 0; j < nblk; ++j) {
-                // K / V first: their stage is free once block j-4 has been consumed, while the bias tile
-                // below has to wait for block j-3 -- issued in the other order, that wait also held back
-                // the K / V copy and left it a single step of lead over the MMA that needs it
                 const int s = j % kKvStages;
-                DBG_T(p0);
                 if (!mbar_wait(kv_empty(s), ((j / kKvStages) & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidCore, 1);
                     break;
                 }
-                DBG_T(p1);
-                DBG_ADD(16, p0, p1);
                 mbar_arrive_expect_tx(kv_full(s), kLines * 4096);
-                const long long tile0 = ((bh * nkb + j) * rpad + line0) << 10;  // first of the 4 lines' tiles
+                const long long tile0 = ((bh * nkb + j) * rpad + line0) << 10;  // first of the lines' tiles
                 bulk_load(sbase + CoreSmem::kK + s * kLines * 2048, k_img + tile0, kLines * 2048, kv_full(s));
-                bulk_load(sbase + CoreSmem::kV + s * kLines * 2048, v_img + tile0, kLines * 2048, kv_full(s));
-                DBG_T(p2);
-                DBG_ADD(17, p1, p2);
-                if ((j & 1) == 0) {  // pair-bias tile for the key blocks j and j+1 (64 keys), shared by all lines
-                    const int t = j >> 1, ts = t & 1;
-                    if (!mbar_wait(tb_empty(ts), ((t >> 1) & 1u) ^ 1u, abort_flag)) {
-                        report_wait_failure(status, abort_flag, kKidCore, 11);
-                        break;
-                    }
-                    mbar_arrive_expect_tx(tb_full(ts), kKBlockBytes);
-                    tma_load_3d(sbase + CoreSmem::kTb + ts * kKBlockBytes, &tmTb, tb_full(ts), t * 64, q0, b * kH + h);
+                for (int L = 0; L < kLines; ++L)
+                    bulk_load(sbase + CoreSmem::kV + (s * kLines + L) * kVSlot, v_img + tile0 + L * 1024, 2048,
+                              kv_full(s));
+                // pair-bias tile of key block j (all lines of the CTA share it)
+                const int ts = j & 1;
+                if (!mbar_wait(tb_empty(ts), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidCore, 11);
+                    break;
                 }
+                mbar_arrive_expect_tx(tb_full(ts), tb_bytes);
+                bulk_load(sbase + CoreSmem::kTb + ts * kTbTileBytes,
+                          tb_img + ((bh * nkb + j) * (long long)N + q0) * kTbPitch, tb_bytes,
+                          tb_full(ts));
             }
         }
     } else if (warp <= kLines) {
-        // ---------------------------------------------------------------- one MMA-issuing warp per line:
-        // a single issuing thread for all lines spent ~3400 cycles per step on its 16 MMAs, 8 commits and
-        // 9 barrier waits and was the critical path; per line it is a quarter of that
+        // ---------------------------------------------------------------- one MMA-issuing warp per line
         if (lane == 0) {
             const int L = warp - 1;
-            constexpr uint32_t idesc = idesc_bf16_f32(128, 32);  // both GEMMs are 128 x 32 x 32
+            constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);  // S: 128 x 32, K = 32
+            constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 48, K = 32
             bool ok = mbar_wait(q_full, 0, abort_flag);
             if (!ok) report_wait_failure(status, abort_flag, kKidCore, 2);
             const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ + L * 8192);
-            const uint32_t d_o = tmem_base + L * 128 + 64;
-#ifdef OF3_CORE_TIMING
-            const bool dbg_on = blockIdx.x == 300 && L == 0;
-#endif
+            const uint32_t t_line = tmem_base + L * 128;
+            const uint32_t d_o = t_line + 64;
             for (int j = 0; j <= nblk && ok; ++j) {
-                DBG_T(m0);
-                if (j < nblk) {  // S_j = Q K_j^T
+                if (j < nblk) {  // S_j = Q K_j^T; its slot was last read by P_{j-2} V_{j-2}, issued before this
                     const int s = j & 1;
                     const int ks = j % kKvStages;
                     if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
                         report_wait_failure(status, abort_flag, kKidCore, 3);
                         break;
                     }
-                    DBG_T(m1);
-                    DBG_ADD(18, m0, m1);
-                    if (!mbar_wait(s_empty(L, s), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
-                        report_wait_failure(status, abort_flag, kKidCore, 4);
-                        break;
-                    }
-                    tc_fence_after_sync();
                     const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (ks * kLines + L) * 2048);
-                    const uint32_t d = tmem_base + L * 128 + s * kBK;
-                    mma_bf16(d, qdesc, kdesc, idesc, 0u);
-                    mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc, 1u);
+                    const uint32_t d = t_line + s * kBK;
+                    mma_bf16(d, qdesc, kdesc, idesc_s, 0u);
+                    mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
                     mma_commit(s_full(L, s));
                 }
-                DBG_T(m2);
-                DBG_ADD(19, m0, m2);
-                if (j >= 1) {  // O += P_{j-1} V_{j-1}
+                if (j >= 1) {  // O += P_{j-1} V'_{j-1}
                     const int jj = j - 1;
                     const int s = jj & 1;
                     const int ks = jj % kKvStages;
@@ -537,15 +549,13 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint64_t pdesc = smem_desc_k_sw64(sbase + CoreSmem::kP + (L * 2 + s) * 8192);
-                    const uint64_t vdesc = smem_desc_k_sw64(sbase + CoreSmem::kV + (ks * kLines + L) * 2048);
-                    mma_bf16(d_o, pdesc, vdesc, idesc, jj != 0 ? 1u : 0u);
-                    mma_bf16(d_o, pdesc + 2u, vdesc + 2u, idesc, 1u);
+                    const uint32_t a_p = t_line + s * kBK;  // P: 16 columns of packed bf16 pairs
+                    const uint64_t vdesc = smem_desc_k_sw64(sbase + CoreSmem::kV + (ks * kLines + L) * kVSlot);
+                    mma_bf16_ts(d_o, a_p, vdesc, idesc_o, jj != 0 ? 1u : 0u);
+                    mma_bf16_ts(d_o, a_p + 8u, vdesc + 2u, idesc_o, 1u);
                     mma_commit(pv_done(L, s));
                     mma_commit(kv_empty(ks));
                 }
-                DBG_T(m3);
-                DBG_ADD(20, m2, m3);
             }
         }
     } else {
@@ -557,40 +567,19 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         const bool line_valid = line0 + L < R;
         const long long bl = (long long)b * R + line_of(L);
         const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 128;
+        const uint32_t tb_row = sbase + CoreSmem::kTb + (uint32_t)row * (kTbPitch * 4);
         const float* mbl = mbs + L * nkp;
-        float m_used = 0.f, l = 0.f;
+        float m_used = 0.f;
         bool ok = true;
-#ifdef OF3_CORE_TIMING
-        const bool dbg_on = (blockIdx.x == 300) && lane == 0 && (warp == 1 + kLines || warp == 4 * kLines + kLines);
-#endif
-        DBG_T(t_loop);
-        DBG_ADD(24, t_entry, t_loop);
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
-            const int k0 = j * kBK;
-            DBG_T(t0);
-            const int tbs = (j >> 1) & 1;
-            if (!mbar_wait(tb_full(tbs), (j >> 2) & 1u, abort_flag)) {
-                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
-                ok = false;
-                break;
-            }
-            uint4 tbv[4];  // this row's 32 pair-bias values: half of its 128-byte row of the shared tile
-            {
-                const uint32_t tbt = sbase + CoreSmem::kTb + tbs * kKBlockBytes;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) tbv[i] = lds128(chunk_addr(tbt, row, (j & 1) * 4 + i));
-            }
-            __syncwarp();
-            if ((j & 1) && lane == 0) mbar_arrive(tb_empty(tbs));
-            DBG_T(t1);
-            if (!mbar_wait(s_full(L, s), (j >> 1) & 1u, abort_flag)) {
+            const uint32_t ph = (j >> 1) & 1u;
+            if (!mbar_wait(s_full(L, s), ph, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 7);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            DBG_T(t2);
             float sv[kBK];
             {
                 uint32_t r0[32];
@@ -599,12 +588,26 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
 #pragma unroll
                 for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r0[e]);
             }
-            DBG_T(t3);
-            tc_fence_before_sync();
+            if (!mbar_wait(tb_full(s), ph, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
+                ok = false;
+                break;
+            }
+            {   // + pair bias: this row's 32 fp32 values of the shared tile
+                const uint32_t tba = tb_row + s * kTbTileBytes;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const uint4 w = lds128(tba + i * 16);
+                    add2(sv[i * 4], sv[i * 4 + 1], __uint_as_float(w.x), __uint_as_float(w.y));
+                    add2(sv[i * 4 + 2], sv[i * 4 + 3], __uint_as_float(w.z), __uint_as_float(w.w));
+                }
+            }
             __syncwarp();
-            if (lane == 0) mbar_arrive(s_empty(L, s));
-            // (q.k + mask bias) + pair bias: the reference's order, in fp32
+            if (lane == 0) mbar_arrive(tb_empty(s));
+            // + mask bias (blocks without a masked key skip it): (q.k + pair bias) + inf * (mask - 1); a masked
+            // key ends at -inf-like 1.44e9 either way, an unmasked one adds exactly 0
             if (mbflag[L * 128 + j]) {
+                const int k0 = j * kBK;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const float4 mb = *reinterpret_cast<const float4*>(mbl + k0 + i * 4);
@@ -614,18 +617,13 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                     sv[i * 4 + 3] += mb.w;
                 }
             }
-            float mx = -INFINITY;
+            float mx0 = max3(sv[0], sv[1], sv[2]), mx1 = max3(sv[3], sv[4], sv[5]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const uint32_t w[4] = {tbv[i].x, tbv[i].y, tbv[i].z, tbv[i].w};
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const int e = i * 8 + jj * 2;
-                    sv[e] += bf16lo(w[jj]);
-                    sv[e + 1] += bf16hi(w[jj]);
-                    mx = max3(mx, sv[e], sv[e + 1]);
-                }
+            for (int e = 6; e < 30; e += 4) {
+                mx0 = max3(mx0, sv[e], sv[e + 1]);
+                mx1 = max3(mx1, sv[e + 2], sv[e + 3]);
             }
+            const float mx = max3(mx0, mx1, fmaxf(sv[30], sv[31]));
             if (j == 0) {
                 m_used = mx;  // finite: block 0 always holds a key < N, masked keys are -1e9-ish, not -inf
             } else {
@@ -641,62 +639,37 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                     const float f = need ? ex2_approx(m_used - mx) : 1.0f;
                     uint32_t orow[32];
                     tmem_ld32(trow + 64, orow);
+                    const uint32_t osum = tmem_ld1(trow + 64 + 32);
                     tmem_ld_wait();
 #pragma unroll
                     for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * f);
                     tmem_st32(trow + 64, orow);
+                    tmem_st1(trow + 64 + 32, __float_as_uint(__uint_as_float(osum) * f));
                     tmem_st_wait();
-                    if (need) {
-                        l *= f;
-                        m_used = mx;
-                    }
+                    if (need) m_used = mx;
                 }
             }
-            DBG_T(t4);
-            // the P buffer of this parity was last read by the P V of block j-2
-            if (j >= 2 && !mbar_wait(pv_done(L, s), ((j - 2) >> 1) & 1u, abort_flag)) {
-                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 9);
-                ok = false;
-                break;
-            }
-            DBG_T(t5);
-            const uint32_t ptile = sbase + CoreSmem::kP + (L * 2 + s) * 8192;
-            float sum = 0.f;
+            uint32_t pk[16];
+            const float nm = -m_used;
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                uint32_t pk[4];
-#pragma unroll
-                for (int jj = 0; jj < 4; ++jj) {
-                    const int e = ch * 8 + jj * 2;
-                    const float p0 = ex2_approx(sv[e] - m_used);
-                    const float p1 = ex2_approx(sv[e + 1] - m_used);
-                    sum += p0 + p1;
-                    pk[jj] = pack_bf16x2(p0, p1);
-                }
-                sts128(chunk_addr64(ptile, row, ch), make_uint4(pk[0], pk[1], pk[2], pk[3]));
+            for (int e = 0; e < 32; e += 2) {
+                add2(sv[e], sv[e + 1], nm, nm);
+                pk[e >> 1] = pack_bf16x2(ex2_approx(sv[e]), ex2_approx(sv[e + 1]));
             }
-            l += sum;
-            DBG_T(t6);
+            tmem_st16(trow + s * kBK, pk);
+            tmem_st_wait();
             tc_fence_before_sync();
-            fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready(L, s));
-            DBG_T(t7);
-#ifdef OF3_CORE_TIMING
-            { const int o8 = (warp == 1 + kLines) ? 0 : 8;
-              DBG_ADD(o8 + 0, t0, t1); DBG_ADD(o8 + 1, t1, t2); DBG_ADD(o8 + 2, t2, t3); DBG_ADD(o8 + 3, t3, t4);
-              DBG_ADD(o8 + 4, t4, t5); DBG_ADD(o8 + 5, t5, t6); DBG_ADD(o8 + 6, t6, t7); DBG_ADD(o8 + 7, t0, t7); }
-#endif
         }
-        DBG_T(t_loop_end);
-        DBG_ADD(25, t_loop, t_loop_end);
         if (ok) {
             if (mbar_wait(pv_done(L, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1u, abort_flag)) {
                 tc_fence_after_sync();
                 uint32_t r[32];
                 tmem_ld32(trow + 64, r);
+                const uint32_t osum = tmem_ld1(trow + 64 + 32);
                 tmem_ld_wait();
-                const float inv = 1.0f / l;
+                const float inv = 1.0f / __uint_as_float(osum);
                 if (qpos < N && line_valid) {
                     uint4* dst = reinterpret_cast<uint4*>(o_out + ((bl * N + qpos) * (long long)kC) + h * kD);
 #pragma unroll
@@ -720,12 +693,6 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         tc_fence_after_sync();
         tmem_dealloc(tmem_base, kLines * 128);
     }
-#ifdef OF3_CORE_TIMING
-    if (blockIdx.x == 300 && threadIdx.x == 32 * (1 + kLines)) {
-        const long long t_exit = clock64();
-        atomicAdd((unsigned long long*)&g_core_dbg[26], (unsigned long long)(t_exit - t_entry));
-    }
-#endif
 }
 
 // =====================================================================================
@@ -1005,20 +972,20 @@ int z_tmap(CUtensorMap* m, const void* z, int B, int R, int N, bool transposed) 
 
 template <bool kT>
 int set_attrs() {
-    static bool attr_done = false;
-    if (!attr_done) {
+    constexpr int kAttrKey = kT ? 7 : 6;  // per-device function attributes
+    if (!device_configured(kAttrKey)) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_proj_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, ProjSmem::kDyn));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_core_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                             CoreSmem::dyn_bytes(kMaxKeys / kBK)));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(triattn_out_kernel<kT>, cudaFuncAttributeMaxDynamicSharedMemorySize, AOutSmem::kDyn));
-        attr_done = true;
+        device_mark_configured(kAttrKey);
     }
     return OF3_OK;
 }
 
 template <bool kT>
 int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
-                 __nv_bfloat16* tb, int B, int R, int N, int ldn, const of3_triattn_params* p, cudaStream_t st) {
+                 float* tb, int B, int R, int N, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
     CUtensorMap tmZ, tmW[3], tmWb;
     if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
@@ -1038,28 +1005,22 @@ int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __n
     LaunchScope scope(kKidProj, st);
     triattn_proj_kernel<kT><<<grid, kProjThreads, ProjSmem::kDyn, st>>>(
         tmZ, tmW[0], tmW[1], tmW[2], tmWb, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, q, k, vt,
-        tb, B, R, N, ldn, (int)align_up(N, kBK), device_status_ptr());
+        tb, B, R, N, (int)align_up(N, kBK), device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
 
 template <bool kT>
 int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, const __nv_bfloat16* q,
-                const __nv_bfloat16* k, const __nv_bfloat16* vt, const __nv_bfloat16* tb, __nv_bfloat16* o, int B,
-                int R, int N, int ldn, float inf, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
+                const __nv_bfloat16* k, const __nv_bfloat16* vt, const float* tb, __nv_bfloat16* o, int B,
+                int R, int N, float inf, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
-    CUtensorMap tmZ, tmOut, tmO, tmWg, tmWo, tmTb;
+    CUtensorMap tmZ, tmOut, tmO, tmWg, tmWo;
     if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
     if ((rc = z_tmap(&tmOut, out, B, R, N, kT))) return rc;
     if ((rc = z_tmap(&tmO, o, B, R, N, false))) return rc;  // o is [line][pos][128] in view order
     if ((rc = weight_tmap128(&tmWg, p->w_g))) return rc;
     if ((rc = weight_tmap128(&tmWo, p->w_o))) return rc;
-    {   // pair bias [b*H + h][q][k] for ALL N query positions, row pitch ldn: tile = 128 queries x 64 keys
-        uint64_t dimt[3] = {(uint64_t)ldn, (uint64_t)N, (uint64_t)B * kH};
-        uint64_t strt[2] = {(uint64_t)ldn * 2, (uint64_t)N * ldn * 2};
-        uint32_t boxt[3] = {64, kBQ, 1};
-        if ((rc = make_tmap_bf16(&tmTb, tb, 3, dimt, strt, boxt, 1))) return rc;
-    }
     if ((rc = set_attrs<kT>())) return rc;
     int* status = device_status_ptr();
     const long long ctas = (long long)B * ceil_div(R, kLines) * kH * ceil_div(N, kBQ);
@@ -1067,7 +1028,7 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
     {
         LaunchScope scope(kKidCore, st);
         triattn_core_kernel<kT><<<(unsigned)ctas, kCoreThreads, CoreSmem::dyn_bytes(ceil_div(N, kBK)), st>>>(
-            q, k, vt, tmTb, mask, o, B, R, N, (int)align_up(N, kBK), inf, status);
+            q, k, vt, tb, mask, o, B, R, N, (int)align_up(N, kBK), inf, status);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     const long long tiles = (long long)B * R * ceil_div(N, kRows);
@@ -1099,47 +1060,53 @@ size_t triattn_image_elems(int B, int R, int N) {
     return (size_t)B * kH * ceil_div(N, kBQ) * align_up(R, kLinePad) * kBQ * kD;
 }
 
-// q, k [line][head][pos][32], v transposed, and this shard's rows of the pair bias
-// tb[(b*H + h)][line][ldn] from R lines of N positions. transposed: whole square tensors only.
+// Floats of the pair-bias image of B samples with R query rows and N keys: [B*4][key blocks of 32][R][36].
+size_t triattn_bias_elems(int B, int R, int N) {
+    return (size_t)B * kH * ceil_div(N, kBK) * R * kTbPitch;
+}
+
+// q, k, v operand images and this shard's rows of the pair-bias image tb[(b*H + h)][key block][line][36]
+// (fp32) from R lines of N positions. transposed: whole square tensors only.
 int triattn_project(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
-                    __nv_bfloat16* tb, int B, int R, int N, int ldn, bool transposed,
+                    float* tb, int B, int R, int N, bool transposed,
                     const of3_triattn_params* p, cudaStream_t st) {
     OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "triattn: z must be 16-byte aligned");
     OF3_REQUIRE(!transposed || R == N, OF3_ERR_SHAPE, "triattn: transposed view needs the whole tensor");
-    return transposed ? project_impl<true>(z, q, k, vt, tb, B, R, N, ldn, p, st)
-                      : project_impl<false>(z, q, k, vt, tb, B, R, N, ldn, p, st);
+    return transposed ? project_impl<true>(z, q, k, vt, tb, B, R, N, p, st)
+                      : project_impl<false>(z, q, k, vt, tb, B, R, N, p, st);
 }
 
-// attention over the R lines with the pair bias of all N query rows, gate, output projection, residual.
+// attention over the R lines with the pair-bias image of all N query rows (tb [(b*H + h)][key block][N][36]),
+// gate, output projection, residual.
 int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
                    const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
-                   const __nv_bfloat16* tb, __nv_bfloat16* o, int B, int R, int N, int ldn, float inf,
+                   const float* tb, __nv_bfloat16* o, int B, int R, int N, float inf,
                    bool transposed, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
+    OF3_REQUIRE(((uintptr_t)tb & 15) == 0, OF3_ERR_ALIGN, "triattn: the pair-bias image must be 16-byte aligned");
     OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
                 "triattn: z/out must be 16-byte aligned");
     OF3_REQUIRE(N <= kMaxKeys, OF3_ERR_SHAPE, "triattn: N %d above the %d keys one CTA keeps a mask row for", N,
                 kMaxKeys);
     OF3_REQUIRE(!transposed || R == N, OF3_ERR_SHAPE, "triattn: transposed view needs the whole tensor");
-    return transposed ? finish_impl<true>(z, mask, out, q, k, vt, tb, o, B, R, N, ldn, inf, add_residual, p, st)
-                      : finish_impl<false>(z, mask, out, q, k, vt, tb, o, B, R, N, ldn, inf, add_residual, p, st);
+    return transposed ? finish_impl<true>(z, mask, out, q, k, vt, tb, o, B, R, N, inf, add_residual, p, st)
+                      : finish_impl<false>(z, mask, out, q, k, vt, tb, o, B, R, N, inf, add_residual, p, st);
 }
 
 int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, int B, int N,
             float inf, int flags, const of3_triattn_params* p, Arena& ws, cudaStream_t st) {
-    const int ldn = (int)align_up(N, 64);
     const size_t plane = (size_t)B * N * N * kC * sizeof(__nv_bfloat16);
     const size_t img = triattn_image_elems(B, N, N) * sizeof(__nv_bfloat16);
     __nv_bfloat16* q = (__nv_bfloat16*)ws.take(img);
     __nv_bfloat16* k = (__nv_bfloat16*)ws.take(img);
     __nv_bfloat16* vt = (__nv_bfloat16*)ws.take(img);
     __nv_bfloat16* o = (__nv_bfloat16*)ws.take(plane);
-    __nv_bfloat16* tb = (__nv_bfloat16*)ws.take((size_t)B * kH * N * ldn * sizeof(__nv_bfloat16) + 256);
+    float* tb = (float*)ws.take(triattn_bias_elems(B, N, N) * sizeof(float));
     if (!ws.base) return OF3_OK;
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "triattn: workspace too small (%zu needed)", ws.off);
     const bool tr = (flags & OF3_FLAG_TRANSPOSED) != 0;
-    int rc = triattn_project(z, q, k, vt, tb, B, N, N, ldn, tr, p, st);
+    int rc = triattn_project(z, q, k, vt, tb, B, N, N, tr, p, st);
     if (rc) return rc;
-    return triattn_finish(z, mask, out, q, k, vt, tb, o, B, N, N, ldn, inf, tr,
+    return triattn_finish(z, mask, out, q, k, vt, tb, o, B, N, N, inf, tr,
                           (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, st);
 }
 

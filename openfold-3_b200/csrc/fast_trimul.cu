@@ -560,12 +560,11 @@ extern "C" int of3_out_dbg(long long* out, int reset) {
 bool trimul_supported(int c_z, int c_h) { return c_z == 128 && c_h == 128; }
 
 static int set_attrs() {
-    static bool attr_done = false;
-    if (!attr_done) {
+    if (!device_configured(5)) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, OutSmem::kDyn));
-        attr_done = true;
+        device_mark_configured(5);
     }
     return OF3_OK;
 }

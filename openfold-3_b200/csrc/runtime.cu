@@ -7,6 +7,8 @@
 #include <string.h>
 
 #include <mutex>
+#include <string>
+#include <unordered_map>
 #include <vector>
 
 namespace of3 {
@@ -51,6 +53,22 @@ int sm_count() {
     return g_sm_count[dev];
 }
 
+static unsigned g_configured[kMaxDevices] = {0};
+
+bool device_configured(int key) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || key < 0 || key >= 32) return false;
+    std::lock_guard<std::mutex> lk(g_mu);
+    return (g_configured[dev] >> key) & 1u;
+}
+
+void device_mark_configured(int key) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || key < 0 || key >= 32) return;
+    std::lock_guard<std::mutex> lk(g_mu);
+    g_configured[dev] |= 1u << key;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -72,6 +90,9 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
+static std::unordered_map<std::string, CUtensorMap> g_tmaps;
+static const size_t kMaxCachedTmaps = 8192;
+
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_bytes, const uint32_t* box, int swizzle) {
     EncodeTiledFn fn = encode_fn();
@@ -92,6 +113,25 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
             gstr[i - 1] = strides_bytes[i - 1];
         }
     }
+    // cache key: every argument of the encoding (a tensor map holds no device state: the same
+    // arguments give the same 128 bytes on every device of the process)
+    std::string key;
+    key.reserve(8 + 4 + rank * 20 + 4);
+    auto put = [&key](const void* p, size_t n) { key.append((const char*)p, n); };
+    put(&base, sizeof(base));
+    put(&rank, sizeof(rank));
+    put(gdim, rank * sizeof(cuuint64_t));
+    put(gstr, (rank - 1) * sizeof(cuuint64_t));
+    put(bx, rank * sizeof(cuuint32_t));
+    put(&swizzle, sizeof(swizzle));
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        auto it = g_tmaps.find(key);
+        if (it != g_tmaps.end()) {
+            *out = it->second;
+            return OF3_OK;
+        }
+    }
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base),
                     gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B
@@ -99,6 +139,11 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     OF3_REQUIRE(r == CUDA_SUCCESS, OF3_ERR_DRIVER, "cuTensorMapEncodeTiled failed with CUresult %d",
                 (int)r);
+    {
+        std::lock_guard<std::mutex> lk(g_mu);
+        if (g_tmaps.size() >= kMaxCachedTmaps) g_tmaps.clear();  // bounded: callers with ever-new buffers
+        g_tmaps.emplace(std::move(key), *out);
+    }
     return OF3_OK;
 }
 

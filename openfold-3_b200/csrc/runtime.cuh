@@ -8,7 +8,8 @@ namespace of3 {
 
 // Encodes a tiled bf16 tensor map. dims/strides are innermost-first; strides_bytes has
 // rank-1 entries (stride of dim 1.., the innermost is dense). Returns OF3_OK or an error code.
-// swizzle: 0 none, 1 (or true) 128-byte, 2 64-byte.
+// swizzle: 0 none, 1 (or true) 128-byte, 2 64-byte. Encoded maps are kept in a locked cache keyed by
+// every argument, so a steady-state launch costs a lookup instead of a driver call per operand.
 int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
                    const uint64_t* strides_bytes, const uint32_t* box, int swizzle);
 
@@ -28,5 +29,11 @@ struct LaunchScope {
 
 // Number of SMs of the current device (cached per device).
 int sm_count();
+
+// Function attributes (e.g. the dynamic shared-memory limit) are per device: a launch site asks whether
+// its kernels (identified by `key`, one per launch site, < 32) are configured on the CURRENT device and
+// marks them once cudaFuncSetAttribute has succeeded there. Guarded by the runtime's mutex.
+bool device_configured(int key);
+void device_mark_configured(int key);
 
 }  // namespace of3

@@ -42,6 +42,12 @@ def _pitch(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
+def triattn_bias_shape(R: int, N: int) -> tuple:
+    """Shape (fp32) of the triangle-attention pair-bias image of R query rows and N keys: [4 heads x key
+    blocks of 32][R][36] -- 32 keys + 4 floats of row padding (of3_dap_triattn_bias_elems in the library)."""
+    return (4 * ((N + 31) // 32), R, 36)
+
+
 # ----------------------------------------------------------------------------- collectives
 def all_gather_lines(x_loc: torch.Tensor, world: int, group=None) -> torch.Tensor:
     """x_loc [G, R, L] (G groups: channels or heads) -> [G, world * R, L], rank-major along dim 1."""
@@ -184,13 +190,14 @@ class CudaOps:
     # ---- triangle attention
     def triattn_project(self, z_loc, mod, out=None):
         R, N, _ = z_loc.shape
-        ldn = _pitch(N, 64)
         dt, dev = z_loc.dtype, z_loc.device
         img = int(self.l.of3_dap_triattn_image_elems(R, N))  # opaque pre-swizzled operand tiles
         q = torch.empty(img, dtype=dt, device=dev)
         k = torch.empty(img, dtype=dt, device=dev)
         vt = torch.empty(img, dtype=dt, device=dev)
-        tb = torch.empty((4, R, ldn), dtype=dt, device=dev) if out is None else out.view(4, R, ldn)
+        shape = triattn_bias_shape(R, N)
+        assert shape[0] * shape[1] * shape[2] == int(self.l.of3_dap_triattn_bias_elems(R, N))
+        tb = torch.empty(shape, dtype=torch.float32, device=dev) if out is None else out.view(shape)
         p = lib.TriattnParams(*[t.data_ptr() for t in mod._params(dt, dev)])
         lib._check(self.l.of3_dap_triattn_project(z_loc.data_ptr(), q.data_ptr(), k.data_ptr(), vt.data_ptr(),
                                                   tb.data_ptr(), R, N, ctypes.byref(p), self._st()),
@@ -446,9 +453,10 @@ class PeerExchange:
     def heap_bytes(N: int, world: int, c_s: int = 384) -> int:
         """Bytes of peer heap one rank needs for a Pairformer trunk at N tokens (bf16)."""
         R = N // world
-        ld, ldn = _pitch(N, 8), _pitch(N, 64)
+        ld = _pitch(N, 8)
         ab = 2 * 128 * max(R * ld, N * _pitch(R, 8)) * 2
-        return 2 * R * N * 128 * 2 + ab + 128 * R * ld * 2 + 4 * R * ldn * 2 + 2 * R * c_s * 2 + 16 * 256 + 4096
+        g, r, w = triattn_bias_shape(R, N)
+        return 2 * R * N * 128 * 2 + ab + 128 * R * ld * 2 + g * r * w * 4 + 2 * R * c_s * 2 + 16 * 256 + 4096
 
 
 # ----------------------------------------------------------------------------- orchestration
@@ -489,7 +497,7 @@ class DapPairFormerStack:
     def _triattn(self, z_loc, mask_rows, mod):
         ops, X = self.ops, self.x
         R, N, _ = z_loc.shape
-        qkv, tb_loc = ops.triattn_project(z_loc, mod, out=X.buf("tb", (4, R, _pitch(N, 64)), z_loc.dtype, z_loc.device))
+        qkv, tb_loc = ops.triattn_project(z_loc, mod, out=X.buf("tb", triattn_bias_shape(R, N), torch.float32, z_loc.device))
         ops.triattn_finish(z_loc, mask_rows, qkv, X.gather_lines(tb_loc), mod)
 
     def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):

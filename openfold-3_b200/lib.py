@@ -70,6 +70,7 @@ SIGNATURES = {
                                             c_void_p]),
     "of3_dap_pitch": (c_int, [c_int, c_int]),
     "of3_dap_triattn_image_elems": (c_longlong, [c_int, c_int]),
+    "of3_dap_triattn_bias_elems": (c_longlong, [c_int, c_int]),
     "of3_dap_trimul_project": (c_int, [c_void_p] * 3 + [c_int] * 4 + [ctypes.POINTER(TrimulParams), c_void_p]),
     "of3_dap_trimul_contract": (c_int, [c_void_p] * 2 + [c_int] * 3 + [c_void_p]),
     "of3_dap_trimul_output": (c_int, [c_void_p] * 3 + [c_int] * 3 + [ctypes.POINTER(TrimulParams), c_void_p]),

@@ -177,9 +177,10 @@ def test_peer_heap_layout_fits_and_is_deterministic(world, n_token):
 
     dap = cases.pkg.dap
     R = n_token // world
-    ld, ldn = dap._pitch(n_token, 8), dap._pitch(n_token, 64)
+    ld = dap._pitch(n_token, 8)
+    tb = dap.triattn_bias_shape(R, n_token)
     requests = [("z0", R * n_token * 128 * 2), ("ab", 2 * 128 * max(R * ld, n_token * dap._pitch(R, 8)) * 2),
-                ("xb", 128 * R * ld * 2), ("tb", 4 * R * ldn * 2), ("z1", R * n_token * 128 * 2),
+                ("xb", 128 * R * ld * 2), ("tb", tb[0] * tb[1] * tb[2] * 4), ("z1", R * n_token * 128 * 2),
                 ("s0", R * 384 * 2), ("s1", R * 384 * 2)]
     layouts = []
     for rank in range(world):

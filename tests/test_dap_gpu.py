@@ -181,7 +181,7 @@ def _virtual_pair_block_peer(ops, X, z, mask, pb, P):
             ops.trimul_output(z[r], x_t[r], mod)
 
     def attn(zz, mm, mod):
-        proj = [ops.triattn_project(zz[r], mod, out=X[r].buf("tb", (4, R, dap._pitch(N, 64)), bf, dev)) for r in range(P)]
+        proj = [ops.triattn_project(zz[r], mod, out=X[r].buf("tb", dap.triattn_bias_shape(R, N), torch.float32, dev)) for r in range(P)]
         tb_all = [X[r].gather_lines(proj[r][1]) for r in range(P)]
         for r in range(P):
             ops.triattn_finish(zz[r], mm[r], proj[r][0], tb_all[r], mod)
