@@ -232,10 +232,11 @@ int of3_cond_transition_forward(const void* a, const void* s, const void* mask, 
  *   (all-to-all of the P blocks: x_t [128][R][ld(N)] = this rank's rows of every channel)
  *   output    LayerNorm_out(x) -> linear_z, sigmoid(linear_g(LayerNorm_in(z))) gate, residual, on z_rows.
  * Attention: z_rows, out_rows [R, N, 128]; mask_rows [R, N] or NULL; q, k, vt: opaque images of
- *   of3_dap_triattn_image_elems(R, N) elements each (pre-swizzled operand tiles); the pair bias is an
- *   fp32 image, pre-scaled by log2(e): bias_rows [4 heads][nkb = ceil(N / 32) key blocks][R query rows][36]
- *   (of3_dap_triattn_bias_elems(R, N) floats; 32 keys + 4 floats of row padding), bias_all the same with
- *   all N query rows [4][nkb][N][36]: an all-gather of the ranks' rows along the third index;
+ *   of3_dap_triattn_image_elems(R, N) elements each (pre-swizzled operand tiles); the pair bias is a
+ *   bf16 image, pre-scaled by log2(e): bias_rows [4 heads][nkb = ceil(N / 32) key blocks][R query rows][32]
+ *   (of3_dap_triattn_bias_elems(R, N) elements; each 64-byte row in tensor-core operand order, which
+ *   depends on the row's index among all N query rows: row0 = index of this rank's first row), bias_all the
+ *   same with all N query rows [4][nkb][N][32]: an all-gather of the ranks' rows along the third index;
  *   o_scratch [R, N, 128]. out_rows may alias z_rows. */
 int of3_dap_pitch(int N, int multiple);
 long long of3_dap_triattn_image_elems(int R, int N);
@@ -251,7 +252,7 @@ int of3_dap_trimul_output(const void* z_rows, void* out_rows, const void* x_t, i
  * all-to-all's rank-major blocks and the layouts the kernels read. */
 int of3_copy_rows_3d(const void* src, void* dst, int n0, int n1, int n2, long long s0, long long s1, long long s2,
                      long long t0, long long t1, long long t2, int row_bytes, void* stream);
-int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N,
+int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N, int row0,
                             const of3_triattn_params* p, void* stream);
 int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_rows, const void* q, const void* k,
                            const void* vt, const void* bias_all, void* o_scratch, int R, int N, float inf, int flags,

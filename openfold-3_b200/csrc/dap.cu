@@ -142,12 +142,14 @@ int of3_dap_trimul_output(const void* z_rows, void* out_rows, const void* x_t, i
                                (cudaStream_t)stream);
 }
 
-int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N,
+int of3_dap_triattn_project(const void* z_rows, void* q, void* k, void* vt, void* bias_rows, int R, int N, int row0,
                             const of3_triattn_params* p, void* stream) {
     OF3_REQUIRE(z_rows && q && k && vt && bias_rows && p, OF3_ERR_ARG, "dap_triattn_project: null pointer argument");
-    OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_triattn_project: non-positive size");
+    OF3_REQUIRE(R > 0 && N > 0 && row0 >= 0 && row0 + R <= N, OF3_ERR_ARG,
+                "dap_triattn_project: bad sizes R=%d N=%d row0=%d", R, N, row0);
     return fast::triattn_project((const __nv_bfloat16*)z_rows, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-                                 (__nv_bfloat16*)vt, (float*)bias_rows, 1, R, N, false, p, (cudaStream_t)stream);
+                                 (__nv_bfloat16*)vt, (__nv_bfloat16*)bias_rows, 1, R, N, row0, false, p,
+                                 (cudaStream_t)stream);
 }
 
 int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_rows, const void* q, const void* k,
@@ -158,7 +160,7 @@ int of3_dap_triattn_finish(const void* z_rows, const void* mask_rows, void* out_
     OF3_REQUIRE(R > 0 && N > 0, OF3_ERR_ARG, "dap_triattn_finish: non-positive size");
     return fast::triattn_finish((const __nv_bfloat16*)z_rows, (const __nv_bfloat16*)mask_rows,
                                 (__nv_bfloat16*)out_rows, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-                                (const __nv_bfloat16*)vt, (const float*)bias_all, (__nv_bfloat16*)o_scratch, 1, R,
+                                (const __nv_bfloat16*)vt, (const __nv_bfloat16*)bias_all, (__nv_bfloat16*)o_scratch, 1, R,
                                 N, inf, false, (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, (cudaStream_t)stream);
 }
 

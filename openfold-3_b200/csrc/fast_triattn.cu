@@ -78,10 +78,11 @@ struct ProjSmem {
 // slot 1: v and the 4-wide triangle bias). The bias projection is a fourth GEMM (N = 16 with 12 zero rows)
 // instead of 1024 FMAs per row inside the LayerNorm pass.
 constexpr int kProjThreads = 320;
-// Pair-bias image: fp32, pre-scaled by log2(e), [b*4 + head][key block of 32][query row][kTbPitch]. A query
-// tile's 128 rows of one key block are contiguous (one untiled bulk copy), and with a row pitch of 36 floats
-// (144 B) the 16-byte reads of eight consecutive rows fall into distinct shared-memory banks.
-constexpr int kTbPitch = 36;
+constexpr int kBiasK = 32;  // keys per bias row = keys per attention step
+// Pair-bias image: bf16, pre-scaled by log2(e), [b*4 + head][key block of 32][query row][32 keys]: the 128 rows
+// of a query tile and one key block are contiguous (one untiled bulk copy) and each 64-byte row is stored in the
+// 64-byte swizzle of a K-major tcgen05 A operand (16-byte chunk c of query row q at chunk c ^ ((q / 2) % 4)),
+// because the attention kernel adds the bias on the tensor pipe: S += bias_tile * I_32^T.
 
 template <bool kTransposed>
 __global__ void __launch_bounds__(kProjThreads, 1)
@@ -91,7 +92,7 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
                     const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
                     __nv_bfloat16* __restrict__ q_out,
                     __nv_bfloat16* __restrict__ k_out, __nv_bfloat16* __restrict__ vt_out,
-                    float* __restrict__ tb_out, int B, int R, int N, int npad, int* status) {
+                    __nv_bfloat16* __restrict__ tb_out, int B, int R, int N, int npad, int row0, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -297,10 +298,12 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(slot_empty(1));
             if (valid) {  // key padding [N, npad) is read by the attention kernel: zeros
+                // row0 = index of this shard's first line among all query rows (the swizzle follows the global row)
+                const int kc = (((pos & 31) >> 3) ^ (((row0 + tc.line) >> 1) & 3)) * 8 + (pos & 7);
 #pragma unroll
                 for (int h = 0; h < kH; ++h)
-                    tb_out[((((long long)tc.b * kH + h) * nkb + (pos >> 5)) * R + tc.line) * kTbPitch + (pos & 31)] =
-                        live ? __uint_as_float(tbr[h]) * kLog2e : 0.f;
+                    tb_out[((((long long)tc.b * kH + h) * nkb + (pos >> 5)) * R + tc.line) * kBiasK + kc] =
+                        __float2bfloat16_rn(live ? __uint_as_float(tbr[h]) * kLog2e : 0.f);
             }
         }
     }
@@ -319,8 +322,10 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 // One CTA = one head, 128 queries and TWO lines of the pair tensor, 32 keys per step; two CTAs share an SM
 // (their prologues, epilogues and waits interleave). Per line and step:
 //   MMA warp      S = Q K^T (128 x 32, K = 32) into one of two TMEM slots
-//   softmax warps thread = query row = TMEM lane: S -> registers, + pair bias (fp32 tile in shared memory,
-//                 one tile per step shared by both lines) [+ mask bias where the block has masked keys],
+//   MMA warp      S += Tb I^T: the pair-bias tile [128 q x 32 k] (bf16, shared by both lines) as the A operand
+//                 against a 32 x 32 identity: the tensor pipe adds the bias (a bf16 value times 1.0 accumulated in
+//                 fp32 is exact), the softmax threads never touch it
+//   softmax warps thread = query row = TMEM lane: S -> registers [+ mask bias where the block has masked keys],
 //                 row maximum, P = exp2(S - m) rounded to bf16 and written back to TMEM over the S slot
 //   MMA warp      O[128 x 48] += P V' with P read from TMEM as the A operand; V' is the V tile [32 d x 32 keys]
 //                 followed by 16 constant rows, the first of them all ones: column 32 of O is the row sum of
@@ -330,15 +335,21 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 // The running maximum m used for scaling is only raised when the row maximum exceeds it by more than 8
 // (2^8 head room in P): then, and only then, the thread rescales its O row (sum column included) in TMEM.
 // The result is exact: numerator and denominator always share one scale.
+#ifndef OF3_CORE_STAGES
+#define OF3_CORE_STAGES 4
+#endif
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 32;       // keys per step
 constexpr int kMaxKeys = 2048;   // one CTA keeps a mask-bias row per line in shared memory
-constexpr int kKvStages = 3;     // K / V ring (untiled bulk copies of pre-swizzled tiles): covers the load round trip
+constexpr int kKvStages = OF3_CORE_STAGES;     // K / V / bias ring (untiled bulk copies of pre-swizzled tiles): covers the load round trip
 constexpr int kLines = 2;     // lines per CTA
 constexpr int kLinePad = 4;   // the operand images pad the line count of a sample to a multiple of this
 constexpr int kCoreThreads = 32 * (1 + kLines + 4 * kLines);  // producer, one MMA warp per line, softmax
 constexpr float kRescaleThreshold = 8.0f;
-constexpr uint32_t kTbTileBytes = kBQ * kTbPitch * 4;  // 18432
+#ifndef OF3_CORE_POLY_PAIRS
+#define OF3_CORE_POLY_PAIRS 0
+#endif
+constexpr uint32_t kTbTileBytes = kBQ * kBiasK * 2;    // 8192
 constexpr uint32_t kVSlot = 3072;                      // V tile (2 KB) + 16 constant rows of 64 B
 constexpr int kON = 48;                                // N of the P V GEMM: 32 output channels + the row-sum column (+ 15 unused)
 
@@ -346,8 +357,9 @@ struct CoreSmem {
     static constexpr uint32_t kQ = 0;                                   // lines x 8 KB
     static constexpr uint32_t kK = kQ + kLines * 8192;                  // stages x lines x 2 KB
     static constexpr uint32_t kV = kK + kKvStages * kLines * 2048;      // stages x lines x 3 KB
-    static constexpr uint32_t kTb = kV + kKvStages * kLines * kVSlot;   // 2 x 18 KB: bias tiles [128 q][36] fp32
-    static constexpr uint32_t kBars = kTb + 2 * kTbTileBytes;
+    static constexpr uint32_t kTb = kV + kKvStages * kLines * kVSlot;   // stages x 8 KB: bias tiles [128 q][32 k] bf16
+    static constexpr uint32_t kIdent = kTb + kKvStages * kTbTileBytes;  // 2 KB: 32 x 32 identity (B operand)
+    static constexpr uint32_t kBars = kIdent + 2048;
     static constexpr uint32_t kFlags = kBars + 256;                     // lines x 128 block flags (bytes)
     static constexpr uint32_t kMb = kFlags + kLines * 128;              // lines x nkeys_pad floats
     static uint32_t dyn_bytes(int nblk) { return kMb + kLines * nblk * kBK * 4 + 1024; }
@@ -383,10 +395,44 @@ __device__ __forceinline__ void add2(float& x0, float& x1, float y0, float y1) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(a));
 }
 
+// (x0, x1) = (x0, x1) * (y0, y1) + (z0, z1), packed
+__device__ __forceinline__ void fma2(float& x0, float& x1, float y0, float y1, float z0, float z1) {
+    unsigned long long a, b, c;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x0), "f"(x1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(y0), "f"(y1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(z0), "f"(z1));
+    asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(a) : "l"(b), "l"(c));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(a));
+}
+// 2^x for a pair of arguments x <= ~100 on the FMA / ALU pipes (no MUFU): round-to-nearest split x = n + f with
+// the 1.5 * 2^23 trick, a cubic for 2^f on [-0.5, 0.5] (relative error 7.7e-5, far below the bf16 rounding
+// of P), and n added into the exponent field. Arguments below -126 (masked keys, -inf padding) give 2^-126.
+// The MUFU unit delivers 16 exp2 per clock and SM and shares its issue queue with shared-memory, TMEM
+// and mbarrier operations; at a head dimension of 32 it is the busiest unit of this kernel, so a share of
+// the exponentials is computed here instead.
+__device__ __forceinline__ void exp2_poly2(float& x0, float& x1) {
+    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.0f);
+    x1 = fmaxf(x1, -126.0f);
+    float t0 = x0, t1 = x1;
+    add2(t0, t1, kMagic, kMagic);             // low mantissa bits of t = round(x)
+    float n0 = t0, n1 = t1;
+    add2(n0, n1, -kMagic, -kMagic);           // round(x) as a float
+    fma2(n0, n1, -1.0f, -1.0f, x0, x1);       // f = x - round(x)
+    float p0 = 0.05508868396282196f, p1 = 0.05508868396282196f;
+    fma2(p0, p1, n0, n1, 0.24260404706001282f, 0.24260404706001282f);
+    fma2(p0, p1, n0, n1, 0.6932762265205383f, 0.6932762265205383f);
+    fma2(p0, p1, n0, n1, 0.9999289512634277f, 0.9999289512634277f);
+    x0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
+    x1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
+}
+// pairs (of each group of four pairs) whose exponentials run on the FMA pipe
+constexpr int kPolyPairsOf4 = OF3_CORE_POLY_PAIRS;
+
 template <bool kTransposed>
 __global__ void __launch_bounds__(kCoreThreads, 2)
 triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16* __restrict__ k_img,
-                    const __nv_bfloat16* __restrict__ v_img, const float* __restrict__ tb_img,
+                    const __nv_bfloat16* __restrict__ v_img, const __nv_bfloat16* __restrict__ tb_img,
                     const __nv_bfloat16* __restrict__ mask, __nv_bfloat16* __restrict__ o_out, int B,
                     int R, int N, int npad, float inf, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -396,11 +442,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     volatile uint8_t* mbflag = gbase + CoreSmem::kFlags;
     const uint32_t bars = sbase + CoreSmem::kBars;
     const uint32_t q_full = bars;
-    constexpr int kB0 = 1 + 2 * kKvStages + 4;
+    constexpr int kB0 = 1 + 2 * kKvStages;
     auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
     auto kv_empty = [&](int s) { return bars + 8u * (1 + kKvStages + s); };
-    auto tb_full = [&](int s) { return bars + 8u * (1 + 2 * kKvStages + s); };
-    auto tb_empty = [&](int s) { return bars + 8u * (3 + 2 * kKvStages + s); };
     auto s_full = [&](int L, int s) { return bars + 8u * (kB0 + L * 2 + s); };
     auto p_ready = [&](int L, int s) { return bars + 8u * (kB0 + 2 * kLines + L * 2 + s); };
     auto pv_done = [&](int L, int s) { return bars + 8u * (kB0 + 4 * kLines + L * 2 + s); };
@@ -429,8 +473,6 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             mbar_init(kv_empty(s), kLines);  // each line's commit after the P V that read the stage
         }
         for (int s = 0; s < 2; ++s) {
-            mbar_init(tb_full(s), 1);
-            mbar_init(tb_empty(s), 4 * kLines);  // every softmax warp has read its rows of the bias tile
             for (int L = 0; L < kLines; ++L) {
                 mbar_init(s_full(L, s), 1);
                 mbar_init(p_ready(L, s), 4);
@@ -462,6 +504,16 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         const uint32_t v = (w16 < 4) ? 0x3F803F80u : 0u;
         *reinterpret_cast<uint4*>(gbase + CoreSmem::kV + slot * kVSlot + 2048 + w16 * 16) = make_uint4(v, v, v, v);
     }
+    // 32 x 32 identity, bf16, K-major with the 64-byte swizzle: element (n, n) of row n
+    for (int idx = threadIdx.x; idx < 32 * 16; idx += blockDim.x) {
+        const int n = idx >> 4, w = idx & 15;  // row, 32-bit word of the row (2 elements)
+        const int k = w * 2;                   // first element of the word
+        uint32_t v = 0;
+        if (k == n) v = 0x00003F80u;
+        if (k + 1 == n) v = 0x3F800000u;
+        const int chunk = (k >> 3) ^ ((n >> 1) & 3);
+        *reinterpret_cast<uint32_t*>(gbase + CoreSmem::kIdent + n * 64 + chunk * 16 + (w & 3) * 4) = v;
+    }
     fence_proxy_async_smem();
     if (warp == 1) {
         tmem_alloc(smem_u32((const void*)tmem_ptr), kLines * 128);
@@ -490,72 +542,78 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             bulk_load(sbase + CoreSmem::kQ, q_img + (((bh * n_qt + qt) * rpad + line0) * kBQ) * kD, kLines * kBQ * 64,
                       q_full);
             const int q_rows = (N - q0 < kBQ) ? N - q0 : kBQ;  // rows of the bias tile that exist
-            const uint32_t tb_bytes = (uint32_t)q_rows * kTbPitch * 4;
+            const uint32_t tb_bytes = (uint32_t)q_rows * kBiasK * 2;
             for (int j = 0; j < nblk; ++j) {
                 const int s = j % kKvStages;
                 if (!mbar_wait(kv_empty(s), ((j / kKvStages) & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidCore, 1);
                     break;
                 }
-                mbar_arrive_expect_tx(kv_full(s), kLines * 4096);
+                mbar_arrive_expect_tx(kv_full(s), kLines * 4096 + tb_bytes);
                 const long long tile0 = ((bh * nkb + j) * rpad + line0) << 10;  // first of the lines' tiles
                 bulk_load(sbase + CoreSmem::kK + s * kLines * 2048, k_img + tile0, kLines * 2048, kv_full(s));
+                // pair-bias tile of key block j (all lines of the CTA share it)
+                bulk_load(sbase + CoreSmem::kTb + s * kTbTileBytes,
+                          tb_img + ((bh * nkb + j) * (long long)N + q0) * kBiasK, tb_bytes, kv_full(s));
                 for (int L = 0; L < kLines; ++L)
                     bulk_load(sbase + CoreSmem::kV + (s * kLines + L) * kVSlot, v_img + tile0 + L * 1024, 2048,
                               kv_full(s));
-                // pair-bias tile of key block j (all lines of the CTA share it)
-                const int ts = j & 1;
-                if (!mbar_wait(tb_empty(ts), ((j >> 1) & 1u) ^ 1u, abort_flag)) {
-                    report_wait_failure(status, abort_flag, kKidCore, 11);
-                    break;
-                }
-                mbar_arrive_expect_tx(tb_full(ts), tb_bytes);
-                bulk_load(sbase + CoreSmem::kTb + ts * kTbTileBytes,
-                          tb_img + ((bh * nkb + j) * (long long)N + q0) * kTbPitch, tb_bytes,
-                          tb_full(ts));
             }
         }
     } else if (warp <= kLines) {
         // ---------------------------------------------------------------- one MMA-issuing warp per line
-        if (lane == 0) {
-            const int L = warp - 1;
-            constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);  // S: 128 x 32, K = 32
-            constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 48, K = 32
-            bool ok = mbar_wait(q_full, 0, abort_flag);
-            if (!ok) report_wait_failure(status, abort_flag, kKidCore, 2);
-            const uint64_t qdesc = smem_desc_k_sw64(sbase + CoreSmem::kQ + L * 8192);
-            const uint32_t t_line = tmem_base + L * 128;
-            const uint32_t d_o = t_line + 64;
-            for (int j = 0; j <= nblk && ok; ++j) {
-                if (j < nblk) {  // S_j = Q K_j^T; its slot was last read by P_{j-2} V_{j-2}, issued before this
-                    const int s = j & 1;
-                    const int ks = j % kKvStages;
-                    if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
-                        report_wait_failure(status, abort_flag, kKidCore, 3);
-                        break;
-                    }
-                    const uint64_t kdesc = smem_desc_k_sw64(sbase + CoreSmem::kK + (ks * kLines + L) * 2048);
-                    const uint32_t d = t_line + s * kBK;
+        // The whole warp walks the loop and lane 0 issues: with warp-uniform control flow and operands (the
+        // shuffles tell the compiler so) descriptors and addresses live in uniform registers, instead of being
+        // moved there one by one in front of every tcgen05.mma of a single-lane loop.
+        const int L = __shfl_sync(0xffffffffu, warp, 0) - 1;
+        const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
+        const uint32_t sb = __shfl_sync(0xffffffffu, sbase, 0);
+        constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);  // S: 128 x 32, K = 32
+        constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 48, K = 32
+        bool ok = mbar_wait(q_full, 0, abort_flag);
+        if (!ok && lane == 0) report_wait_failure(status, abort_flag, kKidCore, 2);
+        const uint64_t qdesc = smem_desc_k_sw64(sb + CoreSmem::kQ + L * 8192);
+        const uint64_t identdesc = smem_desc_k_sw64(sb + CoreSmem::kIdent);
+        const uint32_t t_line = tm + L * 128;
+        const uint32_t d_o = t_line + 64;
+        for (int j = 0; j <= nblk && ok; ++j) {
+            if (j < nblk) {  // S_j = Q K_j^T + Tb_j; its slot was last read by P_{j-2} V_{j-2}, issued before this
+                const int s = j & 1;
+                const int ks = j % kKvStages;
+                if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 3);
+                    break;
+                }
+                const uint64_t kdesc = smem_desc_k_sw64(sb + CoreSmem::kK + (ks * kLines + L) * 2048);
+                const uint64_t tbdesc = smem_desc_k_sw64(sb + CoreSmem::kTb + ks * kTbTileBytes);
+                const uint32_t d = t_line + s * kBK;
+                if (lane == 0) {
                     mma_bf16(d, qdesc, kdesc, idesc_s, 0u);
                     mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
+                    mma_bf16(d, tbdesc, identdesc, idesc_s, 1u);            // + pair bias
+                    mma_bf16(d, tbdesc + 2u, identdesc + 2u, idesc_s, 1u);
                     mma_commit(s_full(L, s));
                 }
-                if (j >= 1) {  // O += P_{j-1} V'_{j-1}
-                    const int jj = j - 1;
-                    const int s = jj & 1;
-                    const int ks = jj % kKvStages;
-                    if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag)) {
-                        report_wait_failure(status, abort_flag, kKidCore, 5);
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const uint32_t a_p = t_line + s * kBK;  // P: 16 columns of packed bf16 pairs
-                    const uint64_t vdesc = smem_desc_k_sw64(sbase + CoreSmem::kV + (ks * kLines + L) * kVSlot);
+                __syncwarp();
+            }
+            if (j >= 1) {  // O += P_{j-1} V'_{j-1}
+                const int jj = j - 1;
+                const int s = jj & 1;
+                const int ks = jj % kKvStages;
+                if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 5);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t a_p = t_line + s * kBK;  // P: 16 columns of packed bf16 pairs
+                const uint64_t vdesc = smem_desc_k_sw64(sb + CoreSmem::kV + (ks * kLines + L) * kVSlot);
+                if (lane == 0) {
                     mma_bf16_ts(d_o, a_p, vdesc, idesc_o, jj != 0 ? 1u : 0u);
                     mma_bf16_ts(d_o, a_p + 8u, vdesc + 2u, idesc_o, 1u);
                     mma_commit(pv_done(L, s));
                     mma_commit(kv_empty(ks));
                 }
+                __syncwarp();
             }
         }
     } else {
@@ -567,8 +625,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         const bool line_valid = line0 + L < R;
         const long long bl = (long long)b * R + line_of(L);
         const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 128;
-        const uint32_t tb_row = sbase + CoreSmem::kTb + (uint32_t)row * (kTbPitch * 4);
         const float* mbl = mbs + L * nkp;
+        unsigned long long mflags = 0ull;  // bit j: key block j of this line has a masked (or padding) key
+        for (int jj = 0; jj < nblk; ++jj) mflags |= (unsigned long long)mbflag[L * 128 + jj] << jj;
         float m_used = 0.f;
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
@@ -588,25 +647,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
 #pragma unroll
                 for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r0[e]);
             }
-            if (!mbar_wait(tb_full(s), ph, abort_flag)) {
-                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 6);
-                ok = false;
-                break;
-            }
-            {   // + pair bias: this row's 32 fp32 values of the shared tile
-                const uint32_t tba = tb_row + s * kTbTileBytes;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const uint4 w = lds128(tba + i * 16);
-                    add2(sv[i * 4], sv[i * 4 + 1], __uint_as_float(w.x), __uint_as_float(w.y));
-                    add2(sv[i * 4 + 2], sv[i * 4 + 3], __uint_as_float(w.z), __uint_as_float(w.w));
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(tb_empty(s));
             // + mask bias (blocks without a masked key skip it): (q.k + pair bias) + inf * (mask - 1); a masked
-            // key ends at -inf-like 1.44e9 either way, an unmasked one adds exactly 0
-            if (mbflag[L * 128 + j]) {
+            // key ends at the same -1.44e9 in either order of the two additions, an unmasked one adds exactly 0
+            if ((mflags >> j) & 1ull) {
                 const int k0 = j * kBK;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -654,7 +697,12 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
 #pragma unroll
             for (int e = 0; e < 32; e += 2) {
                 add2(sv[e], sv[e + 1], nm, nm);
-                pk[e >> 1] = pack_bf16x2(ex2_approx(sv[e]), ex2_approx(sv[e + 1]));
+                if (((e >> 1) & 3) < kPolyPairsOf4) {
+                    exp2_poly2(sv[e], sv[e + 1]);
+                    pk[e >> 1] = pack_bf16x2(sv[e], sv[e + 1]);
+                } else {
+                    pk[e >> 1] = pack_bf16x2(ex2_approx(sv[e]), ex2_approx(sv[e + 1]));
+                }
             }
             tmem_st16(trow + s * kBK, pk);
             tmem_st_wait();
@@ -985,7 +1033,7 @@ int set_attrs() {
 
 template <bool kT>
 int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
-                 float* tb, int B, int R, int N, const of3_triattn_params* p, cudaStream_t st) {
+                 __nv_bfloat16* tb, int B, int R, int N, int row0, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
     CUtensorMap tmZ, tmW[3], tmWb;
     if ((rc = z_tmap(&tmZ, z, B, R, N, kT))) return rc;
@@ -1005,14 +1053,14 @@ int project_impl(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __n
     LaunchScope scope(kKidProj, st);
     triattn_proj_kernel<kT><<<grid, kProjThreads, ProjSmem::kDyn, st>>>(
         tmZ, tmW[0], tmW[1], tmW[2], tmWb, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, q, k, vt,
-        tb, B, R, N, (int)align_up(N, kBK), device_status_ptr());
+        tb, B, R, N, (int)align_up(N, kBK), row0, device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
 
 template <bool kT>
 int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out, const __nv_bfloat16* q,
-                const __nv_bfloat16* k, const __nv_bfloat16* vt, const float* tb, __nv_bfloat16* o, int B,
+                const __nv_bfloat16* k, const __nv_bfloat16* vt, const __nv_bfloat16* tb, __nv_bfloat16* o, int B,
                 int R, int N, float inf, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
     int rc;
     CUtensorMap tmZ, tmOut, tmO, tmWg, tmWo;
@@ -1060,27 +1108,28 @@ size_t triattn_image_elems(int B, int R, int N) {
     return (size_t)B * kH * ceil_div(N, kBQ) * align_up(R, kLinePad) * kBQ * kD;
 }
 
-// Floats of the pair-bias image of B samples with R query rows and N keys: [B*4][key blocks of 32][R][36].
+// Elements (bf16) of the pair-bias image of B samples with R query rows and N keys: [B*4][key blocks of 32][R][32].
 size_t triattn_bias_elems(int B, int R, int N) {
-    return (size_t)B * kH * ceil_div(N, kBK) * R * kTbPitch;
+    return (size_t)B * kH * ceil_div(N, kBK) * R * kBiasK;
 }
 
-// q, k, v operand images and this shard's rows of the pair-bias image tb[(b*H + h)][key block][line][36]
-// (fp32) from R lines of N positions. transposed: whole square tensors only.
+// q, k, v operand images and this shard's rows of the pair-bias image tb[(b*H + h)][key block][line][32]
+// from R lines of N positions; row0 = index of the shard's first line among all N query rows (0 for a whole
+// tensor). transposed: whole square tensors only.
 int triattn_project(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
-                    float* tb, int B, int R, int N, bool transposed,
+                    __nv_bfloat16* tb, int B, int R, int N, int row0, bool transposed,
                     const of3_triattn_params* p, cudaStream_t st) {
     OF3_REQUIRE(((uintptr_t)z & 15) == 0, OF3_ERR_ALIGN, "triattn: z must be 16-byte aligned");
     OF3_REQUIRE(!transposed || R == N, OF3_ERR_SHAPE, "triattn: transposed view needs the whole tensor");
-    return transposed ? project_impl<true>(z, q, k, vt, tb, B, R, N, p, st)
-                      : project_impl<false>(z, q, k, vt, tb, B, R, N, p, st);
+    return transposed ? project_impl<true>(z, q, k, vt, tb, B, R, N, row0, p, st)
+                      : project_impl<false>(z, q, k, vt, tb, B, R, N, row0, p, st);
 }
 
-// attention over the R lines with the pair-bias image of all N query rows (tb [(b*H + h)][key block][N][36]),
+// attention over the R lines with the pair-bias image of all N query rows (tb [(b*H + h)][key block][N][32]),
 // gate, output projection, residual.
 int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
                    const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
-                   const float* tb, __nv_bfloat16* o, int B, int R, int N, float inf,
+                   const __nv_bfloat16* tb, __nv_bfloat16* o, int B, int R, int N, float inf,
                    bool transposed, int add_residual, const of3_triattn_params* p, cudaStream_t st) {
     OF3_REQUIRE(((uintptr_t)tb & 15) == 0, OF3_ERR_ALIGN, "triattn: the pair-bias image must be 16-byte aligned");
     OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)out & 15) == 0, OF3_ERR_ALIGN,
@@ -1100,11 +1149,11 @@ int triattn(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* ou
     __nv_bfloat16* k = (__nv_bfloat16*)ws.take(img);
     __nv_bfloat16* vt = (__nv_bfloat16*)ws.take(img);
     __nv_bfloat16* o = (__nv_bfloat16*)ws.take(plane);
-    float* tb = (float*)ws.take(triattn_bias_elems(B, N, N) * sizeof(float));
+    __nv_bfloat16* tb = (__nv_bfloat16*)ws.take(triattn_bias_elems(B, N, N) * sizeof(__nv_bfloat16));
     if (!ws.base) return OF3_OK;
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "triattn: workspace too small (%zu needed)", ws.off);
     const bool tr = (flags & OF3_FLAG_TRANSPOSED) != 0;
-    int rc = triattn_project(z, q, k, vt, tb, B, N, N, tr, p, st);
+    int rc = triattn_project(z, q, k, vt, tb, B, N, N, 0, tr, p, st);
     if (rc) return rc;
     return triattn_finish(z, mask, out, q, k, vt, tb, o, B, N, N, inf, tr,
                           (flags & OF3_FLAG_ADD_RESIDUAL) ? 1 : 0, p, st);

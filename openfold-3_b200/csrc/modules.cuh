@@ -47,13 +47,13 @@ int trimul_finish(const __nv_bfloat16* z, __nv_bfloat16* out, const __nv_bfloat1
                   const __nv_bfloat16* b_t, __nv_bfloat16* x_t, int B, int R, int N, int ld, int add_residual,
                   const of3_trimul_params* p, cudaStream_t st);
 size_t triattn_image_elems(int B, int R, int N);
-size_t triattn_bias_elems(int B, int R, int N);  // floats of the pair-bias image [B*4][key blocks][R][36]
+size_t triattn_bias_elems(int B, int R, int N);  // bf16 elements of the pair-bias image [B*4][key blocks][R][32]
 int triattn_project(const __nv_bfloat16* z, __nv_bfloat16* q, __nv_bfloat16* k, __nv_bfloat16* vt,
-                    float* tb, int B, int R, int N, bool transposed,
+                    __nv_bfloat16* tb, int B, int R, int N, int row0, bool transposed,
                     const of3_triattn_params* p, cudaStream_t st);
 int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16* out,
                    const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* vt,
-                   const float* tb, __nv_bfloat16* o, int B, int R, int N, float inf,
+                   const __nv_bfloat16* tb, __nv_bfloat16* o, int B, int R, int N, float inf,
                    bool transposed, int add_residual, const of3_triattn_params* p, cudaStream_t st);
 bool transition_supported(int c, int n);
 int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows,

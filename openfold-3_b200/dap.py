@@ -43,9 +43,9 @@ def _pitch(n: int, m: int) -> int:
 
 
 def triattn_bias_shape(R: int, N: int) -> tuple:
-    """Shape (fp32) of the triangle-attention pair-bias image of R query rows and N keys: [4 heads x key
-    blocks of 32][R][36] -- 32 keys + 4 floats of row padding (of3_dap_triattn_bias_elems in the library)."""
-    return (4 * ((N + 31) // 32), R, 36)
+    """Shape (bf16) of the triangle-attention pair-bias image of R query rows and N keys: [4 heads x key
+    blocks of 32][R][32] (of3_dap_triattn_bias_elems in the library)."""
+    return (4 * ((N + 31) // 32), R, 32)
 
 
 # ----------------------------------------------------------------------------- collectives
@@ -188,7 +188,8 @@ class CudaOps:
                    "of3_dap_trimul_output")
 
     # ---- triangle attention
-    def triattn_project(self, z_loc, mod, out=None):
+    def triattn_project(self, z_loc, mod, out=None, row0=0):
+        """row0: index of z_loc's first line among the N lines of the (possibly transposed) pair tensor."""
         R, N, _ = z_loc.shape
         dt, dev = z_loc.dtype, z_loc.device
         img = int(self.l.of3_dap_triattn_image_elems(R, N))  # opaque pre-swizzled operand tiles
@@ -197,10 +198,10 @@ class CudaOps:
         vt = torch.empty(img, dtype=dt, device=dev)
         shape = triattn_bias_shape(R, N)
         assert shape[0] * shape[1] * shape[2] == int(self.l.of3_dap_triattn_bias_elems(R, N))
-        tb = torch.empty(shape, dtype=torch.float32, device=dev) if out is None else out.view(shape)
+        tb = torch.empty(shape, dtype=dt, device=dev) if out is None else out.view(shape)
         p = lib.TriattnParams(*[t.data_ptr() for t in mod._params(dt, dev)])
         lib._check(self.l.of3_dap_triattn_project(z_loc.data_ptr(), q.data_ptr(), k.data_ptr(), vt.data_ptr(),
-                                                  tb.data_ptr(), R, N, ctypes.byref(p), self._st()),
+                                                  tb.data_ptr(), R, N, row0, ctypes.byref(p), self._st()),
                    "of3_dap_triattn_project")
         return (q, k, vt), tb
 
@@ -456,7 +457,7 @@ class PeerExchange:
         ld = _pitch(N, 8)
         ab = 2 * 128 * max(R * ld, N * _pitch(R, 8)) * 2
         g, r, w = triattn_bias_shape(R, N)
-        return 2 * R * N * 128 * 2 + ab + 128 * R * ld * 2 + g * r * w * 4 + 2 * R * c_s * 2 + 16 * 256 + 4096
+        return 2 * R * N * 128 * 2 + ab + 128 * R * ld * 2 + g * r * w * 2 + 2 * R * c_s * 2 + 16 * 256 + 4096
 
 
 # ----------------------------------------------------------------------------- orchestration
@@ -497,7 +498,8 @@ class DapPairFormerStack:
     def _triattn(self, z_loc, mask_rows, mod):
         ops, X = self.ops, self.x
         R, N, _ = z_loc.shape
-        qkv, tb_loc = ops.triattn_project(z_loc, mod, out=X.buf("tb", triattn_bias_shape(R, N), torch.float32, z_loc.device))
+        qkv, tb_loc = ops.triattn_project(z_loc, mod, out=X.buf("tb", triattn_bias_shape(R, N), z_loc.dtype, z_loc.device),
+                                          row0=self.rank * R)
         ops.triattn_finish(z_loc, mask_rows, qkv, X.gather_lines(tb_loc), mod)
 
     def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):

@@ -78,7 +78,7 @@ SIGNATURES = {
     "of3_attn_pair_bias_rows_workspace_bytes": (c_size_t, [c_int] * 3),
     "of3_attn_pair_bias_forward_rows": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_float, c_int, c_int,
                                                 ctypes.POINTER(AttnPairBiasParams), c_void_p, c_size_t, c_void_p]),
-    "of3_dap_triattn_project": (c_int, [c_void_p] * 5 + [c_int, c_int, ctypes.POINTER(TriattnParams), c_void_p]),
+    "of3_dap_triattn_project": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, ctypes.POINTER(TriattnParams), c_void_p]),
     "of3_dap_triattn_finish": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_int,
                                        ctypes.POINTER(TriattnParams), c_void_p]),
     "of3_pair_bias_project": (c_int, [c_void_p] * 5 + [c_longlong, c_int, c_int, c_int, c_void_p]),

@@ -69,7 +69,7 @@ class OracleOps:
         g = torch.sigmoid(o._lin(o._ln(z_loc, P, "layer_norm_in.", z_loc.shape[-1]), P, "linear_g."))
         z_loc += x * g
 
-    def triattn_project(self, z_loc, mod, out=None):
+    def triattn_project(self, z_loc, mod, out=None, row0=0):
         P, o = self._P(mod), self.o
         N = z_loc.shape[1]
         xn = o._ln(z_loc, P, "layer_norm.", z_loc.shape[-1])
@@ -180,7 +180,7 @@ def test_peer_heap_layout_fits_and_is_deterministic(world, n_token):
     ld = dap._pitch(n_token, 8)
     tb = dap.triattn_bias_shape(R, n_token)
     requests = [("z0", R * n_token * 128 * 2), ("ab", 2 * 128 * max(R * ld, n_token * dap._pitch(R, 8)) * 2),
-                ("xb", 128 * R * ld * 2), ("tb", tb[0] * tb[1] * tb[2] * 4), ("z1", R * n_token * 128 * 2),
+                ("xb", 128 * R * ld * 2), ("tb", tb[0] * tb[1] * tb[2] * 2), ("z1", R * n_token * 128 * 2),
                 ("s0", R * 384 * 2), ("s1", R * 384 * 2)]
     layouts = []
     for rank in range(world):

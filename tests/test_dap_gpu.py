@@ -36,12 +36,12 @@ def _virtual_pair_block(ops, shards, mask, pb, P):
         x_t = _exchange(xb) if P > 1 else xb
         for r in range(P):
             ops.trimul_output(shards[r], x_t[r], mod)
-    proj = [ops.triattn_project(shards[r], pb.tri_att_start) for r in range(P)]
+    proj = [ops.triattn_project(shards[r], pb.tri_att_start, row0=r * R) for r in range(P)]
     tb_all = gather([p[1] for p in proj])
     for r in range(P):
         ops.triattn_finish(shards[r], mrow[r], proj[r][0], tb_all, pb.tri_att_start)
     zT = transpose_all(shards)
-    proj = [ops.triattn_project(zT[r], pb.tri_att_end) for r in range(P)]
+    proj = [ops.triattn_project(zT[r], pb.tri_att_end, row0=r * R) for r in range(P)]
     tb_all = gather([p[1] for p in proj])
     for r in range(P):
         ops.triattn_finish(zT[r], mcol[r], proj[r][0], tb_all, pb.tri_att_end)
@@ -181,7 +181,7 @@ def _virtual_pair_block_peer(ops, X, z, mask, pb, P):
             ops.trimul_output(z[r], x_t[r], mod)
 
     def attn(zz, mm, mod):
-        proj = [ops.triattn_project(zz[r], mod, out=X[r].buf("tb", dap.triattn_bias_shape(R, N), torch.float32, dev)) for r in range(P)]
+        proj = [ops.triattn_project(zz[r], mod, out=X[r].buf("tb", dap.triattn_bias_shape(R, N), bf, dev), row0=r * R) for r in range(P)]
         tb_all = [X[r].gather_lines(proj[r][1]) for r in range(P)]
         for r in range(P):
             ops.triattn_finish(zz[r], mm[r], proj[r][0], tb_all[r], mod)
