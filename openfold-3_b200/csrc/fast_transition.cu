@@ -26,14 +26,6 @@ constexpr int kHidden = 512;
 constexpr int kChunk = 64;
 constexpr int kNumChunks = kHidden / kChunk;  // 8
 
-#ifdef OF3_CORE_TIMING
-__device__ long long g_tr_dbg[32];
-#define TDBG_T(var) const long long var = clock64()
-#define TDBG_ADD(slot, a, b) do { if (tdbg) atomicAdd((unsigned long long*)&g_tr_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
-#else
-#define TDBG_T(var)
-#define TDBG_ADD(slot, a, b)
-#endif
 
 struct TrSmem {
     static constexpr uint32_t kWStage = 49152;                 // [Wa|Wb] slab 32 KB + Wout chunk 16 KB
@@ -177,9 +169,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 report_wait_failure(status, abort_flag, kKidTrans, site);
                 ok = false;
             };
-#ifdef OF3_CORE_TIMING
-            const bool tdbg = blockIdx.x == 40 && g == 0;
-#endif
             // Software-pipelined per tile: G1 of chunk c+1 is issued as soon as the row group has read D1 of
             // chunk c, BEFORE waiting for that chunk's silu pass and its G2, so the row group finds its next
             // accumulator ready when it comes back (the serial G2 -> weights -> G1 hop cost ~1900 cycles per chunk).
@@ -212,10 +201,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 for (int c = 0; c < kNumChunks && ok; ++c, ++wi) {
                     const int s = wi & 1;
                     const uint32_t cpar = (uint32_t)c & 1u;  // 8 chunks per tile: chunk parity is global
-                    TDBG_T(m0);
                     if (c + 1 < kNumChunks && !issue_g1(wi + 1, c + 1)) break;
-                    TDBG_T(m2);
-                    TDBG_ADD(17, m0, m2);
                     if (c == 0 && !mbar_wait(d2_empty(g), ppar ^ 1u, abort_flag)) { fail(6); break; }
                     if (!mbar_wait(wo_full(s), (wi >> 1) & 1u, abort_flag)) { fail(13); break; }
                     if (!mbar_wait(h_ready(g), cpar, abort_flag)) { fail(7); break; }
@@ -229,9 +215,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     mma_commit(h_free(g));
                     if (c == kNumChunks - 1) mma_commit(d2_full(g));
                     mma_commit(wo_empty(s));
-                    TDBG_T(m3);
-                    TDBG_ADD(18, m2, m3);
-                    TDBG_ADD(19, m0, m0 + 1);
                 }
             }
         }
@@ -246,19 +229,14 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         const uint32_t t_d1 = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
         const uint32_t t_d2 = t_d1 + 128;
         bool ok = true;
-#ifdef OF3_CORE_TIMING
-        const bool tdbg = blockIdx.x == 40 && gtid == 0 && g == 0;
-#endif
         for (long long pi = 0; pi * 2 + g < my_tiles && ok; ++pi) {
             const uint32_t ppar = (uint32_t)pi & 1u;
             const long long tile = blockIdx.x + (pi * 2 + g) * gridDim.x;
             const long long grow = tile * kRows + row;
-            TDBG_T(r0);
             if (!mbar_wait(x_full(g), ppar, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 8);
                 break;
             }
-            TDBG_T(r1);
             uint32_t raw[64];
             load_row(xtile, row, raw);
             {
@@ -269,22 +247,17 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(g));
-            TDBG_T(r2);
-            TDBG_ADD(0, r0, r1);
-            TDBG_ADD(1, r1, r2);
             float m = 1.0f;
             if (mask != nullptr && grow < rows) m = __bfloat162float(mask[grow]);
 
             for (int c = 0; c < kNumChunks; ++c) {
                 const uint32_t cpar = (uint32_t)c & 1u;
-                TDBG_T(c0);
                 if (!mbar_wait(d1_full(g), cpar, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 9);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-                TDBG_T(c1);
                 uint32_t hpk[32];  // 64 hidden values of this row, packed bf16x2
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
@@ -303,7 +276,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(d1_empty(g));
-                TDBG_T(c2);
                 // the previous chunk's G2 must have consumed the H buffer before it is overwritten
                 if (!mbar_wait(h_free(g), cpar ^ 1u, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 10);
@@ -314,18 +286,11 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 for (int ch = 0; ch < 8; ++ch)
                     sts128(chunk_addr(htile, row, ch),
                            make_uint4(hpk[ch * 4], hpk[ch * 4 + 1], hpk[ch * 4 + 2], hpk[ch * 4 + 3]));
-                TDBG_T(c3);
                 fence_proxy_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(h_ready(g));
-                TDBG_T(c4);
-                TDBG_ADD(2, c0, c1);
-                TDBG_ADD(3, c1, c2);
-                TDBG_ADD(4, c2, c3);
-                TDBG_ADD(5, c3, c4);
             }
             if (!ok) break;
-            TDBG_T(r3);
             if (!mbar_wait(d2_full(g), ppar, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 11);
                 break;
@@ -366,10 +331,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 tma_store_wait_read<0>();
                 mbar_arrive(x_empty(g));
             }
-            TDBG_T(r4);
-            TDBG_ADD(6, r3, r4);
-            TDBG_ADD(7, r0, r4);
-            TDBG_ADD(8, r0, r0 + 1);
         }
         if (gtid == 0) tma_store_wait_all<0>();
     }
@@ -384,12 +345,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
 
 }  // namespace
 
-#ifdef OF3_CORE_TIMING
-extern "C" int of3_tr_dbg(long long* out, int reset) {
-    if (reset) { long long z[32] = {0}; return (int)cudaMemcpyToSymbol(g_tr_dbg, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(out, g_tr_dbg, 32 * sizeof(long long));
-}
-#endif
 
 bool transition_supported(int c, int n) { return c == 128 && n == 4; }
 

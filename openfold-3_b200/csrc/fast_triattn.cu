@@ -320,47 +320,44 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 // triattn_core
 // =====================================================================================
 // One CTA = one head, 128 queries and TWO lines of the pair tensor, 32 keys per step; two CTAs share an SM
-// (their prologues, epilogues and waits interleave). Per line and step:
-//   MMA warp      S = Q K^T (128 x 32, K = 32) into one of two TMEM slots
-//   MMA warp      S += Tb I^T: the pair-bias tile [128 q x 32 k] (bf16, shared by both lines) as the A operand
-//                 against a 32 x 32 identity: the tensor pipe adds the bias (a bf16 value times 1.0 accumulated in
-//                 fp32 is exact), the softmax threads never touch it
+// (their prologues, epilogues and waits interleave). Per line and step j:
+//   MMA warp      S_j = Q K_j^T + Tb_j I^T into one of two TMEM slots: 128 x 32 logits, K = 32, and the pair-bias
+//                 tile [128 q x 32 k] (bf16, shared by both lines) as a second A operand against a 32 x 32
+//                 identity, so the tensor pipe adds the bias (a bf16 value times 1.0 accumulated in fp32 is exact)
+//                 and the softmax threads never touch it. S_{j+2} is issued as soon as the softmax threads have
+//                 read S_j out of the slot, i.e. two steps before it is needed.
 //   softmax warps thread = query row = TMEM lane: S -> registers [+ mask bias where the block has masked keys],
-//                 row maximum, P = exp2(S - m) rounded to bf16 and written back to TMEM over the S slot
-//   MMA warp      O[128 x 48] += P V' with P read from TMEM as the A operand; V' is the V tile [32 d x 32 keys]
-//                 followed by 16 constant rows, the first of them all ones: column 32 of O is the row sum of
-//                 exactly the bf16 values of P that entered the product, so the softmax threads keep no sum.
-// The slot of S_j is next written by S_{j+2}, which the MMA thread issues after P_j V_j: tcgen05 operations of
-// one thread execute in issue order, so neither the S slots nor P need an "empty" barrier.
+//                 row maximum, P = exp2(S - m) (row sum kept in a register), P rounded to bf16 and written to one
+//                 of the line's two P buffers in TMEM
+//   MMA warp      O[128 x 32] += P V with P read from TMEM as the A operand
+// TMEM columns of a line (128): S slots [0,32) [32,64), P buffers [64,80) [80,96) (16 columns of bf16 pairs
+// each), O [96,128). With S and P both double-buffered no step waits for the GEMM of the step before it: S_{j+2}
+// only needs S_j read out, P_j only needs P_{j-2} V_{j-2} done.
 // The running maximum m used for scaling is only raised when the row maximum exceeds it by more than 8
-// (2^8 head room in P): then, and only then, the thread rescales its O row (sum column included) in TMEM.
+// (2^8 head room in P): then, and only then, the thread rescales its O row in TMEM and its running sum.
 // The result is exact: numerator and denominator always share one scale.
-#ifndef OF3_CORE_STAGES
-#define OF3_CORE_STAGES 4
-#endif
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 32;       // keys per step
 constexpr int kMaxKeys = 2048;   // one CTA keeps a mask-bias row per line in shared memory
-constexpr int kKvStages = OF3_CORE_STAGES;     // K / V / bias ring (untiled bulk copies of pre-swizzled tiles): covers the load round trip
+constexpr int kKbStages = 4;     // ring of K tiles + bias tile (read by S_j, two steps ahead of the softmax)
+constexpr int kVStages = 4;      // ring of V tiles (read by P_j V_j)
 constexpr int kLines = 2;     // lines per CTA
 constexpr int kLinePad = 4;   // the operand images pad the line count of a sample to a multiple of this
 constexpr int kCoreThreads = 32 * (1 + kLines + 4 * kLines);  // producer, one MMA warp per line, softmax
 constexpr float kRescaleThreshold = 8.0f;
-#ifndef OF3_CORE_POLY_PAIRS
-#define OF3_CORE_POLY_PAIRS 0
-#endif
 constexpr uint32_t kTbTileBytes = kBQ * kBiasK * 2;    // 8192
-constexpr uint32_t kVSlot = 3072;                      // V tile (2 KB) + 16 constant rows of 64 B
-constexpr int kON = 48;                                // N of the P V GEMM: 32 output channels + the row-sum column (+ 15 unused)
+constexpr uint32_t kVSlot = 2048;                      // V tile [32 d][32 keys]
+constexpr int kON = 32;                                // N of the P V GEMM: the head's 32 output channels
+constexpr uint32_t kColP = 64, kColO = 96;
 
 struct CoreSmem {
     static constexpr uint32_t kQ = 0;                                   // lines x 8 KB
     static constexpr uint32_t kK = kQ + kLines * 8192;                  // stages x lines x 2 KB
-    static constexpr uint32_t kV = kK + kKvStages * kLines * 2048;      // stages x lines x 3 KB
-    static constexpr uint32_t kTb = kV + kKvStages * kLines * kVSlot;   // stages x 8 KB: bias tiles [128 q][32 k] bf16
-    static constexpr uint32_t kIdent = kTb + kKvStages * kTbTileBytes;  // 2 KB: 32 x 32 identity (B operand)
+    static constexpr uint32_t kTb = kK + kKbStages * kLines * 2048;     // stages x 8 KB: bias tiles [128 q][32 k] bf16
+    static constexpr uint32_t kV = kTb + kKbStages * kTbTileBytes;      // stages x lines x 3 KB
+    static constexpr uint32_t kIdent = kV + kVStages * kLines * kVSlot; // 2 KB: 32 x 32 identity (B operand)
     static constexpr uint32_t kBars = kIdent + 2048;
-    static constexpr uint32_t kFlags = kBars + 256;                     // lines x 128 block flags (bytes)
+    static constexpr uint32_t kFlags = kBars + 320;                     // lines x 128 block flags (bytes)
     static constexpr uint32_t kMb = kFlags + kLines * 128;              // lines x nkeys_pad floats
     static uint32_t dyn_bytes(int nblk) { return kMb + kLines * nblk * kBK * 4 + 1024; }
 };
@@ -395,40 +392,6 @@ __device__ __forceinline__ void add2(float& x0, float& x1, float y0, float y1) {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(a));
 }
 
-// (x0, x1) = (x0, x1) * (y0, y1) + (z0, z1), packed
-__device__ __forceinline__ void fma2(float& x0, float& x1, float y0, float y1, float z0, float z1) {
-    unsigned long long a, b, c;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x0), "f"(x1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(y0), "f"(y1));
-    asm("mov.b64 %0, {%1, %2};" : "=l"(c) : "f"(z0), "f"(z1));
-    asm("fma.rn.f32x2 %0, %0, %1, %2;" : "+l"(a) : "l"(b), "l"(c));
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(a));
-}
-// 2^x for a pair of arguments x <= ~100 on the FMA / ALU pipes (no MUFU): round-to-nearest split x = n + f with
-// the 1.5 * 2^23 trick, a cubic for 2^f on [-0.5, 0.5] (relative error 7.7e-5, far below the bf16 rounding
-// of P), and n added into the exponent field. Arguments below -126 (masked keys, -inf padding) give 2^-126.
-// The MUFU unit delivers 16 exp2 per clock and SM and shares its issue queue with shared-memory, TMEM
-// and mbarrier operations; at a head dimension of 32 it is the busiest unit of this kernel, so a share of
-// the exponentials is computed here instead.
-__device__ __forceinline__ void exp2_poly2(float& x0, float& x1) {
-    constexpr float kMagic = 12582912.0f;  // 1.5 * 2^23
-    x0 = fmaxf(x0, -126.0f);
-    x1 = fmaxf(x1, -126.0f);
-    float t0 = x0, t1 = x1;
-    add2(t0, t1, kMagic, kMagic);             // low mantissa bits of t = round(x)
-    float n0 = t0, n1 = t1;
-    add2(n0, n1, -kMagic, -kMagic);           // round(x) as a float
-    fma2(n0, n1, -1.0f, -1.0f, x0, x1);       // f = x - round(x)
-    float p0 = 0.05508868396282196f, p1 = 0.05508868396282196f;
-    fma2(p0, p1, n0, n1, 0.24260404706001282f, 0.24260404706001282f);
-    fma2(p0, p1, n0, n1, 0.6932762265205383f, 0.6932762265205383f);
-    fma2(p0, p1, n0, n1, 0.9999289512634277f, 0.9999289512634277f);
-    x0 = __uint_as_float(__float_as_uint(p0) + (__float_as_uint(t0) << 23));
-    x1 = __uint_as_float(__float_as_uint(p1) + (__float_as_uint(t1) << 23));
-}
-// pairs (of each group of four pairs) whose exponentials run on the FMA pipe
-constexpr int kPolyPairsOf4 = OF3_CORE_POLY_PAIRS;
-
 template <bool kTransposed>
 __global__ void __launch_bounds__(kCoreThreads, 2)
 triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16* __restrict__ k_img,
@@ -442,15 +405,20 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     volatile uint8_t* mbflag = gbase + CoreSmem::kFlags;
     const uint32_t bars = sbase + CoreSmem::kBars;
     const uint32_t q_full = bars;
-    constexpr int kB0 = 1 + 2 * kKvStages;
-    auto kv_full = [&](int s) { return bars + 8u * (1 + s); };
-    auto kv_empty = [&](int s) { return bars + 8u * (1 + kKvStages + s); };
-    auto s_full = [&](int L, int s) { return bars + 8u * (kB0 + L * 2 + s); };
-    auto p_ready = [&](int L, int s) { return bars + 8u * (kB0 + 2 * kLines + L * 2 + s); };
-    auto pv_done = [&](int L, int s) { return bars + 8u * (kB0 + 4 * kLines + L * 2 + s); };
-    static_assert(8 * (kB0 + 6 * kLines) + 16 <= 256, "barrier block");
-    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * (kB0 + 6 * kLines));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * (kB0 + 6 * kLines) + 8);
+    auto kb_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto kb_empty = [&](int s) { return bars + 8u * (1 + kKbStages + s); };
+    constexpr int kB1 = 1 + 2 * kKbStages;
+    auto v_full = [&](int s) { return bars + 8u * (kB1 + s); };
+    auto v_empty = [&](int s) { return bars + 8u * (kB1 + kVStages + s); };
+    constexpr int kB2 = kB1 + 2 * kVStages;
+    auto s_full = [&](int L, int s) { return bars + 8u * (kB2 + L * 2 + s); };
+    auto s_empty = [&](int L, int s) { return bars + 8u * (kB2 + 2 * kLines + L * 2 + s); };
+    auto p_ready = [&](int L, int s) { return bars + 8u * (kB2 + 4 * kLines + L * 2 + s); };
+    auto pv_done = [&](int L, int s) { return bars + 8u * (kB2 + 6 * kLines + L * 2 + s); };
+    constexpr int kNumBars = kB2 + 8 * kLines;
+    static_assert(8 * kNumBars + 16 <= 320, "barrier block");
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * kNumBars);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * kNumBars + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_qt = (N + kBQ - 1) / kBQ;
@@ -468,41 +436,24 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < kKvStages; ++s) {
-            mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), kLines);  // each line's commit after the P V that read the stage
+        for (int s = 0; s < kKbStages; ++s) {
+            mbar_init(kb_full(s), 1);
+            mbar_init(kb_empty(s), 4 * kLines);  // every softmax warp has read the S that consumed the stage
         }
-        for (int s = 0; s < 2; ++s) {
-            for (int L = 0; L < kLines; ++L) {
+        for (int s = 0; s < kVStages; ++s) {
+            mbar_init(v_full(s), 1);
+            mbar_init(v_empty(s), kLines);       // each line's commit after the P V that read the stage
+        }
+        for (int L = 0; L < kLines; ++L) {
+            for (int s = 0; s < 2; ++s) {
                 mbar_init(s_full(L, s), 1);
+                mbar_init(s_empty(L, s), 4);
                 mbar_init(p_ready(L, s), 4);
                 mbar_init(pv_done(L, s), 1);
             }
         }
         *abort_flag = 0;
         mbar_fence_init();
-    }
-    // additive key mask of each line, pre-scaled for exp2: inf * (mask - 1) * log2(e); -inf beyond N
-    for (int idx = threadIdx.x; idx < kLines * nkp; idx += blockDim.x) {
-        const int L = idx / nkp, k = idx % nkp;
-        const int line = line_of(L);
-        float v = -INFINITY;
-        if (k < N) {
-            v = 0.f;
-            if (mask != nullptr) {
-                const long long mi = kTransposed ? ((long long)b * N + k) * N + line
-                                                 : ((long long)b * R + line) * N + k;
-                v = inf * (__bfloat162float(mask[mi]) - 1.0f) * kLog2e;
-            }
-        }
-        mbs[idx] = v;
-    }
-    // constant rows 32..47 of every V slot: row 32 = ones (bf16 1.0), the rest zeros; the swizzle permutes
-    // 16-byte chunks inside a row only, and every chunk of a row holds the same value
-    for (int idx = threadIdx.x; idx < kKvStages * kLines * 64; idx += blockDim.x) {
-        const int slot = idx >> 6, w16 = idx & 63;  // 64 chunks of 16 B per slot tail
-        const uint32_t v = (w16 < 4) ? 0x3F803F80u : 0u;
-        *reinterpret_cast<uint4*>(gbase + CoreSmem::kV + slot * kVSlot + 2048 + w16 * 16) = make_uint4(v, v, v, v);
     }
     // 32 x 32 identity, bf16, K-major with the 64-byte swizzle: element (n, n) of row n
     for (int idx = threadIdx.x; idx < 32 * 16; idx += blockDim.x) {
@@ -520,18 +471,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         tmem_relinquish();
     }
     tc_fence_before_sync();
-    __syncthreads();
+    __syncthreads();  // the only CTA-wide barrier before the teardown: the copies and GEMMs start right behind it
     tc_fence_after_sync();
-    // per (line, block): does any key carry a non-zero mask bias?
-    for (int idx = threadIdx.x; idx < kLines * nblk; idx += blockDim.x) {
-        const float* m = mbs + (idx / nblk) * nkp + (idx % nblk) * kBK;
-        bool any = false;
-        for (int e = 0; e < kBK; ++e) any |= (m[e] != 0.f);
-        mbflag[(idx / nblk) * 128 + (idx % nblk)] = any ? 1 : 0;
-    }
-    __syncthreads();
     const uint32_t tmem_base = *tmem_ptr;
-    // TMEM columns of line L: L*128 + { S0 / P0 [0,32)  S1 / P1 [32,64)  O [64,96)  row sum 96 }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -544,20 +486,27 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             const int q_rows = (N - q0 < kBQ) ? N - q0 : kBQ;  // rows of the bias tile that exist
             const uint32_t tb_bytes = (uint32_t)q_rows * kBiasK * 2;
             for (int j = 0; j < nblk; ++j) {
-                const int s = j % kKvStages;
-                if (!mbar_wait(kv_empty(s), ((j / kKvStages) & 1u) ^ 1u, abort_flag)) {
-                    report_wait_failure(status, abort_flag, kKidCore, 1);
-                    break;
-                }
-                mbar_arrive_expect_tx(kv_full(s), kLines * 4096 + tb_bytes);
                 const long long tile0 = ((bh * nkb + j) * rpad + line0) << 10;  // first of the lines' tiles
-                bulk_load(sbase + CoreSmem::kK + s * kLines * 2048, k_img + tile0, kLines * 2048, kv_full(s));
-                // pair-bias tile of key block j (all lines of the CTA share it)
-                bulk_load(sbase + CoreSmem::kTb + s * kTbTileBytes,
-                          tb_img + ((bh * nkb + j) * (long long)N + q0) * kBiasK, tb_bytes, kv_full(s));
-                for (int L = 0; L < kLines; ++L)
-                    bulk_load(sbase + CoreSmem::kV + (s * kLines + L) * kVSlot, v_img + tile0 + L * 1024, 2048,
-                              kv_full(s));
+                {   // K tiles of both lines + the pair-bias tile of key block j (shared by the lines)
+                    const int s = j % kKbStages;
+                    if (!mbar_wait(kb_empty(s), ((j / kKbStages) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 1);
+                        break;
+                    }
+                    mbar_arrive_expect_tx(kb_full(s), kLines * 2048 + tb_bytes);
+                    bulk_load(sbase + CoreSmem::kK + s * kLines * 2048, k_img + tile0, kLines * 2048, kb_full(s));
+                    bulk_load(sbase + CoreSmem::kTb + s * kTbTileBytes,
+                              tb_img + ((bh * nkb + j) * (long long)N + q0) * kBiasK, tb_bytes, kb_full(s));
+                }
+                {   // V tiles
+                    const int s = j % kVStages;
+                    if (!mbar_wait(v_empty(s), ((j / kVStages) & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidCore, 11);
+                        break;
+                    }
+                    mbar_arrive_expect_tx(v_full(s), kLines * 2048);
+                    bulk_load(sbase + CoreSmem::kV + s * kLines * kVSlot, v_img + tile0, kLines * 2048, v_full(s));
+                }
             }
         }
     } else if (warp <= kLines) {
@@ -569,52 +518,62 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
         const uint32_t sb = __shfl_sync(0xffffffffu, sbase, 0);
         constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);  // S: 128 x 32, K = 32
-        constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 48, K = 32
+        constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 32, K = 32
         bool ok = mbar_wait(q_full, 0, abort_flag);
         if (!ok && lane == 0) report_wait_failure(status, abort_flag, kKidCore, 2);
         const uint64_t qdesc = smem_desc_k_sw64(sb + CoreSmem::kQ + L * 8192);
         const uint64_t identdesc = smem_desc_k_sw64(sb + CoreSmem::kIdent);
         const uint32_t t_line = tm + L * 128;
-        const uint32_t d_o = t_line + 64;
-        for (int j = 0; j <= nblk && ok; ++j) {
-            if (j < nblk) {  // S_j = Q K_j^T + Tb_j; its slot was last read by P_{j-2} V_{j-2}, issued before this
-                const int s = j & 1;
-                const int ks = j % kKvStages;
-                if (!mbar_wait(kv_full(ks), (j / kKvStages) & 1u, abort_flag)) {
-                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 3);
-                    break;
-                }
-                const uint64_t kdesc = smem_desc_k_sw64(sb + CoreSmem::kK + (ks * kLines + L) * 2048);
-                const uint64_t tbdesc = smem_desc_k_sw64(sb + CoreSmem::kTb + ks * kTbTileBytes);
-                const uint32_t d = t_line + s * kBK;
-                if (lane == 0) {
-                    mma_bf16(d, qdesc, kdesc, idesc_s, 0u);
-                    mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
-                    mma_bf16(d, tbdesc, identdesc, idesc_s, 1u);            // + pair bias
-                    mma_bf16(d, tbdesc + 2u, identdesc + 2u, idesc_s, 1u);
-                    mma_commit(s_full(L, s));
-                }
-                __syncwarp();
+        // S_i = Q K_i^T + Tb_i into slot i % 2 (free once the softmax threads have read S_{i-2} out of it)
+        auto issue_s = [&](int i) -> bool {
+            const int s = i & 1;
+            const int ks = i % kKbStages;
+            if (i >= 2 && !mbar_wait(s_empty(L, s), ((i - 2) >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 4);
+                return false;
             }
-            if (j >= 1) {  // O += P_{j-1} V'_{j-1}
-                const int jj = j - 1;
-                const int s = jj & 1;
-                const int ks = jj % kKvStages;
-                if (!mbar_wait(p_ready(L, s), (jj >> 1) & 1u, abort_flag)) {
-                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 5);
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t a_p = t_line + s * kBK;  // P: 16 columns of packed bf16 pairs
-                const uint64_t vdesc = smem_desc_k_sw64(sb + CoreSmem::kV + (ks * kLines + L) * kVSlot);
-                if (lane == 0) {
-                    mma_bf16_ts(d_o, a_p, vdesc, idesc_o, jj != 0 ? 1u : 0u);
-                    mma_bf16_ts(d_o, a_p + 8u, vdesc + 2u, idesc_o, 1u);
-                    mma_commit(pv_done(L, s));
-                    mma_commit(kv_empty(ks));
-                }
-                __syncwarp();
+            if (!mbar_wait(kb_full(ks), (i / kKbStages) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 3);
+                return false;
             }
+            tc_fence_after_sync();
+            const uint64_t kdesc = smem_desc_k_sw64(sb + CoreSmem::kK + (ks * kLines + L) * 2048);
+            const uint64_t tbdesc = smem_desc_k_sw64(sb + CoreSmem::kTb + ks * kTbTileBytes);
+            const uint32_t d = t_line + s * kBK;
+            if (lane == 0) {
+                mma_bf16(d, qdesc, kdesc, idesc_s, 0u);
+                mma_bf16(d, qdesc + 2u, kdesc + 2u, idesc_s, 1u);
+                mma_bf16(d, tbdesc, identdesc, idesc_s, 1u);            // + pair bias
+                mma_bf16(d, tbdesc + 2u, identdesc + 2u, idesc_s, 1u);
+                mma_commit(s_full(L, s));
+            }
+            __syncwarp();
+            return true;
+        };
+        ok = ok && issue_s(0);
+        if (ok && nblk > 1) ok = issue_s(1);
+        for (int j = 0; j < nblk && ok; ++j) {
+            if (j + 2 < nblk && !issue_s(j + 2)) break;   // early in step j: the softmax threads release slot j % 2
+            // O += P_j V_j at the end of step j
+            const int vs = j % kVStages;
+            if (!mbar_wait(v_full(vs), (j / kVStages) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 12);
+                break;
+            }
+            if (!mbar_wait(p_ready(L, j & 1), (j >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 5);
+                break;
+            }
+            tc_fence_after_sync();
+            const uint64_t vdesc = smem_desc_k_sw64(sb + CoreSmem::kV + (vs * kLines + L) * kVSlot);
+            if (lane == 0) {
+                const uint32_t a_p = t_line + kColP + (j & 1) * 16;
+                mma_bf16_ts(t_line + kColO, a_p, vdesc, idesc_o, j != 0 ? 1u : 0u);
+                mma_bf16_ts(t_line + kColO, a_p + 8u, vdesc + 2u, idesc_o, 1u);
+                mma_commit(pv_done(L, j & 1));
+                mma_commit(v_empty(vs));
+            }
+            __syncwarp();
         }
     } else {
         // ---------------------------------------------------------------- softmax warpgroups
@@ -625,28 +584,70 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         const bool line_valid = line0 + L < R;
         const long long bl = (long long)b * R + line_of(L);
         const uint32_t trow = tmem_base + ((uint32_t)(quad * 32) << 16) + L * 128;
-        const float* mbl = mbs + L * nkp;
+        float* mbl = mbs + L * nkp;
+        // Additive key mask of this line, pre-scaled for exp2: inf * (mask - 1) * log2(e), -inf beyond N. The four
+        // warps of the line prepare it for themselves (eight keys per thread and pass, the loads of a pass
+        // independent of each other) while the first copies and GEMMs are already under way.
+        {
+            const int gt = (warp - 1 - kLines - 4 * L) * 32 + lane;  // 0..127 within the line's warps
+            const int line = line_of(L);
+            for (int base = 0; base < nkp; base += 128 * 8) {   // warp-uniform trip count (ballot below)
+                const int c0 = base + gt * 8;
+                const bool active = c0 < nkp;
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const int k = c0 + e;
+                    float m = 1.0f;
+                    if (mask != nullptr && k < N) {
+                        const long long mi = kTransposed ? ((long long)b * N + k) * N + line
+                                                         : ((long long)b * R + line) * N + k;
+                        m = __bfloat162float(mask[mi]);
+                    }
+                    v[e] = (k < N) ? inf * (m - 1.0f) * kLog2e : -INFINITY;
+                }
+                bool any = false;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) any |= (v[e] != 0.f);
+                if (active) {
+                    *reinterpret_cast<float4*>(mbl + c0) = make_float4(v[0], v[1], v[2], v[3]);
+                    *reinterpret_cast<float4*>(mbl + c0 + 4) = make_float4(v[4], v[5], v[6], v[7]);
+                }
+                // a key block of 32 = four consecutive threads: does any of its keys carry a non-zero bias?
+                const unsigned bal = __ballot_sync(0xffffffffu, any);
+                if (active && (lane & 3) == 0) mbflag[L * 128 + (c0 >> 5)] = ((bal >> lane) & 0xFu) ? 1 : 0;
+            }
+            group_sync(1 + L, 128);
+        }
         unsigned long long mflags = 0ull;  // bit j: key block j of this line has a masked (or padding) key
-        for (int jj = 0; jj < nblk; ++jj) mflags |= (unsigned long long)mbflag[L * 128 + jj] << jj;
-        float m_used = 0.f;
+        {
+            const unsigned lo = __ballot_sync(0xffffffffu, lane < nblk && mbflag[L * 128 + lane]);
+            const unsigned hi = __ballot_sync(0xffffffffu, lane + 32 < nblk && mbflag[L * 128 + 32 + lane]);
+            mflags = ((unsigned long long)hi << 32) | lo;
+        }
+        float m_used = 0.f, l = 0.f;
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
-            const uint32_t ph = (j >> 1) & 1u;
-            if (!mbar_wait(s_full(L, s), ph, abort_flag)) {
+            if (!mbar_wait(s_full(L, s), (j >> 1) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 7);
                 ok = false;
                 break;
             }
             tc_fence_after_sync();
-            float sv[kBK];
-            {
-                uint32_t r0[32];
-                tmem_ld32(trow + s * kBK, r0);
-                tmem_ld_wait();
-#pragma unroll
-                for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(r0[e]);
+            uint32_t sr[32];
+            tmem_ld32(trow + s * kBK, sr);
+            tmem_ld_wait();
+            // S_j is in registers: its slot can take S_{j+2}, the K / bias stage its GEMM read can be refilled
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(s_empty(L, s));
+                mbar_arrive(kb_empty(j % kKbStages));
             }
+            float sv[kBK];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(sr[e]);
             // + mask bias (blocks without a masked key skip it): (q.k + pair bias) + inf * (mask - 1); a masked
             // key ends at the same -1.44e9 in either order of the two additions, an unmasked one adds exactly 0
             if ((mflags >> j) & 1ull) {
@@ -667,44 +668,53 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                 mx1 = max3(mx1, sv[e + 2], sv[e + 3]);
             }
             const float mx = max3(mx0, mx1, fmaxf(sv[30], sv[31]));
+            bool rescale = false;
             if (j == 0) {
                 m_used = mx;  // finite: block 0 always holds a key < N, masked keys are -1e9-ish, not -inf
             } else {
-                const bool need = mx - m_used > kRescaleThreshold;
-                if (__any_sync(0xffffffffu, need)) {
-                    // every P V issued so far must have landed in O before it is rescaled
-                    if (!mbar_wait(pv_done(L, (j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) {
-                        if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 8);
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after_sync();
-                    const float f = need ? ex2_approx(m_used - mx) : 1.0f;
-                    uint32_t orow[32];
-                    tmem_ld32(trow + 64, orow);
-                    const uint32_t osum = tmem_ld1(trow + 64 + 32);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * f);
-                    tmem_st32(trow + 64, orow);
-                    tmem_st1(trow + 64 + 32, __float_as_uint(__uint_as_float(osum) * f));
-                    tmem_st_wait();
-                    if (need) m_used = mx;
+                rescale = __any_sync(0xffffffffu, mx - m_used > kRescaleThreshold);
+            }
+            if (rescale) {
+                float f = 1.0f;
+                if (mx - m_used > kRescaleThreshold) {
+                    f = ex2_approx(m_used - mx);
+                    m_used = mx;
                 }
+                // every P V issued so far must have landed in O before it is rescaled
+                if (!mbar_wait(pv_done(L, (j - 1) & 1), ((j - 1) >> 1) & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 8);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                uint32_t orow[32];
+                tmem_ld32(trow + kColO, orow);
+                tmem_ld_wait();
+#pragma unroll
+                for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * f);
+                tmem_st32(trow + kColO, orow);
+                tmem_st_wait();
+                l *= f;
             }
             uint32_t pk[16];
             const float nm = -m_used;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < 32; e += 2) {
                 add2(sv[e], sv[e + 1], nm, nm);
-                if (((e >> 1) & 3) < kPolyPairsOf4) {
-                    exp2_poly2(sv[e], sv[e + 1]);
-                    pk[e >> 1] = pack_bf16x2(sv[e], sv[e + 1]);
-                } else {
-                    pk[e >> 1] = pack_bf16x2(ex2_approx(sv[e]), ex2_approx(sv[e + 1]));
-                }
+                const float p0 = ex2_approx(sv[e]), p1 = ex2_approx(sv[e + 1]);
+                add2(sum[(e >> 1) & 1 ? 2 : 0], sum[(e >> 1) & 1 ? 3 : 1], p0, p1);
+                pk[e >> 1] = pack_bf16x2(p0, p1);
             }
-            tmem_st16(trow + s * kBK, pk);
+            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+            // this step's P buffer was last read by P_{j-2} V_{j-2}
+            if (j >= 2 && !mbar_wait(pv_done(L, s), ((j - 2) >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 9);
+                ok = false;
+                break;
+            }
+            tc_fence_after_sync();
+            tmem_st16(trow + kColP + s * 16, pk);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
@@ -714,19 +724,18 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             if (mbar_wait(pv_done(L, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1u, abort_flag)) {
                 tc_fence_after_sync();
                 uint32_t r[32];
-                tmem_ld32(trow + 64, r);
-                const uint32_t osum = tmem_ld1(trow + 64 + 32);
+                tmem_ld32(trow + kColO, r);
                 tmem_ld_wait();
-                const float inv = 1.0f / __uint_as_float(osum);
+                const float inv = 1.0f / l;
                 if (qpos < N && line_valid) {
                     uint4* dst = reinterpret_cast<uint4*>(o_out + ((bl * N + qpos) * (long long)kC) + h * kD);
 #pragma unroll
                     for (int v4 = 0; v4 < 4; ++v4) {
-                        float f[8];
+                        float fo[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(r[v4 * 8 + e]) * inv;
-                        dst[v4] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]),
-                                             pack_bf16x2(f[4], f[5]), pack_bf16x2(f[6], f[7]));
+                        for (int e = 0; e < 8; ++e) fo[e] = __uint_as_float(r[v4 * 8 + e]) * inv;
+                        dst[v4] = make_uint4(pack_bf16x2(fo[0], fo[1]), pack_bf16x2(fo[2], fo[3]),
+                                             pack_bf16x2(fo[4], fo[5]), pack_bf16x2(fo[6], fo[7]));
                     }
                 }
             } else if (lane == 0) {
@@ -1091,12 +1100,6 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
 
 }  // namespace
 
-#ifdef OF3_CORE_TIMING
-extern "C" int of3_core_dbg(long long* out, int reset) {
-    if (reset) { long long z[64] = {0}; return (int)cudaMemcpyToSymbol(g_core_dbg, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(out, g_core_dbg, 64 * sizeof(long long));
-}
-#endif
 
 bool triattn_supported(int c_z, int H, int d, int N) {
     return c_z == 128 && H == kH && d == kD && N <= kMaxKeys;

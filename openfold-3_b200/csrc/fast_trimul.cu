@@ -23,17 +23,6 @@ namespace {
 using namespace umma;
 using namespace rowtile;
 
-#ifdef OF3_CORE_TIMING
-__device__ long long g_out_dbg[16];
-__device__ long long g_in_dbg[16];
-#define IDBG_ADD(slot, a, b) do { if (idbg) atomicAdd((unsigned long long*)&g_in_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
-#define ODBG_T(var) const long long var = clock64()
-#define ODBG_ADD(slot, a, b) do { if (odbg) atomicAdd((unsigned long long*)&g_out_dbg[slot], (unsigned long long)((b) - (a))); } while (0)
-#else
-#define ODBG_T(var)
-#define ODBG_ADD(slot, a, b)
-#define IDBG_ADD(slot, a, b)
-#endif
 constexpr int kKidIn = 2;
 constexpr int kKidOut = 3;
 
@@ -156,34 +145,22 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             bool ok = mbar_wait(w_full, 0, abort_flag);
             if (!ok) report_wait_failure(status, abort_flag, kKidIn, 2);
             uint32_t it = 0;
-#ifdef OF3_CORE_TIMING
-            const bool idbg = blockIdx.x == 40;
-#endif
             for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
                 const int s = it & 1;
-                ODBG_T(i0);
                 if (!mbar_wait(a_ready(s), (it >> 1) & 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidIn, 3);
                     break;
                 }
-                ODBG_T(i1);
-                IDBG_ADD(0, i0, i1);
                 for (int q = 0; q < 2; ++q) {
-                    ODBG_T(i2);
                     if (!mbar_wait(slot_empty(q), (it & 1u) ^ 1u, abort_flag)) {
                         report_wait_failure(status, abort_flag, kKidIn, 4);
                         ok = false;
                         break;
                     }
-                    ODBG_T(i3);
-                    IDBG_ADD(1, i2, i3);
                     tc_fence_after_sync();
                     mma_k128(tmem_base + q * 256, sbase + InSmem::kZ + s * kTileBytes,
                              sbase + InSmem::kW + q * 256 * 128, InSmem::kWKb, idesc, false);
                     mma_commit(slot_full(q));
-                    ODBG_T(i4);
-                    IDBG_ADD(2, i3, i4);
-                    IDBG_ADD(3, i0, i0 + (q == 0 ? 1 : 0));
                 }
                 if (ok) mma_commit(z_empty(s));
             }
@@ -194,15 +171,10 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         uint32_t it = 0;
         for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const int s = it & 1;
-#ifdef OF3_CORE_TIMING
-            const bool idbg = blockIdx.x == 40 && threadIdx.x == 64;
-#endif
-            ODBG_T(l0);
             if (!mbar_wait(z_full(s), (it >> 1) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 5);
                 break;
             }
-            ODBG_T(l1);
             const uint32_t tile = sbase + InSmem::kZ + s * kTileBytes;
             uint32_t raw[64];
             load_row(tile, row, raw);
@@ -212,9 +184,6 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(s));
-            ODBG_T(l2);
-            IDBG_ADD(4, l0, l1);
-            IDBG_ADD(5, l1, l2);
         }
     } else {
         // ---------------------------------------------------------------- epilogue warps: 6..9 take the a
@@ -236,20 +205,13 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                                                 : ((long long)(tc.b * N + k) * R + tc.fixed);
                 m = __bfloat162float(mask[lin]);
             }
-#ifdef OF3_CORE_TIMING
-            const bool idbg = blockIdx.x == 40 && threadIdx.x == 6 * 32;
-#endif
             for (int q = qset; q <= qset; ++q) {
-                ODBG_T(e0);
                 if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
                     ok = false;
                     break;
                 }
                 tc_fence_after_sync();
-#ifdef OF3_CORE_TIMING
-                { const long long e1 = clock64(); IDBG_ADD(6, e0, e1); }
-#endif
                 // channel c lives at (c >> group_shift) * group_stride + (c & group_mask) * R * ld: one
                 // contiguous plane [128][R][ld] by default, or one group of channels per destination
                 // rank when the planes are about to be exchanged
@@ -282,9 +244,6 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 tc_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(slot_empty(q));
-#ifdef OF3_CORE_TIMING
-                { const long long e2 = clock64(); IDBG_ADD(7, e0, e2); }
-#endif
             }
         }
     }
@@ -434,18 +393,13 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
         const int gtid = (warp - 2 - g * 4) * 32 + lane;  // 0..127 inside the group
         const uint32_t ztile = sbase + OutSmem::kZ + g * kTileBytes;
         const uint32_t xtile = sbase + OutSmem::kX + g * kTileBytes;
-#ifdef OF3_CORE_TIMING
-        const bool odbg = blockIdx.x == 40 && gtid == 0 && g == 0;
-#endif
         for (long long lt = g; lt < my_tiles; lt += 2) {
             const uint32_t use = (uint32_t)(lt >> 1);
             const TileCoord tc = tile_coord(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
-            ODBG_T(o0);
             if (!mbar_wait(x_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 4);
                 break;
             }
-            ODBG_T(o1);
             float mean, rstd;
             // --- x column of this position: 128 channels, [c][j] layout, stride 256 B
             {
@@ -463,7 +417,6 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                 group_sync(1 + g, 128);  // everyone has read its column before rows overwrite the buffer
                 store_normalized_row(xtile, row, xraw, mean, rstd, prm + 256, prm + 384);
             }
-            ODBG_T(o2);
             // --- z row: keep the raw values for the residual, normalise in place (A operand 1)
             if (!mbar_wait(z_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 7);
@@ -476,13 +429,11 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(g));
-            ODBG_T(o3);
             // --- wait for both GEMMs, combine, write the output tile over the z buffer
             if (!mbar_wait(d_full(g), use & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
                 break;
             }
-            ODBG_T(o4);
             tc_fence_after_sync();
             const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
 #pragma unroll
@@ -509,11 +460,9 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                     sts128(chunk_addr(ztile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
                 }
             }
-            ODBG_T(o5);
             tc_fence_before_sync();
             fence_proxy_async_smem();
             group_sync(1 + g, 128);
-            ODBG_T(o6);
             if (gtid == 0) {
                 for (int kb = 0; kb < 2; ++kb)
                     tma_store_3d(&tmOut, ztile + kb * kKBlockBytes, kb * 64, tc.t0, tc.b * R + tc.fixed);
@@ -521,10 +470,6 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant
                 tma_store_wait_read<0>();
                 mbar_arrive(z_empty(g));
             }
-            ODBG_T(o7);
-            ODBG_ADD(0, o0, o1); ODBG_ADD(1, o1, o2); ODBG_ADD(2, o2, o3); ODBG_ADD(3, o3, o4);
-            ODBG_ADD(4, o4, o5); ODBG_ADD(5, o5, o6); ODBG_ADD(6, o6, o7); ODBG_ADD(7, o0, o7);
-            ODBG_ADD(8, o0, o0 + 1);
         }
         if (gtid == 0) tma_store_wait_all<0>();
     }
@@ -546,16 +491,6 @@ int weight_tmap(CUtensorMap* m, const void* w, int rows) {
 
 }  // namespace
 
-#ifdef OF3_CORE_TIMING
-extern "C" int of3_in_dbg(long long* out, int reset) {
-    if (reset) { long long z[16] = {0}; return (int)cudaMemcpyToSymbol(g_in_dbg, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(out, g_in_dbg, 16 * sizeof(long long));
-}
-extern "C" int of3_out_dbg(long long* out, int reset) {
-    if (reset) { long long z[16] = {0}; return (int)cudaMemcpyToSymbol(g_out_dbg, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(out, g_out_dbg, 16 * sizeof(long long));
-}
-#endif
 
 bool trimul_supported(int c_z, int c_h) { return c_z == 128 && c_h == 128; }
 
