@@ -49,7 +49,7 @@ def token_pair_mask(single_mask):
 
 # ----------------------------------------------------------------------------- cases
 def block_n64():
-    """BASELINE config 0: one PairFormerBlock, N=64, all-ones masks, N(0, 0.02) for zero-inits."""
+    """One PairFormerBlock of the OpenFold3 trunk widths, N=64, all-ones masks, N(0, 0.02) for zero-inits."""
     N = 64
     g = _gen(100)
     inputs = dict(s=torch.randn(1, N, 384, generator=g), z=torch.randn(1, N, N, 128, generator=g),
@@ -219,6 +219,44 @@ def diffusion_stack2_n16():
     return P, inputs, run
 
 
+DEPTHS = (1, 4, 48)
+
+
+def depth_curve_n64():
+    """A 48-block PairFormerStack at N=64 (one padded token), tapped after 1, 4 and 48 blocks: how the bf16 error
+    grows with depth. Not a golden case (no stored outputs): the oracle is evaluated where the test runs."""
+    N = 64
+    g = _gen(110)
+    sm = torch.ones(1, N)
+    sm[:, -1] = 0
+    inputs = dict(s=torch.randn(1, N, 384, generator=g), z=torch.randn(1, N, N, 128, generator=g),
+                  single_mask=sm, pair_mask=token_pair_mask(sm))
+    P = W.pairformer_stack_params(seed=21, no_blocks=max(DEPTHS), **OF3)
+
+    def run(P, x):
+        s, z = x["s"], x["z"]
+        out = {}
+        for i in range(max(DEPTHS)):
+            s, z = oracle.pairformer_block(s, z, x["single_mask"], x["pair_mask"], P, f"blocks.{i}.", 4, 16)
+            if i + 1 in DEPTHS:
+                out[f"s@{i + 1}"], out[f"z@{i + 1}"] = s, z
+        return out
+
+    return P, inputs, run
+
+
+def run_depth_curve(stack, x: dict) -> dict:
+    """Taps a PairFormerStack-like module (``.blocks``) after the depths of ``DEPTHS``."""
+    s, z = x["s"], x["z"]
+    out = {}
+    with torch.no_grad():
+        for i, blk in enumerate(stack.blocks):
+            s, z = blk(s, z, x["single_mask"], x["pair_mask"])
+            if i + 1 in DEPTHS:
+                out[f"s@{i + 1}"], out[f"z@{i + 1}"] = s.clone(), z.clone()
+    return out
+
+
 CASES = {f.__name__: f for f in (
     block_n64, block_n40_padded, pair_taps_n24, trimul_n22_b2, triattn_n33_masked_rows, pair_odd_dims,
     single_track_n50, stack2_n20, diffusion_block_n24, diffusion_stack2_n16)}
@@ -230,6 +268,14 @@ def rel_err(got: torch.Tensor, ref: torch.Tensor, where: torch.Tensor | None = N
     if where is not None:
         got, ref = got[where], ref[where]
     return float((got - ref).abs().max() / ref.pow(2).mean().sqrt())
+
+
+def rms_err(got: torch.Tensor, ref: torch.Tensor, where: torch.Tensor | None = None) -> float:
+    """RMS(got - ref) / RMS(ref): the error of the whole tensor, not of its single worst element."""
+    got, ref = got.double(), ref.double()
+    if where is not None:
+        got, ref = got[where], ref[where]
+    return float((got - ref).pow(2).mean().sqrt() / ref.pow(2).mean().sqrt())
 
 
 # ----------------------------------------------------------------------------- drop-in runners
@@ -336,3 +382,13 @@ def excess_err(got: torch.Tensor, ref: torch.Tensor, n_round: int) -> float:
     got, ref = got.double(), ref.double()
     d = ((got - ref).abs() - n_round * 2.0 ** -8 * ref.abs()).clamp_min(0)
     return float(d.max() / ref.pow(2).mean().sqrt())
+
+
+def record(name, key, raw, excess, rms, ref_raw=None, ref_rms=None):
+    """Appends one row of the bf16 parity table when OF3_PARITY_TABLE names a file."""
+    import os
+    path = os.environ.get("OF3_PARITY_TABLE")
+    if path:
+        with open(path, "a") as f:
+            f.write(f"{name}\t{key}\t{raw:.3e}\t{excess:.3e}\t{rms:.3e}\t"
+                    f"{'' if ref_raw is None else f'{ref_raw:.3e}'}\t{'' if ref_rms is None else f'{ref_rms:.3e}'}\n")

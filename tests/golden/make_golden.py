@@ -2,7 +2,7 @@
 
 Run where the reference source tree is available:
 
-    python tests/golden/make_golden.py [/path/to/openfold-3]
+    python tests/golden/make_golden.py /path/to/openfold-3
 
 It imports the reference's own ``openfold3.core.model`` modules (CPU, fp32, every kernel flag
 off, ``eval()``), loads the seeded parameters of ``tests/cases.py`` with ``strict=True`` and
@@ -24,7 +24,9 @@ import torch
 
 HERE = Path(__file__).resolve().parent
 sys.path.insert(0, str(HERE.parent))
-REF = Path(sys.argv[1]) if len(sys.argv) > 1 else Path("/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_golden.py /path/to/openfold-3   (the reference's source tree)")
+REF = Path(sys.argv[1])
 
 
 def install_stubs():
@@ -154,7 +156,7 @@ def main():
     )
     assert set(ref_runs) == set(cases.CASES)
 
-    bf16_err = {}
+    bf16_err, bf16_rms = {}, {}
     for name, make in cases.CASES.items():
         P, x, run_oracle = make()
         # the reference's own bf16 path on the same (bf16-rounded) inputs and weights, measured
@@ -165,6 +167,7 @@ def main():
         ref_bf = ref_runs[name](Pq, xq)
         ora_q = run_oracle({k: v.float() for k, v in Pq.items()}, {k: v.float() for k, v in xq.items()})
         bf16_err[name] = {k: cases.rel_err(ref_bf[k].float(), ora_q[k]) for k in ref_bf}
+        bf16_rms[name] = {k: cases.rms_err(ref_bf[k].float(), ora_q[k]) for k in ref_bf}
         ref = ref_runs[name](P, x)
         ora = run_oracle(P, x)
         errs = {k: cases.rel_err(ora[k], ref[k]) for k in ref}
@@ -178,8 +181,22 @@ def main():
         assert all(e < 2e-5 for e in errs.values()), (name, errs)
         print(" " * 29 + "reference bf16 path vs fp32 oracle: "
               + ", ".join(f"{k}={e:.2e}" for k, e in bf16_err[name].items()))
+    # error growth with depth of the reference's own bf16 path (48 blocks, N = 64)
+    P, x, run_oracle = cases.depth_curve_n64()
+    bf = torch.bfloat16
+    Pq = {k: v.to(bf) for k, v in P.items()}
+    xq = {k: v.to(bf) for k, v in x.items()}
+    st = load(PairFormerStack(**cases.OF3, **pf_kw, no_blocks=max(cases.DEPTHS), blocks_per_ckpt=None), Pq)
+    ref_bf = cases.run_depth_curve(st, xq)
+    ora_q = run_oracle({k: v.float() for k, v in Pq.items()}, {k: v.float() for k, v in xq.items()})
+    valid = dict(s=x["single_mask"][0].bool(), z=x["pair_mask"][0].bool())
+    curve = {k: dict(max=cases.rel_err(ref_bf[k].float()[0], ora_q[k][0], valid[k[0]]),
+                     rms=cases.rms_err(ref_bf[k].float()[0], ora_q[k][0], valid[k[0]])) for k in ora_q}
+    print("reference bf16 path vs fp32 oracle by depth:", curve)
     import json
+    (HERE / "reference_bf16_depth_curve.json").write_text(json.dumps(curve, indent=1, sort_keys=True) + "\n")
     (HERE / "reference_bf16_error.json").write_text(json.dumps(bf16_err, indent=1, sort_keys=True) + "\n")
+    (HERE / "reference_bf16_rms_error.json").write_text(json.dumps(bf16_rms, indent=1, sort_keys=True) + "\n")
 
 
 if __name__ == "__main__":

@@ -1,9 +1,14 @@
-"""Full-size checks on the GPU through properties that do not need the CPU oracle (which takes
-minutes at these sizes): the tcgen05 kernels against the shape-generic kernels (themselves pinned to the
-reference at small sizes), invariance of the valid region to what sits in padded tokens, and equivariance
-under a relabelling of the tokens. Sizes follow the benchmark configurations: N = 384 with the last 32
-tokens padded, N = 768 (the trunk's size), N = 2048 with 5 % of the tokens padded.
+"""Full-size checks on the GPU at the benchmark configurations' sizes.
+
+Against the CPU oracle (seconds per block at these sizes): the pair stack of 4 blocks at N = 384 with the last
+32 tokens padded, per sub-layer taps of its first block, and one whole PairFormerBlock at N = 768 -- the
+tcgen05 kernels at the sizes the benchmark times them at -- plus the growth of the bf16 error over 1, 4 and
+48 blocks at N = 64. And through properties that need no oracle (N = 2048 is minutes on the CPU): both
+kernel families against each other, invariance of the valid region to what sits in padded tokens,
+equivariance under a relabelling of the tokens.
 """
+
+import json
 
 import pytest
 import torch
@@ -106,3 +111,141 @@ def test_n768_relabelling_the_tokens_permutes_the_output(pkg):
     # the sums run in another order, so bf16 roundings of the intermediates differ; over 7.5e7 outputs of five
     # chained layers the largest difference stays under the bar of the chained bf16 parity cases
     assert _rel(b[0], ap[0], valid) < 6e-2
+
+
+# ----------------------------------------------------------------------------- against the CPU oracle
+# Fixed bars for chained bf16 layers (d = number of PairBlocks / PairFormerBlocks run back to back); what they
+# bound is the kernels' own arithmetic, the reference's bf16 path is printed as context where it was measured.
+def _bars(depth):
+    return dict(rms=8e-3 * depth ** 0.5, max=8e-2 * depth ** 0.5)
+
+
+def _check(tag, key, got, ref, valid, depth, n_round):
+    g, r = got.float().cpu(), ref
+    assert torch.isfinite(g).all(), (tag, key)
+    out = {}
+    for where, w in (("valid", valid), ("all", None)):
+        out[where] = (cases.rel_err(g, r, w), cases.rms_err(g, r, w))
+    exc = cases.excess_err(g[valid], r[valid], n_round)
+    print(f"{tag}.{key}: max-abs/RMS valid {out['valid'][0]:.3e} all {out['all'][0]:.3e}; RMS error valid "
+          f"{out['valid'][1]:.3e} all {out['all'][1]:.3e}; beyond storage rounding {exc:.3e}")
+    cases.record(tag, key, out["valid"][0], exc, out["valid"][1])
+    bars = _bars(depth)
+    assert out["valid"][1] <= bars["rms"], (tag, key, "rms", out["valid"][1])
+    assert out["valid"][0] <= bars["max"], (tag, key, "max", out["valid"][0])
+    # padded positions keep evolving through the stack (only keys are masked): they must stay finite and close too
+    assert out["all"][1] <= 2 * bars["rms"], (tag, key, "rms over all positions", out["all"][1])
+
+
+def test_c1_pair_stack_n384_padded_matches_oracle(pkg):
+    """4 consecutive PairBlocks, N = 384, the last 32 tokens padded (pair mask = outer product), bf16, against the
+    fp32 CPU oracle on the bf16-rounded inputs and weights; every sub-layer of the first block is tapped."""
+    dev = torch.device("cuda:0")
+    n, n_blocks = 384, 4
+    g = torch.Generator().manual_seed(3840)
+    z0 = torch.randn(1, n, n, 128, generator=g).to(BF)
+    tm = _token_mask(n, 32, g, tail=True)
+    pm = (tm[:, None] * tm[None, :])[None]
+    valid = pm[0] > 0
+    blocks, params = [], []
+    for i in range(n_blocks):
+        P = pkg.weights.pair_block_params(seed=400 + i)
+        blk = pkg.PairBlock(c_z=128, c_hidden_mul=128, c_hidden_pair_att=32, no_heads_pair=4, transition_type="swiglu",
+                            transition_n=4, pair_dropout=0.25, fuse_projection_weights=False, inf=1e9)
+        blk.load_state_dict(P, strict=True)
+        blocks.append(blk.to(dev, BF).eval())
+        params.append({k: v.to(BF).float() for k, v in P.items()})
+    o = cases.oracle
+    zr = z0.float()
+    zg = z0.to(dev)
+    pmg = pm.to(dev, BF)
+    with torch.no_grad():
+        for i in range(n_blocks):
+            P, blk = params[i], blocks[i]
+            if i == 0:  # per sub-layer taps: the drop-in modules one by one, as PairBlock.forward chains them
+                taps_r, taps_g = {}, {}
+                zr = zr + o.triangle_multiplicative_update(zr, pm, P, "tri_mul_out.", True)
+                taps_r["tri_mul_out"] = zr
+                zr = zr + o.triangle_multiplicative_update(zr, pm, P, "tri_mul_in.", False)
+                taps_r["tri_mul_in"] = zr
+                zr = zr + o.triangle_attention(zr, pm, P, "tri_att_start.", 4)
+                taps_r["tri_att_start"] = zr
+                zr = zr + o.triangle_attention(zr, pm, P, "tri_att_end.", 4, starting=False)
+                taps_r["tri_att_end"] = zr
+                zr = zr + o.swiglu_transition(zr, pm, P, "pair_transition.")
+                taps_r["pair_transition"] = zr
+                zt = zg.clone()
+                blk.tri_mul_out(zt, mask=pmg, inplace_safe=True, _add_with_inplace=True)
+                taps_g["tri_mul_out"] = zt.clone()
+                blk.tri_mul_in(zt, mask=pmg, inplace_safe=True, _add_with_inplace=True)
+                taps_g["tri_mul_in"] = zt.clone()
+                blk.tri_att_start._run(zt, pmg, transposed=False, in_place=True)
+                taps_g["tri_att_start"] = zt.clone()
+                blk.tri_att_end._run(zt, pmg, transposed=True, in_place=True)
+                taps_g["tri_att_end"] = zt.clone()
+                blk.pair_transition._run(zt, pmg, in_place=True)
+                taps_g["pair_transition"] = zt.clone()
+                for d_i, k in enumerate(taps_r):
+                    _check("c1_n384.block0", k, taps_g[k][0], taps_r[k][0], valid, 1, 2 * (d_i + 1))
+                zg = blk(zg, pmg, inplace_safe=True)
+                assert torch.equal(zg, zt), "PairBlock.forward differs from its sub-layers run one by one"
+            else:
+                zr = o.pair_block(zr, pm, P, "", 4)
+                zg = blk(zg, pmg, inplace_safe=True)
+            torch.cuda.synchronize()
+            pkg.lib.check_device_status()
+            _check("c1_n384", f"z@{i + 1}", zg[0], zr[0], valid, i + 1, 10 * (i + 1))
+
+
+def test_c2_pairformer_block_n768_matches_oracle(pkg):
+    """One whole PairFormerBlock (pair stack + single track) at the trunk's size, N = 768, all-ones masks."""
+    dev = torch.device("cuda:0")
+    n = 768
+    g = torch.Generator().manual_seed(7680)
+    s0 = torch.randn(1, n, 384, generator=g).to(BF)
+    z0 = torch.randn(1, n, n, 128, generator=g).to(BF)
+    sm, pm = torch.ones(1, n), torch.ones(1, n, n)
+    P = pkg.weights.pairformer_block_params(seed=768)
+    blk = pkg.PairFormerBlock(**cases.OF3, transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False,
+                              inf=1e9)
+    blk.load_state_dict(P, strict=True)
+    blk = blk.to(dev, BF).eval()
+    Pq = {k: v.to(BF).float() for k, v in P.items()}
+    with torch.no_grad():
+        s_r, z_r = cases.oracle.pairformer_block(s0.float(), z0.float(), sm, pm, Pq, "", 4, 16)
+        s_g, z_g = blk(s0.to(dev), z0.to(dev), sm.to(dev, BF), pm.to(dev, BF), inplace_safe=True)
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    _check("c2_n768.block", "z", z_g[0], z_r[0], pm[0] > 0, 1, 10)
+    _check("c2_n768.block", "s", s_g[0], s_r[0], sm[0] > 0, 1, 4)
+
+
+def test_bf16_error_growth_with_depth(pkg):
+    """48 PairFormerBlocks at N = 64, tapped after 1, 4 and 48 blocks, against the fp32 oracle on the rounded
+    inputs and weights. Fixed bars per depth; the reference's own bf16 path (measured where the reference tree
+    is available, tests/golden/reference_bf16_depth_curve.json) is printed next to ours."""
+    dev = torch.device("cuda:0")
+    P, x, run_oracle = cases.depth_curve_n64()
+    Pq = {k: v.to(BF).float() for k, v in P.items()}
+    xq = {k: v.to(BF).float() for k, v in x.items()}
+    ref = run_oracle(Pq, xq)
+    st = pkg.PairFormerStack(**cases.OF3, transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False,
+                             inf=1e9, no_blocks=max(cases.DEPTHS), blocks_per_ckpt=None)
+    st.load_state_dict(P, strict=True)
+    st = st.to(dev, BF).eval()
+    got = cases.run_depth_curve(st, {k: v.to(dev, BF) for k, v in x.items()})
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    ref_curve = json.loads((cases.ROOT / "tests" / "golden" / "reference_bf16_depth_curve.json").read_text())
+    valid = dict(s=x["single_mask"][0].bool(), z=x["pair_mask"][0].bool())
+    for k, r in ref.items():
+        depth = int(k.split("@")[1])
+        g = got[k].float().cpu()[0]
+        assert torch.isfinite(g).all(), k
+        raw, rms = cases.rel_err(g, r[0], valid[k[0]]), cases.rms_err(g, r[0], valid[k[0]])
+        print(f"depth curve {k}: max-abs/RMS {raw:.3e}, RMS error {rms:.3e} (reference bf16 path, context only: "
+              f"max {ref_curve[k]['max']:.3e}, RMS {ref_curve[k]['rms']:.3e})")
+        cases.record("depth_curve_n64", k, raw, float("nan"), rms, ref_curve[k]["max"], ref_curve[k]["rms"])
+        bars = _bars(depth)
+        assert rms <= bars["rms"], (k, "rms", rms)
+        assert raw <= bars["max"], (k, "max", raw)

@@ -2,16 +2,18 @@
 of the reference (fp32 validation mode) and against the CPU oracle evaluated on bf16-rounded
 inputs and weights (bf16 mode).
 
-Tolerances (max |got - ref| / RMS(ref)):
-  fp32 validation mode  1e-4
-  bf16, fp32 accumulate 2e-2 -- or, where the reference's own bf16 path is itself further than
-                        that from the fp32 oracle on the same rounded inputs (it is, on every case
-                        here: 2.3e-2 .. 1.0e-1, tests/golden/reference_bf16_error.json, measured
-                        by tests/golden/make_golden.py), no worse than the reference's bf16 path.
-                        The reason is representational: rounding one value x to bf16 moves it by up
-                        to 2^-8 |x|, which at the 5-sigma tail of a tensor is already 2e-2 x RMS, and
-                        tensor-core operands (LayerNorm output, gated projections) must be bf16.
-                        The error in excess of the output's own storage rounding is printed too.
+Tolerances:
+  fp32 validation mode  max |got - ref| / RMS(ref) <= 1e-4
+  bf16, fp32 accumulate three fixed bars, none of which depends on how the reference's own bf16 path behaves:
+                        RMS(got - ref) / RMS(ref)            <= BF16_RMS_BAR      (error of the whole tensor)
+                        max |got - ref| / RMS(ref)           <= BF16_MAX_BAR      (its worst element)
+                        the same beyond the storage roundings <= BF16_EXCESS_BAR  (cases.excess_err)
+                        A single bf16 rounding moves a value x by up to 2^-8 |x|, which at the 5-sigma tail of
+                        a tensor is already 2e-2 x RMS, and tensor-core operands (LayerNorm output, gated
+                        projections, probabilities) must be bf16: the worst element of ~1e5 cannot meet 2e-2 in
+                        any bf16-operand pipeline (the reference's own is at 2.3e-2 .. 1.0e-1 on these cases,
+                        tests/golden/reference_bf16_error.json). The RMS bar is the sharp regression detector.
+                        The reference's figures are printed next to ours as context only.
 """
 
 import json
@@ -24,7 +26,15 @@ import cases
 pytestmark = pytest.mark.gpu
 
 TOL_F32 = 1e-4
-TOL_BF16 = 2e-2
+# per block of chained layers; d blocks back to back scale the bars by sqrt(d) (independent rounding errors add
+# in quadrature; measured growth over 1, 4 and 48 blocks: tests/test_fullsize_gpu.py)
+BF16_RMS_BAR = 8e-3
+BF16_MAX_BAR = 8e-2
+BF16_EXCESS_BAR = 4e-2
+DEPTH = {"stack2_n20": 2, "diffusion_stack2_n16": 2}
+# The conditioned attention update of the diffusion block is a small difference of large terms (output gate
+# sigmoid(. - 2)): its RMS is ~1/8 of the RMS of what is summed, and relative bars scale accordingly.
+SMALL_OUTPUT = {("diffusion_block_n24", "attn_update"): 2.5}
 
 
 @pytest.fixture(scope="module")
@@ -72,17 +82,22 @@ def test_bf16_matches_oracle_on_rounded_inputs(pkg, dev, name, force_generic):
         pkg.lib.check_device_status()
     finally:
         pkg.lib.extra_flags = 0
-    ref_bf16 = json.loads((cases.ROOT / "tests" / "golden" / "reference_bf16_error.json").read_text())[name]
+    gold = cases.ROOT / "tests" / "golden"
+    ref_max = json.loads((gold / "reference_bf16_error.json").read_text())[name]
+    ref_rms = json.loads((gold / "reference_bf16_rms_error.json").read_text())[name]
     for k, r in ref.items():
         g = got[k].float().cpu()
         assert torch.isfinite(g).all(), (name, k)
-        err = cases.rel_err(g, r)
-        # the maximum over ~1e5 elements is an extreme-value statistic: allow 25 % scatter around
-        # the reference path's own figure
-        bar = max(TOL_BF16, 1.25 * ref_bf16[k])
-        print(f"{name}.{k}: bf16 max-abs/RMS {err:.3e} (reference bf16 path: {ref_bf16[k]:.3e}; beyond "
-              f"storage rounding: {cases.excess_err(g, r, cases.BF16_ROUNDINGS[name][k]):.3e})")
-        assert err <= bar, (name, k, err, bar)
+        raw, rms = cases.rel_err(g, r), cases.rms_err(g, r)
+        excess = cases.excess_err(g, r, cases.BF16_ROUNDINGS[name][k])
+        print(f"{name}.{k}: bf16 max-abs/RMS {raw:.3e}, beyond storage rounding {excess:.3e}, RMS error {rms:.3e} "
+              f"(reference bf16 path, context only: max {ref_max[k]:.3e}, RMS {ref_rms[k]:.3e})")
+        if not force_generic:
+            cases.record(name, k, raw, excess, rms, ref_max[k], ref_rms[k])
+        scale = SMALL_OUTPUT.get((name, k), 1.0) * DEPTH.get(name, 1) ** 0.5
+        assert rms <= scale * BF16_RMS_BAR, (name, k, "rms", rms)
+        assert raw <= scale * BF16_MAX_BAR, (name, k, "max", raw)
+        assert excess <= scale * BF16_EXCESS_BAR, (name, k, "excess", excess)
 
 
 def test_contract_kernel_matches_einsum(pkg, dev):
