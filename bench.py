@@ -1,20 +1,31 @@
 #!/usr/bin/env python
-"""Benchmark of the Pairformer hot path: the 48-block trunk at N_token = 768 in bf16.
+"""Benchmark of the Pairformer hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c1|c2|c3|c4]
 
-One "step" is one pass of the whole trunk (48 PairFormerBlocks: pair stack + single track) over
-one synthetic input (seeded N(0,1) activations, all-ones masks, seeded random weights with the
-reference's zero-initialised matrices re-drawn N(0, 0.02)). Rank 0 prints ONE JSON line:
+The headline workload (default, ``--config c2``) is the 48-block Pairformer trunk at N_token = 768 in bf16:
+one "step" is one pass of the whole trunk (48 PairFormerBlocks: pair stack + single track) over one synthetic
+input (seeded N(0,1) activations, seeded random weights with the reference's zero-initialised matrices
+re-drawn N(0, 0.02)). The other configurations of the benchmark description produce their own lines:
+  c1  pair stack only, 4 PairBlocks, N = 384, the last 32 tokens padded
+  c3  pair stack only, 8 PairBlocks, N = 2048, 5 % of the tokens padded at random (meant for 8 GPUs)
+  c4  diffusion token stack, 24 blocks, N = 768, 5 samples sharing one pair tensor (samples split over GPUs)
+At N > 1 the pair tensor is row-sharded over the ranks (c1 - c3) or the samples are dealt out (c4).
+Rank 0 prints ONE JSON line:
 
-  value        algorithmic TFLOP/s of the whole job with inputs resident in HBM
-  e2e          the same through the public module API with pinned HOST buffers: per step the
-               inputs are copied host->device and the results device->host inside the timed region
-  roofline     the kernel with the largest share of device time, timed live with CUDA-event pairs
-               around each of its launches (library launch accounting), against the measured bf16
-               tensor peak of this pool
-  cpu_baseline the CPU oracle (a restatement of the reference's stock PyTorch path) on the host
-               cores, on a bounded sample (one of the 48 blocks), scaled to the trunk
+  value        algorithmic TFLOP/s of the whole job with inputs resident in HBM, timed with one CUDA-event pair
+               around the K steps (no per-launch instrumentation inside the timed region)
+  e2e          the same through the public module API with pinned HOST buffers: per step the inputs are copied
+               host->device and the results device->host inside the timed region
+  kernels      per-kernel device time of ONE more step, run after the timed region with an event pair around
+               every launch (library launch accounting)
+  roofline     a list, dominant kernel first: algorithmic flop (or bytes) per launch / that kernel's average launch
+               time, against the measured bf16 tensor peak (or copy bandwidth) of this pool; `traffic` = DRAM bytes
+               per launch from the committed ncu summary profiles/kernel_dram_traffic_n768.md
+  cpu_baseline the CPU oracle (a restatement of the reference's stock PyTorch path) on the host cores, on a bounded
+               sample (one block), in the same TFLOP/s
+  parity_vs_single_gpu  (N > 1) the row-sharded path against the single-GPU path on the same inputs, outside the
+               timed region; the run fails if they disagree
 
 `--impl reference` times that CPU path alone, with all host threads, one block per step.
 """
@@ -24,6 +35,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -37,6 +49,20 @@ sys.path.insert(0, str(ROOT))
 C_Z, C_S, H_PAIR, H_SINGLE = 128, 384, 4, 16
 OF3 = dict(c_s=C_S, c_z=C_Z, c_hidden_pair_bias=24, no_heads_pair_bias=H_SINGLE, c_hidden_mul=128,
            c_hidden_pair_att=32, no_heads_pair=H_PAIR, transition_n=4)
+PAIR = dict(c_z=C_Z, c_hidden_mul=128, c_hidden_pair_att=32, no_heads_pair=H_PAIR, transition_n=4)
+DIFF = dict(c_a=768, c_s=C_S, c_z=C_Z, c_hidden=48, no_heads=16, n_transition=2)
+
+# kind: "trunk" = PairFormerStack (pair stack + single track), "pair" = PairBlocks only, "diffusion" = token stack
+CONFIGS = {
+    "c1": dict(kind="pair", n=384, blocks=4, pad=("tail", 32),
+               label="pair stack only, 4 PairBlocks, N_token=384, last 32 tokens padded"),
+    "c2": dict(kind="trunk", n=768, blocks=48, pad=None,
+               label="Pairformer trunk, 48 blocks, N_token=768, all-ones masks"),
+    "c3": dict(kind="pair", n=2048, blocks=8, pad=("random", 0.05),
+               label="pair stack only, 8 PairBlocks, N_token=2048, 5 % of the tokens padded at random"),
+    "c4": dict(kind="diffusion", n=768, blocks=24, samples=5, pad=None,
+               label="diffusion token stack, 24 blocks, N_token=768, 5 samples sharing one pair tensor"),
+}
 
 
 def flops_pair_block(n: int) -> float:
@@ -50,8 +76,28 @@ def flops_single_block(n: int) -> float:
     return 2.0 * n**2 * C_Z * H_SINGLE + 10.0 * n * C_S**2 + 4.0 * n**2 * C_S + 24.0 * n * C_S**2
 
 
+def flops_diffusion_block(n: int, samples: int) -> float:
+    """One DiffusionTransformerBlock over `samples` samples that share one pair tensor (c_a = 768, c_s = 384,
+    16 heads x 48, transition n = 2). Per sample: q / k / v / g / o projections (10 N c_a^2), the three
+    conditioning linears of the attention and the three of the transition (12 N c_s c_a), attention
+    (4 N^2 c_a), the three SwiGLU GEMMs of N x c_a x 2 c_a. Once per block: the pair-bias projection
+    (2 N^2 c_z H). 24 blocks, 5 samples, N = 768: 1.797e12 flop."""
+    c_a, c_s = DIFF["c_a"], DIFF["c_s"]
+    per_sample = (10.0 * n * c_a**2 + 12.0 * n * c_s * c_a + 4.0 * n**2 * c_a
+                  + 3 * 2.0 * n * c_a * (DIFF["n_transition"] * c_a))
+    return samples * per_sample + 2.0 * n**2 * C_Z * DIFF["no_heads"]
+
+
+def workload_flops(cfg: dict, n: int, blocks: int) -> float:
+    if cfg["kind"] == "trunk":
+        return blocks * (flops_pair_block(n) + flops_single_block(n))
+    if cfg["kind"] == "pair":
+        return blocks * flops_pair_block(n)
+    return blocks * flops_diffusion_block(n, cfg["samples"])
+
+
 def kernel_flops(n: int) -> dict:
-    """Algorithmic flop per launch of each tcgen05 kernel (c = 128)."""
+    """Algorithmic flop per launch of each tcgen05 kernel of the pair stack (c = 128)."""
     c2 = float(C_Z * C_Z)
     return {
         "trimul_in": 8.0 * n * n * c2,         # four 128x128 projections
@@ -64,17 +110,31 @@ def kernel_flops(n: int) -> dict:
     }
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at N = 768 from the committed ncu
-# summaries under profiles/ (captured at N = 768 itself, one block).
-KERNEL_DRAM_TRAFFIC = {
-    "triattn_core": 593.1e6,
-    "trimul_in": 411e6,
-    "contract": 417e6,
-    "trimul_out": 411e6,
-    "triattn_proj": 552e6,
-    "triattn_out": 413e6,
-    "transition": 268e6,
-}
+def kernel_min_bytes(n: int) -> dict:
+    """Algorithmic HBM bytes per launch of the row-tile kernels (the tensors each one must read and write once)."""
+    plane = float(n) * n * C_Z * 2          # one [N, N, 128] bf16 tensor
+    return {
+        "trimul_in": 3 * plane,             # z in, a_t and b_t out
+        "trimul_out": 3 * plane,            # x_t and z in, z out
+        "triattn_proj": 4 * plane,          # z in, q, k, v images out
+        "triattn_out": 3 * plane,           # z and o in, z out
+    }
+
+
+TENSOR_BOUND = ("triattn_core", "trimul_contract", "transition")
+
+
+def dram_traffic_table() -> dict:
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) at N = 768, read from the committed
+    ncu summary: rows `| kernel | read MB | written MB | ...`."""
+    out = {}
+    p = ROOT / "profiles" / "kernel_dram_traffic_n768.md"
+    if p.exists():
+        for line in p.read_text().splitlines():
+            m = re.match(r"\|\s*`?(\w+)`?\s*\|\s*([\d.]+)\s*\|\s*([\d.]+)\s*\|", line)
+            if m:
+                out[m.group(1)] = (float(m.group(2)) + float(m.group(3))) * 1e6
+    return out
 
 
 def peaks() -> tuple[float, float, str]:
@@ -158,8 +218,24 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def oracle_block_seconds(n: int, repeats: int = 1) -> tuple[float, int]:
-    """Seconds for one PairFormerBlock of the CPU oracle at N_token = n (fp32, all host threads)."""
+def token_mask(cfg: dict, n: int):
+    """The configuration's token mask [n] (float 0/1), seeded."""
+    import torch
+
+    m = torch.ones(n)
+    if cfg["pad"] is not None:
+        how, amount = cfg["pad"]
+        if how == "tail":
+            m[n - int(amount):] = 0
+        else:
+            g = torch.Generator().manual_seed(2048)
+            m[torch.randperm(n, generator=g)[:int(round(amount * n))]] = 0
+    return m
+
+
+def oracle_sample(cfg: dict, n: int) -> tuple[float, float, int, str]:
+    """One bounded sample of the workload on the CPU oracle (fp32, all host threads):
+    -> (seconds, algorithmic flop of the sample, threads, description)."""
     import torch
 
     from __graft_entry__ import load_package
@@ -168,49 +244,168 @@ def oracle_block_seconds(n: int, repeats: int = 1) -> tuple[float, int]:
     pkg = load_package()
     torch.set_num_threads(os.cpu_count() or 1)
     g = torch.Generator().manual_seed(1)
-    s = torch.randn(1, n, C_S, generator=g)
-    z = torch.randn(1, n, n, C_Z, generator=g)
-    sm, pm = torch.ones(1, n), torch.ones(1, n, n)
-    P = pkg.weights.pairformer_block_params(seed=7, **OF3)
-    best = float("inf")
+    kind = cfg["kind"]
     with torch.no_grad():
-        for _ in range(repeats):
+        if kind == "diffusion":
+            S = cfg["samples"]
+            a = torch.randn(1, S, n, DIFF["c_a"], generator=g)
+            s = torch.randn(1, S, n, C_S, generator=g)
+            z = torch.randn(1, 1, n, n, C_Z, generator=g)
+            mask = torch.ones(1, 1, n)
+            P = pkg.weights.diffusion_block_params(seed=7, **DIFF)
             t0 = time.perf_counter()
-            oracle.pairformer_block(s, z, sm, pm, P, "", H_PAIR, H_SINGLE)
-            best = min(best, time.perf_counter() - t0)
-    return best, torch.get_num_threads()
+            oracle.diffusion_transformer_block(a, s, z, mask, P, "", DIFF["no_heads"])
+            dt = time.perf_counter() - t0
+            return dt, flops_diffusion_block(n, S), torch.get_num_threads(), \
+                f"one of the {cfg['blocks']} DiffusionTransformerBlocks ({S} samples, N_token={n})"
+        # the oracle materialises the [N, H, N, N] logits: above N = 768 that is more memory than a host has, so the
+        # large-N pair stack is sampled at N = 768 (the figure is a rate, TFLOP/s, which grows slowly with N)
+        ns = min(n, 768)
+        z = torch.randn(1, ns, ns, C_Z, generator=g)
+        tm = token_mask(cfg, ns) if cfg["pad"] is not None and ns == n else torch.ones(ns)
+        pm = (tm[:, None] * tm[None, :])[None]
+        if kind == "pair":
+            P = pkg.weights.pair_block_params(seed=7, **PAIR)
+            t0 = time.perf_counter()
+            oracle.pair_block(z, pm, P, "", H_PAIR)
+            dt = time.perf_counter() - t0
+            return dt, flops_pair_block(ns), torch.get_num_threads(), \
+                f"one PairBlock at N_token={ns} (the workload: {cfg['blocks']} blocks at N_token={n})"
+        s = torch.randn(1, ns, C_S, generator=g)
+        P = pkg.weights.pairformer_block_params(seed=7, **OF3)
+        t0 = time.perf_counter()
+        oracle.pairformer_block(s, z, tm[None], pm, P, "", H_PAIR, H_SINGLE)
+        dt = time.perf_counter() - t0
+        return dt, flops_pair_block(ns) + flops_single_block(ns), torch.get_num_threads(), \
+            f"one of the {cfg['blocks']} PairFormerBlocks at N_token={ns}"
 
 
-def run_reference(args) -> None:
-    """The CPU path alone: one block of the trunk per step on all host threads."""
+def run_reference(args, cfg) -> None:
+    """The CPU path alone: one block of the workload per step on all host threads."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    import torch
-
-    n, blocks = args.n_token, args.blocks
+    n = args.n_token or cfg["n"]
     for _ in range(args.warmup):
-        oracle_block_seconds(n)
-    times = [oracle_block_seconds(n)[0] for _ in range(args.steps)]
-    t = sum(times) / len(times)
-    flop = flops_pair_block(n) + flops_single_block(n)
+        oracle_sample(cfg, n)
+    samples = [oracle_sample(cfg, n) for _ in range(args.steps)]
+    t = sum(x[0] for x in samples) / len(samples)
+    _, flop, cores, what = samples[0]
     value = flop / t / 1e12
-    cores = torch.get_num_threads()
     line = {
         "impl": "reference", "metric": "pairformer_trunk_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"Pairformer trunk, {blocks} blocks, N_token={n}, CPU fp32 oracle of the reference's "
-                               "PyTorch path; each step = one block (1/%d of the trunk)" % blocks},
-        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-                         "sample": f"one PairFormerBlock at N_token={n} per step"},
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.config}: {cfg['label']}; CPU fp32 oracle of the reference's PyTorch path, "
+                               f"each step = {what}; the metric is a rate (algorithmic TFLOP/s), so a step of one "
+                               "block is comparable with a step of the whole workload",
+                   "same_config": False},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": what + " per step"},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
 
 
-def run_ours(args) -> None:
+def build_job(pkg, cfg, n, blocks, dev, world, rank):
+    """Model (seeded weights), pinned host inputs / outputs of THIS rank, and the functions that run one step.
+
+    Returns a dict: model, host_in (tuple of pinned tensors or tuples of them), host_out, run(dev_inputs) ->
+    tuple of device outputs for the single-GPU path, and for the row-sharded path the pieces DapPairFormerStack needs.
+    """
+    import torch
+
+    bf = torch.bfloat16
+    kind = cfg["kind"]
+    kw = dict(transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False, inf=1e9)
+    g = torch.Generator().manual_seed(768)
+    job = {"kind": kind}
+    if kind == "diffusion":
+        S = cfg["samples"]
+        model = pkg.DiffusionTransformer(**DIFF, no_blocks=blocks, use_ada_layer_norm=True, n_query=None, n_key=None,
+                                         inf=1e9)
+        model.load_state_dict(pkg.weights.diffusion_stack_params(seed=2024, no_blocks=blocks, **DIFF), strict=True)
+        a = torch.randn(1, S, n, DIFF["c_a"], generator=g).to(bf)
+        s = torch.randn(1, S, n, C_S, generator=g).to(bf)
+        z = torch.randn(1, 1, n, n, C_Z, generator=g).to(bf)
+        mask = torch.ones(1, 1, n, dtype=bf)
+        # samples are independent: rank r takes samples r, r + world, ... (3+2 / 2+1+1+1 / 5 of 8 ranks busy);
+        # z, s and the mask of a rank's samples are its inputs, nothing is exchanged between the ranks
+        mine = list(range(rank, S, world))
+        job["samples_here"] = mine
+        if mine:
+            a, s = a[:, mine].contiguous(), s[:, mine].contiguous()
+            job["host_in"] = tuple(t.pin_memory() for t in (a, s, z, mask))
+            job["host_out"] = (torch.empty_like(a).pin_memory(),)
+        else:
+            job["host_in"], job["host_out"] = (), ()
+        model = model.to(dev, bf).eval()
+        job["model"] = model
+        job["run"] = lambda x: (model(x[0], x[1], x[2], mask=x[3]),) if x else ()
+        return job
+    tm = token_mask(cfg, n)
+    pm = tm[:, None] * tm[None, :]
+    z = torch.randn(1, n, n, C_Z, generator=g).to(bf)
+    if kind == "trunk":
+        model = pkg.PairFormerStack(**OF3, no_blocks=blocks, blocks_per_ckpt=None, **kw)
+        model.load_state_dict(pkg.weights.pairformer_stack_params(seed=2024, no_blocks=blocks, **OF3), strict=True)
+        s = torch.randn(1, n, C_S, generator=g).to(bf)
+    else:
+        model = pkg.PairStack(no_blocks=blocks, **PAIR, **kw)
+        model.load_state_dict(pkg.weights.pair_stack_params(seed=2024, no_blocks=blocks, **PAIR), strict=True)
+        s = None
+    model = model.to(dev, bf).eval()
+    job["model"] = model
+    sm = tm[None].to(bf)
+    if world == 1:
+        pmh = pm[None].to(bf)
+        if kind == "trunk":
+            job["host_in"] = tuple(t.pin_memory() for t in (s, z, sm, pmh))
+            job["host_out"] = (torch.empty_like(s).pin_memory(), torch.empty_like(z).pin_memory())
+            job["run"] = lambda x: model(x[0], x[1], x[2], x[3])   # clones the inputs, then updates the clones in place
+            job["run_inplace"] = lambda x: model(x[0], x[1], x[2], x[3], inplace_safe=True)
+        else:
+            job["host_in"] = tuple(t.pin_memory() for t in (z, pmh))
+            job["host_out"] = (torch.empty_like(z).pin_memory(),)
+            job["run"] = lambda x: (model(x[0], x[1]),)
+            job["run_inplace"] = lambda x: (model(x[0], x[1], inplace_safe=True),)
+        return job
+    # row-sharded: a rank holds, uploads and downloads only its R = n / world rows of z and of the pair mask (and of
+    # the mask's transpose); s and the token mask are whole on every rank
+    R = n // world
+    rows = slice(rank * R, (rank + 1) * R)
+    z_rows = z[:, rows].contiguous().pin_memory()
+    pm_rows = (pm[rows].to(bf).contiguous().pin_memory(), pm[:, rows].t().to(bf).contiguous().pin_memory())
+    job["whole"] = (s, z, sm, pm[None].to(bf))   # for the parity check against the single-GPU path
+    job["rows"] = rows
+    if kind == "trunk":
+        job["host_in"] = (s.pin_memory(), z_rows, sm.pin_memory(), pm_rows)
+        job["host_out"] = (torch.empty_like(s).pin_memory(), torch.empty_like(z_rows).pin_memory())
+    else:
+        job["host_in"] = (z_rows, pm_rows)
+        job["host_out"] = (torch.empty_like(z_rows).pin_memory(),)
+    return job
+
+
+def to_dev(t, dev, **kw):
+    return tuple(to_dev(x, dev, **kw) for x in t) if isinstance(t, tuple) else t.to(dev, **kw)
+
+
+def nbytes(t) -> int:
+    return sum(nbytes(x) for x in t) if isinstance(t, tuple) else t.numel() * t.element_size()
+
+
+def rel_errors(got, ref):
+    """(max |got - ref| / RMS(ref), RMS(got - ref) / RMS(ref)) in fp64 on the device."""
+    d = got.double() - ref.double()
+    rms = ref.double().pow(2).mean().sqrt()
+    return float(d.abs().max() / rms), float(d.pow(2).mean().sqrt() / rms)
+
+
+def run_ours(args, cfg) -> None:
+    import datetime
+    import types
+
     import torch
     import torch.distributed as dist
 
@@ -224,31 +419,33 @@ def run_ours(args) -> None:
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        import datetime
         # a collective that cannot complete ends the run with an error after two minutes instead of hanging
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
 
     pkg = load_package()
     lib = pkg.lib
     lib.load()
-    n, blocks = args.n_token, args.blocks
-    bf = torch.bfloat16
+    n, blocks = args.n_token or cfg["n"], args.blocks or cfg["blocks"]
+    kind = cfg["kind"]
+    sharded = world > 1 and kind != "diffusion"
+    if sharded and n % world:
+        raise SystemExit(f"N_token {n} is not divisible by {world} ranks")
+    job = build_job(pkg, cfg, n, blocks, dev, world, rank)
+    model = job["model"]
 
-    # ---- model and synthetic inputs (identical on every rank)
-    stack = pkg.PairFormerStack(**OF3, no_blocks=blocks, transition_type="swiglu", pair_dropout=0.25,
-                                fuse_projection_weights=False, blocks_per_ckpt=None, inf=1e9)
-    stack.load_state_dict(pkg.weights.pairformer_stack_params(seed=2024, no_blocks=blocks, **OF3), strict=True)
-    stack = stack.to(dev, bf).eval()
-    g = torch.Generator().manual_seed(768)
-    s_host = torch.randn(1, n, C_S, generator=g).to(bf).pin_memory()
-    z_host = torch.randn(1, n, n, C_Z, generator=g).to(bf).pin_memory()
-    sm_host = torch.ones(1, n, dtype=bf).pin_memory()
-    pm_host = torch.ones(1, n, n, dtype=bf).pin_memory()
-    s_out_host = torch.empty_like(s_host).pin_memory()
-    z_out_host = torch.empty_like(z_host).pin_memory()
+    def stage(msg):  # progress on stderr: a stalled multi-GPU run shows where it stopped
+        if rank == 0 and world > 1:
+            print(f"[bench] {msg}", file=sys.stderr, flush=True)
 
-    heap = None
-    if world > 1:
+    def sync():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    heap = runner = graphed = None
+    parity = None
+    if sharded:
         ops = pkg.dap.CudaOps(dev)
         xchg = None  # None: torch.distributed collectives (NCCL)
         if args.exchange == "peer":
@@ -266,95 +463,123 @@ def run_ours(args) -> None:
                     heap.close()
                     heap = None
                 args.exchange = "nccl"
-        runner = pkg.dap.DapPairFormerStack(stack, world, rank, ops=ops, exchange=xchg)
-    else:
-        runner = None
+        runner = pkg.dap.DapPairFormerStack(model, world, rank, ops=ops, exchange=xchg)
 
-    def stage(msg):  # progress on stderr: a stalled multi-GPU run shows where it stopped
-        if rank == 0 and world > 1:
-            print(f"[bench] {msg}", file=sys.stderr, flush=True)
+        def dap_step(r, x):
+            if kind == "trunk":
+                return r(x[0], x[1], x[2], x[3], sharded=True)
+            return r(None, x[0], None, x[1], sharded=True)[1:]
 
-    graphed = None  # N > 1: the step captured into a CUDA graph (kernels of both streams + collectives)
-
-    def step_resident(s_d, z_d, sm_d, pm_d):
-        if graphed is not None:
-            return graphed(s_d, z_d, sm_d, pm_d)
-        if runner is not None:
-            return runner(s_d, z_d, sm_d, pm_d, sharded=True)
-        return stack(s_d, z_d, sm_d, pm_d)  # clones the inputs, then updates the clones in place
-
-    def sync():
-        torch.cuda.synchronize(dev)
-        if world > 1:
-            dist.barrier()
+        # ---- correctness of the sharded path on these GPUs, outside any timed region: the first two blocks
+        # through the same runner and exchange against the single-GPU modules on the whole tensors (this rank's
+        # rows), and the peer-memory exchange against the NCCL one (bit for bit)
+        with torch.no_grad():
+            nb = min(2, blocks)
+            sub = types.SimpleNamespace(blocks=model.blocks[:nb])
+            s_w, z_w, sm_w, pm_w = (None if t is None else t.to(dev) for t in job["whole"])
+            z_ref, s_ref = z_w.clone(), (None if s_w is None else s_w.clone())
+            for b in sub.blocks:
+                if kind == "trunk":
+                    s_ref, z_ref = b(s_ref, z_ref, sm_w, pm_w, inplace_safe=True)
+                else:
+                    z_ref = b(z_ref, pm_w, inplace_safe=True)
+            x_dev = to_dev(job["host_in"], dev)
+            r2 = pkg.dap.DapPairFormerStack(sub, world, rank, ops=ops, exchange=xchg)
+            out2 = [t.clone() for t in dap_step(r2, x_dev)]
             torch.cuda.synchronize(dev)
+            zmax, zrms = rel_errors(out2[-1][0], z_ref[0, job["rows"]])
+            parity = {"blocks": nb, "z_max": zmax, "z_rms": zrms}
+            if kind == "trunk":
+                parity["s_max"], parity["s_rms"] = rel_errors(out2[0], s_ref)
+            if xchg is not None:
+                r3 = pkg.dap.DapPairFormerStack(sub, world, rank, ops=ops, exchange=None)
+                out3 = dap_step(r3, x_dev)
+                torch.cuda.synchronize(dev)
+                parity["peer_equals_nccl"] = bool(all(torch.equal(a, b) for a, b in zip(out2, out3)))
+            t = torch.tensor([parity["z_max"], parity["z_rms"], parity.get("s_max", 0.0), parity.get("s_rms", 0.0),
+                              0.0 if parity.get("peer_equals_nccl", True) else 1.0], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)   # worst rank
+            parity.update(z_max=float(t[0]), z_rms=float(t[1]))
+            if kind == "trunk":
+                parity.update(s_max=float(t[2]), s_rms=float(t[3]))
+            if xchg is not None:
+                parity["peer_equals_nccl"] = float(t[4]) == 0.0
+            parity["bar_max"] = 2e-2
+            del s_w, z_w, z_ref, s_ref, out2, r2
+            stage(f"parity vs single GPU over {nb} blocks: {parity}")
+            if parity["z_max"] > parity["bar_max"] or parity.get("s_max", 0.0) > parity["bar_max"] or \
+                    not parity.get("peer_equals_nccl", True):
+                raise SystemExit(f"row-sharded path disagrees with the single-GPU path: {parity}")
 
-    if world > 1:
-        # N > 1: the job's input and output are row-sharded -- a rank moves only its R = N / world rows of z and
-        # of the pair mask (and of the mask's transpose) between host and device; s and the token mask are whole
-        R = n // world
-        rows = slice(rank * R, (rank + 1) * R)
-        z_host = z_host[:, rows].contiguous().pin_memory()
-        pm_host = (pm_host[0, rows].contiguous().pin_memory(), pm_host[0][:, rows].t().contiguous().pin_memory())
-        z_out_host = torch.empty_like(z_host).pin_memory()
+    def step_resident(x):
+        if graphed is not None:
+            if kind == "trunk":
+                return graphed(x[0], x[1], x[2], x[3])
+            return graphed(None, x[0], None, x[1])[1:]
+        if runner is not None:
+            return dap_step(runner, x)
+        return job["run"](x)
 
-    def to_dev(t, **kw):
-        return tuple(x.to(dev, **kw) for x in t) if isinstance(t, tuple) else t.to(dev, **kw)
+    def step_eager(x):
+        return dap_step(runner, x) if runner is not None else job["run"](x)
 
     with torch.no_grad():
-        s_d, z_d = s_host.to(dev), z_host.to(dev)
-        sm_d, pm_d = sm_host.to(dev), to_dev(pm_host)
+        x_dev = to_dev(job["host_in"], dev)
         for _ in range(args.warmup):
-            step_resident(s_d, z_d, sm_d, pm_d)
+            step_resident(x_dev)
         sync()
         lib.check_device_status()
         graph_note = "eager launches"
         stage(f"eager warm-up done ({args.warmup} steps)")
         if runner is not None and not args.no_graph:
-            graphed = pkg.dap.GraphedDapRunner(runner, s_d, z_d, sm_d, pm_d, warmup=1, sharded=True)
+            runner.check_status = False  # replays are checked one step late by the graph runner
+            if kind == "trunk":
+                graphed = pkg.dap.GraphedDapRunner(runner, x_dev[0], x_dev[1], x_dev[2], x_dev[3], warmup=1, sharded=True)
+            else:
+                graphed = pkg.dap.GraphedDapRunner(runner, None, x_dev[0], None, x_dev[1], warmup=1, sharded=True)
             stage("graph captured")
-            graph_note = "one CUDA graph per step (kernels of both streams and the NCCL collectives)"
+            graph_note = "one CUDA graph per step (kernels of both streams and the exchanges)"
             for _ in range(args.warmup):
-                step_resident(s_d, z_d, sm_d, pm_d)
+                step_resident(x_dev)
             sync()
 
-        # ---- device-resident timing (value) with per-kernel event pairs
+        # ---- device-resident timing (value): one event pair around the K steps, nothing else inside
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with ClockSampler(local_rank) as clocks:
-            lib.profile_begin(timing=graphed is None)
+            lib.profile_begin(timing=False)
             sync()
             clocks.region_start()
             e0.record()
             for _ in range(args.steps):
-                s_o, z_o = step_resident(s_d, z_d, sm_d, pm_d)
+                out = step_resident(x_dev)
             e1.record()
             sync()
             clocks.region_end()
-            prof = lib.profile_end()
+            counted = lib.profile_end()
         ms_resident = e0.elapsed_time(e1) / args.steps
         stage(f"resident timing done: {ms_resident:.2f} ms per step")
         lib.check_device_status()
-        assert torch.isfinite(z_o.float()).all() and torch.isfinite(s_o.float()).all(), "non-finite trunk output"
+        if graphed is not None:
+            graphed.check()
+        for t in out:
+            assert torch.isfinite(t.float()).all(), "non-finite output"
 
         # ---- end to end through the public API with host buffers
-        def nbytes(*ts):
-            return sum(x.numel() * x.element_size() for t in ts for x in (t if isinstance(t, tuple) else (t,)))
-
-        # whole-job bytes per step: every rank copies its own shard (and the small replicated tensors)
-        h2d = nbytes(s_host, z_host, sm_host, pm_host) * world
-        d2h = nbytes(s_out_host, z_out_host) * world
+        h2d = nbytes(job["host_in"])
+        d2h = nbytes(job["host_out"])
+        if world > 1:
+            t = torch.tensor([h2d, d2h], device=dev, dtype=torch.float64)
+            dist.all_reduce(t)   # whole job: every rank copies its own shard (and the small replicated tensors)
+            h2d, d2h = int(t[0]), int(t[1])
 
         def step_e2e():
-            s_in = s_host.to(dev, non_blocking=True)
-            z_in = z_host.to(dev, non_blocking=True)
-            sm_in = sm_host.to(dev, non_blocking=True)
-            pm_in = to_dev(pm_host, non_blocking=True)
+            x = to_dev(job["host_in"], dev, non_blocking=True)
             if runner is not None:
-                s_r, z_r = step_resident(s_in, z_in, sm_in, pm_in)
+                res = step_resident(x)
             else:
-                s_r, z_r = stack(s_in, z_in, sm_in, pm_in, inplace_safe=True)
-            s_out_host.copy_(s_r, non_blocking=True)
-            z_out_host.copy_(z_r, non_blocking=True)
+                res = job.get("run_inplace", job["run"])(x)
+            for dst, src in zip(job["host_out"], res):
+                dst.copy_(src, non_blocking=True)
 
         step_e2e()
         sync()
@@ -366,14 +591,16 @@ def run_ours(args) -> None:
         sync()
         ms_e2e = e2.elapsed_time(e3) / args.steps
 
-        launches_in_timed_region = int(sum(l for l, _ in prof.values()))
-        if graphed is not None:
-            # per-kernel breakdown and launch count of a step: one eager, profiled step outside the timed region
-            lib.profile_begin(timing=True)
-            runner(s_d, z_d, sm_d, pm_d, sharded=True)
-            sync()
-            prof = lib.profile_end()
-            launches_in_timed_region = int(sum(l for l, _ in prof.values())) * args.steps
+        # ---- per-kernel breakdown and launch count: ONE more step, eager, an event pair around every launch
+        if runner is not None:
+            runner.check_status = True
+        lib.profile_begin(timing=True)
+        step_eager(x_dev)
+        sync()
+        prof = lib.profile_end()
+        launches_per_step = int(sum(l for l, _ in prof.values()))
+        eager_launches = int(sum(l for l, _ in counted.values()))
+        launches_in_timed_region = eager_launches if graphed is None else launches_per_step * args.steps
 
     # ---- max over ranks
     if world > 1:
@@ -381,73 +608,90 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms_resident, ms_e2e = float(t[0]), float(t[1])
 
-    flop = blocks * (flops_pair_block(n) + flops_single_block(n))
+    flop = workload_flops(cfg, n, blocks)
     value = flop / (ms_resident * 1e-3) / 1e12
     e2e_value = flop / (ms_e2e * 1e-3) / 1e12
 
     if rank == 0:
         tensor_peak, hbm_peak, peak_kind = peaks()
-        kf = kernel_flops(n)
+        kf, kb = kernel_flops(n), kernel_min_bytes(n)
+        traffic = dram_traffic_table() if (n == 768 and world == 1) else {}
+        share_of = 1.0 / world if sharded else 1.0   # a rank's share of a layer's work
         total_kernel_ms = sum(ms for _, ms in prof.values()) or 1.0
-        kernels = {}
+        kernels, roofline = {}, []
+        clk = clocks.summary()
         for name, (launches, ms) in sorted(prof.items(), key=lambda kv: -kv[1][1]):
             per_launch_ms = ms / max(1, launches)
             entry = {"launches": launches, "total_ms": round(ms, 3), "share": round(ms / total_kernel_ms, 4),
                      "ms_per_launch": round(per_launch_ms, 4)}
-            if name in kf and world == 1:
-                entry["tflops"] = round(kf[name] / (per_launch_ms * 1e-3) / 1e12, 1)
             kernels[name] = entry
-        top = next((k for k in kernels if k in kf), None)
-        roofline = None
-        if top is not None:
-            per_launch_ms = kernels[top]["ms_per_launch"]
-            achieved = kf[top] / world / (per_launch_ms * 1e-3) / 1e12
-            roofline = {"kernel": top, "bound": "tensor", "achieved": round(achieved, 1), "peak": tensor_peak,
-                        "unit": "TFLOP/s", "frac": round(achieved / tensor_peak, 4),
-                        "traffic": KERNEL_DRAM_TRAFFIC.get(top) if (n == 768 and world == 1) else None, "peak_kind": f"bf16 sustained, {peak_kind}",
-                        "algorithmic_flop_per_launch": kf[top] / world}
-            if top == "triattn_core":
-                # second ceiling of this kernel: one exp2 per logit on the MUFU pipe (16 per clock and SM)
-                exps = 4.0 * n * n * n / world
-                sm_hz = (clocks.summary().get("sm_mhz") or 1965.0) * 1e6
-                exp_peak = 16.0 * 148 * sm_hz
-                roofline["exp_bound"] = {"exps_per_launch": exps, "peak_exps_per_s": exp_peak,
-                                         "frac": round(exps / (per_launch_ms * 1e-3) / exp_peak, 4)}
-        cpu_s, cores = oracle_block_seconds(n) if world == 1 and not args.no_cpu_baseline else (None, 0)
+            if kind == "diffusion" or per_launch_ms <= 0:
+                continue
+            sec = per_launch_ms * 1e-3
+            if name in TENSOR_BOUND:
+                ach = kf[name] * share_of / sec / 1e12
+                r = {"kernel": name, "bound": "tensor", "achieved": round(ach, 1), "peak": tensor_peak, "unit": "TFLOP/s",
+                     "frac": round(ach / tensor_peak, 4), "traffic": traffic.get(name),
+                     "peak_kind": f"bf16 sustained, {peak_kind}", "algorithmic_flop_per_launch": kf[name] * share_of}
+                if name == "triattn_core":
+                    # second ceiling of this kernel: one exp2 per logit on the MUFU pipe (16 per clock and SM)
+                    exps = 4.0 * n * n * n * share_of
+                    exp_peak = 16.0 * 148 * (clk.get("sm_mhz") or 1965.0) * 1e6
+                    r["exp_bound"] = {"exps_per_launch": exps, "peak_exps_per_s": exp_peak,
+                                      "frac": round(exps / sec / exp_peak, 4)}
+                entry["tflops"] = round(ach, 1)
+                roofline.append(r)
+            elif name in kb:
+                ach = kb[name] * share_of / sec / 1e9
+                roofline.append({"kernel": name, "bound": "hbm", "achieved": round(ach, 1), "peak": hbm_peak,
+                                 "unit": "GB/s", "frac": round(ach / hbm_peak, 4), "traffic": traffic.get(name),
+                                 "peak_kind": f"copy bandwidth, {peak_kind}",
+                                 "algorithmic_bytes_per_launch": kb[name] * share_of})
+                entry["gbs"] = round(ach, 1)
+        if not roofline:  # no per-kernel model of this workload: the whole step against the tensor peak
+            roofline.append({"kernel": "whole step", "bound": "tensor", "achieved": round(value / world, 1),
+                             "peak": tensor_peak, "unit": "TFLOP/s", "frac": round(value / world / tensor_peak, 4),
+                             "traffic": None, "peak_kind": f"bf16 sustained, {peak_kind}"})
         cpu_baseline = None
-        if cpu_s is not None:
-            cpu_baseline = {"value": (flops_pair_block(n) + flops_single_block(n)) / cpu_s / 1e12, "unit": "TFLOP/s",
-                            "cores": cores, "kind": "port",
-                            "sample": f"one of the {blocks} PairFormerBlocks at N_token={n} on the CPU oracle "
-                                      f"({cpu_s:.1f} s); the trunk is {blocks} such blocks"}
+        if world == 1 and not args.no_cpu_baseline:
+            cpu_s, cpu_flop, cores, what = oracle_sample(cfg, n)
+            cpu_baseline = {"value": cpu_flop / cpu_s / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+                            "sample": f"{what} on the CPU oracle ({cpu_s:.1f} s)"}
+        if kind == "diffusion":
+            par = "single GPU" if world == 1 else f"samples dealt over {world} GPUs (rank r: samples r, r+{world}, ...)"
+            io = "each rank uploads its samples, the pair tensor and the conditioning; downloads its samples"
+            exch = "none"
+        else:
+            par = "single GPU" if world == 1 else f"DAP row-sharded over {world} GPUs"
+            io = ("whole tensors" if world == 1 else
+                  "row-sharded: each rank holds, uploads and downloads its N/world rows of z; s replicated")
+            exch = ("none" if world == 1 else "barrier + pull kernels over NVLink peer memory"
+                    if args.exchange == "peer" else "NCCL all-to-all / all-gather")
         line = {
             "metric": "pairformer_trunk_tflops", "value": round(value, 2), "unit": "TFLOP/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_resident, 3),
             "ms_per_block": round(ms_resident / blocks, 4), "higher_is_better": True,
-            "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"Pairformer trunk, {blocks} blocks, N_token={n}, bf16, all-ones masks, "
-                                   "seeded random weights",
-                       "parallelism": "single GPU" if world == 1 else f"DAP row-sharded over {world} GPUs",
-                       "launch": graph_note,
-                       "io": ("whole tensors" if world == 1 else
-                              "row-sharded: each rank holds, uploads and downloads its N/world rows of z; s replicated"),
-                       "exchange": ("none" if world == 1 else
-                                    "barrier + pull kernels over NVLink peer memory" if args.exchange == "peer"
-                                    else "NCCL all-to-all / all-gather"),
-                       "l2": "inputs and per-layer working set (>1 GB) exceed the 126 MB L2; no explicit flush"},
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{args.config}: {cfg['label'] if (n, blocks) == (cfg['n'], cfg['blocks']) else cfg['kind'] + f' stack, {blocks} blocks, N_token={n}'}"
+                                   ", bf16, seeded random weights",
+                       "parallelism": par, "launch": graph_note, "io": io, "exchange": exch,
+                       "l2": "inputs and per-layer working set exceed the 126 MB L2; no explicit flush"
+                             if n >= 768 else "per-layer working set of a few hundred MB exceeds the 126 MB L2; no explicit flush"},
             "e2e": {"value": round(e2e_value, 2), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e, 3),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": launches_in_timed_region,
-            "clocks": clocks.summary(),
+            "clocks": clk,
             "roofline": roofline,
             "cpu_baseline": cpu_baseline,
             "kernels": kernels,
             "frac_of_tensor_peak": round(value / world / tensor_peak, 4),
         }
+        if parity is not None:
+            line["parity_vs_single_gpu"] = parity
         print(json.dumps(line))
     if world > 1:
         if graphed is not None:  # a live graph still holds the communicator's captured work
-            s_o = z_o = None
+            out = None
             graphed.release()
         torch.cuda.synchronize(dev)
         dist.barrier()
@@ -463,17 +707,20 @@ def main():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--blocks", type=int, default=48)
-    ap.add_argument("--n-token", type=int, default=768)
+    ap.add_argument("--config", choices=sorted(CONFIGS), default="c2",
+                    help="workload; c2 (the 48-block trunk at N_token = 768) is the headline")
+    ap.add_argument("--blocks", type=int, default=0, help="override the configuration's depth (profiling runs)")
+    ap.add_argument("--n-token", type=int, default=0, help="override the configuration's N_token (profiling runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how shards move between GPUs")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
+    cfg = CONFIGS[args.config]
     if args.impl == "reference":
-        run_reference(args)
+        run_reference(args, cfg)
     else:
-        run_ours(args)
+        run_ours(args, cfg)
 
 
 if __name__ == "__main__":

@@ -55,6 +55,8 @@ const char* of3_last_error_string(void);
  * {code, kernel id, block, wait site} here instead of spinning forever. Synchronises the device. */
 int of3_device_status(int* out4);
 int of3_device_status_clear(void);
+/* Stream-ordered copy of the four status words into pinned host memory; no synchronisation. */
+int of3_device_status_async(int* host4, void* stream);
 
 /* Launch accounting. Every kernel launch of the library is counted per kernel id; with timing
  * enabled a CUDA-event pair is recorded around each launch on the launching stream (the events
@@ -282,7 +284,10 @@ int of3_attn_pair_bias_forward_rows(const void* a, const float* pair_bias_rows, 
  * the other processes (any host transport); open maps a peer's heap; close / free undo them.
  * of3_peer_barrier: a one-warp kernel; returns (on the stream) once every rank has launched the same
  *   barrier. flag_blocks[r] = address IN THIS PROCESS of a zero-initialised 64-byte block inside rank r's
- *   heap (the same offset on every rank). Waits are bounded (2 s), then of3_device_status reports kernel 30.
+ *   heap (the same offset on every rank). Waits are bounded (2 s; 60 s for of3_peer_barrier_step_entry, the
+ *   first barrier of a step, where the ranks' hosts may be far apart), then of3_device_status reports kernel
+ *   30, every later of3_peer_pull_rows of the process moves nothing and later barriers do not wait, until
+ *   of3_device_status_clear: a step whose barrier failed cannot produce a silently wrong result.
  * of3_peer_pull_rows: world*n1*n2 rows of row_bytes; row (r, i1, i2) is read from rank r's heap at
  *   srcs[r] + src_off + i1*s1 + i2*s2 and written to dst + r*t0 + i1*t1 + i2*t2 (byte strides):
  *   all-to-all, all-gather and the repack into the consumer's layout in one pass. Call it after a
@@ -292,6 +297,7 @@ int of3_peer_heap_open(const void* handle64, void** ptr);
 int of3_peer_heap_close(void* ptr);
 int of3_peer_heap_free(void* ptr);
 int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream);
+int of3_peer_barrier_step_entry(void* const* flag_blocks, int world, int rank, void* stream);
 int of3_peer_pull_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
                        long long s1, long long s2, long long t0, long long t1, long long t2, int row_bytes,
                        void* stream);

@@ -20,6 +20,7 @@ from .modules import (
     PairBlock,
     PairFormerBlock,
     PairFormerStack,
+    PairStack,
     SwiGLU,
     SwiGLUTransition,
     TriangleAttention,

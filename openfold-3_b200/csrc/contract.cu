@@ -215,7 +215,8 @@ contract_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
 template <int BN>
 int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
                     int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
-                    long long o_bs, int rows_per_block, long long row_block_stride, cudaStream_t stream) {
+                    long long o_bs, int rows_per_block, long long row_block_stride, cudaStream_t stream,
+                    int account_as) {
     using Cfg = ContractCfg<BN>;
     CUtensorMap tmA, tmB;
     {
@@ -242,7 +243,7 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
     const long long tiles = (long long)batch * ceil_div(M, kBM) * ceil_div(N, BN);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     int* status = device_status_ptr();
-    LaunchScope scope(kKernelIdContract, stream);
+    LaunchScope scope(account_as, stream);  // launch accounting: the triangle einsum or a plain linear layer
     contract_nt_kernel<BN><<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, batch,
                                                                    o_bs, ldo, rows_per_block, row_block_stride,
                                                                    status);
@@ -254,7 +255,8 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
 
 int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
                      int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
-                     long long o_bs, cudaStream_t stream, int rows_per_block, long long row_block_stride) {
+                     long long o_bs, cudaStream_t stream, int rows_per_block, long long row_block_stride,
+                     int account_as) {
     OF3_REQUIRE(a && b && out, OF3_ERR_ARG, "contract: null pointer");
     OF3_REQUIRE(batch > 0 && M > 0 && N > 0 && K > 0, OF3_ERR_ARG, "contract: non-positive size");
     OF3_REQUIRE(lda % 8 == 0 && ldb % 8 == 0 && ldo % 8 == 0 && a_bs % 8 == 0 && b_bs % 8 == 0 &&
@@ -266,9 +268,9 @@ int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat
                 "contract: row block stride must be a multiple of 8 elements");
     if (N > 128)
         return launch_contract<256>(a, b, out, batch, M, N, K, lda, ldb, ldo, a_bs, b_bs, o_bs, rows_per_block,
-                                    row_block_stride, stream);
+                                    row_block_stride, stream, account_as);
     return launch_contract<128>(a, b, out, batch, M, N, K, lda, ldb, ldo, a_bs, b_bs, o_bs, rows_per_block,
-                                row_block_stride, stream);
+                                row_block_stride, stream, account_as);
 }
 
 }  // namespace of3
@@ -280,5 +282,5 @@ extern "C" int of3_contract_nt_bf16(const void* a, const void* b, void* out, int
                                     void* stream) {
     return of3::contract_nt_bf16((const __nv_bfloat16*)a, (const __nv_bfloat16*)b,
                                  (__nv_bfloat16*)out, batch, M, N, K, lda, ldb, ldo, a_batch_stride,
-                                 b_batch_stride, out_batch_stride, (cudaStream_t)stream, 0, 0);
+                                 b_batch_stride, out_batch_stride, (cudaStream_t)stream, 0, 0, 1);
 }

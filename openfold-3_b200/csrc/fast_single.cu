@@ -18,6 +18,7 @@ namespace {
 
 typedef __nv_bfloat16 bf16;
 constexpr int kKidSingle = 8;
+constexpr int kKidLinear = 10;  // linear layers on the contraction kernel: accounted apart from the triangle einsum
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -284,7 +285,7 @@ __global__ void gate_residual_bf16_kernel(const bf16* __restrict__ upd, const bf
 
 int linear_bf16(const bf16* x, const bf16* w, bf16* y, long long rows, int out_dim, int in_dim, cudaStream_t st) {
     return contract_nt_bf16(x, w, y, 1, (int)rows, out_dim, in_dim, in_dim, in_dim, out_dim, rows * in_dim,
-                            (long long)out_dim * in_dim, rows * out_dim, st);
+                            (long long)out_dim * in_dim, rows * out_dim, st, 0, 0, kKidLinear);
 }
 
 template <int D>

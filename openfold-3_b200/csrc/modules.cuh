@@ -81,6 +81,7 @@ int transition_wide(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bflo
 
 int contract_nt_bf16(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat16* out, int batch,
                      int M, int N, int K, int lda, int ldb, int ldo, long long a_bs, long long b_bs,
-                     long long o_bs, cudaStream_t stream, int rows_per_block = 0, long long row_block_stride = 0);
+                     long long o_bs, cudaStream_t stream, int rows_per_block = 0, long long row_block_stride = 0,
+                     int account_as = 1);  // kernel id of the launch accounting: 1 triangle einsum, 10 linear layer
 
 }  // namespace of3

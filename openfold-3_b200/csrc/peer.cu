@@ -10,6 +10,9 @@
 //   * the barrier is a kernel of one warp: lane p stores this rank's epoch into peer p's flag word and
 //     spins, for at most two seconds, until peer p's epoch has arrived in its own flag words. When the
 //     limit runs out the kernel records a status word (kernel id 30) and returns; nothing waits forever.
+//     The pull kernels that follow see the status word and move nothing, the host raises on its next status
+//     check: a step with a failed barrier never yields a silently wrong result. The first barrier of a step
+//     (of3_peer_barrier_step_entry) has a one-minute limit, because there the ranks' hosts may be far apart.
 //     Each rank runs on its own GPU, so the waiting kernels are always co-resident.
 //
 // A buffer may be overwritten by its owner only after another barrier has been passed since the peers
@@ -27,7 +30,8 @@ namespace {
 
 constexpr int kMaxPeers = 8;
 constexpr int kKidBarrier = 30;
-constexpr uint64_t kBarrierLimitNs = 2000000000ull;
+constexpr uint64_t kBarrierLimitNs = 2000000000ull;         // between the layers of a step: ranks are in lock step
+constexpr uint64_t kStepEntryLimitNs = 60000000000ull;      // first barrier of a step: covers host skew between ranks
 
 struct PeerPtrs {
     void* p[kMaxPeers];
@@ -48,7 +52,8 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
 }
 
 // flags.p[r] -> rank r's flag block: words [0, 8) = epoch last announced by rank 0..7, word 8 = r's own epoch
-__global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs flags, int world, int rank, int* status) {
+__global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs flags, int world, int rank, uint64_t limit_ns,
+                                                          int* status) {
     unsigned* mine = reinterpret_cast<unsigned*>(flags.p[rank]);
     unsigned epoch = 0;
     if (threadIdx.x == 0) {
@@ -59,10 +64,12 @@ __global__ void __launch_bounds__(32) peer_barrier_kernel(PeerPtrs flags, int wo
     if ((int)threadIdx.x < world && (int)threadIdx.x != rank) {
         __threadfence_system();  // everything earlier kernels of this GPU wrote is visible before the flag
         st_release_sys(reinterpret_cast<unsigned*>(flags.p[threadIdx.x]) + rank, epoch);
+        // a step that has already failed announces its epoch (the peers are not held up) but waits no more
+        if (status != nullptr && *reinterpret_cast<volatile int*>(status) != 0) return;
         const uint64_t t0 = gtimer();
         unsigned spins = 0;
         while ((int)(ld_acquire_sys(mine + threadIdx.x) - epoch) < 0) {
-            if ((++spins & 255u) == 0 && gtimer() - t0 > kBarrierLimitNs) {
+            if ((++spins & 255u) == 0 && gtimer() - t0 > limit_ns) {
                 if (status != nullptr && atomicCAS(status, 0, 1) == 0) {
                     status[1] = kKidBarrier;
                     status[2] = (int)threadIdx.x;  // the peer that did not arrive
@@ -85,7 +92,10 @@ template <typename V, bool kPush>
 __global__ void __launch_bounds__(256)
 peer_pull_rows_kernel(PeerPtrs srcs, long long src_off, uint8_t* __restrict__ dst, int n0, int n1, int n2,
                       long long s1, long long s2, long long t0, long long t1, long long t2, int vec_per_row,
-                      int rank) {
+                      int rank, const int* __restrict__ status) {
+    // a barrier that gave up (or any other bounded wait of this step) has recorded a status word: the peers'
+    // buffers may be stale or half written, so nothing is moved and the step's result stays visibly unfinished
+    if (status != nullptr && *reinterpret_cast<const volatile int*>(status) != 0) return;
     const long long total = (long long)n0 * n1 * n2 * vec_per_row;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (long long base = (long long)blockIdx.x * blockDim.x + threadIdx.x; base < total; base += 4 * stride) {
@@ -159,7 +169,7 @@ int of3_peer_heap_free(void* ptr) {
     return OF3_OK;
 }
 
-int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream) {
+static int peer_barrier(void* const* flag_blocks, int world, int rank, uint64_t limit_ns, void* stream) {
     OF3_REQUIRE(flag_blocks && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, OF3_ERR_ARG,
                 "peer_barrier: bad argument (world %d, rank %d)", world, rank);
     PeerPtrs f{};
@@ -168,9 +178,17 @@ int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream
         f.p[r] = flag_blocks[r];
     }
     LaunchScope scope(kKidBarrier, (cudaStream_t)stream);
-    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, world, rank, device_status_ptr());
+    peer_barrier_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, world, rank, limit_ns, device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
+}
+
+int of3_peer_barrier(void* const* flag_blocks, int world, int rank, void* stream) {
+    return peer_barrier(flag_blocks, world, rank, kBarrierLimitNs, stream);
+}
+
+int of3_peer_barrier_step_entry(void* const* flag_blocks, int world, int rank, void* stream) {
+    return peer_barrier(flag_blocks, world, rank, kStepEntryLimitNs, stream);
 }
 
 static int peer_rows(void* const* srcs, long long src_off, void* dst, int world, int rank, int n1, int n2,
@@ -197,18 +215,19 @@ static int peer_rows(void* const* srcs, long long src_off, void* dst, int world,
     LaunchScope scope(31, (cudaStream_t)stream);
     cudaStream_t st = (cudaStream_t)stream;
     uint8_t* d = (uint8_t*)dst;
+    const int* status = device_status_ptr();
     if (vec && push)
         peer_pull_rows_kernel<uint4, true><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2, t0, t1,
-                                                                             t2, vpr, rank);
+                                                                             t2, vpr, rank, status);
     else if (vec)
         peer_pull_rows_kernel<uint4, false><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2, t0,
-                                                                              t1, t2, vpr, rank);
+                                                                              t1, t2, vpr, rank, status);
     else if (push)
         peer_pull_rows_kernel<uint16_t, true><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2, t0,
-                                                                                t1, t2, vpr, rank);
+                                                                                t1, t2, vpr, rank, status);
     else
         peer_pull_rows_kernel<uint16_t, false><<<(unsigned)blocks, 256, 0, st>>>(s, src_off, d, world, n1, n2, s1, s2,
-                                                                                 t0, t1, t2, vpr, rank);
+                                                                                 t0, t1, t2, vpr, rank, status);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }

@@ -233,6 +233,16 @@ extern "C" int of3_device_status(int* out4) {
     return OF3_OK;
 }
 
+// Stream-ordered copy of the status block into pinned host memory (no synchronisation): callers that replay
+// CUDA graphs read it one step late instead of stalling the stream.
+extern "C" int of3_device_status_async(int* host4, void* stream) {
+    int* p = of3::device_status_ptr();
+    OF3_REQUIRE(p != nullptr, OF3_ERR_ARG, "no device status block (no CUDA device?)");
+    OF3_REQUIRE(host4 != nullptr, OF3_ERR_ARG, "host4 is null");
+    OF3_CUDA_CHECK(cudaMemcpyAsync(host4, p, 4 * sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return OF3_OK;
+}
+
 extern "C" int of3_device_status_clear(void) {
     int* p = of3::device_status_ptr();
     OF3_REQUIRE(p != nullptr, OF3_ERR_ARG, "no device status block (no CUDA device?)");

@@ -17,7 +17,9 @@ int make_tmap_bf16(CUtensorMap* out, const void* base, int rank, const uint64_t*
 // kernel id: launches are always counted; when timing is enabled (of3_profile_enable) a CUDA event
 // pair is recorded around the launch on the launching stream, and of3_profile_read sums their
 // elapsed times. Ids: 1 contract, 2 trimul_in, 3 trimul_out, 4 transition, 5 triattn_proj,
-// 6 triattn_core, 7 triattn_out, 20 the shape-generic SIMT kernels.
+// 6 triattn_core, 7 triattn_out, 8 single-track kernels, 9 pair-bias projection, 10 linear layers of the
+// single track (the contraction kernel as a plain GEMM), 20 the shape-generic SIMT kernels, 30 / 31 peer
+// barrier / pull.
 constexpr int kMaxKernelIds = 32;
 struct LaunchScope {
     int kid;

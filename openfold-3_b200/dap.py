@@ -389,8 +389,11 @@ class PeerExchange:
         return self.heap.tensor(name, shape, dtype)
 
     def begin(self):
-        """Start of a step: the peers have finished reading the previous step's buffers."""
-        self.barrier()
+        """Start of a step: the peers have finished reading the previous step's buffers. The ranks' hosts may
+        reach this point far apart (data loading, a first graph replay), so this barrier alone has a long limit."""
+        if self.use_barrier and self.world > 1:
+            lib._check(self.l.of3_peer_barrier_step_entry(self.heap.c_bases, self.world, self.rank, self.ops._st()),
+                       "of3_peer_barrier_step_entry")
 
     def barrier(self):
         if self.use_barrier and self.world > 1:
@@ -476,6 +479,7 @@ class DapPairFormerStack:
         self.stack, self.world, self.rank, self.group = stack, world, rank, group
         self.ops = ops
         self.x = exchange if exchange is not None else NcclExchange(world, rank, group, ops)
+        self.check_status = True  # eager steps end with a (synchronising) read of the device status block
 
     def shard(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
         R = t.shape[dim] // self.world
@@ -533,7 +537,7 @@ class DapPairFormerStack:
             z_loc = z_in.contiguous().clone()
         else:
             z_loc.copy_(z_in)
-        s_full = s[0].clone(memory_format=torch.contiguous_format)
+        s_full = None if s is None else s[0].clone(memory_format=torch.contiguous_format)
         if sharded:
             mask_rows, maskT_rows = (m.to(z.dtype).contiguous() for m in pair_mask)
         else:
@@ -547,7 +551,11 @@ class DapPairFormerStack:
         zb_buf, zb_free = [None, None], [None, None]
         pending = None  # (rows of s updated on the side stream, event after them)
         for i, block in enumerate(self.stack.blocks):
-            z_loc = self.pair_block(z_loc, mask_rows, maskT_rows, block.pair_stack, _mask_trans)
+            # a PairFormerBlock (pair stack + single track) or a bare PairBlock (pair stack only: s is None)
+            pair_stack = getattr(block, "pair_stack", block)
+            z_loc = self.pair_block(z_loc, mask_rows, maskT_rows, pair_stack, _mask_trans)
+            if s_full is None or not hasattr(block, "attn_pair_bias"):
+                continue
             slot = i & 1
             wait(zb_free[slot])  # the side stream has finished with this buffer (two blocks ago)
             zb_buf[slot] = ops.pair_bias_project(z_loc, block.attn_pair_bias, out=zb_buf[slot])   # [H, R, N]
@@ -562,12 +570,24 @@ class DapPairFormerStack:
         if pending is not None:
             wait(pending[1])
             s_full = X.gather_rows(pending[0])
-        if s_full.is_cuda and not torch.cuda.is_current_stream_capturing():
+        if s_full is not None and s_full.is_cuda and not torch.cuda.is_current_stream_capturing():
             s_full.record_stream(torch.cuda.current_stream(s_full.device))
+        if s_full is None:
+            if sharded:
+                return self._checked(None, z_loc.unsqueeze(0))
+            return self._checked(None, X.gather_rows(z_loc.view(R, -1)).view(1, N, N, z_loc.shape[-1]))
         if sharded:
-            return s_full.unsqueeze(0), z_loc.unsqueeze(0)
+            return self._checked(s_full.unsqueeze(0), z_loc.unsqueeze(0))
         z_full = X.gather_rows(z_loc.view(R, -1)).view(1, N, N, z_loc.shape[-1])
-        return s_full.unsqueeze(0), z_full
+        return self._checked(s_full.unsqueeze(0), z_full)
+
+    def _checked(self, s_out, z_out):
+        """End of an eager step on a GPU: a bounded device-side wait that ran out (a peer that never reached a
+        barrier, a stalled pipeline) raises here instead of handing back a half-exchanged result. Synchronises;
+        a captured step is checked by its replayer (GraphedDapRunner) one step late instead."""
+        if z_out.is_cuda and not torch.cuda.is_current_stream_capturing() and self.check_status:
+            lib.check_device_status()
+        return s_out, z_out
 
 
 class GraphedDapRunner:
@@ -583,7 +603,7 @@ class GraphedDapRunner:
     def __init__(self, runner: DapPairFormerStack, s, z, single_mask, pair_mask, warmup: int = 2,
                  sharded: bool = False):
         self.runner, self.sharded = runner, sharded
-        self.s_in, self.z_in = s.clone(), z.clone()
+        self.s_in, self.z_in = (None if s is None else s.clone()), z.clone()
         self.sm_in = None if single_mask is None else single_mask.clone()
         self.pm_in = tuple(m.clone() for m in pair_mask) if sharded else pair_mask.clone()
         dev = z.device
@@ -598,6 +618,9 @@ class GraphedDapRunner:
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph), torch.no_grad():
             self.s_out, self.z_out = runner(self.s_in, self.z_in, self.sm_in, self.pm_in, sharded=sharded)
+        # status of each replay, copied stream-ordered into pinned memory and looked at before the next replay
+        self._status = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._status_ready = None
 
     def __call__(self, s, z, single_mask, pair_mask):
         pairs = [(self.s_in, s), (self.z_in, z), (self.sm_in, single_mask)]
@@ -605,8 +628,31 @@ class GraphedDapRunner:
         for dst, src in pairs:
             if dst is not None and src is not None and dst.data_ptr() != src.data_ptr():
                 dst.copy_(src, non_blocking=True)
+        self.check(wait=False)
         self.graph.replay()
+        l = lib.load()
+        st = torch.cuda.current_stream(self.z_in.device)
+        lib._check(l.of3_device_status_async(self._status.data_ptr(), st.cuda_stream), "of3_device_status_async")
+        self._status_ready = torch.cuda.Event()
+        self._status_ready.record(st)
         return self.s_out, self.z_out
+
+    def check(self, wait: bool = True):
+        """Raises if a device-side wait of an earlier replay ran out (e.g. a rank that never reached a barrier):
+        the outputs of that replay are not to be used. Called without waiting before every replay, so a failure
+        surfaces at most one step late; call it with ``wait=True`` before consuming the last step's result."""
+        if self._status_ready is None:
+            return
+        if wait:
+            self._status_ready.synchronize()
+        elif not self._status_ready.query():
+            return
+        self._status_ready = None
+        if int(self._status[0]) != 0:
+            code = [int(v) for v in self._status]
+            lib.load().of3_device_status_clear()
+            raise RuntimeError(f"device-side wait ran out during a replayed step: code {code[0]}, kernel {code[1]}, "
+                               f"block {code[2]}, site {code[3]}")
 
     def release(self):
         """Drops the graph (and with it its hold on the communicator) and the static buffers."""

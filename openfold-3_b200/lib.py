@@ -43,6 +43,7 @@ SIGNATURES = {
     "of3_last_error_string": (c_char_p, []),
     "of3_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "of3_device_status_clear": (c_int, []),
+    "of3_device_status_async": (c_int, [c_void_p, c_void_p]),
     "of3_profile_enable": (c_int, [c_int]),
     "of3_profile_reset": (c_int, []),
     "of3_profile_read": (c_int, [c_int, ctypes.POINTER(c_longlong), ctypes.POINTER(c_float)]),
@@ -90,6 +91,7 @@ SIGNATURES = {
     "of3_peer_heap_close": (c_int, [c_void_p]),
     "of3_peer_heap_free": (c_int, [c_void_p]),
     "of3_peer_barrier": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "of3_peer_barrier_step_entry": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
     "of3_peer_pull_rows": (c_int, [ctypes.POINTER(c_void_p), c_longlong, c_void_p, c_int, c_int, c_int, c_int]
                            + [c_longlong] * 5 + [c_int, c_void_p]),
     "of3_peer_push_rows": (c_int, [ctypes.POINTER(c_void_p), c_longlong, c_void_p, c_int, c_int, c_int, c_int]
@@ -138,7 +140,8 @@ def check_device_status():
 
 
 KERNEL_NAMES = {1: "trimul_contract", 2: "trimul_in", 3: "trimul_out", 4: "transition", 5: "triattn_proj",
-                6: "triattn_core", 7: "triattn_out", 8: "single_track", 9: "pair_bias", 20: "generic", 30: "peer_barrier",
+                6: "triattn_core", 7: "triattn_out", 8: "single_track", 9: "pair_bias", 10: "single_linear",
+                20: "generic", 30: "peer_barrier",
                 31: "peer_pull"}
 
 

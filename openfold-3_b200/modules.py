@@ -522,6 +522,33 @@ class PairFormerStack(nn.Module):
         return s, z
 
 
+class PairStack(nn.Module):
+    """Consecutive ``PairBlock``s applied to one pair tensor: the "pair stack only" workloads. The reference has no
+    class for it; its callers keep a ``nn.ModuleList`` of ``PairBlock``s and call them in sequence with the same
+    pair mask (openfold3/core/model/latent/template_module.py:148-189), which is what ``forward`` does.
+    Parameters are named ``blocks.{i}.<PairBlock key>``."""
+
+    def __init__(self, no_blocks, c_z, c_hidden_mul, c_hidden_pair_att, no_heads_pair, transition_type,
+                 transition_n, pair_dropout, fuse_projection_weights, inf,
+                 linear_init_params=lin_init.pair_block_init):
+        super().__init__()
+        self.blocks = nn.ModuleList([
+            PairBlock(c_z=c_z, c_hidden_mul=c_hidden_mul, c_hidden_pair_att=c_hidden_pair_att,
+                      no_heads_pair=no_heads_pair, transition_type=transition_type, transition_n=transition_n,
+                      pair_dropout=pair_dropout, fuse_projection_weights=fuse_projection_weights, inf=inf,
+                      linear_init_params=linear_init_params)
+            for _ in range(no_blocks)
+        ])
+
+    def forward(self, z, pair_mask, inplace_safe=False, _mask_trans=True):
+        _forward_only(self, z)
+        if not (inplace_safe and z.is_contiguous()):
+            z = z.clone(memory_format=torch.contiguous_format)
+        for b in self.blocks:
+            z = b(z, pair_mask, inplace_safe=True, _mask_trans=_mask_trans)
+        return z
+
+
 class DiffusionTransformerBlock(nn.Module):
     """AF3 Algorithm 23 block. Drop-in for openfold3/core/model/layers/diffusion_transformer.py:30-179
     (the ``n_query is None`` token-level branch)."""

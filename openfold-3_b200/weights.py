@@ -115,6 +115,14 @@ def pairformer_block_params(seed: int, c_s=384, c_z=128, c_hidden_pair_bias=24, 
     return P
 
 
+def pair_stack_params(seed: int, no_blocks: int, prefix: str = "", **kw) -> dict[str, torch.Tensor]:
+    """Parameters of a ``PairStack`` (keys ``blocks.{i}.…``)."""
+    P: dict[str, torch.Tensor] = {}
+    for i in range(no_blocks):
+        P.update(pair_block_params(seed * 1000 + i, prefix=f"{prefix}blocks.{i}.", **kw))
+    return P
+
+
 def pairformer_stack_params(seed: int, no_blocks: int, prefix: str = "", **kw) -> dict[str, torch.Tensor]:
     """Parameters of a ``PairFormerStack`` (keys ``blocks.{i}.…``)."""
     P: dict[str, torch.Tensor] = {}

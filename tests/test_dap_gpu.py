@@ -233,3 +233,42 @@ def test_peer_exchange_matches_whole_tensor(pkg, P, N):
         assert torch.equal(s_all[r], s_all[0]) and torch.equal(z_all[r], z_all[0])
     assert cases.rel_err(z_all[0].float().cpu(), z_ref.float().cpu()) < 2e-2
     assert cases.rel_err(s_all[0].unsqueeze(0).float().cpu(), s_ref.float().cpu()) < 2e-2
+
+
+def test_barrier_whose_peer_never_arrives_poisons_the_step(pkg):
+    """Failure detection without a fault: rank 0 of a 2-rank world runs the barrier kernel, nobody plays rank 1,
+    so its flag word is never set. The kernel's bounded wait (2 s) runs out, it records a status word and returns;
+    the pull queued behind it moves nothing (its destination keeps its contents), later barriers do not wait
+    again, and the host's status check raises and clears the block. The context stays usable."""
+    import ctypes
+    import time
+
+    dev = torch.device("cuda:0")
+    l = pkg.lib.load()
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    heaps = pkg.dap.LocalPeerHeaps(1 << 16, 2, dev)
+    h0 = heaps.view(0)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    src = h0.tensor("src", (2, 64), torch.float32)
+    heaps.store[0][:] = 0
+    heaps.store[1][:] = 0
+    heaps.view(0).tensor("src", (2, 64), torch.float32).fill_(1.0)
+    heaps.view(1).tensor("src", (2, 64), torch.float32).fill_(2.0)
+    dst = torch.full((2, 2, 64), -7.0, device=dev)
+    t0 = time.time()
+    assert l.of3_peer_barrier(h0.c_bases, 2, 0, st) == 0
+    off = h0.offset_of(src)
+    assert l.of3_peer_pull_rows(h0.c_bases, off, dst.data_ptr(), 2, 0, 1, 2, 0, 256, 512, 0, 256, 256, st) == 0
+    assert l.of3_peer_barrier(h0.c_bases, 2, 0, st) == 0   # must not wait another two seconds
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    assert 1.5 < waited < 3.5, waited
+    assert torch.all(dst == -7.0), "a pull behind a failed barrier must move nothing"
+    with pytest.raises(RuntimeError, match="kernel 30"):
+        pkg.lib.check_device_status()
+    pkg.lib.check_device_status()  # cleared
+    # with the status clear the same pull moves the rows
+    assert l.of3_peer_pull_rows(h0.c_bases, off, dst.data_ptr(), 2, 0, 1, 2, 0, 256, 512, 0, 256, 256, st) == 0
+    torch.cuda.synchronize()
+    assert torch.all(dst[0] == 1.0) and torch.all(dst[1] == 2.0)
