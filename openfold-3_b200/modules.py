@@ -368,7 +368,17 @@ class AttentionPairBias(nn.Module):
                     m.linear_q.weight, m.linear_q.bias, m.linear_k.weight, m.linear_v.weight,
                     m.linear_g.weight, m.linear_o.weight), dtype, device)
 
-    def _run(self, a, z, s, mask, in_place: bool):
+    def _run(self, a, z, s, mask, in_place: bool, high_precision: bool = False):
+        """``high_precision`` (the reference's ``use_high_precision_attention``, which computes logits and softmax
+        in fp32: openfold3/core/model/primitives/attention.py:99-120, 314-339): bf16 inputs are evaluated by the
+        fp32 validation kernels (true fp32 products everywhere) and the result is rounded once at the end."""
+        if high_precision and a.dtype != torch.float32:
+            f32 = lambda t: None if t is None else t.float()
+            upd = self._run(f32(a), f32(z), f32(s), f32(mask), in_place=False)
+            if in_place:
+                a.add_(upd.to(a.dtype))
+                return a
+            return upd.to(a.dtype)
         N = a.shape[-2]
         batch = a.shape[:-2]
         ac = a.contiguous().view(-1, N, self.c_q)
@@ -400,7 +410,7 @@ class AttentionPairBias(nn.Module):
                 use_cueq_triangle_kernels=False, use_lma=False, use_high_precision_attention=False):
         """a [*, N, C_q], z [*, N, N, C_z], s [*, N, C_s], mask [*, N] -> update [*, N, C_q]."""
         _forward_only(self, a, z, s)
-        return self._run(a, z, s, mask, in_place=False)
+        return self._run(a, z, s, mask, in_place=False, high_precision=use_high_precision_attention)
 
 
 # --------------------------------------------------------------------------- blocks and stacks
@@ -572,7 +582,7 @@ class DiffusionTransformerBlock(nn.Module):
                 use_lma=False, use_high_precision_attention=False, _mask_trans=True, _in_place=False):
         _forward_only(self, a, s, z)
         a = a if _in_place and a.is_contiguous() else a.clone(memory_format=torch.contiguous_format)
-        self.attention_pair_bias._run(a, z, s, mask, in_place=True)
+        self.attention_pair_bias._run(a, z, s, mask, in_place=True, high_precision=use_high_precision_attention)
         self.conditioned_transition._run(a, s, mask if _mask_trans else None, in_place=True)
         return a
 
@@ -599,5 +609,6 @@ class DiffusionTransformer(nn.Module):
         _forward_only(self, a, s, z)
         a = a.clone(memory_format=torch.contiguous_format)
         for b in self.blocks:
-            a = b(a, s, z, mask=mask, _mask_trans=_mask_trans, _in_place=True)
+            a = b(a, s, z, mask=mask, use_high_precision_attention=use_high_precision_attention,
+                  _mask_trans=_mask_trans, _in_place=True)
         return a

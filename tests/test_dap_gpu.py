@@ -272,3 +272,44 @@ def test_barrier_whose_peer_never_arrives_poisons_the_step(pkg):
     assert l.of3_peer_pull_rows(h0.c_bases, off, dst.data_ptr(), 2, 0, 1, 2, 0, 256, 512, 0, 256, 256, st) == 0
     torch.cuda.synchronize()
     assert torch.all(dst[0] == 1.0) and torch.all(dst[1] == 2.0)
+
+
+def test_large_complex_shape_p8_n2048_row_shards_match_whole_tensor(pkg):
+    """The large-complex configuration's shape on one GPU: N = 2048 split into 8 virtual ranks of 256 rows,
+    5 % of the tokens padded at random (outer-product pair mask), one PairBlock through the phase kernels with
+    the peer-heap exchange (pulls between the virtual ranks' heaps; the host's program order stands in for
+    the barrier kernel) against the same block on the whole tensor. N = 2048 is the largest size the attention
+    core keeps a mask row for, and the only benchmark shape with 64 key blocks per line."""
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    P, N = 8, 2048
+    R = N // P
+    g = torch.Generator().manual_seed(2048)
+    z = torch.randn(1, N, N, 128, generator=g).to(bf)
+    tm = torch.ones(N)
+    tm[torch.randperm(N, generator=g)[:102]] = 0
+    pm = (tm[:, None] * tm[None, :]).to(bf)
+    blk = pkg.PairBlock(**cases.PAIR, transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False,
+                        inf=1e9)
+    blk.load_state_dict(pkg.weights.pair_block_params(seed=2048, **cases.PAIR), strict=True)
+    blk = blk.to(dev, bf).eval()
+    ops = pkg.dap.CudaOps(dev)
+    heaps = pkg.dap.LocalPeerHeaps(pkg.dap.PeerExchange.heap_bytes(N, P), P, dev)
+    X = [pkg.dap.PeerExchange(heaps.view(r), ops, barrier=False) for r in range(P)]
+    zd, pmd = z.to(dev), pm.to(dev)
+    with torch.no_grad():
+        z_ref = blk(zd, pmd[None], inplace_safe=False)
+        shards = []
+        for r in range(P):
+            t = X[r].buf("z0", (R, N, 128), bf, dev)
+            t.copy_(zd[0, r * R:(r + 1) * R])
+            shards.append(t)
+        out = _virtual_pair_block_peer(ops, X, shards, pmd, blk, P)
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    z_dap = torch.cat([o for o in out], 0)
+    valid = (pmd > 0)
+    d = (z_dap.float() - z_ref[0].float())[valid]
+    rms = z_ref[0].float()[valid].pow(2).mean().sqrt()
+    assert torch.isfinite(z_dap.float()).all()
+    assert float(d.abs().max() / rms) < 2e-2, float(d.abs().max() / rms)

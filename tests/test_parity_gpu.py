@@ -125,3 +125,28 @@ def test_repeatable(pkg, dev):
     b = cases.run_dropin("block_n40_padded", P, x, dev, torch.bfloat16)
     torch.cuda.synchronize()
     assert torch.equal(a["z"], b["z"]) and torch.equal(a["s"], b["s"])
+
+
+def test_high_precision_attention_flag_selects_the_fp32_kernels(pkg, dev):
+    """``use_high_precision_attention=True`` (openfold3/core/model/primitives/attention.py:99-120): bf16 tensors
+    in and out, fp32 arithmetic in between -- the update then carries only the bf16 rounding of inputs already
+    rounded and of the result (2^-9 relative), well below the bf16 kernels' own error."""
+    name = "diffusion_block_n24"
+    P, x, run_oracle = cases.CASES[name]()
+    bf = torch.bfloat16
+    Pq = {k: v.to(bf).float() for k, v in P.items()}
+    xq = {k: v.to(bf).float() for k, v in x.items()}
+    ref = run_oracle(Pq, xq)["attn_update"]
+    blk = pkg.DiffusionTransformerBlock(**cases.DIFF, use_ada_layer_norm=True, n_query=None, n_key=None, inf=1e9)
+    blk.load_state_dict(P, strict=True)
+    blk = blk.to(dev, bf).eval()
+    xd = {k: v.to(dev, bf) for k, v in x.items()}
+    with torch.no_grad():
+        hp = blk.attention_pair_bias(a=xd["a"], z=xd["z"], s=xd["s"], mask=xd["mask"], use_high_precision_attention=True)
+        lp = blk.attention_pair_bias(a=xd["a"], z=xd["z"], s=xd["s"], mask=xd["mask"])
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    assert hp.dtype == bf
+    e_hp, e_lp = cases.rms_err(hp.float().cpu(), ref), cases.rms_err(lp.float().cpu(), ref)
+    print(f"attn_update RMS error: high precision {e_hp:.3e}, bf16 kernels {e_lp:.3e}")
+    assert e_hp < 2.5e-3 and e_hp < 0.6 * e_lp
