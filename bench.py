@@ -340,6 +340,9 @@ def build_job(pkg, cfg, n, blocks, dev, world, rank):
         else:
             job["host_in"], job["host_out"] = (), ()
         model = model.to(dev, bf).eval()
+        # the timed step recomputes the 24 pair-bias projections like the reference does (a step whose outputs
+        # come out of a cache would not be the workload); the hoisted variant is timed separately
+        model.hoist_pair_bias = False
         job["model"] = model
         job["run"] = lambda x: (model(x[0], x[1], x[2], mask=x[3]),) if x else ()
         return job
@@ -602,11 +605,29 @@ def run_ours(args, cfg) -> None:
         eager_launches = int(sum(l for l, _ in counted.values()))
         launches_in_timed_region = eager_launches if graphed is None else launches_per_step * args.steps
 
+    ms_hoisted = 0.0
+    if kind == "diffusion" and job["host_in"]:
+        # the same step inside a rollout: the pair tensor is unchanged from call to call, so the projections of all
+        # blocks are computed once and kept (DiffusionTransformer.hoist_pair_bias); reported next to the headline
+        with torch.no_grad():
+            model.hoist_pair_bias = True
+            for _ in range(2):
+                step_resident(x_dev)
+            torch.cuda.synchronize(dev)
+            e4, e5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e4.record()
+            for _ in range(args.steps):
+                step_resident(x_dev)
+            e5.record()
+            torch.cuda.synchronize(dev)
+            ms_hoisted = e4.elapsed_time(e5) / args.steps
+            model.hoist_pair_bias = False
+
     # ---- max over ranks
     if world > 1:
-        t = torch.tensor([ms_resident, ms_e2e], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms_resident, ms_e2e, ms_hoisted], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_resident, ms_e2e = float(t[0]), float(t[1])
+        ms_resident, ms_e2e, ms_hoisted = float(t[0]), float(t[1]), float(t[2])
 
     flop = workload_flops(cfg, n, blocks)
     value = flop / (ms_resident * 1e-3) / 1e12
@@ -688,6 +709,11 @@ def run_ours(args, cfg) -> None:
         }
         if parity is not None:
             line["parity_vs_single_gpu"] = parity
+        if ms_hoisted > 0:
+            line["rollout_step_with_hoisted_pair_bias"] = {
+                "ms_per_step": round(ms_hoisted, 3), "value": round(flop / (ms_hoisted * 1e-3) / 1e12, 2),
+                "note": "same step when the pair tensor is unchanged since the previous call (a diffusion rollout): the "
+                        "blocks' pair-bias projections are reused; the flop count still includes them"}
         print(json.dumps(line))
     if world > 1:
         if graphed is not None:  # a live graph still holds the communicator's captured work

@@ -269,6 +269,41 @@ def attn_pair_bias_forward(a, z, s, mask, out, params, H: int, d: int, inf: floa
            "of3_attn_pair_bias_forward")
 
 
+def pair_bias_project(z, ln_w, ln_b, w, out=None):
+    """Pair-bias projection of AttentionPairBias for whole pair tensors: z [Bz, N, N, 128], LayerNorm_z weight /
+    bias (bias may be None), linear_z.weight [16, 128] -> [Bz, 16, N, N] fp32."""
+    _require_cuda(z, "z")
+    lib = load()
+    Bz, N = z.shape[0], z.shape[1]
+    H = w.shape[0]
+    if out is None:
+        out = torch.empty((Bz, H, N, N), dtype=torch.float32, device=z.device)
+    for b in range(Bz):
+        _check(lib.of3_pair_bias_project(z[b].data_ptr(), _ptr(ln_w), _ptr(ln_b), w.data_ptr(), out[b].data_ptr(),
+                                         N * N, z.shape[-1], H, dtype_code(z.dtype), _stream(z.device)),
+               "of3_pair_bias_project")
+    return out
+
+
+def attn_pair_bias_forward_prebias(a, pair_bias, s, mask, out, params, H: int, d: int, inf: float, ada: bool,
+                                   add_residual: bool):
+    """attn_pair_bias_forward with the pair bias [Bz, H, N, N] (fp32) already projected (c_z = 128)."""
+    _require_cuda(a, "a")
+    lib = load()
+    Ba, N, c_a = a.shape
+    Bz = pair_bias.shape[0]
+    c_s = s.shape[-1] if s is not None else 0
+    dt = dtype_code(a.dtype)
+    flags = extra_flags | (FLAG_ADA_LN if ada else 0) | (FLAG_ADD_RESIDUAL if add_residual else 0)
+    nbytes = lib.of3_attn_pair_bias_workspace_bytes(Ba, Bz, N, c_a, c_s, 128, H, d, dt, flags)
+    ws = workspace(nbytes, a.device)
+    p = AttnPairBiasParams(*[_ptr(t) for t in params])
+    _check(lib.of3_attn_pair_bias_forward_prebias(a.data_ptr(), pair_bias.data_ptr(), _ptr(s), _ptr(mask),
+                                                  out.data_ptr(), Ba, Bz, N, c_a, c_s, H, d, float(inf), dt, flags,
+                                                  ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream(a.device)),
+           "of3_attn_pair_bias_forward_prebias")
+
+
 def cond_transition_forward(a, s, mask, out, params, n: int, add_residual: bool):
     _require_cuda(a, "a")
     lib = load()

@@ -368,7 +368,21 @@ class AttentionPairBias(nn.Module):
                     m.linear_q.weight, m.linear_q.bias, m.linear_k.weight, m.linear_v.weight,
                     m.linear_g.weight, m.linear_o.weight), dtype, device)
 
-    def _run(self, a, z, s, mask, in_place: bool, high_precision: bool = False):
+    def can_hoist_pair_bias(self, z) -> bool:
+        """Whether ``project_pair_bias`` has a kernel for this layer (c_z = 128, 16 heads, bf16 or fp32)."""
+        return (self.c_z == 128 and self.no_heads == 16 and z.is_cuda
+                and z.dtype in (torch.bfloat16, torch.float32) and lib.extra_flags == 0)
+
+    def project_pair_bias(self, z):
+        """linear_z(LayerNorm_z(z)) permuted to [*, H, N, N] (fp32): the part of this layer that depends on z only
+        (openfold3/core/model/layers/attention_pair_bias.py:154-163), so callers that apply the layer many times to
+        one pair tensor -- the diffusion rollout -- compute it once and pass it to ``_run(pair_bias=...)``."""
+        N = z.shape[-2]
+        zc = z.contiguous().view(-1, N, N, self.c_z)
+        prm = self._params(z.dtype, z.device)
+        return lib.pair_bias_project(zc, prm[8], prm[9], prm[10])
+
+    def _run(self, a, z, s, mask, in_place: bool, high_precision: bool = False, pair_bias=None):
         """``high_precision`` (the reference's ``use_high_precision_attention``, which computes logits and softmax
         in fp32: openfold3/core/model/primitives/attention.py:99-120, 314-339): bf16 inputs are evaluated by the
         fp32 validation kernels (true fp32 products everywhere) and the result is rounded once at the end."""
@@ -401,9 +415,15 @@ class AttentionPairBias(nn.Module):
         m = _mask_like(mask, a.shape[:-1], a.dtype)
         m = None if m is None else m.view(-1, N)
         out = ac if in_place else torch.empty_like(ac)
-        lib.attn_pair_bias_forward(ac, zc, sc, m, out, self._params(a.dtype, a.device), self.no_heads,
-                                   self.c_hidden, self.inf, self.use_ada_layer_norm, add_residual=in_place)
         assert Ba % zc.shape[0] == 0
+        if pair_bias is not None:
+            assert pair_bias.shape == (zc.shape[0], self.no_heads, N, N) and pair_bias.dtype == torch.float32
+            lib.attn_pair_bias_forward_prebias(ac, pair_bias, sc, m, out, self._params(a.dtype, a.device),
+                                               self.no_heads, self.c_hidden, self.inf, self.use_ada_layer_norm,
+                                               add_residual=in_place)
+        else:
+            lib.attn_pair_bias_forward(ac, zc, sc, m, out, self._params(a.dtype, a.device), self.no_heads,
+                                       self.c_hidden, self.inf, self.use_ada_layer_norm, add_residual=in_place)
         return out.view(a.shape)
 
     def forward(self, a, z, s=None, mask=None, use_deepspeed_evo_attention=False,
@@ -579,10 +599,12 @@ class DiffusionTransformerBlock(nn.Module):
             c_a=c_a, c_s=c_s, n=n_transition, linear_init_params=linear_init_params.cond_transition)
 
     def forward(self, a, s, z, mask=None, use_deepspeed_evo_attention=False, use_cueq_triangle_kernels=False,
-                use_lma=False, use_high_precision_attention=False, _mask_trans=True, _in_place=False):
+                use_lma=False, use_high_precision_attention=False, _mask_trans=True, _in_place=False,
+                _pair_bias=None):
         _forward_only(self, a, s, z)
         a = a if _in_place and a.is_contiguous() else a.clone(memory_format=torch.contiguous_format)
-        self.attention_pair_bias._run(a, z, s, mask, in_place=True, high_precision=use_high_precision_attention)
+        self.attention_pair_bias._run(a, z, s, mask, in_place=True, high_precision=use_high_precision_attention,
+                                      pair_bias=None if use_high_precision_attention else _pair_bias)
         self.conditioned_transition._run(a, s, mask if _mask_trans else None, in_place=True)
         return a
 
@@ -603,12 +625,39 @@ class DiffusionTransformer(nn.Module):
                                       linear_init_params=linear_init_params)
             for _ in range(no_blocks)
         ])
+        # Pair-bias hoisting: every block's linear_z(LayerNorm_z(z)) depends on z only, and the diffusion rollout
+        # calls this stack ~200 times with the same pair tensor (openfold3/core/model/structure/
+        # diffusion_module.py:362-398). The projections of all blocks are kept ([no_blocks][*, H, N, N] fp32,
+        # 0.9 GB at N = 768) for as long as the caller passes the same, unmodified z; set to False to recompute them
+        # in every call (what the reference does).
+        self.hoist_pair_bias = True
+        self._bias_cache = None   # (weakref to z, z._version, parameter versions, [bias per block])
+
+    def _pair_biases(self, z):
+        import weakref
+
+        apbs = [b.attention_pair_bias for b in self.blocks]
+        if not (self.hoist_pair_bias and all(m.can_hoist_pair_bias(z) for m in apbs)):
+            return [None] * len(apbs)
+        pv = tuple((m.layer_norm_z.weight._version, m.linear_z.weight._version, m.linear_z.weight.data_ptr())
+                   for m in apbs)
+        try:
+            zv = z._version
+        except RuntimeError:   # inference tensors do not track versions: nothing to key the cache on
+            return [m.project_pair_bias(z) for m in apbs]
+        c = self._bias_cache
+        if c is not None and c[0]() is z and c[1] == zv and c[2] == pv:
+            return c[3]
+        biases = [m.project_pair_bias(z) for m in apbs]
+        self._bias_cache = (weakref.ref(z), zv, pv, biases)
+        return biases
 
     def forward(self, a, s, z, mask=None, use_deepspeed_evo_attention=False, use_cueq_triangle_kernels=False,
                 use_lma=False, use_high_precision_attention=False, _mask_trans=True):
         _forward_only(self, a, s, z)
         a = a.clone(memory_format=torch.contiguous_format)
-        for b in self.blocks:
+        biases = self._pair_biases(z)
+        for b, pb in zip(self.blocks, biases):
             a = b(a, s, z, mask=mask, use_high_precision_attention=use_high_precision_attention,
-                  _mask_trans=_mask_trans, _in_place=True)
+                  _mask_trans=_mask_trans, _in_place=True, _pair_bias=pb)
         return a

@@ -150,3 +150,33 @@ def test_high_precision_attention_flag_selects_the_fp32_kernels(pkg, dev):
     e_hp, e_lp = cases.rms_err(hp.float().cpu(), ref), cases.rms_err(lp.float().cpu(), ref)
     print(f"attn_update RMS error: high precision {e_hp:.3e}, bf16 kernels {e_lp:.3e}")
     assert e_hp < 2.5e-3 and e_hp < 0.6 * e_lp
+
+
+def test_diffusion_stack_hoists_the_pair_bias_of_an_unchanged_pair_tensor(pkg, dev):
+    """Rollout behaviour of DiffusionTransformer: calls with the same, unmodified z reuse the blocks' pair-bias
+    projections; the result equals the recomputing path bit for bit; modifying z in place (or passing another
+    tensor) recomputes them."""
+    name = "diffusion_stack2_n16"
+    P, x, _ = cases.CASES[name]()
+    bf = torch.bfloat16
+    st = pkg.DiffusionTransformer(**cases.DIFF, use_ada_layer_norm=True, n_query=None, n_key=None, inf=1e9, no_blocks=2)
+    st.load_state_dict(P, strict=True)
+    st = st.to(dev, bf).eval()
+    xd = {k: v.to(dev, bf) for k, v in x.items()}
+    with torch.no_grad():
+        st.hoist_pair_bias = False
+        ref = st(xd["a"], xd["s"], xd["z"], mask=xd["mask"])
+        assert st._bias_cache is None
+        st.hoist_pair_bias = True
+        out1 = st(xd["a"], xd["s"], xd["z"], mask=xd["mask"])
+        cached = st._bias_cache[3]
+        out2 = st(xd["a"], xd["s"], xd["z"], mask=xd["mask"])
+        assert st._bias_cache[3] is cached, "second call with the same z must reuse the projections"
+        assert torch.equal(out1, ref) and torch.equal(out2, ref)
+        xd["z"].mul_(0.5)   # in-place change: the cache must not be used
+        ref2 = st(xd["a"], xd["s"], xd["z"], mask=xd["mask"])
+        assert st._bias_cache[3] is not cached
+        st.hoist_pair_bias = False
+        assert torch.equal(st(xd["a"], xd["s"], xd["z"], mask=xd["mask"]), ref2)
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
