@@ -35,6 +35,15 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// (x0, x1) += (y0, y1) as one packed instruction (half the issue slots of two scalar adds)
+__device__ __forceinline__ void add2(float& x0, float& x1, float y0, float y1) {
+    unsigned long long a, b;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(x0), "f"(x1));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b) : "f"(y0), "f"(y1));
+    asm("add.rn.f32x2 %0, %0, %1;" : "+l"(a) : "l"(b));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(x0), "=f"(x1) : "l"(a));
+}
+
 // Named barrier for a subset of the CTA's warps (id 1..15; nthreads multiple of 32).
 __device__ __forceinline__ void group_sync(int id, int nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
