@@ -646,9 +646,24 @@ def run_ours(args, cfg) -> None:
             entry = {"launches": launches, "total_ms": round(ms, 3), "share": round(ms / total_kernel_ms, 4),
                      "ms_per_launch": round(per_launch_ms, 4)}
             kernels[name] = entry
-            if kind == "diffusion" or per_launch_ms <= 0:
+            if per_launch_ms <= 0:
                 continue
             sec = per_launch_ms * 1e-3
+            if name == "single_attn_core":
+                # Q K^T + P V over 16 heads of 24 (trunk) or 48 (diffusion): 4 N^2 (H d) flop per sample; a
+                # row-sharded rank holds 1 / world of the queries, a diffusion rank its share of the samples
+                if kind == "diffusion":
+                    fl = 4.0 * n * n * DIFF["c_a"] * -(-cfg["samples"] // world)
+                else:
+                    fl = 4.0 * n * n * 384 * share_of
+                ach = fl / sec / 1e12
+                entry["tflops"] = round(ach, 1)
+                roofline.append({"kernel": name, "bound": "tensor", "achieved": round(ach, 1), "peak": tensor_peak,
+                                 "unit": "TFLOP/s", "frac": round(ach / tensor_peak, 4), "traffic": None,
+                                 "peak_kind": f"bf16 sustained, {peak_kind}", "algorithmic_flop_per_launch": fl})
+                continue
+            if kind == "diffusion":
+                continue
             if name in TENSOR_BOUND:
                 ach = kf[name] * share_of / sec / 1e12
                 r = {"kernel": name, "bound": "tensor", "achieved": round(ach, 1), "peak": tensor_peak, "unit": "TFLOP/s",

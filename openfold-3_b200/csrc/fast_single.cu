@@ -3,8 +3,8 @@
 //
 // The token dimension is tiny next to the pair tensor (N x 384 against N x N x 128), so these are
 // launch/latency-bound chains, not roofline kernels. The linears run on the tcgen05 contraction
-// kernel (activation rows x weight rows, both K-major), the attention keeps one head's K and V
-// resident in shared memory, and everything in between is bf16 in HBM with fp32 arithmetic.
+// kernel (activation rows x weight rows, both K-major), the attention on the streaming tensor-pipe
+// kernel of fast_single_attn.cu, and everything in between is bf16 in HBM with fp32 arithmetic.
 // Reference: openfold3/core/model/layers/attention_pair_bias.py:123-227,
 //            openfold3/core/model/primitives/attention.py:94-135, 270-310,
 //            openfold3/core/model/layers/transition.py:225-271.
@@ -25,12 +25,6 @@ __device__ __forceinline__ float warp_sum(float v) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     return v;
 }
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
 // ---------------------------------------------------------------- LayerNorm rows -> bf16
 __global__ void __launch_bounds__(256) ln_rows_kernel(const bf16* __restrict__ x, const bf16* __restrict__ gamma,
                                                       const bf16* __restrict__ beta, bf16* __restrict__ y,
@@ -54,171 +48,6 @@ __global__ void __launch_bounds__(256) ln_rows_kernel(const bf16* __restrict__ x
         if (beta) o += __bfloat162float(beta[c]);
         y[r * C + c] = __float2bfloat16_rn(o);
     }
-}
-
-// ---------------------------------------------------------------- attention, one head resident
-// grid (query chunks of 16, H, BB); 8 warps, each warp owns TWO queries (they share every K / V read).
-// K and V of (bb, h) sit in shared memory as bf16 rows at a 16-byte-aligned pitch chosen so that eight
-// lanes reading eight consecutive rows with 128-bit loads touch all 32 banks once (48 B for d = 24,
-// 112 B for d = 48). A lane owns the keys lane, lane + 32, ...: logits, exponentials and the P V
-// accumulation are lane-private (no shuffles per key); per chunk of 256 keys the warp agrees on the
-// running maximum (one max-reduction), and the 2 x d partial outputs are summed over lanes once at the end.
-// q, g, out and the pair bias hold nq query rows per sample (nq = N, or a window of the rows when the
-// queries are split over ranks); k, v and the mask always hold all N keys.
-constexpr int kQPB = 16;  // queries per block
-
-template <int D>
-struct AttnCfg {
-    static constexpr int kPitch = (D == 24) ? 48 : 112;  // bytes per K / V row in shared memory
-    static constexpr int kVec = D / 8;                    // 16-byte vectors per row
-};
-
-__device__ __forceinline__ void unpack8(const uint4& w, float* f) {
-    f[0] = bf16lo(w.x); f[1] = bf16hi(w.x); f[2] = bf16lo(w.y); f[3] = bf16hi(w.y);
-    f[4] = bf16lo(w.z); f[5] = bf16hi(w.z); f[6] = bf16lo(w.w); f[7] = bf16hi(w.w);
-}
-
-template <int D>
-__global__ void __launch_bounds__(256, (D <= 24) ? 2 : 1)
-single_attn_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k, const bf16* __restrict__ v,
-                   const bf16* __restrict__ g, const bf16* __restrict__ q_bias, const float* __restrict__ pair_bias,
-                   const bf16* __restrict__ mask, bf16* __restrict__ out, int N, int nq, int H, float scale, float inf,
-                   long long rows_per_bias, int passes) {
-    constexpr int PB = AttnCfg<D>::kPitch, NV = AttnCfg<D>::kVec;
-    constexpr int kChunk = 8;  // keys per lane between two agreements on the running maximum
-    extern __shared__ __align__(16) uint8_t smem[];
-    uint8_t* Ks = smem;
-    uint8_t* Vs = Ks + (size_t)N * PB;
-    float* mb = reinterpret_cast<float*>(Vs + (size_t)N * PB);  // additive key mask
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long bb = blockIdx.z;
-    const int h = blockIdx.y;
-    const int HD = H * D;
-    for (int idx = threadIdx.x; idx < N * NV; idx += 256) {
-        const int kk = idx / NV, c = idx % NV;
-        const long long off = (bb * N + kk) * HD + h * D + c * 8;
-        *reinterpret_cast<uint4*>(Ks + kk * PB + c * 16) = *reinterpret_cast<const uint4*>(k + off);
-        *reinterpret_cast<uint4*>(Vs + kk * PB + c * 16) = *reinterpret_cast<const uint4*>(v + off);
-    }
-    const int npad = (N + 31) & ~31;
-    for (int kk = threadIdx.x; kk < npad; kk += 256)
-        mb[kk] = kk < N ? (mask ? inf * (__bfloat162float(mask[bb * N + kk]) - 1.0f) : 0.f) : -INFINITY;
-    __syncthreads();
-
-    // a block serves `passes` groups of 16 queries with one load of the head's K and V
-    for (int pass = 0; pass < passes; ++pass) {
-    const int qa = (blockIdx.x * passes + pass) * kQPB + warp * 2;  // this warp's queries qa, qa + 1
-    if (qa >= nq) break;
-    const bool has_b = qa + 1 < nq;
-    const int qb = has_b ? qa + 1 : qa;
-    const float* pb_base = pair_bias + ((bb / rows_per_bias) * H + h) * (long long)nq * N;
-    const float* pba = pb_base + (long long)qa * N;
-    const float* pbb = pb_base + (long long)qb * N;
-    const long long offa = (bb * nq + qa) * HD + h * D, offb = (bb * nq + qb) * HD + h * D;
-    float fa[D], fb[D];
-#pragma unroll
-    for (int c = 0; c < D; ++c) {
-        const float bq = q_bias ? __bfloat162float(q_bias[h * D + c]) : 0.f;
-        fa[c] = (__bfloat162float(q[offa + c]) + bq) * scale;
-        fb[c] = (__bfloat162float(q[offb + c]) + bq) * scale;
-    }
-    float oa[D], ob[D];
-#pragma unroll
-    for (int c = 0; c < D; ++c) oa[c] = ob[c] = 0.f;
-    float ma = -INFINITY, mbq = -INFINITY, la = 0.f, lb = 0.f;
-
-    for (int k0 = 0; k0 < npad; k0 += 32 * kChunk) {
-        float sa[kChunk], sb[kChunk];
-        float cma = -INFINITY, cmb = -INFINITY;
-#pragma unroll
-        for (int i = 0; i < kChunk; ++i) {
-            const int kk = k0 + i * 32 + lane;
-            sa[i] = sb[i] = -INFINITY;
-            if (kk < N) {
-                float da = 0.f, db = 0.f;
-#pragma unroll
-                for (int c8 = 0; c8 < NV; ++c8) {
-                    float kf[8];
-                    unpack8(*reinterpret_cast<const uint4*>(Ks + kk * PB + c8 * 16), kf);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        da = fmaf(fa[c8 * 8 + e], kf[e], da);
-                        db = fmaf(fb[c8 * 8 + e], kf[e], db);
-                    }
-                }
-                const float m = mb[kk];
-                sa[i] = (da + m) + pba[kk];  // the reference's order: (q.k + mask bias) + pair bias
-                sb[i] = (db + m) + pbb[kk];
-            }
-            cma = fmaxf(cma, sa[i]);
-            cmb = fmaxf(cmb, sb[i]);
-        }
-        const float na = fmaxf(ma, warp_max(cma)), nb = fmaxf(mbq, warp_max(cmb));  // finite: key k0 exists
-        const float ca = __expf(ma - na), cb = __expf(mbq - nb);                     // 0 on the first chunk
-        ma = na;
-        mbq = nb;
-        la *= ca;
-        lb *= cb;
-#pragma unroll
-        for (int c = 0; c < D; ++c) {
-            oa[c] *= ca;
-            ob[c] *= cb;
-        }
-#pragma unroll
-        for (int i = 0; i < kChunk; ++i) {
-            const int kk = k0 + i * 32 + lane;
-            if (kk < N) {
-                const float pa = __expf(sa[i] - ma), pq = __expf(sb[i] - mbq);
-                la += pa;
-                lb += pq;
-#pragma unroll
-                for (int c8 = 0; c8 < NV; ++c8) {
-                    float vf[8];
-                    unpack8(*reinterpret_cast<const uint4*>(Vs + kk * PB + c8 * 16), vf);
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        oa[c8 * 8 + e] = fmaf(pa, vf[e], oa[c8 * 8 + e]);
-                        ob[c8 * 8 + e] = fmaf(pq, vf[e], ob[c8 * 8 + e]);
-                    }
-                }
-            }
-        }
-    }
-    la = warp_sum(la);
-    lb = warp_sum(lb);
-    float ra = 0.f, rb = 0.f;  // lane c keeps output dim c (and c + 32 for d = 48)
-    float ra2 = 0.f, rb2 = 0.f;
-#pragma unroll
-    for (int c = 0; c < D; ++c) {
-        const float ta = warp_sum(oa[c]), tb = warp_sum(ob[c]);
-        if (c < 32) {
-            if (lane == c) { ra = ta; rb = tb; }
-        } else {
-            if (lane == c - 32) { ra2 = ta; rb2 = tb; }
-        }
-    }
-    const float ia = 1.0f / la, ib = 1.0f / lb;
-    if (lane < D) {
-        float r = ra * ia;
-        if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offa + lane])));
-        out[offa + lane] = __float2bfloat16_rn(r);
-        if (has_b) {
-            float r2 = rb * ib;
-            if (g) r2 *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offb + lane])));
-            out[offb + lane] = __float2bfloat16_rn(r2);
-        }
-    }
-    if (D > 32 && lane + 32 < D) {
-        float r = ra2 * ia;
-        if (g) r *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offa + lane + 32])));
-        out[offa + lane + 32] = __float2bfloat16_rn(r);
-        if (has_b) {
-            float r2 = rb2 * ib;
-            if (g) r2 *= 1.0f / (1.0f + __expf(-__bfloat162float(g[offb + lane + 32])));
-            out[offb + lane + 32] = __float2bfloat16_rn(r2);
-        }
-    }
-    }  // passes
 }
 
 // ---------------------------------------------------------------- elementwise
@@ -288,25 +117,6 @@ int linear_bf16(const bf16* x, const bf16* w, bf16* y, long long rows, int out_d
                             (long long)out_dim * in_dim, rows * out_dim, st, 0, 0, kKidLinear);
 }
 
-template <int D>
-int launch_attn(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias, const float* pb,
-                const bf16* mask, bf16* out, int BB, int N, int nq, int H, float inf, long long rows_per_bias,
-                cudaStream_t st) {
-    const size_t smem = (size_t)N * AttnCfg<D>::kPitch * 2 + (size_t)((N + 31) & ~31) * 4;
-    // the limit depends on N and function attributes are per device: set on every launch (a host-side store)
-    OF3_CUDA_CHECK(cudaFuncSetAttribute(single_attn_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        (int)smem));
-    // enough blocks for a few waves, as few loads of K / V as that allows
-    int passes = 1;
-    while (passes < 8 && (long long)ceil_div(nq, kQPB * passes * 2) * H * BB >= 4LL * sm_count()) passes *= 2;
-    dim3 grid(ceil_div(nq, kQPB * passes), H, BB);
-    LaunchScope scope(kKidSingle, st);
-    single_attn_kernel<D><<<grid, 256, smem, st>>>(q, k, v, g, q_bias, pb, mask, out, N, nq, H, rsqrtf((float)D),
-                                                   inf, rows_per_bias, passes);
-    OF3_CUDA_CHECK(cudaGetLastError());
-    return OF3_OK;
-}
-
 // an = AdaLN(a, s) (normalization.py:89-140): LN(a) without affine, LN_s(s) with scale only, two linears
 // from it, combine. t_ln / t_sn / t_g / t_s: scratch [rows, c_a], [rows, c_s], [rows, c_a], [rows, c_a].
 int ada_ln_bf16(const bf16* a, const bf16* s, bf16* an, bf16* t_sn, bf16* t_g, bf16* t_s, long long rows, int c_a,
@@ -334,14 +144,13 @@ int ada_ln_bf16(const bf16* a, const bf16* s, bf16* an, bf16* t_sn, bf16* t_g, b
 
 }  // namespace
 
-// bf16, LayerNorm variant, one pair tensor per sample; c_a = H * d a multiple of 64; d in {24, 48};
-// K and V of one head must fit in shared memory.
+// bf16, one pair tensor per group of samples; c_a = H * d a multiple of 64; d in {24, 48}.
 bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H, int d, int flags) {
     if (flags & OF3_FLAG_FORCE_GENERIC) return false;
     if ((flags & OF3_FLAG_ADA_LN) && (c_s <= 0 || c_s % 64 != 0)) return false;
     if (!(d == 24 || d == 48) || H * d != c_a || c_a % 64 != 0) return false;
     if (c_z != 128 || H != 16 || Bz <= 0 || Ba % Bz != 0) return false;
-    return (size_t)N * (d == 24 ? 48 : 112) * 2 + (size_t)N * 4 + 1024 <= 200 * 1024;
+    return single_attn_tc_supported(N, H, d);
 }
 
 int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask, bf16* out, int Ba, int Bz, int N,
@@ -360,7 +169,9 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
     bf16* og = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     bf16* y = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     float* zb = (float*)ws.take((size_t)Bz * H * N * N * sizeof(float));
-    if (!ws.base) return OF3_OK;
+    if (!ws.base)   // sizing pass: the operand images of the attention come last
+        return single_attn_tc(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, Ba, N, N, H, d, inf,
+                              Ba / Bz, ws, st);
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "attn_pair_bias: workspace too small (%zu needed)", ws.off);
     int rc;
     if (pair_bias == nullptr) {
@@ -383,12 +194,8 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
     if ((rc = linear_bf16(an, (const bf16*)p->w_k, k, rows, c_a, c_a, st))) return rc;
     if ((rc = linear_bf16(an, (const bf16*)p->w_v, v, rows, c_a, c_a, st))) return rc;
     if ((rc = linear_bf16(an, (const bf16*)p->w_g, g, rows, c_a, c_a, st))) return rc;
-    const long long rpb = Ba / Bz;
-    if (d == 24)
-        rc = launch_attn<24>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, inf, rpb, st);
-    else
-        rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, inf, rpb, st);
-    if (rc) return rc;
+    if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, d, inf, Ba / Bz, ws, st)))
+        return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
     if (ada) {  // output gate from the raw conditioning: sigmoid(linear_ada_out(s)) * y
         if ((rc = linear_bf16(s, (const bf16*)p->w_ada_out, t_g, rows, c_a, c_s, st))) return rc;
@@ -459,7 +266,9 @@ int attn_pair_bias_rows(const bf16* a, const float* pair_bias_rows, const bf16* 
     bf16* g = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
     bf16* og = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
     bf16* y = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
-    if (!ws.base) return OF3_OK;
+    if (!ws.base)
+        return single_attn_tc(nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, 1, N, R, H, d, inf, 1,
+                              ws, st);
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "attn_pair_bias_rows: workspace too small (%zu needed)", ws.off);
     OF3_REQUIRE(row0 >= 0 && R > 0 && row0 + R <= N, OF3_ERR_ARG, "attn_pair_bias_rows: window [%d, %d) outside %d rows",
                 row0, row0 + R, N);
@@ -475,11 +284,8 @@ int attn_pair_bias_rows(const bf16* a, const float* pair_bias_rows, const bf16* 
     if ((rc = linear_bf16(an, (const bf16*)p->w_v, v, N, c_a, c_a, st))) return rc;
     if ((rc = linear_bf16(an_w, (const bf16*)p->w_q, q, R, c_a, c_a, st))) return rc;
     if ((rc = linear_bf16(an_w, (const bf16*)p->w_g, g, R, c_a, c_a, st))) return rc;
-    if (d == 24)
-        rc = launch_attn<24>(q, k, v, g, (const bf16*)p->b_q, pair_bias_rows, mask, og, 1, N, R, H, inf, 1, st);
-    else
-        rc = launch_attn<48>(q, k, v, g, (const bf16*)p->b_q, pair_bias_rows, mask, og, 1, N, R, H, inf, 1, st);
-    if (rc) return rc;
+    if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias_rows, mask, og, 1, N, R, H, d, inf, 1, ws, st)))
+        return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, R, c_a, c_a, st))) return rc;
     {
         LaunchScope scope(kKidSingle, st);

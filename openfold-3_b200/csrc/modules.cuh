@@ -58,7 +58,13 @@ int triattn_finish(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
 bool transition_supported(int c, int n);
 int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows,
                int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
-// single-track layers (bf16): linears on the tcgen05 contraction kernel, one head of K/V resident per CTA
+// gated attention with pair bias on the tensor pipe: q, g, out [BB, nq, H*d]; k, v [BB, N, H*d]; pair_bias fp32
+// [BB / rows_per_bias, H, nq, N]; with ws.base == nullptr only the workspace need is accumulated
+bool single_attn_tc_supported(int N, int H, int d);
+int single_attn_tc(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, const __nv_bfloat16* g,
+                   const __nv_bfloat16* q_bias, const float* pair_bias, const __nv_bfloat16* mask, __nv_bfloat16* out,
+                   int BB, int N, int nq, int H, int d, float inf, int rows_per_bias, Arena& ws, cudaStream_t st);
+// single-track layers (bf16): linears on the tcgen05 contraction kernel, attention on single_attn_tc
 // (LayerNorm variant of the trunk, or with OF3_FLAG_ADA_LN the conditioned variant of the diffusion stack)
 bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H, int d, int flags);
 int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bfloat16* s, const __nv_bfloat16* mask,

@@ -141,7 +141,7 @@ def check_device_status():
 
 KERNEL_NAMES = {1: "trimul_contract", 2: "trimul_in", 3: "trimul_out", 4: "transition", 5: "triattn_proj",
                 6: "triattn_core", 7: "triattn_out", 8: "single_track", 9: "pair_bias", 10: "single_linear",
-                20: "generic", 30: "peer_barrier",
+                11: "single_attn_core", 20: "generic", 30: "peer_barrier",
                 31: "peer_pull"}
 
 

@@ -249,3 +249,59 @@ def test_bf16_error_growth_with_depth(pkg):
         bars = _bars(depth)
         assert rms <= bars["rms"], (k, "rms", rms)
         assert raw <= bars["max"], (k, "max", raw)
+
+
+# ----------------------------------------------------------------------------- single-track attention, several tiles
+def test_single_track_attention_n300_masked_matches_oracle(pkg):
+    """AttentionPairBias of the trunk (16 heads of 24), batch 2, N = 300 (three query tiles and ten key blocks, the
+    last of each partial), random token masks: every key block carries masked keys."""
+    dev = torch.device("cuda:0")
+    n = 300
+    g = torch.Generator().manual_seed(3000)
+    s0 = torch.randn(2, n, 384, generator=g).to(BF)
+    z0 = torch.randn(2, n, n, 128, generator=g).to(BF)
+    sm = cases.rand_mask((2, n), g)
+    P = pkg.weights.pairformer_block_params(seed=300, final_std=None, **cases.OF3)
+    blk = pkg.PairFormerBlock(**cases.OF3, transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False,
+                              inf=1e9)
+    blk.load_state_dict(P, strict=True)
+    blk = blk.to(dev, BF).eval()
+    Pq = {k: v.to(BF).float() for k, v in P.items()}
+    with torch.no_grad():
+        ref = cases.oracle.attention_pair_bias(s0.float(), z0.float(), None, sm, Pq, "attn_pair_bias.", 16)
+        got = blk.attn_pair_bias(a=s0.to(dev), z=z0.to(dev), s=None, mask=sm.to(dev, BF))
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    valid = sm > 0
+    _check("single_n300", "attn_update", got, ref, valid, 1, 4)
+
+
+def test_diffusion_attention_n300_three_samples_matches_oracle(pkg):
+    """AttentionPairBias of the diffusion stack (AdaLN, 16 heads of 48): three samples sharing one pair tensor (the
+    second line of the second CTA of each group has no sample), N = 300, random token mask."""
+    dev = torch.device("cuda:0")
+    n = 300
+    g = torch.Generator().manual_seed(3001)
+    a0 = torch.randn(1, 3, n, 768, generator=g).to(BF)
+    s0 = torch.randn(1, 3, n, 384, generator=g).to(BF)
+    z0 = torch.randn(1, 1, n, n, 128, generator=g).to(BF)
+    m = cases.rand_mask((1, 1, n), g)
+    P = pkg.weights.diffusion_block_params(seed=301, final_std=None, **cases.DIFF)
+    blk = pkg.DiffusionTransformerBlock(**cases.DIFF, use_ada_layer_norm=True, n_query=None, n_key=None, inf=1e9)
+    blk.load_state_dict(P, strict=True)
+    blk = blk.to(dev, BF).eval()
+    Pq = {k: v.to(BF).float() for k, v in P.items()}
+    with torch.no_grad():
+        ref = cases.oracle.attention_pair_bias(a0.float(), z0.float(), s0.float(), m, Pq, "attention_pair_bias.", 16,
+                                               use_ada_layer_norm=True)
+        got = blk.attention_pair_bias(a=a0.to(dev), z=z0.to(dev), s=s0.to(dev), mask=m.to(dev, BF))
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    valid = (m > 0).expand(1, 3, n)
+    g_, r_ = got.float().cpu(), ref
+    assert torch.isfinite(g_).all()
+    raw, rms = cases.rel_err(g_, r_, valid), cases.rms_err(g_, r_, valid)
+    print(f"diffusion_n300.attn_update: max-abs/RMS {raw:.3e}; RMS error {rms:.3e}")
+    cases.record("diffusion_n300", "attn_update", raw, float("nan"), rms)
+    # the conditioned layer multiplies two bf16 gates into the update: 2.5 x the single-layer bars
+    assert rms <= 2.5 * 8e-3 and raw <= 2.5 * 8e-2, (raw, rms)
