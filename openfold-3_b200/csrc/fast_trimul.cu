@@ -1,9 +1,11 @@
 // Triangle multiplicative update, bf16 / tcgen05 family (c_z = c_hidden = 128).
 //
 // Three kernels per layer, all fed by TMA:
-//   trimul_in   z tile -> LayerNorm_in (in place in the A operand) -> [a_p|a_g|b_p|b_g] projection
-//               (tcgen05, N = 256 per MMA) -> mask * sigmoid(gate) * proj -> a, b stored
-//               CHANNEL-MAJOR with the contracted index innermost: a_t[c][i][k], b_t[c][j][k].
+//   trimul_in   z tile -> LayerNorm_in (in place) -> the four projections a_p, a_g, b_p, b_g TRANSPOSED
+//               (tcgen05: the weights are the A operand, the normalised tile the B operand, so a TMEM lane is an
+//               output channel and its columns are the tile's 128 positions) -> mask * sigmoid(gate) * proj ->
+//               a, b stored CHANNEL-MAJOR with the contracted index innermost, a_t[c][i][k], b_t[c][j][k]:
+//               every epilogue thread writes its channel's 256 contiguous bytes with 16-byte stores.
 //               For the incoming update the tile walks z along its first index instead, so that
 //               both directions feed the same K-major x K-major contraction.
 //   contract    x_t[c][i][j] = sum_k a_t[c][i][k] * b_t[c][j][k]      (contract.cu)
@@ -48,13 +50,16 @@ struct InSmem {
     static constexpr uint32_t kZ = 2 * kWKb;                   // 2 stages x 32768
     static constexpr uint32_t kGamma = kZ + 2 * kTileBytes;    // 128 floats
     static constexpr uint32_t kBeta = kGamma + 512;
-    static constexpr uint32_t kBars = kBeta + 512;
+    static constexpr uint32_t kMask = kBeta + 512;             // 4 x 128 floats: 0.5 * mask of the tile's positions
+    static constexpr uint32_t kBars = kMask + 4 * 512;
     static constexpr uint32_t kTotal = kBars + 128;
     static constexpr uint32_t kDyn = kTotal + 1024;
 };
 
 // outgoing: tmZ is 3-D {c, second index, b*N + first index}; incoming: 4-D {c, second, first, b}
-constexpr int kInThreads = 448;  // producer, MMA, 4 LayerNorm warps, 2 x 4 epilogue warps
+constexpr int kInLnWarps = 8;    // two threads per position
+constexpr int kInEpiSets = 2;    // epilogue warp sets: a / b projection x first / second half of the tile's positions
+constexpr int kInThreads = 32 * (2 + kInLnWarps + 4 * kInEpiSets);  // producer, MMA, LayerNorm and epilogue warps
 
 template <bool kOutgoing>
 __global__ void __launch_bounds__(kInThreads, 1)
@@ -63,12 +68,13 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                  const __grid_constant__ CUtensorMap tmWbg, const __nv_bfloat16* __restrict__ mask,
                  const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
                  __nv_bfloat16* __restrict__ a_t, __nv_bfloat16* __restrict__ b_t, int B, int R,
-                 int N, int ld, int group_shift, long long group_stride, int* status) {
+                 int N, int ld, int group_shift, long long group_stride, int wide_stores, int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
     float* gamma = reinterpret_cast<float*>(gbase + InSmem::kGamma);
     float* beta = reinterpret_cast<float*>(gbase + InSmem::kBeta);
+    float* mask05 = reinterpret_cast<float*>(gbase + InSmem::kMask);
     const uint32_t bars = sbase + InSmem::kBars;
     const uint32_t w_full = bars;
     auto z_full = [&](int s) { return bars + 8u * (1 + s); };
@@ -88,9 +94,9 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         for (int s = 0; s < 2; ++s) {
             mbar_init(z_full(s), 1);
             mbar_init(z_empty(s), 1);
-            mbar_init(a_ready(s), 4);
+            mbar_init(a_ready(s), kInLnWarps);
             mbar_init(slot_full(s), 1);
-            mbar_init(slot_empty(s), 4);
+            mbar_init(slot_empty(s), 2 * kInEpiSets);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -141,7 +147,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     } else if (warp == 1) {
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_bf16_f32(128, 256);
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 128);
             bool ok = mbar_wait(w_full, 0, abort_flag);
             if (!ok) report_wait_failure(status, abort_flag, kKidIn, 2);
             uint32_t it = 0;
@@ -151,6 +157,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                     report_wait_failure(status, abort_flag, kKidIn, 3);
                     break;
                 }
+                const uint32_t ztile = sbase + InSmem::kZ + s * kTileBytes;
                 for (int q = 0; q < 2; ++q) {
                     if (!mbar_wait(slot_empty(q), (it & 1u) ^ 1u, abort_flag)) {
                         report_wait_failure(status, abort_flag, kKidIn, 4);
@@ -158,16 +165,29 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                         break;
                     }
                     tc_fence_after_sync();
-                    mma_k128(tmem_base + q * 256, sbase + InSmem::kZ + s * kTileBytes,
-                             sbase + InSmem::kW + q * 256 * 128, InSmem::kWKb, idesc, false);
+                    // D[channel][position] = W[channel][:] . LN(z)[position][:]: projection, then gate
+                    for (int hg = 0; hg < 2; ++hg) {
+                        const uint32_t w_tile = sbase + InSmem::kW + (q * 2 + hg) * 128 * 128;
+#pragma unroll
+                        for (int kb = 0; kb < 2; ++kb) {
+                            const uint64_t ad = smem_desc_k_sw128(w_tile + kb * InSmem::kWKb);
+                            const uint64_t bd = smem_desc_k_sw128(ztile + kb * kKBlockBytes);
+#pragma unroll
+                            for (int k4 = 0; k4 < 4; ++k4)
+                                mma_bf16(tmem_base + q * 256 + hg * 128, ad + 2u * k4, bd + 2u * k4, idesc,
+                                         (kb != 0 || k4 != 0) ? 1u : 0u);
+                        }
+                    }
                     mma_commit(slot_full(q));
                 }
                 if (ok) mma_commit(z_empty(s));
             }
         }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- LayerNorm warps (2..5)
-        const int row = (warp - 2) * 32 + lane;
+    } else if (warp < 2 + kInLnWarps) {
+        // ---------------------------------------------------------------- LayerNorm warps: a warp takes 16 positions,
+        // lanes 0..15 their first 64 channels, lanes 16..31 the other 64 (statistics joined by one shuffle)
+        const int row = (warp - 2) * 16 + (lane & 15);
+        const int half = lane >> 4;
         uint32_t it = 0;
         for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const int s = it & 1;
@@ -176,75 +196,113 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 break;
             }
             const uint32_t tile = sbase + InSmem::kZ + s * kTileBytes;
-            uint32_t raw[64];
-            load_row(tile, row, raw);
+            uint32_t raw[32];
+            load_half_row(tile, row, half, raw);
             float mean, rstd;
-            row_stats(raw, mean, rstd);
-            store_normalized_row(tile, row, raw, mean, rstd, gamma, beta);
+            half_row_stats(raw, mean, rstd);
+            store_normalized_half_row(tile, row, half, raw, mean, rstd, gamma, beta);
+            const TileCoord tc = tile_coord(t, R, tiles_per_line);
+            const int k = tc.t0 + row;
+            float m = 0.f;   // positions past the end of the line are never stored
+            if (k < N) {
+                m = 0.5f;
+                if (mask != nullptr) {
+                    const long long lin = kOutgoing ? ((long long)(tc.b * R + tc.fixed) * N + k)
+                                                    : ((long long)(tc.b * N + k) * R + tc.fixed);
+                    m = 0.5f * __bfloat162float(mask[lin]);
+                }
+            }
+            // four mask buffers: the epilogue of tile `it` may still read its buffer while tile it + 2 is normalised;
+            // tile it + 4 cannot get here before that epilogue has released its TMEM slot
+            if (half == 0) mask05[(it & 3) * 128 + row] = m;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) mbar_arrive(a_ready(s));
         }
     } else {
-        // ---------------------------------------------------------------- epilogue warps: 6..9 take the a
-        // projection (TMEM slot 0), 10..13 the b projection (slot 1). One set of four warps doing both
-        // (2 x 128 sigmoid / multiply / convert / store per row and tile on one thread) was the longest
-        // chain of the kernel.
-        const int qset = (warp - 6) >> 2;
+        // ---------------------------------------------------------------- epilogue warps: the first four take the a
+        // projection (TMEM slot 0), the other four the b projection (slot 1); thread = output channel, columns =
+        // positions
+        const int set = (warp - 2 - kInLnWarps) >> 2;
+        const int q = set / (kInEpiSets / 2), khalf = set % (kInEpiSets / 2);
+        constexpr int kSpan = kRows / (kInEpiSets / 2);   // positions per set
         const int quad = warp & 3;
-        const int row = quad * 32 + lane;
+        const int c = quad * 32 + lane;
+        const long long cs = (long long)R * ld;
+        // channel c lives at (c >> group_shift) * group_stride + (c & group_mask) * R * ld: one contiguous plane
+        // [128][R][ld] by default, or one group of channels per destination rank when the planes are about to be
+        // exchanged
+        __nv_bfloat16* plane = (q == 0 ? a_t : b_t) + (long long)(c >> group_shift) * group_stride +
+                               (long long)(c & ((1 << group_shift) - 1)) * cs;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + q * 256;
         uint32_t it = 0;
-        bool ok = true;
-        for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
             const TileCoord tc = tile_coord(t, R, tiles_per_line);
-            const int k = tc.t0 + row;
-            const bool valid = k < N;
-            float m = 1.0f;
-            if (valid && mask != nullptr) {
-                const long long lin = kOutgoing ? ((long long)(tc.b * R + tc.fixed) * N + k)
-                                                : ((long long)(tc.b * N + k) * R + tc.fixed);
-                m = __bfloat162float(mask[lin]);
+            const int kmax = (N - tc.t0 < kRows) ? N - tc.t0 : kRows;   // positions of the tile that exist
+            if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
+                break;
             }
-            for (int q = qset; q <= qset; ++q) {
-                if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
-                    if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after_sync();
-                // channel c lives at (c >> group_shift) * group_stride + (c & group_mask) * R * ld: one
-                // contiguous plane [128][R][ld] by default, or one group of channels per destination
-                // rank when the planes are about to be exchanged
-                const long long cs = (long long)R * ld;
-                __nv_bfloat16* dst = (q == 0 ? a_t : b_t) +
-                                     (long long)tc.b * ((kC >> group_shift) * group_stride) +
-                                     (long long)tc.fixed * ld + k;
-                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + q * 256;
-#pragma unroll 1
-                for (int cb = 0; cb < 4; ++cb) {
-                    uint32_t p[32], g[32];
-                    tmem_ld32(taddr + cb * 32, p);
-                    tmem_ld32(taddr + 128 + cb * 32, g);
-                    tmem_ld_wait();
-                    if (valid) {
+            tc_fence_after_sync();
+            const float* mk = mask05 + (it & 3) * 128;
+            // the line pitch ld is a multiple of 8 elements, so a 16-byte store that starts below N ends inside the
+            // row; with a pitch that is a multiple of 16 (and 32-byte aligned planes) the same holds for 32 bytes
+            __nv_bfloat16* dst = plane + (long long)tc.b * ((kC >> group_shift) * group_stride) +
+                                 (long long)tc.fixed * ld + tc.t0;
+            // 16 positions per pass; the TMEM load of the next pass is in flight while this one is computed
+            auto emit = [&](const uint32_t (&p)[16], const uint32_t (&g)[16], int k0) {
+                uint32_t o[8];
 #pragma unroll
-                        for (int hf = 0; hf < 2; ++hf) {  // groups hold >= 16 channels: no boundary inside a half
-                            const int c0 = cb * 32 + hf * 16;
-                            __nv_bfloat16* d0 = dst + (long long)(c0 >> group_shift) * group_stride +
-                                                (long long)(c0 & ((1 << group_shift) - 1)) * cs;
+                for (int j = 0; j < 2; ++j) {
+                    const float4 m0 = *reinterpret_cast<const float4*>(mk + k0 + j * 8);
+                    const float4 m1 = *reinterpret_cast<const float4*>(mk + k0 + j * 8 + 4);
+                    const float mm[8] = {m0.x, m0.y, m0.z, m0.w, m1.x, m1.y, m1.z, m1.w};
+                    float v[8];
 #pragma unroll
-                            for (int e = 0; e < 16; ++e) {
-                                const float v = m * __uint_as_float(p[hf * 16 + e]) *
-                                                sigmoid_fast(__uint_as_float(g[hf * 16 + e]));
-                                d0[(long long)e * cs] = __float2bfloat16_rn(v);
-                            }
-                        }
+                    for (int e = 0; e < 8; ++e) {
+                        // mask * p * sigmoid(g) = pm * tanh(g / 2) + pm with pm = (mask / 2) * p
+                        const float pm = mm[e] * __uint_as_float(p[j * 8 + e]);
+                        v[e] = fmaf(tanh_approx(0.5f * __uint_as_float(g[j * 8 + e])), pm, pm);
                     }
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) o[j * 4 + e] = pack_bf16x2(v[2 * e], v[2 * e + 1]);
                 }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(slot_empty(q));
+                if (wide_stores) {   // one full 32-byte sector per thread
+                    asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + k0), "r"(o[0]),
+                                 "r"(o[1]), "r"(o[2]), "r"(o[3]), "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7])
+                                 : "memory");
+                } else {
+                    *reinterpret_cast<uint4*>(dst + k0) = make_uint4(o[0], o[1], o[2], o[3]);
+                    if (k0 + 8 < kmax) *reinterpret_cast<uint4*>(dst + k0 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+                }
+            };
+            const int k_begin = khalf * kSpan;
+            const int k_end = (kmax < (khalf + 1) * kSpan) ? kmax : (khalf + 1) * kSpan;
+            uint32_t pa[16], ga[16], pb[16], gb[16];
+            if (k_begin < k_end) {
+                tmem_ld16(taddr + k_begin, pa);
+                tmem_ld16(taddr + 128 + k_begin, ga);
             }
+#pragma unroll 1
+            for (int k0 = k_begin; k0 < k_end; k0 += 32) {
+                tmem_ld_wait();
+                if (k0 + 16 < k_end) {
+                    tmem_ld16(taddr + k0 + 16, pb);
+                    tmem_ld16(taddr + 128 + k0 + 16, gb);
+                }
+                emit(pa, ga, k0);
+                if (k0 + 16 < k_end) {
+                    tmem_ld_wait();
+                    if (k0 + 32 < k_end) {
+                        tmem_ld16(taddr + k0 + 32, pa);
+                        tmem_ld16(taddr + 128 + k0 + 32, ga);
+                    }
+                    emit(pb, gb, k0 + 16);
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(slot_empty(q));
         }
     }
 
@@ -543,15 +601,17 @@ int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
     if ((rc = set_attrs())) return rc;
     const long long tiles = (long long)B * R * ceil_div(N, kRows);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    // 32-byte stores need every channel row of a_t / b_t to start on a 32-byte boundary
+    const int wide = (ld % 16 == 0 && (group_stride % 16) == 0 && ((uintptr_t)a_t & 31) == 0 && ((uintptr_t)b_t & 31) == 0) ? 1 : 0;
     LaunchScope scope(kKidIn, st);
     if (!transposed_walk)
         trimul_in_kernel<true><<<grid, kInThreads, InSmem::kDyn, st>>>(
             tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, device_status_ptr());
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, wide, device_status_ptr());
     else
         trimul_in_kernel<false><<<grid, kInThreads, InSmem::kDyn, st>>>(
             tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, device_status_ptr());
+            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, wide, device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }

@@ -137,6 +137,66 @@ __device__ __forceinline__ void store_normalized_row(uint32_t tile, int row, con
     }
 }
 
+// The same three steps with TWO threads per row: lanes 0..15 of a warp hold channels 0..63 of 16 rows, lanes
+// 16..31 channels 64..127 of the same rows (half = lane >> 4); the statistics are joined by one shuffle.
+__device__ __forceinline__ void load_half_row(uint32_t tile, int row, int half, uint32_t (&raw)[32]) {
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+        const uint4 v = lds128(chunk_addr(tile, row, half * 8 + ch));
+        raw[ch * 4 + 0] = v.x;
+        raw[ch * 4 + 1] = v.y;
+        raw[ch * 4 + 2] = v.z;
+        raw[ch * 4 + 3] = v.w;
+    }
+}
+__device__ __forceinline__ void half_row_stats(const uint32_t (&raw)[32], float& mean, float& rstd) {
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+        for (int a = 0; a < 4; ++a) s[a] += bf16lo(raw[i + a]) + bf16hi(raw[i + a]);
+    }
+    float sum = (s[0] + s[1]) + (s[2] + s[3]);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+    mean = sum * (1.0f / kC);
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const float x0 = bf16lo(raw[i + a]) - mean, x1 = bf16hi(raw[i + a]) - mean;
+            v[a] = fmaf(x0, x0, v[a]);
+            v[a] = fmaf(x1, x1, v[a]);
+        }
+    }
+    float var = (v[0] + v[1]) + (v[2] + v[3]);
+    var += __shfl_xor_sync(0xffffffffu, var, 16);
+    rstd = rsqrtf(var * (1.0f / kC) + kLnEps);
+}
+__device__ __forceinline__ void store_normalized_half_row(uint32_t tile, int row, int half, const uint32_t (&raw)[32],
+                                                          float mean, float rstd, const float* gamma,
+                                                          const float* beta) {
+    const float nm = -mean * rstd;
+#pragma unroll
+    for (int ch = 0; ch < 8; ++ch) {
+        const int c0 = (half * 8 + ch) * 8;
+        const float4 g0 = *reinterpret_cast<const float4*>(gamma + c0);
+        const float4 g1 = *reinterpret_cast<const float4*>(gamma + c0 + 4);
+        const float4 b0 = *reinterpret_cast<const float4*>(beta + c0);
+        const float4 b1 = *reinterpret_cast<const float4*>(beta + c0 + 4);
+        const float gg[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+        const float bb[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float a = fmaf(fmaf(bf16lo(raw[ch * 4 + j]), rstd, nm), gg[j * 2], bb[j * 2]);
+            const float b = fmaf(fmaf(bf16hi(raw[ch * 4 + j]), rstd, nm), gg[j * 2 + 1], bb[j * 2 + 1]);
+            o[j] = pack_bf16x2(a, b);
+        }
+        sts128(chunk_addr(tile, row, half * 8 + ch), make_uint4(o[0], o[1], o[2], o[3]));
+    }
+}
+
 // 8 tcgen05.mma (K = 128 in steps of 16) of one row tile against a weight slab:
 // D[128 x N] (+)= A[128 x 128] * W[N x 128]^T. `w_kb_stride` = bytes between the slab's k-blocks.
 __device__ __forceinline__ void mma_k128(uint32_t d_tmem, uint32_t a_tile, uint32_t w_slab,

@@ -529,6 +529,8 @@ class PairFormerStack(nn.Module):
         self.clear_cache_between_blocks = clear_cache_between_blocks
         self.tune_chunk_size = tune_chunk_size
         self.chunk_size_tuner = None  # nothing to tune: the kernels never materialise N^3 logits
+        self.overlap_single_track = True   # run each block's single track on a second stream (CUDA only)
+        self._side_streams = {}
         self.blocks = nn.ModuleList([
             PairFormerBlock(c_s=c_s, c_z=c_z, c_hidden_pair_bias=c_hidden_pair_bias,
                             no_heads_pair_bias=no_heads_pair_bias, c_hidden_mul=c_hidden_mul,
@@ -546,9 +548,32 @@ class PairFormerStack(nn.Module):
             z = z.clone(memory_format=torch.contiguous_format)
         if not (inplace_safe and s.is_contiguous()):
             s = s.clone(memory_format=torch.contiguous_format)
+        if not (self.overlap_single_track and z.is_cuda and len(self.blocks) > 1
+                and self.blocks[0].attn_pair_bias.can_hoist_pair_bias(z)):
+            for b in self.blocks:
+                s, z = b(s, z, single_mask, pair_mask, chunk_size=chunk_size, inplace_safe=True,
+                         _mask_trans=_mask_trans)
+            return s, z
+        # The pair stack never reads s, so the single track of block i (a chain of small, launch-bound kernels on
+        # N x 384 values) runs on a second stream under the pair stack of block i + 1. The one thing it needs from
+        # z, the pair-bias projection, is computed on the main stream before the next block overwrites z in place.
+        main = torch.cuda.current_stream(z.device)
+        side = self._side_streams.get(z.device)
+        if side is None:
+            side = self._side_streams[z.device] = torch.cuda.Stream(z.device)
+        side.wait_stream(main)
         for b in self.blocks:
-            s, z = b(s, z, single_mask, pair_mask, chunk_size=chunk_size, inplace_safe=True,
-                     _mask_trans=_mask_trans)
+            z = b.pair_stack(z=z, pair_mask=pair_mask, chunk_size=chunk_size, inplace_safe=True,
+                             _mask_trans=_mask_trans)
+            bias = b.attn_pair_bias.project_pair_bias(z)
+            bias.record_stream(side)   # allocated on the main stream, last read on the second one
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(side):
+                side.wait_event(ready)
+                b.attn_pair_bias._run(s, z, None, single_mask, in_place=True, pair_bias=bias)
+                b.single_transition._run(s, single_mask if _mask_trans else None, in_place=True)
+        main.wait_stream(side)
         return s, z
 
 

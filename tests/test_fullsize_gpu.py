@@ -61,8 +61,11 @@ def test_n384_tensor_core_kernels_match_generic_kernels(pkg):
     torch.cuda.synchronize()
     pkg.lib.check_device_status()
     valid = (pm[0] > 0)
-    # two bf16 pipelines that round at different points, five chained layers: the bar of the chained parity cases
-    assert _rel(fast[0], slow[0], valid) < 6e-2
+    # two bf16 pipelines that round at different points, five chained layers: the worst-element bar one block
+    # has against the oracle (the difference of two results that each meet it stays of that order)
+    rel = _rel(fast[0], slow[0], valid)
+    print(f"n384 tensor-core vs generic kernels: max-abs/RMS {rel:.3e}")
+    assert rel < _bars(1)["max"]
     assert torch.isfinite(fast.float()).all()
 
 
