@@ -33,16 +33,19 @@ struct TrSmem {
     static constexpr uint32_t kX = 2 * kWStage;                // 2 groups x 32 KB (x tile / A / output)
     static constexpr uint32_t kH = kX + 2 * kTileBytes;        // 2 groups x 16 KB
     static constexpr uint32_t kParams = kH + 2 * kKBlockBytes; // gamma, beta
-    static constexpr uint32_t kBars = kParams + 1024;
+    static constexpr uint32_t kXch = kParams + 1024;           // 2 groups x 512 floats: LayerNorm partial sums
+    static constexpr uint32_t kBars = kXch + 4096;
     static constexpr uint32_t kTotal = kBars + 256;
     static constexpr uint32_t kDyn = kTotal + 1024;
 };
 
-// warps: 0 producer, 1 and 2 the MMA issuers of row group 0 and 1, 3..6 and 7..10 the two row groups.
+// warps: 0 producer, 1 and 2 the MMA issuers of row group 0 and 1, 3..10 and 11..18 the two row groups: two
+// threads share a row (TMEM lane) and take half of its channels each through LayerNorm, half of every hidden chunk
+// through silu * mul, and half of the output row -- the per-row chains were the longest thing in the kernel.
 // One issuing thread for both groups was the critical path (in-kernel clock64 phases: 5000 cycles per hidden
 // chunk for 1536 cycles of tensor work -- it waited for one group's silu pass while the other group's next
 // GEMM was ready to go); each group now has its own issuer and the tensor pipe interleaves the two chains.
-constexpr int kTrThreads = 32 * 11;
+constexpr int kTrThreads = 32 * (3 + 2 * 8);
 
 __global__ void __launch_bounds__(kTrThreads, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmOut,
@@ -84,13 +87,13 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             mbar_init(wo_empty(i), 2);
             mbar_init(x_full(i), 1);
             mbar_init(x_empty(i), 1);
-            mbar_init(a_ready(i), 4);
+            mbar_init(a_ready(i), 8);
             mbar_init(d1_full(i), 1);
-            mbar_init(d1_empty(i), 4);
-            mbar_init(h_ready(i), 4);
+            mbar_init(d1_empty(i), 8);
+            mbar_init(h_ready(i), 8);
             mbar_init(h_free(i), 1);
             mbar_init(d2_full(i), 1);
-            mbar_init(d2_empty(i), 4);
+            mbar_init(d2_empty(i), 8);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -220,10 +223,12 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         }
     } else {
         // ---------------------------------------------------------------- two row groups
-        const int g = (warp - 3) >> 2;
+        const int g = (warp - 3) >> 3;
         const int quad = warp & 3;
+        const int half = ((warp - 3) >> 2) & 1;
         const int row = quad * 32 + lane;
-        const int gtid = (warp - 3 - g * 4) * 32 + lane;
+        const int gtid = (warp - 3 - g * 8) * 32 + lane;
+        float* xch = reinterpret_cast<float*>(gbase + TrSmem::kXch) + g * 512;
         const uint32_t xtile = sbase + TrSmem::kX + g * kTileBytes;
         const uint32_t htile = sbase + TrSmem::kH + g * kKBlockBytes;
         const uint32_t t_d1 = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
@@ -237,12 +242,12 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidTrans, 8);
                 break;
             }
-            uint32_t raw[64];
-            load_row(xtile, row, raw);
+            uint32_t raw[32];   // this thread's 64 channels of the row: kept for the residual
+            load_half_row(xtile, row, half, raw);
             {
                 float mean, rstd;
-                row_stats(raw, mean, rstd);
-                store_normalized_row(xtile, row, raw, mean, rstd, prm, prm + 128);
+                half_row_stats_xwarp(raw, row, half, xch, 1 + g, 256, mean, rstd);
+                store_normalized_half_row(xtile, row, half, raw, mean, rstd, prm, prm + 128);
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -258,19 +263,19 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     break;
                 }
                 tc_fence_after_sync();
-                uint32_t hpk[32];  // 64 hidden values of this row, packed bf16x2
+                uint32_t hpk[16];  // 32 of the chunk's 64 hidden values of this row, packed bf16x2
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t a[32], b[32];
-                    tmem_ld32(t_d1 + half * 32, a);
-                    tmem_ld32(t_d1 + 64 + half * 32, b);
+                for (int q = 0; q < 2; ++q) {
+                    uint32_t a[16], b[16];
+                    tmem_ld16(t_d1 + half * 32 + q * 16, a);
+                    tmem_ld16(t_d1 + 64 + half * 32 + q * 16, b);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) {
+                    for (int e = 0; e < 16; e += 2) {
                         const float a0 = __uint_as_float(a[e]), a1 = __uint_as_float(a[e + 1]);
                         const float h0 = a0 * sigmoid_fast(a0) * __uint_as_float(b[e]);
                         const float h1 = a1 * sigmoid_fast(a1) * __uint_as_float(b[e + 1]);
-                        hpk[half * 16 + e / 2] = pack_bf16x2(h0, h1);
+                        hpk[q * 8 + e / 2] = pack_bf16x2(h0, h1);
                     }
                 }
                 tc_fence_before_sync();
@@ -283,8 +288,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                     break;
                 }
 #pragma unroll
-                for (int ch = 0; ch < 8; ++ch)
-                    sts128(chunk_addr(htile, row, ch),
+                for (int ch = 0; ch < 4; ++ch)
+                    sts128(chunk_addr(htile, row, half * 4 + ch),
                            make_uint4(hpk[ch * 4], hpk[ch * 4 + 1], hpk[ch * 4 + 2], hpk[ch * 4 + 3]));
                 fence_proxy_async_smem();
                 __syncwarp();
@@ -297,9 +302,9 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
             }
             tc_fence_after_sync();
 #pragma unroll
-            for (int cb = 0; cb < 8; ++cb) {
+            for (int cb = 0; cb < 4; ++cb) {
                 uint32_t y[16];
-                tmem_ld16(t_d2 + cb * 16, y);
+                tmem_ld16(t_d2 + half * 64 + cb * 16, y);
                 tmem_ld_wait();
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
@@ -316,14 +321,14 @@ transition_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
                         }
                         o[j] = pack_bf16x2(v0, v1);
                     }
-                    sts128(chunk_addr(xtile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
+                    sts128(chunk_addr(xtile, row, half * 8 + cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
                 }
             }
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(d2_empty(g));
             fence_proxy_async_smem();
-            group_sync(1 + g, 128);
+            group_sync(1 + g, 256);
             if (gtid == 0) {
                 tma_store_3d(&tmOut, xtile, 0, (int)(tile * kRows), 0);
                 tma_store_3d(&tmOut, xtile + kKBlockBytes, 64, (int)(tile * kRows), 0);

@@ -731,13 +731,18 @@ struct AOutSmem {
     static constexpr uint32_t kZ = 2 * kTileBytes;            // 2 groups: z tile, then output
     static constexpr uint32_t kO = kZ + 2 * kTileBytes;       // 2 groups: o tile, gated in place
     static constexpr uint32_t kParams = kO + 2 * kTileBytes;  // gamma, beta
-    static constexpr uint32_t kBars = kParams + 1024;
+    static constexpr uint32_t kXch = kParams + 1024;          // 2 groups x 512 floats: LayerNorm partial sums
+    static constexpr uint32_t kBars = kXch + 4096;
     static constexpr uint32_t kTotal = kBars + 160;
     static constexpr uint32_t kDyn = kTotal + 1024;
 };
 
+// producer, MMA issuer, 2 groups x 8 warps: a group alternates tiles with the other one; inside a group two threads
+// share a row (TMEM lane), each with 64 of its 128 channels through LayerNorm, gating and the output pass
+constexpr int kAOutThreads = 32 * (2 + 2 * 8);
+
 template <bool kTransposed>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(kAOutThreads, 1)
 triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmO,
                    const __grid_constant__ CUtensorMap tmOut, const __grid_constant__ CUtensorMap tmWg,
                    const __grid_constant__ CUtensorMap tmWo, const __nv_bfloat16* __restrict__ ln_w,
@@ -774,9 +779,9 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
             mbar_init(o_full(g), 1);
             mbar_init(z_empty(g), 1);
             mbar_init(o_empty(g), 1);
-            mbar_init(a1_ready(g), 4);
+            mbar_init(a1_ready(g), 8);
             mbar_init(g_full(g), 1);
-            mbar_init(a2_ready(g), 4);
+            mbar_init(a2_ready(g), 8);
             mbar_init(d_full(g), 1);
         }
         *abort_flag = 0;
@@ -860,13 +865,15 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
             }
         }
     } else {
-        const int g = (warp - 2) >> 2;
+        const int g = (warp - 2) >> 3;
         const int quad = warp & 3;
+        const int half = ((warp - 2) >> 2) & 1;   // channels [64 * half, 64 * half + 64) of the row
         const int row = quad * 32 + lane;
-        const int gtid = (warp - 2 - g * 4) * 32 + lane;
+        const int gtid = (warp - 2 - g * 8) * 32 + lane;
+        float* xch = reinterpret_cast<float*>(gbase + AOutSmem::kXch) + g * 512;
         const uint32_t ztile = sbase + AOutSmem::kZ + g * kTileBytes;
         const uint32_t otile = sbase + AOutSmem::kO + g * kTileBytes;
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + g * 256 + half * 64;
         for (long long lt = g; lt < my_tiles; lt += 2) {
             const uint32_t use = (uint32_t)(lt >> 1);
             const LineTile tc = line_tile(blockIdx.x + lt * gridDim.x, R, tiles_per_line);
@@ -874,12 +881,12 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidOut, 5);
                 break;
             }
-            uint32_t zraw[64];
-            load_row(ztile, row, zraw);
+            uint32_t zraw[32];
+            load_half_row(ztile, row, half, zraw);
             {
                 float mean, rstd;
-                row_stats(zraw, mean, rstd);
-                store_normalized_row(ztile, row, zraw, mean, rstd, prm, prm + 128);
+                half_row_stats_xwarp(zraw, row, half, xch, 1 + g, 256, mean, rstd);
+                store_normalized_half_row(ztile, row, half, zraw, mean, rstd, prm, prm + 128);
             }
             fence_proxy_async_smem();
             __syncwarp();
@@ -895,13 +902,13 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                 break;
             }
 #pragma unroll
-            for (int cb = 0; cb < 8; ++cb) {
+            for (int cb = 0; cb < 4; ++cb) {
                 uint32_t gate[16];
                 tmem_ld16(taddr + cb * 16, gate);
                 tmem_ld_wait();
 #pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    const uint32_t addr = chunk_addr(otile, row, cb * 2 + ch);
+                    const uint32_t addr = chunk_addr(otile, row, half * 8 + cb * 2 + ch);
                     const uint4 ov = lds128(addr);
                     const uint32_t w[4] = {ov.x, ov.y, ov.z, ov.w};
                     uint32_t o[4];
@@ -925,7 +932,7 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
             }
             tc_fence_after_sync();
 #pragma unroll
-            for (int cb = 0; cb < 8; ++cb) {
+            for (int cb = 0; cb < 4; ++cb) {
                 uint32_t upd[16];
                 tmem_ld16(taddr + 128 + cb * 16, upd);
                 tmem_ld_wait();
@@ -943,12 +950,12 @@ triattn_out_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constan
                         }
                         o[j] = pack_bf16x2(v0, v1);
                     }
-                    sts128(chunk_addr(otile, row, cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
+                    sts128(chunk_addr(otile, row, half * 8 + cb * 2 + ch), make_uint4(o[0], o[1], o[2], o[3]));
                 }
             }
             tc_fence_before_sync();
             fence_proxy_async_smem();
-            group_sync(1 + g, 128);
+            group_sync(1 + g, 256);
             if (gtid == 0) {
                 for (int kb = 0; kb < 2; ++kb) {
                     if (kTransposed) {
@@ -1061,7 +1068,7 @@ int finish_impl(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloat16
     const long long tiles = (long long)B * R * ceil_div(N, kRows);
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     LaunchScope scope(kKidOut, st);
-    triattn_out_kernel<kT><<<grid, 320, AOutSmem::kDyn, st>>>(
+    triattn_out_kernel<kT><<<grid, kAOutThreads, AOutSmem::kDyn, st>>>(
         tmZ, tmO, tmOut, tmWg, tmWo, (const __nv_bfloat16*)p->ln_w, (const __nv_bfloat16*)p->ln_b, B, R, N,
         add_residual, status);
     OF3_CUDA_CHECK(cudaGetLastError());

@@ -314,6 +314,213 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     }
 }
 
+// The same layer with the projections the other way round (the normalised tile is the A operand, a TMEM lane is a
+// position, its columns the output channels; N = 256 per MMA): a warp's store covers 32 consecutive positions of ONE
+// channel plane. Slower than the kernel above while a channel plane stays within a 2 MB page or so (170 against
+// 151 us at N = 768: one 2-byte store per value), faster beyond (1.13 against 2.02 ms at N = 2048, where the 32
+// planes one store of the kernel above touches lie megabytes apart).
+constexpr int kInRowsThreads = 448;  // producer, MMA, 4 LayerNorm warps, 2 x 4 epilogue warps
+
+template <bool kOutgoing>
+__global__ void __launch_bounds__(kInRowsThreads, 1)
+trimul_in_rows_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWap,
+                 const __grid_constant__ CUtensorMap tmWag, const __grid_constant__ CUtensorMap tmWbp,
+                 const __grid_constant__ CUtensorMap tmWbg, const __nv_bfloat16* __restrict__ mask,
+                 const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
+                 __nv_bfloat16* __restrict__ a_t, __nv_bfloat16* __restrict__ b_t, int B, int R,
+                 int N, int ld, int group_shift, long long group_stride, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
+    float* gamma = reinterpret_cast<float*>(gbase + InSmem::kGamma);
+    float* beta = reinterpret_cast<float*>(gbase + InSmem::kBeta);
+    const uint32_t bars = sbase + InSmem::kBars;
+    const uint32_t w_full = bars;
+    auto z_full = [&](int s) { return bars + 8u * (1 + s); };
+    auto z_empty = [&](int s) { return bars + 8u * (3 + s); };
+    auto a_ready = [&](int s) { return bars + 8u * (5 + s); };
+    auto slot_full = [&](int q) { return bars + 8u * (7 + q); };
+    auto slot_empty = [&](int q) { return bars + 8u * (9 + q); };
+    volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + InSmem::kBars + 96);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + InSmem::kBars + 104);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_per_line = (N + kRows - 1) / kRows;
+    const long long num_tiles = (long long)B * R * tiles_per_line;
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(z_full(s), 1);
+            mbar_init(z_empty(s), 1);
+            mbar_init(a_ready(s), 4);
+            mbar_init(slot_full(s), 1);
+            mbar_init(slot_empty(s), 4);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+        prefetch_tmap(&tmZ);
+    }
+    if (threadIdx.x < 128) {
+        gamma[threadIdx.x] = __bfloat162float(ln_w[threadIdx.x]);
+        beta[threadIdx.x] = __bfloat162float(ln_b[threadIdx.x]);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32((const void*)tmem_ptr), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_ptr;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_full, 2 * InSmem::kWKb);
+            const CUtensorMap* wm[4] = {&tmWap, &tmWag, &tmWbp, &tmWbg};
+            for (int w = 0; w < 4; ++w)
+                for (int kb = 0; kb < 2; ++kb)
+                    tma_load_2d(sbase + InSmem::kW + kb * InSmem::kWKb + w * 128 * 128, wm[w], w_full,
+                                kb * 64, 0);
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(z_empty(s), ((it >> 1) & 1u) ^ 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidIn, 1);
+                    break;
+                }
+                const TileCoord tc = tile_coord(t, R, tiles_per_line);
+                mbar_arrive_expect_tx(z_full(s), kTileBytes);
+                const uint32_t dst = sbase + InSmem::kZ + s * kTileBytes;
+                for (int kb = 0; kb < 2; ++kb) {
+                    if (kOutgoing)
+                        tma_load_3d(dst + kb * kKBlockBytes, &tmZ, z_full(s), kb * 64, tc.t0,
+                                    tc.b * R + tc.fixed);
+                    else
+                        tma_load_4d(dst + kb * kKBlockBytes, &tmZ, z_full(s), kb * 64, tc.fixed, tc.t0,
+                                    tc.b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_bf16_f32(128, 256);
+            bool ok = mbar_wait(w_full, 0, abort_flag);
+            if (!ok) report_wait_failure(status, abort_flag, kKidIn, 2);
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int s = it & 1;
+                if (!mbar_wait(a_ready(s), (it >> 1) & 1u, abort_flag)) {
+                    report_wait_failure(status, abort_flag, kKidIn, 3);
+                    break;
+                }
+                for (int q = 0; q < 2; ++q) {
+                    if (!mbar_wait(slot_empty(q), (it & 1u) ^ 1u, abort_flag)) {
+                        report_wait_failure(status, abort_flag, kKidIn, 4);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    mma_k128(tmem_base + q * 256, sbase + InSmem::kZ + s * kTileBytes,
+                             sbase + InSmem::kW + q * 256 * 128, InSmem::kWKb, idesc, false);
+                    mma_commit(slot_full(q));
+                }
+                if (ok) mma_commit(z_empty(s));
+            }
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- LayerNorm warps (2..5)
+        const int row = (warp - 2) * 32 + lane;
+        uint32_t it = 0;
+        for (long long t = blockIdx.x; t < num_tiles; t += gridDim.x, ++it) {
+            const int s = it & 1;
+            if (!mbar_wait(z_full(s), (it >> 1) & 1u, abort_flag)) {
+                if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 5);
+                break;
+            }
+            const uint32_t tile = sbase + InSmem::kZ + s * kTileBytes;
+            uint32_t raw[64];
+            load_row(tile, row, raw);
+            float mean, rstd;
+            row_stats(raw, mean, rstd);
+            store_normalized_row(tile, row, raw, mean, rstd, gamma, beta);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(a_ready(s));
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue warps: 6..9 take the a
+        // projection (TMEM slot 0), 10..13 the b projection (slot 1). One set of four warps doing both
+        // (2 x 128 sigmoid / multiply / convert / store per row and tile on one thread) was the longest
+        // chain of the kernel.
+        const int qset = (warp - 6) >> 2;
+        const int quad = warp & 3;
+        const int row = quad * 32 + lane;
+        uint32_t it = 0;
+        bool ok = true;
+        for (long long t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const TileCoord tc = tile_coord(t, R, tiles_per_line);
+            const int k = tc.t0 + row;
+            const bool valid = k < N;
+            float m = 1.0f;
+            if (valid && mask != nullptr) {
+                const long long lin = kOutgoing ? ((long long)(tc.b * R + tc.fixed) * N + k)
+                                                : ((long long)(tc.b * N + k) * R + tc.fixed);
+                m = __bfloat162float(mask[lin]);
+            }
+            for (int q = qset; q <= qset; ++q) {
+                if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
+                    if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                // channel c lives at (c >> group_shift) * group_stride + (c & group_mask) * R * ld: one
+                // contiguous plane [128][R][ld] by default, or one group of channels per destination
+                // rank when the planes are about to be exchanged
+                const long long cs = (long long)R * ld;
+                __nv_bfloat16* dst = (q == 0 ? a_t : b_t) +
+                                     (long long)tc.b * ((kC >> group_shift) * group_stride) +
+                                     (long long)tc.fixed * ld + k;
+                const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + q * 256;
+#pragma unroll 1
+                for (int cb = 0; cb < 4; ++cb) {
+                    uint32_t p[32], g[32];
+                    tmem_ld32(taddr + cb * 32, p);
+                    tmem_ld32(taddr + 128 + cb * 32, g);
+                    tmem_ld_wait();
+                    if (valid) {
+#pragma unroll
+                        for (int hf = 0; hf < 2; ++hf) {  // groups hold >= 16 channels: no boundary inside a half
+                            const int c0 = cb * 32 + hf * 16;
+                            __nv_bfloat16* d0 = dst + (long long)(c0 >> group_shift) * group_stride +
+                                                (long long)(c0 & ((1 << group_shift) - 1)) * cs;
+#pragma unroll
+                            for (int e = 0; e < 16; ++e) {
+                                const float v = m * __uint_as_float(p[hf * 16 + e]) *
+                                                sigmoid_fast(__uint_as_float(g[hf * 16 + e]));
+                                d0[(long long)e * cs] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(slot_empty(q));
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // =====================================================================================
 // trimul_out
 // =====================================================================================
@@ -556,6 +763,8 @@ static int set_attrs() {
     if (!device_configured(5)) {
         OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_rows_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
+        OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_in_rows_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, InSmem::kDyn));
         OF3_CUDA_CHECK(cudaFuncSetAttribute(trimul_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, OutSmem::kDyn));
         device_mark_configured(5);
     }
@@ -603,15 +812,29 @@ int trimul_project(const __nv_bfloat16* z, const __nv_bfloat16* mask, __nv_bfloa
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     // 32-byte stores need every channel row of a_t / b_t to start on a 32-byte boundary
     const int wide = (ld % 16 == 0 && (group_stride % 16) == 0 && ((uintptr_t)a_t & 31) == 0 && ((uintptr_t)b_t & 31) == 0) ? 1 : 0;
+    // a channel plane of R lines: beyond about one 2 MB page the kernel whose stores stay inside one plane wins
+    const bool planes_far_apart = (long long)R * ld * (long long)sizeof(__nv_bfloat16) > (2LL << 20);
     LaunchScope scope(kKidIn, st);
-    if (!transposed_walk)
+    const __nv_bfloat16* lw = (const __nv_bfloat16*)p->ln_in_w;
+    const __nv_bfloat16* lb = (const __nv_bfloat16*)p->ln_in_b;
+    if (planes_far_apart) {
+        if (!transposed_walk)
+            trimul_in_rows_kernel<true><<<grid, kInRowsThreads, InSmem::kDyn, st>>>(
+                tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, lw, lb, a_t, b_t, B, R, N, ld, group_shift, group_stride,
+                device_status_ptr());
+        else
+            trimul_in_rows_kernel<false><<<grid, kInRowsThreads, InSmem::kDyn, st>>>(
+                tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, lw, lb, a_t, b_t, B, R, N, ld, group_shift, group_stride,
+                device_status_ptr());
+    } else if (!transposed_walk) {
         trimul_in_kernel<true><<<grid, kInThreads, InSmem::kDyn, st>>>(
-            tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, wide, device_status_ptr());
-    else
+            tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, lw, lb, a_t, b_t, B, R, N, ld, group_shift, group_stride, wide,
+            device_status_ptr());
+    } else {
         trimul_in_kernel<false><<<grid, kInThreads, InSmem::kDyn, st>>>(
-            tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, (const __nv_bfloat16*)p->ln_in_w,
-            (const __nv_bfloat16*)p->ln_in_b, a_t, b_t, B, R, N, ld, group_shift, group_stride, wide, device_status_ptr());
+            tmZ, tmW[0], tmW[1], tmW[2], tmW[3], mask, lw, lb, a_t, b_t, B, R, N, ld, group_shift, group_stride, wide,
+            device_status_ptr());
+    }
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }

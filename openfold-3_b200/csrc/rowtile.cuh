@@ -149,16 +149,17 @@ __device__ __forceinline__ void load_half_row(uint32_t tile, int row, int half, 
         raw[ch * 4 + 3] = v.w;
     }
 }
-__device__ __forceinline__ void half_row_stats(const uint32_t (&raw)[32], float& mean, float& rstd) {
+// Sum, and sum of squared deviations, of this thread's 64 of a row's 128 values.
+__device__ __forceinline__ float half_row_sum(const uint32_t (&raw)[32]) {
     float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
 #pragma unroll
         for (int a = 0; a < 4; ++a) s[a] += bf16lo(raw[i + a]) + bf16hi(raw[i + a]);
     }
-    float sum = (s[0] + s[1]) + (s[2] + s[3]);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
-    mean = sum * (1.0f / kC);
+    return (s[0] + s[1]) + (s[2] + s[3]);
+}
+__device__ __forceinline__ float half_row_sqdev(const uint32_t (&raw)[32], float mean) {
     float v[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 32; i += 4) {
@@ -169,9 +170,29 @@ __device__ __forceinline__ void half_row_stats(const uint32_t (&raw)[32], float&
             v[a] = fmaf(x1, x1, v[a]);
         }
     }
-    float var = (v[0] + v[1]) + (v[2] + v[3]);
+    return (v[0] + v[1]) + (v[2] + v[3]);
+}
+// the two halves of a row sit 16 lanes apart in one warp
+__device__ __forceinline__ void half_row_stats(const uint32_t (&raw)[32], float& mean, float& rstd) {
+    float sum = half_row_sum(raw);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 16);
+    mean = sum * (1.0f / kC);
+    float var = half_row_sqdev(raw, mean);
     var += __shfl_xor_sync(0xffffffffu, var, 16);
     rstd = rsqrtf(var * (1.0f / kC) + kLnEps);
+}
+// the two halves of a row belong to the same lane of two warps of a group of `nthreads` threads: the partial
+// results cross through xch (2 x 256 floats of shared memory) and two named barriers (id)
+__device__ __forceinline__ void half_row_stats_xwarp(const uint32_t (&raw)[32], int row, int half, float* xch, int bar_id,
+                                                     int nthreads, float& mean, float& rstd) {
+    const float sum = half_row_sum(raw);
+    xch[half * 128 + row] = sum;
+    group_sync(bar_id, nthreads);
+    mean = (sum + xch[(half ^ 1) * 128 + row]) * (1.0f / kC);
+    const float var = half_row_sqdev(raw, mean);
+    xch[256 + half * 128 + row] = var;
+    group_sync(bar_id, nthreads);
+    rstd = rsqrtf((var + xch[256 + (half ^ 1) * 128 + row]) * (1.0f / kC) + kLnEps);
 }
 __device__ __forceinline__ void store_normalized_half_row(uint32_t tile, int row, int half, const uint32_t (&raw)[32],
                                                           float mean, float rstd, const float* gamma,
