@@ -649,6 +649,8 @@ def run_ours(args, cfg) -> None:
             if per_launch_ms <= 0:
                 continue
             sec = per_launch_ms * 1e-3
+            if name == "single_attn_core" and kind != "diffusion":
+                continue   # runs on the second stream under the next block's pair stack: its event time includes waiting
             if name == "single_attn_core":
                 # Q K^T + P V over 16 heads of 24 (trunk) or 48 (diffusion): 4 N^2 (H d) flop per sample; a
                 # row-sharded rank holds 1 / world of the queries, a diffusion rank its share of the samples
