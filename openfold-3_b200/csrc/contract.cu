@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(192, 1)
 contract_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                    __nv_bfloat16* __restrict__ out, int M, int N, int K, int batch,
                    long long out_batch_stride, int ldo, int rows_per_block, long long row_block_stride,
-                   int* status) {
+                   int a_shared, int* status) {
     using Cfg = ContractCfg<BN>;
     constexpr int S = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
@@ -105,7 +105,7 @@ contract_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     }
                     mbar_arrive_expect_tx(full_bar(s), Cfg::kStageBytes);
                     const uint32_t sa = smem_base + s * Cfg::kStageBytes;
-                    tma_load_3d(sa, &tmA, full_bar(s), kb * kBK, mt * kBM, b);
+                    tma_load_3d(sa, &tmA, full_bar(s), kb * kBK, mt * kBM, a_shared ? 0 : b);
                     tma_load_3d(sa + Cfg::kABytes, &tmB, full_bar(s), kb * kBK, nt * BN, b);
                 }
             }
@@ -220,8 +220,9 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
     using Cfg = ContractCfg<BN>;
     CUtensorMap tmA, tmB;
     {
-        uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)batch};
-        uint64_t str[2] = {(uint64_t)lda * 2, (uint64_t)a_bs * 2};
+        // a_bs == 0: every batch entry multiplies the same A (several linear layers on one input)
+        uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, (uint64_t)(a_bs == 0 ? 1 : batch)};
+        uint64_t str[2] = {(uint64_t)lda * 2, (uint64_t)(a_bs == 0 ? (long long)lda * M : a_bs) * 2};
         uint32_t box[3] = {kBK, kBM, 1};
         int rc = make_tmap_bf16(&tmA, a, 3, dims, str, box, true);
         if (rc) return rc;
@@ -246,7 +247,7 @@ int launch_contract(const __nv_bfloat16* a, const __nv_bfloat16* b, __nv_bfloat1
     LaunchScope scope(account_as, stream);  // launch accounting: the triangle einsum or a plain linear layer
     contract_nt_kernel<BN><<<grid, 192, Cfg::kSmemBytes, stream>>>(tmA, tmB, out, M, N, K, batch,
                                                                    o_bs, ldo, rows_per_block, row_block_stride,
-                                                                   status);
+                                                                   a_bs == 0 ? 1 : 0, status);
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }

@@ -117,6 +117,24 @@ int linear_bf16(const bf16* x, const bf16* w, bf16* y, long long rows, int out_d
                             (long long)out_dim * in_dim, rows * out_dim, st, 0, 0, kKidLinear);
 }
 
+// `count` linear layers of equal shape on ONE input: y[i] = x w[i]^T with w[i] = w[0] + i * out_dim * in_dim and
+// y[i] = y[0] + i * rows * out_dim. One launch when the caller's weights lie back to back in memory (the Python
+// modules pack them that way), one launch per layer otherwise.
+int linear_group_bf16(const bf16* x, const bf16* const* w, bf16* y, int count, long long rows, int out_dim, int in_dim,
+                      cudaStream_t st) {
+    const long long w_elems = (long long)out_dim * in_dim;
+    bool adjacent = true;
+    for (int i = 1; i < count; ++i) adjacent = adjacent && (w[i] == w[0] + i * w_elems);
+    if (adjacent && count > 1)
+        return contract_nt_bf16(x, w[0], y, count, (int)rows, out_dim, in_dim, in_dim, in_dim, out_dim, 0, w_elems,
+                                rows * out_dim, st, 0, 0, kKidLinear);
+    for (int i = 0; i < count; ++i) {
+        const int rc = linear_bf16(x, w[i], y + i * rows * out_dim, rows, out_dim, in_dim, st);
+        if (rc) return rc;
+    }
+    return OF3_OK;
+}
+
 // an = AdaLN(a, s) (normalization.py:89-140): LN(a) without affine, LN_s(s) with scale only, two linears
 // from it, combine. t_ln / t_sn / t_g / t_s: scratch [rows, c_a], [rows, c_s], [rows, c_a], [rows, c_a].
 int ada_ln_bf16(const bf16* a, const bf16* s, bf16* an, bf16* t_sn, bf16* t_g, bf16* t_s, long long rows, int c_a,
@@ -131,8 +149,13 @@ int ada_ln_bf16(const bf16* a, const bf16* s, bf16* an, bf16* t_sn, bf16* t_g, b
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     int rc;
-    if ((rc = linear_bf16(t_sn, w_g, t_g, rows, c_a, c_s, st))) return rc;
-    if ((rc = linear_bf16(t_sn, w_s, t_s, rows, c_a, c_s, st))) return rc;
+    if (t_s == t_g + rows * c_a) {   // the two projections of LN_s(s) as one launch
+        const bf16* w2[2] = {w_g, w_s};
+        if ((rc = linear_group_bf16(t_sn, w2, t_g, 2, rows, c_a, c_s, st))) return rc;
+    } else {
+        if ((rc = linear_bf16(t_sn, w_g, t_g, rows, c_a, c_s, st))) return rc;
+        if ((rc = linear_bf16(t_sn, w_s, t_s, rows, c_a, c_s, st))) return rc;
+    }
     {
         LaunchScope scope(kKidSingle, st);
         const long long n2 = rows * c_a / 2;
@@ -159,13 +182,13 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
     const long long rows = (long long)Ba * N;
     const bool ada = (flags & OF3_FLAG_ADA_LN) != 0;
     bf16* t_sn = ada ? (bf16*)ws.take(rows * c_s * sizeof(bf16)) : nullptr;
-    bf16* t_g = ada ? (bf16*)ws.take(rows * c_a * sizeof(bf16)) : nullptr;
-    bf16* t_s = ada ? (bf16*)ws.take(rows * c_a * sizeof(bf16)) : nullptr;
+    bf16* t_g = ada ? (bf16*)ws.take(2 * rows * c_a * sizeof(bf16)) : nullptr;   // t_g, t_s back to back
+    bf16* t_s = ada ? t_g + rows * c_a : nullptr;
     bf16* an = (bf16*)ws.take(rows * c_a * sizeof(bf16));
-    bf16* q = (bf16*)ws.take(rows * c_a * sizeof(bf16));
-    bf16* k = (bf16*)ws.take(rows * c_a * sizeof(bf16));
-    bf16* v = (bf16*)ws.take(rows * c_a * sizeof(bf16));
-    bf16* g = (bf16*)ws.take(rows * c_a * sizeof(bf16));
+    bf16* q = (bf16*)ws.take(4 * rows * c_a * sizeof(bf16));   // q, g, k, v back to back
+    bf16* g = q + rows * c_a;
+    bf16* k = g + rows * c_a;
+    bf16* v = k + rows * c_a;
     bf16* og = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     bf16* y = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     float* zb = (float*)ws.take((size_t)Bz * H * N * N * sizeof(float));
@@ -190,10 +213,10 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
                                                                    an, rows, c_a);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
-    if ((rc = linear_bf16(an, (const bf16*)p->w_q, q, rows, c_a, c_a, st))) return rc;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_k, k, rows, c_a, c_a, st))) return rc;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_v, v, rows, c_a, c_a, st))) return rc;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_g, g, rows, c_a, c_a, st))) return rc;
+    {
+        const bf16* w4[4] = {(const bf16*)p->w_q, (const bf16*)p->w_g, (const bf16*)p->w_k, (const bf16*)p->w_v};
+        if ((rc = linear_group_bf16(an, w4, q, 4, rows, c_a, c_a, st))) return rc;
+    }
     if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, d, inf, Ba / Bz, ws, st)))
         return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
@@ -222,18 +245,20 @@ int cond_transition(const bf16* a, const bf16* s, const bf16* mask, bf16* out, l
     const int hid = n * c_a;
     bf16* an = (bf16*)ws.take(rows * c_a * sizeof(bf16));
     bf16* t_sn = (bf16*)ws.take(rows * c_s * sizeof(bf16));
-    bf16* t_g = (bf16*)ws.take(rows * c_a * sizeof(bf16));
-    bf16* t_s = (bf16*)ws.take(rows * c_a * sizeof(bf16));
-    bf16* ha = (bf16*)ws.take(rows * hid * sizeof(bf16));
-    bf16* hb = (bf16*)ws.take(rows * hid * sizeof(bf16));
+    bf16* t_g = (bf16*)ws.take(2 * rows * c_a * sizeof(bf16));   // t_g, t_s back to back
+    bf16* t_s = t_g + rows * c_a;
+    bf16* ha = (bf16*)ws.take(2 * rows * hid * sizeof(bf16));    // ha, hb back to back
+    bf16* hb = ha + rows * hid;
     if (!ws.base) return OF3_OK;
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "cond_transition: workspace too small (%zu needed)", ws.off);
     int rc;
     if ((rc = ada_ln_bf16(a, s, an, t_sn, t_g, t_s, rows, c_a, c_s, (const bf16*)p->ada_ln_s_w, (const bf16*)p->ada_w_g,
                           (const bf16*)p->ada_b_g, (const bf16*)p->ada_w_s, st)))
         return rc;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_a, ha, rows, hid, c_a, st))) return rc;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_b, hb, rows, hid, c_a, st))) return rc;
+    {
+        const bf16* w2[2] = {(const bf16*)p->w_a, (const bf16*)p->w_b};
+        if ((rc = linear_group_bf16(an, w2, ha, 2, rows, hid, c_a, st))) return rc;
+    }
     {
         LaunchScope scope(kKidSingle, st);
         const long long n2 = rows * hid / 2;
@@ -260,10 +285,10 @@ int attn_pair_bias_rows(const bf16* a, const float* pair_bias_rows, const bf16* 
                         int R, int c_a, int H, int d, float inf, int flags, const of3_attn_pair_bias_params* p,
                         Arena& ws, cudaStream_t st) {
     bf16* an = (bf16*)ws.take((size_t)N * c_a * sizeof(bf16));
-    bf16* k = (bf16*)ws.take((size_t)N * c_a * sizeof(bf16));
-    bf16* v = (bf16*)ws.take((size_t)N * c_a * sizeof(bf16));
-    bf16* q = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
-    bf16* g = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
+    bf16* k = (bf16*)ws.take((size_t)2 * N * c_a * sizeof(bf16));   // k, v back to back
+    bf16* v = k + (size_t)N * c_a;
+    bf16* q = (bf16*)ws.take((size_t)2 * R * c_a * sizeof(bf16));   // q, g back to back
+    bf16* g = q + (size_t)R * c_a;
     bf16* og = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
     bf16* y = (bf16*)ws.take((size_t)R * c_a * sizeof(bf16));
     if (!ws.base)
@@ -280,10 +305,12 @@ int attn_pair_bias_rows(const bf16* a, const float* pair_bias_rows, const bf16* 
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     const bf16* an_w = an + (long long)row0 * c_a;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_k, k, N, c_a, c_a, st))) return rc;
-    if ((rc = linear_bf16(an, (const bf16*)p->w_v, v, N, c_a, c_a, st))) return rc;
-    if ((rc = linear_bf16(an_w, (const bf16*)p->w_q, q, R, c_a, c_a, st))) return rc;
-    if ((rc = linear_bf16(an_w, (const bf16*)p->w_g, g, R, c_a, c_a, st))) return rc;
+    {
+        const bf16* wkv[2] = {(const bf16*)p->w_k, (const bf16*)p->w_v};
+        const bf16* wqg[2] = {(const bf16*)p->w_q, (const bf16*)p->w_g};
+        if ((rc = linear_group_bf16(an, wkv, k, 2, N, c_a, c_a, st))) return rc;
+        if ((rc = linear_group_bf16(an_w, wqg, q, 2, R, c_a, c_a, st))) return rc;
+    }
     if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias_rows, mask, og, 1, N, R, H, d, inf, 1, ws, st)))
         return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, R, c_a, c_a, st))) return rc;
@@ -304,8 +331,8 @@ int transition_wide(const bf16* x, const bf16* mask, bf16* out, long long rows, 
                     const of3_transition_params* p, Arena& ws, cudaStream_t st) {
     const int hid = n * c;
     bf16* xn = (bf16*)ws.take(rows * c * sizeof(bf16));
-    bf16* ha = (bf16*)ws.take(rows * hid * sizeof(bf16));
-    bf16* hb = (bf16*)ws.take(rows * hid * sizeof(bf16));
+    bf16* ha = (bf16*)ws.take(2 * rows * hid * sizeof(bf16));   // ha, hb back to back
+    bf16* hb = ha + rows * hid;
     bf16* y = (bf16*)ws.take(rows * c * sizeof(bf16));
     if (!ws.base) return OF3_OK;
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "transition: workspace too small (%zu needed)", ws.off);
@@ -317,8 +344,10 @@ int transition_wide(const bf16* x, const bf16* mask, bf16* out, long long rows, 
                                                                    rows, c);
     }
     OF3_CUDA_CHECK(cudaGetLastError());
-    if ((rc = linear_bf16(xn, (const bf16*)p->w_a, ha, rows, hid, c, st))) return rc;
-    if ((rc = linear_bf16(xn, (const bf16*)p->w_b, hb, rows, hid, c, st))) return rc;
+    {
+        const bf16* w2[2] = {(const bf16*)p->w_a, (const bf16*)p->w_b};
+        if ((rc = linear_group_bf16(xn, w2, ha, 2, rows, hid, c, st))) return rc;
+    }
     {
         LaunchScope scope(kKidSingle, st);
         const long long n2 = rows * hid / 2;

@@ -470,6 +470,7 @@ trimul_in_rows_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                                                 : ((long long)(tc.b * N + k) * R + tc.fixed);
                 m = __bfloat162float(mask[lin]);
             }
+            const float mh = 0.5f * m;
             for (int q = qset; q <= qset; ++q) {
                 if (!mbar_wait(slot_full(q), it & 1u, abort_flag)) {
                     if (lane == 0) report_wait_failure(status, abort_flag, kKidIn, 6);
@@ -499,8 +500,10 @@ trimul_in_rows_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                                                 (long long)(c0 & ((1 << group_shift) - 1)) * cs;
 #pragma unroll
                             for (int e = 0; e < 16; ++e) {
-                                const float v = m * __uint_as_float(p[hf * 16 + e]) *
-                                                sigmoid_fast(__uint_as_float(g[hf * 16 + e]));
+                                // the same expression as the kernel above, so that both give the same bits:
+                                // mask * p * sigmoid(g) = pm * tanh(g / 2) + pm with pm = (mask / 2) * p
+                                const float pm = mh * __uint_as_float(p[hf * 16 + e]);
+                                const float v = fmaf(tanh_approx(0.5f * __uint_as_float(g[hf * 16 + e])), pm, pm);
                                 d0[(long long)e * cs] = __float2bfloat16_rn(v);
                             }
                         }

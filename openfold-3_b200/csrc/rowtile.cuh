@@ -82,29 +82,36 @@ __device__ __forceinline__ void load_row(uint32_t tile, int row, uint32_t (&raw)
     }
 }
 
-// LayerNorm statistics of 128 packed bf16 values (fp32, two-pass on registers). Eight independent
-// partial sums: a single accumulator is a 128-deep dependent chain, which with two warps per
-// scheduler is pure latency.
+// LayerNorm statistics of 128 packed bf16 values (fp32, two-pass on registers). Eight independent partial sums (a
+// single accumulator is a 128-deep dependent chain, which with two warps per scheduler is pure latency), associated
+// exactly like the two-threads-per-row variant below -- four partial sums per half row, the halves added last -- so
+// that kernels that split a row over two threads and kernels that do not produce the same bits.
 __device__ __forceinline__ void row_stats(const uint32_t (&raw)[64], float& mean, float& rstd) {
     float s[8];
 #pragma unroll
     for (int a = 0; a < 8; ++a) s[a] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 64; i += 8) {
+    for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int a = 0; a < 8; ++a) s[a] += bf16lo(raw[i + a]) + bf16hi(raw[i + a]);
+        for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+            for (int a = 0; a < 4; ++a) s[h * 4 + a] += bf16lo(raw[h * 32 + i + a]) + bf16hi(raw[h * 32 + i + a]);
+        }
     }
     mean = (((s[0] + s[1]) + (s[2] + s[3])) + ((s[4] + s[5]) + (s[6] + s[7]))) * (1.0f / kC);
     float v[8];
 #pragma unroll
     for (int a = 0; a < 8; ++a) v[a] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 64; i += 8) {
+    for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int a = 0; a < 8; ++a) {
-            const float x0 = bf16lo(raw[i + a]) - mean, x1 = bf16hi(raw[i + a]) - mean;
-            v[a] = fmaf(x0, x0, v[a]);
-            v[a] = fmaf(x1, x1, v[a]);
+        for (int i = 0; i < 32; i += 4) {
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float x0 = bf16lo(raw[h * 32 + i + a]) - mean, x1 = bf16hi(raw[h * 32 + i + a]) - mean;
+                v[h * 4 + a] = fmaf(x0, x0, v[h * 4 + a]);
+                v[h * 4 + a] = fmaf(x1, x1, v[h * 4 + a]);
+            }
         }
     }
     const float var = (((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]))) * (1.0f / kC);

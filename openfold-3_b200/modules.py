@@ -155,12 +155,18 @@ class _PackedParams:
         self._key = None
         self._val = None
 
-    def get(self, tensors, dtype, device):
+    def get(self, tensors, dtype, device, adjacent=()):
+        """``adjacent``: groups of indices of equally shaped tensors whose copies are laid out back to back in one
+        allocation (the library then runs linear layers that share an input as one launch)."""
         key = (dtype, device, tuple((t.data_ptr(), t._version) if t is not None else None for t in tensors))
         if key != self._key:
-            self._val = tuple(
-                None if t is None else t.detach().to(device=device, dtype=dtype).contiguous() for t in tensors
-            )
+            val = [None if t is None else t.detach().to(device=device, dtype=dtype).contiguous() for t in tensors]
+            for group in adjacent:
+                if all(val[i] is not None for i in group):
+                    block = torch.stack([val[i] for i in group])
+                    for n, i in enumerate(group):
+                        val[i] = block[n]
+            self._val = tuple(val)
             self._key = key
         return self._val
 
@@ -279,7 +285,7 @@ class SwiGLUTransition(nn.Module):
     def _params(self, dtype, device):
         return self._packed.get(
             (self.layer_norm.weight, self.layer_norm.bias, self.swiglu.linear_a.weight,
-             self.swiglu.linear_b.weight, self.linear_out.weight), dtype, device)
+             self.swiglu.linear_b.weight, self.linear_out.weight), dtype, device, adjacent=((2, 3),))
 
     def _run(self, x, mask, in_place: bool):
         xc = x.contiguous().view(-1, self.c_in)
@@ -312,7 +318,7 @@ class ConditionedTransitionBlock(nn.Module):
         return self._packed.get(
             (ln.layer_norm_s.weight, ln.linear_g.weight, ln.linear_g.bias, ln.linear_s.weight,
              self.swiglu.linear_a.weight, self.swiglu.linear_b.weight, self.linear_g.weight,
-             self.linear_g.bias, self.linear_out.weight), dtype, device)
+             self.linear_g.bias, self.linear_out.weight), dtype, device, adjacent=((1, 3), (4, 5)))
 
     def _run(self, a, s, mask, in_place: bool):
         ac = a.contiguous().view(-1, self.c_a)
@@ -366,7 +372,8 @@ class AttentionPairBias(nn.Module):
         return self._packed.get(
             head + (self.layer_norm_z.weight, self.layer_norm_z.bias, self.linear_z.weight,
                     m.linear_q.weight, m.linear_q.bias, m.linear_k.weight, m.linear_v.weight,
-                    m.linear_g.weight, m.linear_o.weight), dtype, device)
+                    m.linear_g.weight, m.linear_o.weight), dtype, device,
+            adjacent=((11, 15, 13, 14), (3, 5)))   # q, g, k, v projections; the two AdaLN projections
 
     def can_hoist_pair_bias(self, z) -> bool:
         """Whether ``project_pair_bias`` has a kernel for this layer (c_z = 128, 16 heads, bf16 or fp32)."""

@@ -313,3 +313,27 @@ def test_large_complex_shape_p8_n2048_row_shards_match_whole_tensor(pkg):
     rms = z_ref[0].float()[valid].pow(2).mean().sqrt()
     assert torch.isfinite(z_dap.float()).all()
     assert float(d.abs().max() / rms) < 2e-2, float(d.abs().max() / rms)
+
+
+def test_both_projection_kernels_of_the_triangle_update_give_the_same_bits(pkg):
+    """A whole N = 2048 tensor (channel planes of 8 MB: the row-oriented projection kernel) against a 256-row shard of
+    it (1 MB planes: the transposed kernel), random pair mask: the a / b planes of the shard's rows must be equal bit
+    for bit, or a sharded run could differ from the single-GPU run of the same model."""
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    N, R = 2048, 256
+    g = torch.Generator().manual_seed(11)
+    z = torch.randn(N, N, 128, generator=g).to(dev, bf)
+    m = (torch.rand(N, N, generator=g) > 0.1).to(dev, bf)
+    blk = pkg.PairBlock(**cases.PAIR, transition_type="swiglu", pair_dropout=0.25, fuse_projection_weights=False,
+                        inf=1e9)
+    blk.load_state_dict(pkg.weights.pair_block_params(seed=12, **cases.PAIR), strict=True)
+    blk = blk.to(dev, bf).eval()
+    ops = pkg.dap.CudaOps(dev)
+    with torch.no_grad():
+        for mod, incoming in ((blk.tri_mul_out, False),):
+            whole = ops.trimul_project(z, m, mod, 1, incoming)
+            shard = ops.trimul_project(z[:R].contiguous(), m[:R].contiguous(), mod, 1, incoming)
+            torch.cuda.synchronize()
+            pkg.lib.check_device_status()
+            assert torch.equal(whole[0, :, :, :R, :], shard[0])
