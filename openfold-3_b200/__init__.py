@@ -8,6 +8,7 @@ CUDA kernels from the in-tree C-ABI library ``libof3b200.so``.
 
 from . import dap, init_config, lib, weights
 from .patch import patch_openfold3, unpatch_openfold3
+from .graphs import GraphedModule
 from .modules import (
     AdaLN,
     Attention,
