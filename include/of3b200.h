@@ -163,7 +163,12 @@ int of3_transition_forward(const void* x, const void* mask, void* out, long long
  * token track (AdaLN, openfold3/core/model/primitives/normalization.py:89-140).
  * a, out: [Ba, N, c_a]; z: [Bz, N, N, c_z] with Ba a multiple of Bz (samples sharing one pair
  * tensor are consecutive); s: [Ba, N, c_s] (AdaLN only, else NULL); mask: [Ba, N] or NULL.
- * out may alias a. */
+ * out may alias a.
+ * Launch grouping (bf16 kernels; an optimisation, never a requirement): linear layers that read the
+ * same input run as ONE launch when their weights lie back to back in memory -- here w_q, w_g, w_k,
+ * w_v in this order (w_g == w_q + H*d*c_a elements, ...) and ada_w_g, ada_w_s; in
+ * of3_cond_transition_params ada_w_g, ada_w_s and w_a, w_b; in of3_transition_params w_a, w_b.
+ * Otherwise each layer is its own launch, with the same result. */
 typedef struct {
     const void* ln_a_w;      /* [c_a] layer_norm_a.weight              (LayerNorm variant) */
     const void* ln_a_b;      /* [c_a] layer_norm_a.bias                (LayerNorm variant) */
