@@ -180,3 +180,30 @@ def test_diffusion_stack_hoists_the_pair_bias_of_an_unchanged_pair_tensor(pkg, d
         assert torch.equal(st(xd["a"], xd["s"], xd["z"], mask=xd["mask"]), ref2)
     torch.cuda.synchronize()
     pkg.lib.check_device_status()
+
+
+def test_grouped_linear_launches_equal_separate_launches(pkg):
+    """q | g | k | v and the AdaLN / SwiGLU pairs run as one launch each when their weights lie back to back (how the
+    modules pack them); with every weight in an allocation of its own they run one by one. Same bits either way."""
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    g = torch.Generator().manual_seed(77)
+    n = 70
+    blk = pkg.DiffusionTransformerBlock(**cases.DIFF, use_ada_layer_norm=True, n_query=None, n_key=None, inf=1e9)
+    blk.load_state_dict(pkg.weights.diffusion_block_params(seed=78, final_std=None, **cases.DIFF), strict=True)
+    blk = blk.to(dev, bf).eval()
+    a = torch.randn(1, 2, n, 768, generator=g).to(dev, bf)
+    s = torch.randn(1, 2, n, 384, generator=g).to(dev, bf)
+    z = torch.randn(1, 1, n, n, 128, generator=g).to(dev, bf)
+    m = torch.ones(1, 1, n, device=dev, dtype=bf)
+    with torch.no_grad():
+        grouped = blk(a, s, z, mask=m)
+        for mod in (blk.attention_pair_bias, blk.conditioned_transition):
+            prm = mod._params(bf, dev)
+            ptrs = [t.data_ptr() for t in prm if t is not None]
+            mod._packed._val = tuple(None if t is None else t.clone() for t in prm)   # one allocation per tensor
+            assert [t.data_ptr() for t in mod._packed._val if t is not None] != ptrs
+        separate = blk(a, s, z, mask=m)
+    torch.cuda.synchronize()
+    pkg.lib.check_device_status()
+    assert torch.equal(grouped, separate)
