@@ -524,7 +524,8 @@ def run_ours(args, cfg) -> None:
         if runner is not None:
             return dap_step(runner, x)
         if graphed_mod is not None and x:
-            return (graphed_mod(*x),)
+            res = graphed_mod(*x)
+            return res if isinstance(res, tuple) else (res,)
         return job["run"](x)
 
     def step_eager(x):
@@ -549,9 +550,23 @@ def run_ours(args, cfg) -> None:
             for _ in range(args.warmup):
                 step_resident(x_dev)
             sync()
-        if kind == "diffusion" and job["host_in"] and not args.no_graph:
-            # ~500 launches of a few microseconds per step: replayed from one CUDA graph (openfold-3_b200/graphs.py)
-            graphed_mod = pkg.GraphedModule(lambda a, s, z, m: model(a, s, z, mask=m), *x_dev, warmup=1)
+        if world == 1 and kind != "diffusion" and args.graph_single:
+            # the whole single-GPU step (both streams of PairFormerStack) as one CUDA graph
+            if kind == "trunk":
+                graphed_mod = pkg.GraphedModule(lambda s_, z_, sm_, pm_: model(s_, z_, sm_, pm_, inplace_safe=True),
+                                                *x_dev, warmup=1)
+            else:
+                graphed_mod = pkg.GraphedModule(lambda z_, pm_: (model(z_, pm_, inplace_safe=True),), *x_dev, warmup=1)
+            stage("graph captured")
+            graph_note = "one CUDA graph per step"
+            for _ in range(args.warmup):
+                step_resident(x_dev)
+            sync()
+        if kind == "diffusion" and not args.no_graph:
+            # ~500 launches of a few microseconds per step: replayed from one CUDA graph (openfold-3_b200/graphs.py).
+            # Every rank walks through here (sync() is a collective), ranks without a sample capture nothing.
+            if job["host_in"]:
+                graphed_mod = pkg.GraphedModule(lambda a, s, z, m: model(a, s, z, mask=m), *x_dev, warmup=1)
             stage("graph captured")
             graph_note = "one CUDA graph per step"
             for _ in range(args.warmup):
@@ -589,7 +604,8 @@ def run_ours(args, cfg) -> None:
 
         def step_e2e():
             if graphed_mod is not None and job["host_in"]:
-                res = (graphed_mod(*job["host_in"]),)   # the copy into the graph's input buffers is the upload
+                res = graphed_mod(*job["host_in"])   # the copy into the graph's input buffers is the upload
+                res = res if isinstance(res, tuple) else (res,)
                 for dst, src in zip(job["host_out"], res):
                     dst.copy_(src, non_blocking=True)
                 return
@@ -774,12 +790,18 @@ def main():
                     help="workload; c2 (the 48-block trunk at N_token = 768) is the headline")
     ap.add_argument("--blocks", type=int, default=0, help="override the configuration's depth (profiling runs)")
     ap.add_argument("--n-token", type=int, default=0, help="override the configuration's N_token (profiling runs)")
+    ap.add_argument("--samples", type=int, default=0, help="override c4's sample count (test runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how shards move between GPUs")
+    ap.add_argument("--graph-single", action="store_true",
+                    help="N = 1, trunk / pair stack: replay the step from one CUDA graph (GraphedModule)")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: launch eagerly instead of replaying a CUDA graph")
     args = ap.parse_args()
-    cfg = CONFIGS[args.config]
+    cfg = dict(CONFIGS[args.config])
+    if args.samples and "samples" in cfg:
+        cfg["samples"] = args.samples
+        cfg["label"] = cfg["label"].replace("5 samples", f"{args.samples} samples")
     if args.impl == "reference":
         run_reference(args, cfg)
     else:
