@@ -550,7 +550,7 @@ def run_ours(args, cfg) -> None:
             for _ in range(args.warmup):
                 step_resident(x_dev)
             sync()
-        if world == 1 and kind != "diffusion" and args.graph_single:
+        if world == 1 and kind != "diffusion" and not args.no_graph:
             # the whole single-GPU step (both streams of PairFormerStack) as one CUDA graph
             if kind == "trunk":
                 graphed_mod = pkg.GraphedModule(lambda s_, z_, sm_, pm_: model(s_, z_, sm_, pm_, inplace_safe=True),
@@ -794,9 +794,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="N > 1: how shards move between GPUs")
-    ap.add_argument("--graph-single", action="store_true",
-                    help="N = 1, trunk / pair stack: replay the step from one CUDA graph (GraphedModule)")
-    ap.add_argument("--no-graph", action="store_true", help="N > 1: launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying one CUDA graph per step")
     args = ap.parse_args()
     cfg = dict(CONFIGS[args.config])
     if args.samples and "samples" in cfg:
