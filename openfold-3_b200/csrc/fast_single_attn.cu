@@ -39,23 +39,26 @@ struct Cfg {
     static constexpr int kKD = (D <= 32) ? 32 : 64;      // K dim of Q K^T after zero padding
     static constexpr int kKSteps = (D + 15) / 16;        // K = 16 steps that hold data
     static constexpr int kDV = (D <= 32) ? 32 : 48;      // rows of the V^T tile = columns of O
-    static constexpr int kStages = (D <= 32) ? 4 : 3;    // rings of K + bias tiles and of V tiles
+    static constexpr int kStages = (D <= 32) ? 4 : 3;    // ring of K + bias tiles
+    static constexpr int kVStages = (D <= 32) ? 4 : 2;   // ring of V tiles (two CTAs of 16 x 48 heads must fit an SM)
     static constexpr uint32_t kQBytes = kBQ * kKD * 2;   // 8 or 16 KB
     static constexpr uint32_t kKBytes = kBK * kKD * 2;   // 2 or 4 KB
-    static constexpr uint32_t kVBytes = kDV * kBK * 2;   // 2 or 3 KB
+    static constexpr uint32_t kVBytes = kDV * kBK * 2;   // 2 or 3 KB: the tile a bulk copy brings
+    static constexpr int kON = kDV + 16;                 // N of the P V GEMM: channels, a row of ones (-> row sum), padding
+    static constexpr uint32_t kVSlot = kON * kBK * 2;    // 3 or 4 KB: rows kDV .. kDV + 15 are written once per CTA
     static constexpr uint32_t kTbBytes = kBQ * kBK * 2;  // 8 KB
     // shared memory (offsets from a 1024-byte boundary)
     static constexpr uint32_t kQ = 0;
     static constexpr uint32_t kK = kQ + kLines * kQBytes;
     static constexpr uint32_t kTb = kK + kStages * kLines * kKBytes;
     static constexpr uint32_t kV = kTb + kStages * kTbBytes;
-    static constexpr uint32_t kIdent = kV + kStages * kLines * kVBytes;
+    static constexpr uint32_t kIdent = kV + kVStages * kLines * kVSlot;
     static constexpr uint32_t kBars = kIdent + 2048;
     static constexpr uint32_t kFlags = kBars + 320;       // lines x 256 key-block flags (bytes)
     static constexpr uint32_t kMb = kFlags + kLines * 256;
     static uint32_t dyn_bytes(int nkp) { return kMb + kLines * nkp * 4 + 1024; }
     // TMEM columns of a line (128): S slots [0,32) [32,64), each taking the step's P (16 columns of bf16 pairs)
-    // in place once S has been read out; O [64, 64 + kDV)
+    // in place once S has been read out; O [64, 64 + kON): kDV channels, then the sum of the row's P
     static constexpr uint32_t kColO = 64;
 };
 
@@ -167,7 +170,7 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
                    const bf16* __restrict__ tb_img, const bf16* __restrict__ mask, const bf16* __restrict__ gate,
                    bf16* __restrict__ out, int N, int nq, int H, int rpb, float inf, int* status) {
     using C = Cfg<D>;
-    constexpr int KD = C::kKD, DV = C::kDV, kSt = C::kStages;
+    constexpr int KD = C::kKD, DV = C::kDV, kSt = C::kStages, kVSt = C::kVStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -179,8 +182,8 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
     auto kb_empty = [&](int s) { return bars + 8u * (1 + kSt + s); };
     constexpr int kB1 = 1 + 2 * kSt;
     auto v_full = [&](int s) { return bars + 8u * (kB1 + s); };
-    auto v_empty = [&](int s) { return bars + 8u * (kB1 + kSt + s); };
-    constexpr int kB2 = kB1 + 2 * kSt;
+    auto v_empty = [&](int s) { return bars + 8u * (kB1 + kVSt + s); };
+    constexpr int kB2 = kB1 + 2 * kVSt;
     auto s_full = [&](int L, int s) { return bars + 8u * (kB2 + L * 2 + s); };
     auto p_ready = [&](int L, int s) { return bars + 8u * (kB2 + 2 * kLines + L * 2 + s); };
     auto pv_done = [&](int L, int s) { return bars + 8u * (kB2 + 4 * kLines + L * 2 + s); };
@@ -207,6 +210,8 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
         for (int s = 0; s < kSt; ++s) {
             mbar_init(kb_full(s), 1);
             mbar_init(kb_empty(s), 4 * kLines);  // every softmax warp has read the S that consumed the stage
+        }
+        for (int s = 0; s < kVSt; ++s) {
             mbar_init(v_full(s), 1);
             mbar_init(v_empty(s), kLines);       // each line's commit after the P V that read the stage
         }
@@ -229,6 +234,13 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
         if (k + 1 == n) v = 0x3F800000u;
         const int chunk = (k >> 3) ^ ((n >> 1) & 3);
         *reinterpret_cast<uint32_t*>(gbase + C::kIdent + n * 64 + chunk * 16 + (w & 3) * 4) = v;
+    }
+    // rows kDV .. kDV + 15 of every V slot: a row of ones (column kDV of O then accumulates the row sum of P on the
+    // tensor pipe, rounded exactly like the numerator) and 15 rows of zeros; the bulk copies write rows 0 .. kDV - 1
+    for (int idx = threadIdx.x; idx < kVSt * kLines * 64; idx += blockDim.x) {
+        const int slot = idx >> 6, w = idx & 63;   // 64 uint4 = 1 KB per slot
+        const uint32_t v = (w < 4) ? 0x3F803F80u : 0u;
+        *reinterpret_cast<uint4*>(gbase + C::kV + slot * C::kVSlot + C::kVBytes + w * 16) = make_uint4(v, v, v, v);
     }
     fence_proxy_async_smem();
     if (warp == 1) {
@@ -263,15 +275,16 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
                               kb_full(s));
                 bulk_load(sbase + C::kTb + s * C::kTbBytes, tb_img + ((zh * nblk + j) * (long long)nq + q0) * kBK,
                           tb_bytes, kb_full(s));
-                if (!mbar_wait(v_empty(s), ph, abort_flag)) {
+                const int sv = j % kVSt;
+                if (!mbar_wait(v_empty(sv), ((j / kVSt) & 1u) ^ 1u, abort_flag)) {
                     report_wait_failure(status, abort_flag, kKidSingleCore, 11);
                     break;
                 }
-                mbar_arrive_expect_tx(v_full(s), kLines * C::kVBytes);
+                mbar_arrive_expect_tx(v_full(sv), kLines * C::kVBytes);
                 for (int L = 0; L < kLines; ++L)
-                    bulk_load(sbase + C::kV + (s * kLines + L) * C::kVBytes,
+                    bulk_load(sbase + C::kV + (sv * kLines + L) * C::kVSlot,
                               v_img + (((sample_of(L) * H + h) * nblk + j) * (long long)DV) * kBK, C::kVBytes,
-                              v_full(s));
+                              v_full(sv));
             }
         }
     } else if (warp <= kLines) {
@@ -282,7 +295,7 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
         const uint32_t sb = __shfl_sync(0xffffffffu, sbase, 0);
         constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);
-        constexpr uint32_t idesc_o = idesc_bf16_f32(128, DV);
+        constexpr uint32_t idesc_o = idesc_bf16_f32(128, C::kON);
         auto kdesc_of = [](uint32_t a) { return KD == 32 ? smem_desc_k_sw64(a) : smem_desc_k_sw128(a); };
         bool ok = mbar_wait(q_full, 0, abort_flag);
         if (!ok && lane == 0) report_wait_failure(status, abort_flag, kKidSingleCore, 2);
@@ -319,8 +332,8 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
         ok = ok && issue_s(0);
         if (ok && nblk > 1) ok = issue_s(1);
         for (int j = 0; j < nblk && ok; ++j) {
-            const int vs = j % kSt;
-            if (!mbar_wait(v_full(vs), (j / kSt) & 1u, abort_flag)) {
+            const int vs = j % kVSt;
+            if (!mbar_wait(v_full(vs), (j / kVSt) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidSingleCore, 12);
                 break;
             }
@@ -329,7 +342,7 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
                 break;
             }
             tc_fence_after_sync();
-            const uint64_t vdesc = smem_desc_k_sw64(sb + C::kV + (vs * kLines + L) * C::kVBytes);
+            const uint64_t vdesc = smem_desc_k_sw64(sb + C::kV + (vs * kLines + L) * C::kVSlot);
             if (lane == 0) {
                 const uint32_t a_p = t_line + (j & 1) * kBK;
                 mma_bf16_ts(t_line + C::kColO, a_p, vdesc, idesc_o, j != 0 ? 1u : 0u);
@@ -377,7 +390,7 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
             }
             group_sync(1 + L, 128);
         }
-        float m_used = 0.f, l = 0.f;
+        float m_used = 0.f;
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
@@ -448,22 +461,20 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
                     for (int e = 0; e < 16; ++e) o2[e] = __float_as_uint(__uint_as_float(o2[e]) * f);
                     tmem_st16(trow + C::kColO + 32, o2);
                 }
+                const uint32_t lsum = tmem_ld1(trow + C::kColO + DV);   // the row sum rides in column kDV of O
+                tmem_ld_wait();
+                tmem_st1(trow + C::kColO + DV, __float_as_uint(__uint_as_float(lsum) * f));
                 tmem_st_wait();
-                l *= f;
             }
             uint32_t pk[16];
             const float nm = -m_used;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < 32; e += 2) {
                 add2(sv[e], sv[e + 1], nm, nm);
-                const float p0 = ex2_approx(sv[e]), p1 = ex2_approx(sv[e + 1]);
-                add2(sum[(e >> 1) & 1 ? 2 : 0], sum[(e >> 1) & 1 ? 3 : 1], p0, p1);
-                pk[e >> 1] = pack_bf16x2(p0, p1);
+                pk[e >> 1] = pack_bf16x2(ex2_approx(sv[e]), ex2_approx(sv[e + 1]));
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
             // P_j goes where S_j was: every thread of the warp has its S row in registers (the load above is
-            // warp-wide), other warps own other lanes
+            // warp-wide), other warps own other lanes; the row sum is taken by the tensor pipe from the rounded P
             tmem_st16(trow + s * kBK, pk);
             tmem_st_wait();
             tc_fence_before_sync();
@@ -473,7 +484,9 @@ single_core_kernel(const bf16* __restrict__ q_img, const bf16* __restrict__ k_im
         if (ok) {
             if (mbar_wait(pv_done(L, (nblk - 1) & 1), ((nblk - 1) >> 1) & 1u, abort_flag)) {
                 tc_fence_after_sync();
-                const float inv = 1.0f / l;
+                const uint32_t lsum = tmem_ld1(trow + C::kColO + DV);
+                tmem_ld_wait();
+                const float inv = 1.0f / __uint_as_float(lsum);
                 const bool store = qpos < nq && line_valid;
                 const long long off = (bb * nq + qpos) * (long long)(H * D) + h * D;
 #pragma unroll

@@ -346,9 +346,9 @@ constexpr int kLinePad = 4;   // the operand images pad the line count of a samp
 constexpr int kCoreThreads = 32 * (1 + kLines + 4 * kLines);  // producer, one MMA warp per line, softmax
 constexpr float kRescaleThreshold = 8.0f;
 constexpr uint32_t kTbTileBytes = kBQ * kBiasK * 2;    // 8192
-constexpr uint32_t kVSlot = 2048;                      // V tile [32 d][32 keys]
-constexpr int kON = 32;                                // N of the P V GEMM: the head's 32 output channels
-constexpr uint32_t kColP = 64, kColO = 96;
+constexpr uint32_t kVSlot = 3072;                      // V tile [32 d][32 keys] + a row of ones + 15 unused rows
+constexpr int kON = 48;                                // N of the P V GEMM: 32 output channels, the row sum, padding
+constexpr uint32_t kColO = 64;                         // O [64, 112): 32 channels, column 32 = sum of the row's P
 
 struct CoreSmem {
     static constexpr uint32_t kQ = 0;                                   // lines x 8 KB
@@ -382,10 +382,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
     auto v_empty = [&](int s) { return bars + 8u * (kB1 + kVStages + s); };
     constexpr int kB2 = kB1 + 2 * kVStages;
     auto s_full = [&](int L, int s) { return bars + 8u * (kB2 + L * 2 + s); };
-    auto s_empty = [&](int L, int s) { return bars + 8u * (kB2 + 2 * kLines + L * 2 + s); };
-    auto p_ready = [&](int L, int s) { return bars + 8u * (kB2 + 4 * kLines + L * 2 + s); };
-    auto pv_done = [&](int L, int s) { return bars + 8u * (kB2 + 6 * kLines + L * 2 + s); };
-    constexpr int kNumBars = kB2 + 8 * kLines;
+    auto p_ready = [&](int L, int s) { return bars + 8u * (kB2 + 2 * kLines + L * 2 + s); };
+    auto pv_done = [&](int L, int s) { return bars + 8u * (kB2 + 4 * kLines + L * 2 + s); };
+    constexpr int kNumBars = kB2 + 6 * kLines;
     static_assert(8 * kNumBars + 16 <= 320, "barrier block");
     volatile uint32_t* tmem_ptr = reinterpret_cast<volatile uint32_t*>(gbase + CoreSmem::kBars + 8 * kNumBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(gbase + CoreSmem::kBars + 8 * kNumBars + 8);
@@ -417,7 +416,6 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         for (int L = 0; L < kLines; ++L) {
             for (int s = 0; s < 2; ++s) {
                 mbar_init(s_full(L, s), 1);
-                mbar_init(s_empty(L, s), 4);
                 mbar_init(p_ready(L, s), 4);
                 mbar_init(pv_done(L, s), 1);
             }
@@ -434,6 +432,13 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         if (k + 1 == n) v = 0x3F800000u;
         const int chunk = (k >> 3) ^ ((n >> 1) & 3);
         *reinterpret_cast<uint32_t*>(gbase + CoreSmem::kIdent + n * 64 + chunk * 16 + (w & 3) * 4) = v;
+    }
+    // rows 32..47 of every V slot: a row of ones (column 32 of O then accumulates the row sum of P on the tensor
+    // pipe, rounded exactly like the numerator) and 15 rows of zeros; the bulk copies only ever write rows 0..31
+    for (int idx = threadIdx.x; idx < kVStages * kLines * 64; idx += blockDim.x) {
+        const int slot = idx >> 6, w = idx & 63;   // 64 uint4 = 1 KB per slot
+        const uint32_t v = (w < 4) ? 0x3F803F80u : 0u;
+        *reinterpret_cast<uint4*>(gbase + CoreSmem::kV + slot * kVSlot + 2048 + w * 16) = make_uint4(v, v, v, v);
     }
     fence_proxy_async_smem();
     if (warp == 1) {
@@ -475,7 +480,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                         break;
                     }
                     mbar_arrive_expect_tx(v_full(s), kLines * 2048);
-                    bulk_load(sbase + CoreSmem::kV + s * kLines * kVSlot, v_img + tile0, kLines * 2048, v_full(s));
+                    for (int L = 0; L < kLines; ++L)
+                        bulk_load(sbase + CoreSmem::kV + (s * kLines + L) * kVSlot, v_img + tile0 + L * 1024, 2048,
+                                  v_full(s));
                 }
             }
         }
@@ -488,17 +495,17 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         const uint32_t tm = __shfl_sync(0xffffffffu, tmem_base, 0);
         const uint32_t sb = __shfl_sync(0xffffffffu, sbase, 0);
         constexpr uint32_t idesc_s = idesc_bf16_f32(128, kBK);  // S: 128 x 32, K = 32
-        constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 32, K = 32
+        constexpr uint32_t idesc_o = idesc_bf16_f32(128, kON);  // O: 128 x 48 (channels, row sum, padding), K = 32
         bool ok = mbar_wait(q_full, 0, abort_flag);
         if (!ok && lane == 0) report_wait_failure(status, abort_flag, kKidCore, 2);
         const uint64_t qdesc = smem_desc_k_sw64(sb + CoreSmem::kQ + L * 8192);
         const uint64_t identdesc = smem_desc_k_sw64(sb + CoreSmem::kIdent);
         const uint32_t t_line = tm + L * 128;
-        // S_i = Q K_i^T + Tb_i into slot i % 2 (free once the softmax threads have read S_{i-2} out of it)
+        // S_i = Q K_i^T + Tb_i into slot i % 2, free once P_{i-2} V_{i-2} (which read P out of it) is done
         auto issue_s = [&](int i) -> bool {
             const int s = i & 1;
             const int ks = i % kKbStages;
-            if (i >= 2 && !mbar_wait(s_empty(L, s), ((i - 2) >> 1) & 1u, abort_flag)) {
+            if (i >= 2 && !mbar_wait(pv_done(L, s), ((i - 2) >> 1) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 4);
                 return false;
             }
@@ -523,8 +530,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
         ok = ok && issue_s(0);
         if (ok && nblk > 1) ok = issue_s(1);
         for (int j = 0; j < nblk && ok; ++j) {
-            if (j + 2 < nblk && !issue_s(j + 2)) break;   // early in step j: the softmax threads release slot j % 2
-            // O += P_j V_j at the end of step j
+            // O += P_j V_j at the end of step j, then S_{j+2} into the slot P_j was read from
             const int vs = j % kVStages;
             if (!mbar_wait(v_full(vs), (j / kVStages) & 1u, abort_flag)) {
                 if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 12);
@@ -537,13 +543,14 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             tc_fence_after_sync();
             const uint64_t vdesc = smem_desc_k_sw64(sb + CoreSmem::kV + (vs * kLines + L) * kVSlot);
             if (lane == 0) {
-                const uint32_t a_p = t_line + kColP + (j & 1) * 16;
+                const uint32_t a_p = t_line + (j & 1) * kBK;
                 mma_bf16_ts(t_line + kColO, a_p, vdesc, idesc_o, j != 0 ? 1u : 0u);
                 mma_bf16_ts(t_line + kColO, a_p + 8u, vdesc + 2u, idesc_o, 1u);
                 mma_commit(pv_done(L, j & 1));
                 mma_commit(v_empty(vs));
             }
             __syncwarp();
+            if (j + 2 < nblk && !issue_s(j + 2)) break;
         }
     } else {
         // ---------------------------------------------------------------- softmax warpgroups
@@ -595,7 +602,7 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             const unsigned hi = __ballot_sync(0xffffffffu, lane + 32 < nblk && mbflag[L * 128 + 32 + lane]);
             mflags = ((unsigned long long)hi << 32) | lo;
         }
-        float m_used = 0.f, l = 0.f;
+        float m_used = 0.f;
         bool ok = true;
         for (int j = 0; j < nblk && ok; ++j) {
             const int s = j & 1;
@@ -608,13 +615,10 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
             uint32_t sr[32];
             tmem_ld32(trow + s * kBK, sr);
             tmem_ld_wait();
-            // S_j is in registers: its slot can take S_{j+2}, the K / bias stage its GEMM read can be refilled
+            // S_j is in registers: the K / bias stage its GEMM read can be refilled
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(s_empty(L, s));
-                mbar_arrive(kb_empty(j % kKbStages));
-            }
+            if (lane == 0) mbar_arrive(kb_empty(j % kKbStages));
             float sv[kBK];
 #pragma unroll
             for (int e = 0; e < 32; ++e) sv[e] = __uint_as_float(sr[e]);
@@ -659,32 +663,24 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                 tc_fence_after_sync();
                 uint32_t orow[32];
                 tmem_ld32(trow + kColO, orow);
+                const uint32_t lsum = tmem_ld1(trow + kColO + 32);   // the row sum rides in column 32 of O
                 tmem_ld_wait();
 #pragma unroll
                 for (int e = 0; e < 32; ++e) orow[e] = __float_as_uint(__uint_as_float(orow[e]) * f);
                 tmem_st32(trow + kColO, orow);
+                tmem_st1(trow + kColO + 32, __float_as_uint(__uint_as_float(lsum) * f));
                 tmem_st_wait();
-                l *= f;
             }
             uint32_t pk[16];
             const float nm = -m_used;
-            float sum[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < 32; e += 2) {
                 add2(sv[e], sv[e + 1], nm, nm);
-                const float p0 = ex2_approx(sv[e]), p1 = ex2_approx(sv[e + 1]);
-                add2(sum[(e >> 1) & 1 ? 2 : 0], sum[(e >> 1) & 1 ? 3 : 1], p0, p1);
-                pk[e >> 1] = pack_bf16x2(p0, p1);
+                pk[e >> 1] = pack_bf16x2(ex2_approx(sv[e]), ex2_approx(sv[e + 1]));
             }
-            l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
-            // this step's P buffer was last read by P_{j-2} V_{j-2}
-            if (j >= 2 && !mbar_wait(pv_done(L, s), ((j - 2) >> 1) & 1u, abort_flag)) {
-                if (lane == 0) report_wait_failure(status, abort_flag, kKidCore, 9);
-                ok = false;
-                break;
-            }
-            tc_fence_after_sync();
-            tmem_st16(trow + kColP + s * 16, pk);
+            // P_j goes where S_j was (every thread of the warp has its S row in registers: the load above is
+            // warp-wide); the row sum is taken by the tensor pipe from the rounded P (the ones row of the V tile)
+            tmem_st16(trow + s * kBK, pk);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
@@ -695,8 +691,9 @@ triattn_core_kernel(const __nv_bfloat16* __restrict__ q_img, const __nv_bfloat16
                 tc_fence_after_sync();
                 uint32_t r[32];
                 tmem_ld32(trow + kColO, r);
+                const uint32_t lsum = tmem_ld1(trow + kColO + 32);
                 tmem_ld_wait();
-                const float inv = 1.0f / l;
+                const float inv = 1.0f / __uint_as_float(lsum);
                 if (qpos < N && line_valid) {
                     uint4* dst = reinterpret_cast<uint4*>(o_out + ((bl * N + qpos) * (long long)kC) + h * kD);
 #pragma unroll
