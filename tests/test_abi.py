@@ -80,3 +80,27 @@ def test_state_dict_keys_match_reference_layout(pkg):
                                 fuse_projection_weights=False, inf=1e9)
     zeros = [k for k, v in fresh.state_dict().items() if v.dim() == 2 and v.abs().sum() == 0]
     assert len(zeros) == 16
+
+
+def test_modules_pack_grouped_weights_back_to_back(pkg):
+    """Linear layers that share an input run as one launch when their weights lie back to back in memory (the
+    library compares addresses): the modules' parameter packer must lay q | g | k | v, the AdaLN pair and the
+    SwiGLU pair out that way, with unchanged values."""
+    dt, dev = torch.bfloat16, torch.device("cpu")
+    apb = pkg.AttentionPairBias(c_q=768, c_k=768, c_v=768, c_s=384, c_z=128, c_hidden=48, no_heads=16,
+                                use_ada_layer_norm=True, inf=1e9)
+    prm = apb._params(dt, dev)
+    step = 768 * 768 * 2
+    q, g, k, v = prm[11], prm[15], prm[13], prm[14]
+    assert [t.data_ptr() - q.data_ptr() for t in (g, k, v)] == [step, 2 * step, 3 * step]
+    assert torch.equal(q, apb.mha.linear_q.weight.to(dt)) and torch.equal(v, apb.mha.linear_v.weight.to(dt))
+    assert torch.equal(g, apb.mha.linear_g.weight.to(dt)) and torch.equal(k, apb.mha.linear_k.weight.to(dt))
+    assert prm[5].data_ptr() - prm[3].data_ptr() == 768 * 384 * 2          # AdaLN linear_g, linear_s
+    ctb = pkg.ConditionedTransitionBlock(c_a=768, c_s=384, n=2)
+    prm = ctb._params(dt, dev)
+    assert prm[3].data_ptr() - prm[1].data_ptr() == 768 * 384 * 2          # AdaLN pair
+    assert prm[5].data_ptr() - prm[4].data_ptr() == 2 * 768 * 768 * 2      # SwiGLU linear_a, linear_b
+    tr = pkg.SwiGLUTransition(c_in=384, n=4)
+    prm = tr._params(dt, dev)
+    assert prm[3].data_ptr() - prm[2].data_ptr() == 4 * 384 * 384 * 2
+    assert torch.equal(prm[3], tr.swiglu.linear_b.weight.to(dt))
