@@ -271,8 +271,14 @@ class NcclExchange:
         P, C, R, ld = xb.shape
         return exchange_blocks(xb, self.world, self.group).view(P * C, R, ld)
 
-    def transpose(self, z_loc, dst_name):
-        return all_to_all_transpose(z_loc, self.world, self.group, self.ops)
+    def transpose(self, z_loc, dst_name, rider=None):
+        """``rider``: (rows of s, event after their producer) to gather in the same breath (see PeerExchange)."""
+        out = all_to_all_transpose(z_loc, self.world, self.group, self.ops)
+        self.rider_result = None
+        if rider is not None:
+            getattr(self.ops, "wait_mark", lambda ev: None)(rider[1])
+            self.rider_result = self.gather_rows(rider[0])
+        return out
 
     def gather_lines(self, x_loc):
         return all_gather_lines(x_loc, self.world, self.group)
@@ -426,14 +432,22 @@ class PeerExchange:
         self._pull(self.heap.offset_of(xb) + self.rank * blk, out, 1, 1, 0, 0, blk, 0, 0, blk)
         return out
 
-    def transpose(self, z_loc, dst_name):
+    def transpose(self, z_loc, dst_name, rider=None):
+        """``rider``: (rows of s written by an earlier kernel of another stream, event after it). The main stream
+        waits for the event BEFORE this exchange's barrier, so once the barrier has been passed every rank's rows
+        are complete and they are pulled without a barrier of their own (one barrier less per block)."""
         R, N, C = z_loc.shape
         e = z_loc.element_size()
         out = self.heap.tensor(dst_name, (R, N, C), z_loc.dtype)
+        if rider is not None:
+            getattr(self.ops, "wait_mark", lambda ev: None)(rider[1])
         self.barrier()
         # out[i_loc][src*R + k_loc][:] = z_src[k_loc][rank*R + i_loc][:]; rows (src, k_loc, i_loc) of C elements
         self._pull(self.heap.offset_of(z_loc) + self.rank * R * C * e, out, R, R, N * C * e, C * e, R * C * e, C * e,
                    N * C * e, C * e)
+        self.rider_result = None
+        if rider is not None:
+            self.rider_result = self.gather_rows(rider[0], barrier=False)
         return out
 
     def gather_lines(self, x_loc):
@@ -445,11 +459,12 @@ class PeerExchange:
                    L * e)
         return out
 
-    def gather_rows(self, s_rows):
+    def gather_rows(self, s_rows, barrier=True):
         R, c = s_rows.shape
         e = s_rows.element_size()
         out = torch.empty((self.world * R, c), dtype=s_rows.dtype, device=s_rows.device)
-        self.barrier()
+        if barrier:
+            self.barrier()
         self._pull(self.heap.offset_of(s_rows), out, 1, 1, 0, 0, R * c * e, 0, 0, R * c * e)
         return out
 
@@ -506,9 +521,10 @@ class DapPairFormerStack:
                                           row0=self.rank * R)
         ops.triattn_finish(z_loc, mask_rows, qkv, X.gather_lines(tb_loc), mod)
 
-    def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True):
+    def pair_block(self, z_loc, mask_rows, maskT_rows, pb, mask_trans=True, rider=None):
         """One PairBlock on the local row shard; returns the updated shard (the result of the transpose
-        back: with collectives a new tensor, z_loc itself then holds an intermediate state)."""
+        back: with collectives a new tensor, z_loc itself then holds an intermediate state). ``rider``: the previous
+        block's rows of s, gathered together with the last exchange (result in ``self.x.rider_result``)."""
         self._trimul(z_loc, mask_rows, pb.tri_mul_out, incoming=False)
         self._trimul(z_loc, mask_rows, pb.tri_mul_in, incoming=True)
         self._triattn(z_loc, mask_rows, pb.tri_att_start)
@@ -516,7 +532,9 @@ class DapPairFormerStack:
         zT = self.x.transpose(z_loc, "z1")
         self._triattn(zT, maskT_rows, pb.tri_att_end)
         self.ops.transition(zT, maskT_rows if mask_trans else None, pb.pair_transition)
-        return self.x.transpose(zT, "z0")
+        if rider is None:
+            return self.x.transpose(zT, "z0")
+        return self.x.transpose(zT, "z0", rider=rider)
 
     def __call__(self, s, z, single_mask, pair_mask, _mask_trans=True, sharded: bool = False):
         """Replicated interface (default): z [1, N, N, C] and pair_mask [1, N, N] whole on every rank; returns the
@@ -553,15 +571,15 @@ class DapPairFormerStack:
         for i, block in enumerate(self.stack.blocks):
             # a PairFormerBlock (pair stack + single track) or a bare PairBlock (pair stack only: s is None)
             pair_stack = getattr(block, "pair_stack", block)
-            z_loc = self.pair_block(z_loc, mask_rows, maskT_rows, pair_stack, _mask_trans)
+            # the previous block's rows of s (long finished on the side stream) ride on this block's last exchange
+            z_loc = self.pair_block(z_loc, mask_rows, maskT_rows, pair_stack, _mask_trans, rider=pending)
+            if pending is not None:
+                s_full, pending = X.rider_result, None
             if s_full is None or not hasattr(block, "attn_pair_bias"):
                 continue
             slot = i & 1
             wait(zb_free[slot])  # the side stream has finished with this buffer (two blocks ago)
             zb_buf[slot] = ops.pair_bias_project(z_loc, block.attn_pair_bias, out=zb_buf[slot])   # [H, R, N]
-            if pending is not None:  # the previous block's rows: long finished; gathered on the main stream
-                wait(pending[1])
-                s_full = X.gather_rows(pending[0])
             with side():
                 s_rows = ops.single_rows(s_full, zb_buf[slot], sm, block, self.rank * R, R, _mask_trans,
                                          out=X.buf(f"s{slot}", (R, s.shape[-1]), s.dtype, s.device))
