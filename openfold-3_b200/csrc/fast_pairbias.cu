@@ -34,7 +34,8 @@ struct PbSmem {
 __global__ void __launch_bounds__(kPbThreads, 1)
 pair_bias_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmW,
                     const __nv_bfloat16* __restrict__ ln_w, const __nv_bfloat16* __restrict__ ln_b,
-                    float* __restrict__ dst, long long rows, long long nn, int* status) {
+                    float* __restrict__ dst, __nv_bfloat16* __restrict__ tiles, int n_tok, long long rows, long long nn,
+                    int* status) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t sbase = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gbase = smem_raw + (sbase - smem_u32(smem_raw));
@@ -165,9 +166,22 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
             const long long pos = t * kRows + row;
             if (pos < rows) {
                 const long long b = pos / nn, qk = pos - b * nn;
-                float* d = dst + (b * kHeads) * nn + qk;
+                if (tiles != nullptr) {
+                    // the attention kernel's bias image: bf16, times log2(e), [b*16 + h][key block of 32][query row][32
+                    // keys], each 64-byte row in the 64-byte swizzle of a K-major A operand
+                    const int i = (int)(qk / n_tok), j = (int)(qk - (long long)i * n_tok);
+                    const long long nkb = (n_tok + 31) >> 5;
+                    const long long hs = nkb * n_tok * 32;   // elements per (sample, head)
+                    __nv_bfloat16* d = tiles + (b * kHeads) * hs + ((long long)(j >> 5) * n_tok + i) * 32 +
+                                       (((((j & 31) >> 3) ^ ((i >> 1) & 3)) << 3) | (j & 7));
 #pragma unroll
-                for (int h = 0; h < kHeads; ++h) d[h * nn] = __uint_as_float(r[h]);
+                    for (int h = 0; h < kHeads; ++h)
+                        d[h * hs] = __float2bfloat16_rn(__uint_as_float(r[h]) * 1.4426950408889634f);
+                } else {
+                    float* d = dst + (b * kHeads) * nn + qk;
+#pragma unroll
+                    for (int h = 0; h < kHeads; ++h) d[h * nn] = __uint_as_float(r[h]);
+                }
             }
         }
     }
@@ -182,9 +196,33 @@ pair_bias_tc_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 
 }  // namespace
 
+namespace {
+int pair_bias_launch(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
+                     const __nv_bfloat16* w, float* dst, __nv_bfloat16* tiles, int n_tok, long long B, long long nn,
+                     cudaStream_t st);
+}
+
 // dst[b][h][pos] (fp32) for B samples of nn pair positions each; z [B * nn][128] bf16.
 int pair_bias_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
                        const __nv_bfloat16* w, float* dst, long long B, long long nn, cudaStream_t st) {
+    return pair_bias_launch(z, ln_w, ln_b, w, dst, nullptr, 0, B, nn, st);
+}
+
+// The same projection written straight into the bias image of the single-track attention kernel (bf16 tiles
+// [b*16 + h][key block of 32][N query rows][32], times log2(e)): no fp32 tensor in between. z [B][N][N][128].
+int pair_bias_tiles_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
+                             const __nv_bfloat16* w, __nv_bfloat16* tiles, long long B, int N, cudaStream_t st) {
+    if (N % 32 != 0) {   // the key padding of the last block must read as zeros
+        const size_t bytes = (size_t)B * kHeads * ((N + 31) / 32) * N * 32 * sizeof(__nv_bfloat16);
+        OF3_CUDA_CHECK(cudaMemsetAsync(tiles, 0, bytes, st));
+    }
+    return pair_bias_launch(z, ln_w, ln_b, w, nullptr, tiles, N, B, (long long)N * N, st);
+}
+
+namespace {
+int pair_bias_launch(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
+                     const __nv_bfloat16* w, float* dst, __nv_bfloat16* tiles, int n_tok, long long B, long long nn,
+                     cudaStream_t st) {
     const long long rows = B * nn;
     if (rows <= 0) return OF3_OK;
     OF3_REQUIRE(((uintptr_t)z & 15) == 0 && ((uintptr_t)w & 15) == 0, OF3_ERR_ALIGN,
@@ -209,14 +247,15 @@ int pair_bias_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const 
                                             PbSmem::kDyn));
         device_mark_configured(3);
     }
-    const long long tiles = (rows + kRows - 1) / kRows;
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const long long num_tiles = (rows + kRows - 1) / kRows;
+    const int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
     LaunchScope scope(kKidPairBias, st);
-    pair_bias_tc_kernel<<<grid, kPbThreads, PbSmem::kDyn, st>>>(tmZ, tmW, ln_w, ln_b, dst, rows, nn,
+    pair_bias_tc_kernel<<<grid, kPbThreads, PbSmem::kDyn, st>>>(tmZ, tmW, ln_w, ln_b, dst, tiles, n_tok, rows, nn,
                                                                 device_status_ptr());
     OF3_CUDA_CHECK(cudaGetLastError());
     return OF3_OK;
 }
+}  // namespace
 
 }  // namespace fast
 }  // namespace of3

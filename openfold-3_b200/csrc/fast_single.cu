@@ -197,12 +197,7 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
                               Ba / Bz, ws, st);
     OF3_REQUIRE(ws.ok(), OF3_ERR_WORKSPACE, "attn_pair_bias: workspace too small (%zu needed)", ws.off);
     int rc;
-    if (pair_bias == nullptr) {
-        if ((rc = fast::pair_bias_c128_h16(z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b, (const bf16*)p->w_z, zb,
-                                           Bz, (long long)N * N, st)))
-            return rc;
-        pair_bias = zb;
-    }
+    (void)zb;   // pair_bias == nullptr: the attention projects its bias tiles straight from z (no fp32 bias tensor)
     if (ada) {
         if ((rc = ada_ln_bf16(a, s, an, t_sn, t_g, t_s, rows, c_a, c_s, (const bf16*)p->ada_ln_s_w,
                               (const bf16*)p->ada_w_g, (const bf16*)p->ada_b_g, (const bf16*)p->ada_w_s, st)))
@@ -217,7 +212,8 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
         const bf16* w4[4] = {(const bf16*)p->w_q, (const bf16*)p->w_g, (const bf16*)p->w_k, (const bf16*)p->w_v};
         if ((rc = linear_group_bf16(an, w4, q, 4, rows, c_a, c_a, st))) return rc;
     }
-    if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, d, inf, Ba / Bz, ws, st)))
+    if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, d, inf, Ba / Bz, ws, st,
+                             z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b, (const bf16*)p->w_z)))
         return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
     if (ada) {  // output gate from the raw conditioning: sigmoid(linear_ada_out(s)) * y

@@ -543,7 +543,7 @@ struct Images {
 template <int D>
 int attn_tc_impl(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias, const float* pb,
                  const bf16* mask, bf16* out, int BB, int N, int nq, int H, float inf, int rpb, Arena& ws,
-                 cudaStream_t st) {
+                 cudaStream_t st, const bf16* z, const bf16* ln_z_w, const bf16* ln_z_b, const bf16* w_z) {
     const int Bz = BB / rpb;
     const Images<D> im(BB, Bz, N, nq, H);
     bf16* q_img = (bf16*)ws.take(im.q);
@@ -568,9 +568,14 @@ int attn_tc_impl(const bf16* q, const bf16* k, const bf16* v, const bf16* g, con
         LaunchScope scope(kKidSingleAttn, st);
         single_pack_v_kernel<D><<<dim3(nkb, BB), 256, smem, st>>>(v, v_img, N, H);
     }
-    {
+    if (pb != nullptr) {
         LaunchScope scope(kKidSingleAttn, st);
         single_bias_kernel<<<dim3(nq, Bz * H), 256, 0, st>>>(pb, tb_img, N, nq, nkb);
+    } else {   // straight from the pair tensor: no fp32 bias in between
+        OF3_REQUIRE(z != nullptr && w_z != nullptr && nq == N && H == 16, OF3_ERR_ARG,
+                    "single attention: neither a pair bias nor a whole pair tensor to project it from");
+        const int rc = pair_bias_tiles_c128_h16(z, ln_z_w, ln_z_b, w_z, tb_img, Bz, N, st);
+        if (rc) return rc;
     }
     OF3_CUDA_CHECK(cudaGetLastError());
     const uint32_t smem = Cfg<D>::dyn_bytes(nkb * kBK);
@@ -600,13 +605,16 @@ bool single_attn_tc_supported(int N, int H, int d) {
 // With ws.base == nullptr only the workspace need is accumulated.
 int single_attn_tc(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias,
                    const float* pair_bias, const bf16* mask, bf16* out, int BB, int N, int nq, int H, int d, float inf,
-                   int rows_per_bias, Arena& ws, cudaStream_t st) {
+                   int rows_per_bias, Arena& ws, cudaStream_t st, const bf16* z, const bf16* ln_z_w, const bf16* ln_z_b,
+                   const bf16* w_z) {
     OF3_REQUIRE(single_attn_tc_supported(N, H, d), OF3_ERR_SHAPE, "single attention: N %d, H %d, d %d not supported",
                 N, H, d);
     OF3_REQUIRE(rows_per_bias > 0 && BB % rows_per_bias == 0, OF3_ERR_SHAPE,
                 "single attention: %d samples do not divide into groups of %d", BB, rows_per_bias);
-    return d == 24 ? attn_tc_impl<24>(q, k, v, g, q_bias, pair_bias, mask, out, BB, N, nq, H, inf, rows_per_bias, ws, st)
-                   : attn_tc_impl<48>(q, k, v, g, q_bias, pair_bias, mask, out, BB, N, nq, H, inf, rows_per_bias, ws, st);
+    return d == 24 ? attn_tc_impl<24>(q, k, v, g, q_bias, pair_bias, mask, out, BB, N, nq, H, inf, rows_per_bias, ws, st,
+                                      z, ln_z_w, ln_z_b, w_z)
+                   : attn_tc_impl<48>(q, k, v, g, q_bias, pair_bias, mask, out, BB, N, nq, H, inf, rows_per_bias, ws, st,
+                                      z, ln_z_w, ln_z_b, w_z);
 }
 
 }  // namespace fast

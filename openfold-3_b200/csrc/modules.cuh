@@ -61,9 +61,13 @@ int transition(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16*
 // gated attention with pair bias on the tensor pipe: q, g, out [BB, nq, H*d]; k, v [BB, N, H*d]; pair_bias fp32
 // [BB / rows_per_bias, H, nq, N]; with ws.base == nullptr only the workspace need is accumulated
 bool single_attn_tc_supported(int N, int H, int d);
+// pair_bias == nullptr: the bias tiles are projected straight from z (whole pair tensors only: nq == N) with the
+// LayerNorm weight / bias ln_z_w / ln_z_b and linear_z.weight w_z
 int single_attn_tc(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bfloat16* v, const __nv_bfloat16* g,
                    const __nv_bfloat16* q_bias, const float* pair_bias, const __nv_bfloat16* mask, __nv_bfloat16* out,
-                   int BB, int N, int nq, int H, int d, float inf, int rows_per_bias, Arena& ws, cudaStream_t st);
+                   int BB, int N, int nq, int H, int d, float inf, int rows_per_bias, Arena& ws, cudaStream_t st,
+                   const __nv_bfloat16* z = nullptr, const __nv_bfloat16* ln_z_w = nullptr,
+                   const __nv_bfloat16* ln_z_b = nullptr, const __nv_bfloat16* w_z = nullptr);
 // single-track layers (bf16): linears on the tcgen05 contraction kernel, attention on single_attn_tc
 // (LayerNorm variant of the trunk, or with OF3_FLAG_ADA_LN the conditioned variant of the diffusion stack)
 bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H, int d, int flags);
@@ -80,6 +84,9 @@ int attn_pair_bias_rows(const __nv_bfloat16* a, const float* pair_bias_rows, con
 // pair-bias projection of the single track on the tensor pipe: dst [B][16][nn] fp32 from z [B*nn][128] bf16
 int pair_bias_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
                        const __nv_bfloat16* w, float* dst, long long B, long long nn, cudaStream_t st);
+// the same projection written as the single-track attention kernel's bf16 bias tiles (z [B][N][N][128])
+int pair_bias_tiles_c128_h16(const __nv_bfloat16* z, const __nv_bfloat16* ln_w, const __nv_bfloat16* ln_b,
+                             const __nv_bfloat16* w, __nv_bfloat16* tiles, long long B, int N, cudaStream_t st);
 bool transition_wide_supported(int c, int n);
 int transition_wide(const __nv_bfloat16* x, const __nv_bfloat16* mask, __nv_bfloat16* out, long long rows, int c,
                     int n, int flags, const of3_transition_params* p, Arena& ws, cudaStream_t st);
