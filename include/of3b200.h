@@ -273,6 +273,18 @@ int of3_attn_pair_bias_forward_prebias(const void* a, const float* pair_bias, co
                                        void* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf,
                                        int dtype, int flags, const of3_attn_pair_bias_params* p, void* workspace,
                                        size_t workspace_bytes, void* stream);
+/* The same two steps without the fp32 tensor in between (bf16 only): the projection of ONE sample's pair
+ * tensor z [N, N, 128] written as the attention kernel's own bias tiles -- bf16, times log2(e),
+ * [16 heads][ceil(N / 32) key blocks][N query rows][32 keys], of3_pair_bias_tiles_elems(N) elements; samples
+ * of a batch lie back to back -- and the layer taking tiles [Bz][...]. A caller that applies the layer many
+ * times to one pair tensor (a diffusion rollout) keeps the tiles. */
+long long of3_pair_bias_tiles_elems(int N);
+int of3_pair_bias_project_tiles(const void* z, const void* ln_w, const void* ln_b, const void* w, void* tiles, int N,
+                                int c_z, int H, int dtype, void* stream);
+int of3_attn_pair_bias_forward_pretiles(const void* a, const void* bias_tiles, const void* s, const void* mask,
+                                        void* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf,
+                                        int dtype, int flags, const of3_attn_pair_bias_params* p, void* workspace,
+                                        size_t workspace_bytes, void* stream);
 
 /* The AttentionPairBias layer (attention_pair_bias.py:123-227, LayerNorm variant) for a window of R
  * query rows [row0, row0 + R) of one sample: keys / values from all N rows of a [N, c_a], the pair bias

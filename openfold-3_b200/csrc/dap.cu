@@ -197,4 +197,29 @@ int of3_attn_pair_bias_forward_prebias(const void* a, const float* pair_bias, co
                                           Bz, N, c_a, c_s, 128, H, d, inf, flags, p, ws, (cudaStream_t)stream, pair_bias);
 }
 
+long long of3_pair_bias_tiles_elems(int N) { return 16LL * ((N + 31) / 32) * N * 32; }
+
+int of3_pair_bias_project_tiles(const void* z, const void* ln_w, const void* ln_b, const void* w, void* tiles, int N,
+                                int c_z, int H, int dtype, void* stream) {
+    OF3_REQUIRE(z && w && tiles, OF3_ERR_ARG, "pair_bias_project_tiles: null pointer argument");
+    OF3_REQUIRE(c_z == 128 && H == 16 && dtype == OF3_DTYPE_BF16 && N > 0, OF3_ERR_SHAPE,
+                "pair_bias_project_tiles: only bf16, c_z = 128, 16 heads");
+    return fast::pair_bias_tiles_c128_h16((const __nv_bfloat16*)z, (const __nv_bfloat16*)ln_w, (const __nv_bfloat16*)ln_b,
+                                          (const __nv_bfloat16*)w, (__nv_bfloat16*)tiles, 1, N, (cudaStream_t)stream);
+}
+
+int of3_attn_pair_bias_forward_pretiles(const void* a, const void* bias_tiles, const void* s, const void* mask,
+                                        void* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf,
+                                        int dtype, int flags, const of3_attn_pair_bias_params* p, void* workspace,
+                                        size_t workspace_bytes, void* stream) {
+    OF3_REQUIRE(a && bias_tiles && out && p && workspace, OF3_ERR_ARG, "attn_pair_bias_pretiles: null pointer argument");
+    OF3_REQUIRE(Ba > 0 && Bz > 0 && Ba % Bz == 0 && N > 0, OF3_ERR_ARG, "attn_pair_bias_pretiles: bad sizes");
+    OF3_REQUIRE(dtype == OF3_DTYPE_BF16 && fast::attn_pair_bias_supported(Ba, Bz, N, c_a, c_s, 128, H, d, flags),
+                OF3_ERR_SHAPE, "attn_pair_bias_pretiles: bias tiles only feed the bf16 tensor-core attention");
+    Arena ws(workspace, workspace_bytes);
+    return fast::attn_pair_bias((const __nv_bfloat16*)a, nullptr, (const __nv_bfloat16*)s, (const __nv_bfloat16*)mask,
+                                (__nv_bfloat16*)out, Ba, Bz, N, c_a, c_s, H, d, inf, flags, p, ws, (cudaStream_t)stream,
+                                nullptr, (const __nv_bfloat16*)bias_tiles);
+}
+
 }  // extern "C"

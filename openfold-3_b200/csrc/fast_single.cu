@@ -178,7 +178,7 @@ bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, 
 
 int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask, bf16* out, int Ba, int Bz, int N,
                    int c_a, int c_s, int H, int d, float inf, int flags, const of3_attn_pair_bias_params* p, Arena& ws,
-                   cudaStream_t st, const float* pair_bias) {
+                   cudaStream_t st, const float* pair_bias, const bf16* bias_tiles) {
     const long long rows = (long long)Ba * N;
     const bool ada = (flags & OF3_FLAG_ADA_LN) != 0;
     bf16* t_sn = ada ? (bf16*)ws.take(rows * c_s * sizeof(bf16)) : nullptr;
@@ -213,7 +213,7 @@ int attn_pair_bias(const bf16* a, const bf16* z, const bf16* s, const bf16* mask
         if ((rc = linear_group_bf16(an, w4, q, 4, rows, c_a, c_a, st))) return rc;
     }
     if ((rc = single_attn_tc(q, k, v, g, (const bf16*)p->b_q, pair_bias, mask, og, Ba, N, N, H, d, inf, Ba / Bz, ws, st,
-                             z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b, (const bf16*)p->w_z)))
+                             z, (const bf16*)p->ln_z_w, (const bf16*)p->ln_z_b, (const bf16*)p->w_z, bias_tiles)))
         return rc;
     if ((rc = linear_bf16(og, (const bf16*)p->w_o, y, rows, c_a, c_a, st))) return rc;
     if (ada) {  // output gate from the raw conditioning: sigmoid(linear_ada_out(s)) * y

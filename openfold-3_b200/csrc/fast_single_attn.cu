@@ -543,7 +543,8 @@ struct Images {
 template <int D>
 int attn_tc_impl(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias, const float* pb,
                  const bf16* mask, bf16* out, int BB, int N, int nq, int H, float inf, int rpb, Arena& ws,
-                 cudaStream_t st, const bf16* z, const bf16* ln_z_w, const bf16* ln_z_b, const bf16* w_z) {
+                 cudaStream_t st, const bf16* z, const bf16* ln_z_w, const bf16* ln_z_b, const bf16* w_z,
+                 const bf16* bias_tiles) {
     const int Bz = BB / rpb;
     const Images<D> im(BB, Bz, N, nq, H);
     bf16* q_img = (bf16*)ws.take(im.q);
@@ -568,7 +569,9 @@ int attn_tc_impl(const bf16* q, const bf16* k, const bf16* v, const bf16* g, con
         LaunchScope scope(kKidSingleAttn, st);
         single_pack_v_kernel<D><<<dim3(nkb, BB), 256, smem, st>>>(v, v_img, N, H);
     }
-    if (pb != nullptr) {
+    if (bias_tiles != nullptr) {
+        tb_img = const_cast<bf16*>(bias_tiles);   // projected earlier, in this kernel's layout
+    } else if (pb != nullptr) {
         LaunchScope scope(kKidSingleAttn, st);
         single_bias_kernel<<<dim3(nq, Bz * H), 256, 0, st>>>(pb, tb_img, N, nq, nkb);
     } else {   // straight from the pair tensor: no fp32 bias in between
@@ -606,15 +609,15 @@ bool single_attn_tc_supported(int N, int H, int d) {
 int single_attn_tc(const bf16* q, const bf16* k, const bf16* v, const bf16* g, const bf16* q_bias,
                    const float* pair_bias, const bf16* mask, bf16* out, int BB, int N, int nq, int H, int d, float inf,
                    int rows_per_bias, Arena& ws, cudaStream_t st, const bf16* z, const bf16* ln_z_w, const bf16* ln_z_b,
-                   const bf16* w_z) {
+                   const bf16* w_z, const bf16* bias_tiles) {
     OF3_REQUIRE(single_attn_tc_supported(N, H, d), OF3_ERR_SHAPE, "single attention: N %d, H %d, d %d not supported",
                 N, H, d);
     OF3_REQUIRE(rows_per_bias > 0 && BB % rows_per_bias == 0, OF3_ERR_SHAPE,
                 "single attention: %d samples do not divide into groups of %d", BB, rows_per_bias);
     return d == 24 ? attn_tc_impl<24>(q, k, v, g, q_bias, pair_bias, mask, out, BB, N, nq, H, inf, rows_per_bias, ws, st,
-                                      z, ln_z_w, ln_z_b, w_z)
+                                      z, ln_z_w, ln_z_b, w_z, bias_tiles)
                    : attn_tc_impl<48>(q, k, v, g, q_bias, pair_bias, mask, out, BB, N, nq, H, inf, rows_per_bias, ws, st,
-                                      z, ln_z_w, ln_z_b, w_z);
+                                      z, ln_z_w, ln_z_b, w_z, bias_tiles);
 }
 
 }  // namespace fast

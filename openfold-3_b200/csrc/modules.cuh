@@ -67,13 +67,15 @@ int single_attn_tc(const __nv_bfloat16* q, const __nv_bfloat16* k, const __nv_bf
                    const __nv_bfloat16* q_bias, const float* pair_bias, const __nv_bfloat16* mask, __nv_bfloat16* out,
                    int BB, int N, int nq, int H, int d, float inf, int rows_per_bias, Arena& ws, cudaStream_t st,
                    const __nv_bfloat16* z = nullptr, const __nv_bfloat16* ln_z_w = nullptr,
-                   const __nv_bfloat16* ln_z_b = nullptr, const __nv_bfloat16* w_z = nullptr);
+                   const __nv_bfloat16* ln_z_b = nullptr, const __nv_bfloat16* w_z = nullptr,
+                   const __nv_bfloat16* bias_tiles = nullptr);   // bias_tiles: from pair_bias_tiles_c128_h16
 // single-track layers (bf16): linears on the tcgen05 contraction kernel, attention on single_attn_tc
 // (LayerNorm variant of the trunk, or with OF3_FLAG_ADA_LN the conditioned variant of the diffusion stack)
 bool attn_pair_bias_supported(int Ba, int Bz, int N, int c_a, int c_s, int c_z, int H, int d, int flags);
 int attn_pair_bias(const __nv_bfloat16* a, const __nv_bfloat16* z, const __nv_bfloat16* s, const __nv_bfloat16* mask,
                    __nv_bfloat16* out, int Ba, int Bz, int N, int c_a, int c_s, int H, int d, float inf, int flags,
-                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st, const float* pair_bias);
+                   const of3_attn_pair_bias_params* p, Arena& ws, cudaStream_t st, const float* pair_bias,
+                   const __nv_bfloat16* bias_tiles = nullptr);
 bool cond_transition_supported(int c_a, int c_s, int n, int flags);
 int cond_transition(const __nv_bfloat16* a, const __nv_bfloat16* s, const __nv_bfloat16* mask, __nv_bfloat16* out,
                     long long rows, int c_a, int c_s, int n, int flags, const of3_cond_transition_params* p, Arena& ws,

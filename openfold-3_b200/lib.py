@@ -86,6 +86,11 @@ SIGNATURES = {
     "of3_attn_pair_bias_forward_prebias": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_float, c_int, c_int,
                                                    ctypes.POINTER(AttnPairBiasParams), c_void_p, c_size_t,
                                                    c_void_p]),
+    "of3_pair_bias_tiles_elems": (c_longlong, [c_int]),
+    "of3_pair_bias_project_tiles": (c_int, [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_void_p]),
+    "of3_attn_pair_bias_forward_pretiles": (c_int, [c_void_p] * 5 + [c_int] * 7 + [c_float, c_int, c_int,
+                                                    ctypes.POINTER(AttnPairBiasParams), c_void_p, c_size_t,
+                                                    c_void_p]),
     "of3_peer_heap_alloc": (c_int, [c_size_t, ctypes.POINTER(c_void_p), c_void_p]),
     "of3_peer_heap_open": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "of3_peer_heap_close": (c_int, [c_void_p]),
@@ -302,6 +307,42 @@ def attn_pair_bias_forward_prebias(a, pair_bias, s, mask, out, params, H: int, d
                                                   out.data_ptr(), Ba, Bz, N, c_a, c_s, H, d, float(inf), dt, flags,
                                                   ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream(a.device)),
            "of3_attn_pair_bias_forward_prebias")
+
+
+def pair_bias_project_tiles(z, ln_w, ln_b, w):
+    """The pair-bias projection of AttentionPairBias written as the bias tiles of the tensor-core attention kernel:
+    z [Bz, N, N, 128] bf16 -> [Bz, 16, ceil(N / 32), N, 32] bf16 (times log2(e), 64-byte swizzled rows). Opaque:
+    only ``attn_pair_bias_forward_pretiles`` reads it."""
+    _require_cuda(z, "z")
+    lib = load()
+    Bz, N = z.shape[0], z.shape[1]
+    assert z.dtype == torch.bfloat16 and w.shape[0] == 16 and z.shape[-1] == 128
+    out = torch.empty((Bz, 16, (N + 31) // 32, N, 32), dtype=torch.bfloat16, device=z.device)
+    assert out[0].numel() == lib.of3_pair_bias_tiles_elems(N)
+    for b in range(Bz):
+        _check(lib.of3_pair_bias_project_tiles(z[b].data_ptr(), _ptr(ln_w), _ptr(ln_b), w.data_ptr(), out[b].data_ptr(),
+                                               N, 128, 16, dtype_code(z.dtype), _stream(z.device)),
+               "of3_pair_bias_project_tiles")
+    return out
+
+
+def attn_pair_bias_forward_pretiles(a, tiles, s, mask, out, params, H: int, d: int, inf: float, ada: bool,
+                                    add_residual: bool):
+    """attn_pair_bias_forward with the bias tiles of ``pair_bias_project_tiles`` (bf16 tensor-core path only)."""
+    _require_cuda(a, "a")
+    lib = load()
+    Ba, N, c_a = a.shape
+    Bz = tiles.shape[0]
+    c_s = s.shape[-1] if s is not None else 0
+    dt = dtype_code(a.dtype)
+    flags = extra_flags | (FLAG_ADA_LN if ada else 0) | (FLAG_ADD_RESIDUAL if add_residual else 0)
+    nbytes = lib.of3_attn_pair_bias_workspace_bytes(Ba, Bz, N, c_a, c_s, 128, H, d, dt, flags)
+    ws = workspace(nbytes, a.device)
+    p = AttnPairBiasParams(*[_ptr(t) for t in params])
+    _check(lib.of3_attn_pair_bias_forward_pretiles(a.data_ptr(), tiles.data_ptr(), _ptr(s), _ptr(mask),
+                                                   out.data_ptr(), Ba, Bz, N, c_a, c_s, H, d, float(inf), dt, flags,
+                                                   ctypes.byref(p), ws.data_ptr(), ws.numel(), _stream(a.device)),
+           "of3_attn_pair_bias_forward_pretiles")
 
 
 def cond_transition_forward(a, s, mask, out, params, n: int, add_residual: bool):

@@ -380,13 +380,22 @@ class AttentionPairBias(nn.Module):
         return (self.c_z == 128 and self.no_heads == 16 and z.is_cuda
                 and z.dtype in (torch.bfloat16, torch.float32) and lib.extra_flags == 0)
 
+    def _takes_bias_tiles(self, z) -> bool:
+        """bf16 on the tensor-core attention: the projection can be written as that kernel's own bias tiles."""
+        return (z.dtype == torch.bfloat16 and self.c_hidden in (24, 48) and self.c_q == 16 * self.c_hidden
+                and self.c_q % 64 == 0 and (not self.use_ada_layer_norm or self.c_s % 64 == 0)
+                and z.shape[-2] <= 8192)
+
     def project_pair_bias(self, z):
-        """linear_z(LayerNorm_z(z)) permuted to [*, H, N, N] (fp32): the part of this layer that depends on z only
-        (openfold3/core/model/layers/attention_pair_bias.py:154-163), so callers that apply the layer many times to
-        one pair tensor -- the diffusion rollout -- compute it once and pass it to ``_run(pair_bias=...)``."""
+        """linear_z(LayerNorm_z(z)): the part of this layer that depends on z only (openfold3/core/model/layers/
+        attention_pair_bias.py:154-163), so callers that apply the layer many times to one pair tensor -- the
+        diffusion rollout -- compute it once and pass it to ``_run(pair_bias=...)``. An opaque tensor: fp32
+        [*, H, N, N], or for bf16 inputs the attention kernel's own bf16 bias tiles [*, 16, N / 32, N, 32]."""
         N = z.shape[-2]
         zc = z.contiguous().view(-1, N, N, self.c_z)
         prm = self._params(z.dtype, z.device)
+        if self._takes_bias_tiles(z):
+            return lib.pair_bias_project_tiles(zc, prm[8], prm[9], prm[10])
         return lib.pair_bias_project(zc, prm[8], prm[9], prm[10])
 
     def _run(self, a, z, s, mask, in_place: bool, high_precision: bool = False, pair_bias=None):
@@ -423,7 +432,12 @@ class AttentionPairBias(nn.Module):
         m = None if m is None else m.view(-1, N)
         out = ac if in_place else torch.empty_like(ac)
         assert Ba % zc.shape[0] == 0
-        if pair_bias is not None:
+        if pair_bias is not None and pair_bias.dtype == torch.bfloat16:   # bias tiles of the tensor-core attention
+            assert pair_bias.shape == (zc.shape[0], 16, (N + 31) // 32, N, 32) and a.dtype == torch.bfloat16
+            lib.attn_pair_bias_forward_pretiles(ac, pair_bias, sc, m, out, self._params(a.dtype, a.device),
+                                                self.no_heads, self.c_hidden, self.inf, self.use_ada_layer_norm,
+                                                add_residual=in_place)
+        elif pair_bias is not None:
             assert pair_bias.shape == (zc.shape[0], self.no_heads, N, N) and pair_bias.dtype == torch.float32
             lib.attn_pair_bias_forward_prebias(ac, pair_bias, sc, m, out, self._params(a.dtype, a.device),
                                                self.no_heads, self.c_hidden, self.inf, self.use_ada_layer_norm,
@@ -659,8 +673,8 @@ class DiffusionTransformer(nn.Module):
         ])
         # Pair-bias hoisting: every block's linear_z(LayerNorm_z(z)) depends on z only, and the diffusion rollout
         # calls this stack ~200 times with the same pair tensor (openfold3/core/model/structure/
-        # diffusion_module.py:362-398). The projections of all blocks are kept ([no_blocks][*, H, N, N] fp32,
-        # 0.9 GB at N = 768) for as long as the caller passes the same, unmodified z; set to False to recompute them
+        # diffusion_module.py:362-398). The projections of all blocks are kept ([no_blocks] bias tiles, bf16,
+        # 0.45 GB at N = 768; fp32 [*, H, N, N] for fp32 inputs) for as long as the caller passes the same, unmodified z; set to False to recompute them
         # in every call (what the reference does).
         self.hoist_pair_bias = True
         self._bias_cache = None   # (weakref to z, z._version, parameter versions, [bias per block])
