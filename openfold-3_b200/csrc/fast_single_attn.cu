@@ -1,13 +1,16 @@
 // Attention of the single track and of the diffusion token stack on the tensor pipe (bf16, 16 heads of 24 or 48):
-// the streaming core of the triangle attention (csrc/fast_triattn.cu) with one (sample, head, 128 queries) per CTA.
+// the streaming core of the triangle attention (csrc/fast_triattn.cu) with one (pair tensor, head, 128 queries) and
+// two samples per CTA.
 //
 //   single_pack     q / k / v rows [rows, H*d] (outputs of the linear layers) -> pre-swizzled operand tiles: q with
 //                   its bias added and scaled by log2(e)/sqrt(d), K-dim padded with zeros to 32 (d = 24) or 64
 //                   (d = 48); k likewise per key block of 32; v transposed [d rows][32 keys]; keys >= N are zeros
 //   single_bias     pair bias fp32 [zh][nq][N] -> bf16 tiles [zh][key block][nq][32], pre-scaled by log2(e), each
-//                   64-byte row in the 64-byte swizzle of a K-major A operand
+//                   64-byte row in the 64-byte swizzle of a K-major A operand (callers that project the bias
+//                   themselves get these tiles straight from csrc/fast_pairbias.cu and skip this kernel)
 //   single_core     per CTA and 32-key step: S = Q K^T + bias I^T (tcgen05, TMEM), online softmax by one thread per
-//                   query row (exp2, lazy rescaling), P (bf16) back into TMEM as the A operand of O += P V; epilogue
+//                   query row (exp2, lazy rescaling), P (bf16) back into TMEM over S as the A operand of
+//                   O += P [V; 1] (the row of ones makes the tensor pipe accumulate the row sum l); epilogue
 //                   O / l * sigmoid(gate) -> og [rows, H*d]
 // Queries may be a window of nq rows of the sample (row-sharded callers); keys and values are always all N rows.
 // Reference: openfold3/core/model/layers/attention_pair_bias.py:123-227,
