@@ -324,17 +324,18 @@ triattn_proj_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_consta
 //   MMA warp      S_j = Q K_j^T + Tb_j I^T into one of two TMEM slots: 128 x 32 logits, K = 32, and the pair-bias
 //                 tile [128 q x 32 k] (bf16, shared by both lines) as a second A operand against a 32 x 32
 //                 identity, so the tensor pipe adds the bias (a bf16 value times 1.0 accumulated in fp32 is exact)
-//                 and the softmax threads never touch it. S_{j+2} is issued as soon as the softmax threads have
-//                 read S_j out of the slot, i.e. two steps before it is needed.
+//                 and the softmax threads never touch it. S_{j+2} is issued as soon as P_j V_j, which reads P_j
+//                 out of the same slot, is done: a whole step before the softmax warps want it.
 //   softmax warps thread = query row = TMEM lane: S -> registers [+ mask bias where the block has masked keys],
-//                 row maximum, P = exp2(S - m) (row sum kept in a register), P rounded to bf16 and written to one
-//                 of the line's two P buffers in TMEM
-//   MMA warp      O[128 x 32] += P V with P read from TMEM as the A operand
-// TMEM columns of a line (128): S slots [0,32) [32,64), P buffers [64,80) [80,96) (16 columns of bf16 pairs
-// each), O [96,128). With S and P both double-buffered no step waits for the GEMM of the step before it: S_{j+2}
-// only needs S_j read out, P_j only needs P_{j-2} V_{j-2} done.
+//                 row maximum, P = exp2(S - m), rounded to bf16 and written over S (the first 16 columns of the
+//                 slot, bf16 pairs)
+//   MMA warp      O[128 x 48] += P [V; 1; 0] with P read from TMEM as the A operand: columns 0..31 are the head's
+//                 channels, column 32 -- a row of ones under the V tile in shared memory -- is the row sum of the
+//                 rounded P. A GEMM of N = 48 occupies the tensor pipe no longer than one of N = 32, and the
+//                 softmax threads keep no running sum.
+// TMEM columns of a line (112 of 128): S / P slots [0,32) [32,64), O [64,112).
 // The running maximum m used for scaling is only raised when the row maximum exceeds it by more than 8
-// (2^8 head room in P): then, and only then, the thread rescales its O row in TMEM and its running sum.
+// (2^8 head room in P): then, and only then, the thread rescales its O row (channels and row sum) in TMEM.
 // The result is exact: numerator and denominator always share one scale.
 constexpr int kBQ = 128;      // queries per CTA
 constexpr int kBK = 32;       // keys per step
